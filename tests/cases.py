@@ -1,0 +1,64 @@
+"""Seeded parity cases shared by the golden generator and the tests.
+
+``ref23`` follows the input recipe of the reference's own W8A8 test
+(tests/test_moe_w8a8.py:202-211: seed 23, H=I=64, T=48, int8 weights in [-12,12], scales
+U(0.0005,0.0035), x ~ 0.3*N(0,1), one expert per token) widened to 2 experts; the others use the
+benchmark distributions of fused_cpp_b200.synthetic at small and ragged sizes, and ``cfg1`` is the
+benchmark's small W8A8 configuration itself.
+"""
+from __future__ import annotations
+
+import torch
+
+from fused_cpp_b200 import synthetic
+from fused_cpp_b200.synthetic import MoEShape
+
+W8A8_SHAPES = {
+    "tiny": MoEShape(tokens=8, hidden=64, inter=64, experts=4, top_k=2),
+    "ragged": MoEShape(tokens=37, hidden=144, inter=80, experts=7, top_k=3),
+    "wide": MoEShape(tokens=200, hidden=256, inter=128, experts=3, top_k=2),
+    "cfg1": synthetic.CONFIG_SMALL_W8A8,
+}
+W8A8_CASES = ["ref23", "tiny", "ragged", "wide", "cfg1"]
+
+BF16_SHAPES = {
+    "tiny": MoEShape(tokens=8, hidden=64, inter=64, experts=4, top_k=2),
+    "ragged": MoEShape(tokens=19, hidden=144, inter=80, experts=8, top_k=5),
+    "top8": MoEShape(tokens=33, hidden=256, inter=128, experts=16, top_k=8),
+    "wide": MoEShape(tokens=300, hidden=128, inter=64, experts=2, top_k=1),
+}
+BF16_CASES = ["tiny", "ragged", "top8", "wide"]
+
+
+def _ref23_case() -> dict:
+    generator = torch.Generator().manual_seed(23)
+    experts, hidden, inter, tokens = 2, 64, 64, 48
+    q13 = torch.randint(-12, 13, (experts, 2 * inter, hidden), dtype=torch.int8, generator=generator)
+    q2 = torch.randint(-12, 13, (experts, hidden, inter), dtype=torch.int8, generator=generator)
+    s13 = torch.rand((experts, 2 * inter), generator=generator) * 0.003 + 0.0005
+    s2 = torch.rand((experts, hidden), generator=generator) * 0.003 + 0.0005
+    x = (torch.randn((tokens, hidden), generator=generator) * 0.3).to(torch.bfloat16)
+    topk_ids = torch.tensor([[token % experts] for token in range(tokens)], dtype=torch.int64)
+    topk_weights = torch.ones((tokens, 1), dtype=torch.float32)
+    return {"x": x, "w13": q13, "s13": s13, "w2": q2, "s2": s2, "topk_weights": topk_weights, "topk_ids": topk_ids}
+
+
+def w8a8_case(name: str) -> dict:
+    if name == "ref23":
+        return _ref23_case()
+    shape = W8A8_SHAPES[name]
+    case = synthetic.make_w8a8_case(shape, seed=synthetic.SEED_BASE + 1000 * W8A8_CASES.index(name),
+                                    skew=(name == "ragged"))
+    if name == "ragged":
+        # leave one expert without routes and zero one token row (all-zero row quantisation)
+        ids = case["topk_ids"]
+        case["topk_ids"] = torch.where(ids == 6, torch.full_like(ids, 5), ids)
+        case["x"][3].zero_()
+    return case
+
+
+def bf16_case(name: str) -> dict:
+    shape = BF16_SHAPES[name]
+    std = 0.05 if shape.hidden <= 256 else 0.02
+    return synthetic.make_bf16_case(shape, seed=synthetic.SEED_BASE + 5000 + 1000 * BF16_CASES.index(name),
+                                    skew=(name == "ragged"), std=std)

@@ -1,0 +1,64 @@
+"""Generate the golden fixtures in this directory from the REFERENCE's own Python functions.
+
+Run in a container that has the reference checkout:
+
+    REFERENCE_ROOT=/path/to/fused_cpp python tests/golden/make_golden.py
+
+It imports, unmodified,
+  * tests/test_moe_w8a8.py::_quantize_row and ::_reference   (the W8A8 per-token reference), and
+  * src/fused_cpp/moe/naive.py::fused_moe_naive               (the BF16 reference),
+runs them on seeded inputs from fused_cpp_b200.synthetic (plus the input recipe of the reference's
+own W8A8 test), and stores ONLY their outputs (inputs are regenerated from the seeds by the tests).
+The reference cannot travel to the GPU machine; these files can.
+"""
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REPO = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, REPO)
+
+from fused_cpp_b200 import synthetic  # noqa: E402
+from tests import cases  # noqa: E402
+
+
+def _load_reference():
+    root = os.environ.get("REFERENCE_ROOT", "/root/reference")
+    sys.path.insert(0, os.path.join(root, "src"))
+    sys.path.insert(0, root)
+    spec = importlib.util.spec_from_file_location("ref_test_moe_w8a8", os.path.join(root, "tests", "test_moe_w8a8.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    from fused_cpp.moe.naive import fused_moe_naive
+    return module._quantize_row, module._reference, fused_moe_naive
+
+
+def main() -> None:
+    quantize_row, reference, fused_moe_naive = _load_reference()
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    for name in cases.W8A8_CASES:
+        case = cases.w8a8_case(name)
+        rows = [quantize_row(case["x"][t]) for t in range(case["x"].shape[0])]
+        golden = {
+            "xq": torch.stack([r[0] for r in rows]).to(torch.int8),
+            "a": torch.tensor([r[1] for r in rows], dtype=torch.float64),
+            "out": reference(case["x"], case["w13"], case["s13"], case["w2"], case["s2"], case["topk_weights"],
+                             case["topk_ids"]),
+        }
+        torch.save(golden, os.path.join(HERE, f"w8a8_{name}.pt"))
+        print("w8a8", name, tuple(golden["out"].shape))
+    for name in cases.BF16_CASES:
+        case = cases.bf16_case(name)
+        out = fused_moe_naive(case["x"].float(), case["w13"].float(), case["w2"].float(), case["topk_weights"],
+                              case["topk_ids"]).to(torch.bfloat16)
+        torch.save({"out": out}, os.path.join(HERE, f"bf16_{name}.pt"))
+        print("bf16", name, tuple(out.shape))
+
+
+if __name__ == "__main__":
+    main()
