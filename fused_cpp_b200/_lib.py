@@ -1,0 +1,238 @@
+"""ctypes binding of libfused_moe_b200.so (the C ABI declared in include/fused_moe_b200.h).
+
+There is no fallback: if the library is missing, cannot be loaded, or the current device is not a
+B200-class GPU, calls raise.  Tensors are torch CUDA tensors; only their device pointers cross the
+ABI.  Workspaces come from torch's caching allocator and are cached per (device, size class).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+
+import torch
+
+OK = 0
+ERR_INVALID_ARGUMENT = 1
+ERR_CUDA = 2
+ERR_WORKSPACE = 3
+ERR_EXPERT_ID_RANGE = 4
+ERR_DEVICE_WAIT = 5
+ERR_UNSUPPORTED_DEVICE = 6
+
+NUMERICS_TORCHREF = 0
+NUMERICS_NATIVE = 1
+GEMM_AUTO = 0
+GEMM_SIMT = 1
+GEMM_UMMA = 2
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfused_moe_b200.so")
+
+EXPORTS = (
+    "fmoe_abi_version", "fmoe_last_error", "fmoe_device_supported", "fmoe_read_status",
+    "fmoe_w8a8_workspace_layout", "fmoe_w8a8_forward", "fmoe_quantize_weight_rows", "fmoe_quantize_rows",
+    "fmoe_bf16_workspace_layout", "fmoe_bf16_forward", "fmoe_i8gemm_workspace_bytes", "fmoe_i8gemm_dynamic_scaled_mm",
+)
+
+
+class Config(ctypes.Structure):
+    _fields_ = [
+        ("numerics", ctypes.c_int32), ("gemm_impl", ctypes.c_int32), ("gate_up_tile", ctypes.c_int32),
+        ("down_tile", ctypes.c_int32), ("swiglu_limit", ctypes.c_float), ("reserved0", ctypes.c_int32),
+        ("dump_acc1", ctypes.c_void_p), ("dump_acc2", ctypes.c_void_p),
+    ]
+
+
+class WorkspaceLayout(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_size_t) for name in (
+        "total_bytes", "status", "counts", "offsets", "sorted_routes", "row_expert", "items", "scratch", "a_rows",
+        "a_scale", "y", "yq", "y_scale", "route_out")]
+
+
+class FusedMoEError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+_LIB = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library; raise (never fall back) if it is absent."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(LIB_PATH):
+        raise FusedMoEError(ERR_CUDA, f"{LIB_PATH} is missing: build it with `python -m fused_cpp_b200.build` "
+                                      "(there is no CPU or PyTorch fallback for this path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.fmoe_last_error.restype = ctypes.c_char_p
+    lib.fmoe_i8gemm_workspace_bytes.restype = ctypes.c_size_t
+    lib.fmoe_i8gemm_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
+    p, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+    lib.fmoe_device_supported.argtypes = [ctypes.c_int]
+    lib.fmoe_read_status.argtypes = [p, p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+    for name in ("fmoe_w8a8_workspace_layout", "fmoe_bf16_workspace_layout"):
+        getattr(lib, name).argtypes = [i64, i32, i32, i32, i32, ctypes.POINTER(WorkspaceLayout)]
+    lib.fmoe_w8a8_forward.argtypes = [p, p, p, p, p, p, p, i64, i32, i32, i32, i32, ctypes.POINTER(Config), p, p,
+                                      ctypes.c_size_t, p]
+    lib.fmoe_bf16_forward.argtypes = [p, p, p, p, p, i64, i32, i32, i32, i32, ctypes.POINTER(Config), p, p,
+                                      ctypes.c_size_t, p]
+    lib.fmoe_quantize_weight_rows.argtypes = [p, i64, i32, p, p, p]
+    lib.fmoe_quantize_rows.argtypes = [p, i64, i32, i32, p, p, p]
+    lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
+    _LIB = lib
+    return lib
+
+
+def check(code: int) -> None:
+    if code != OK:
+        message = load().fmoe_last_error().decode("utf-8", "replace")
+        error_type = ValueError if code == ERR_INVALID_ARGUMENT else FusedMoEError
+        if error_type is ValueError:
+            raise ValueError(message)
+        raise FusedMoEError(code, message)
+
+
+def device_supported(device: int | None = None) -> bool:
+    if not torch.cuda.is_available():
+        return False
+    index = torch.cuda.current_device() if device is None else int(device)
+    return bool(load().fmoe_device_supported(index))
+
+
+def _ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def workspace_layout(int8: bool, tokens: int, top_k: int, experts: int, hidden: int, inter: int) -> WorkspaceLayout:
+    layout = WorkspaceLayout()
+    fn = load().fmoe_w8a8_workspace_layout if int8 else load().fmoe_bf16_workspace_layout
+    check(fn(tokens, top_k, experts, hidden, inter, ctypes.byref(layout)))
+    return layout
+
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def get_workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    """A cached uint8 workspace of at least nbytes (grown geometrically, one per device).
+
+    Like the reference's per-thread RuntimeScratch (csrc/moe/arm/i8mm_w8a8/kernels.cpp:177-182) it is
+    reused across calls, so calls on one device must be serialised by the caller (one stream).
+    """
+    key = (device.index if device.index is not None else torch.cuda.current_device(), 0)
+    current = _WORKSPACES.get(key)
+    if current is None or current.numel() < nbytes:
+        size = max(nbytes, 0 if current is None else int(current.numel() * 1.5))
+        _WORKSPACES.pop(key, None)
+        current = torch.empty(size + 256, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = current
+    offset = (-current.data_ptr()) % 256
+    return current[offset:offset + nbytes]
+
+
+@dataclass
+class ForwardResult:
+    out: torch.Tensor
+    workspace: torch.Tensor
+    layout: WorkspaceLayout
+    acc1: torch.Tensor | None = None
+    acc2: torch.Tensor | None = None
+
+    def region(self, name: str, dtype: torch.dtype, shape) -> torch.Tensor:
+        count = 1
+        for dim in shape:
+            count *= int(dim)
+        begin = getattr(self.layout, name)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        return self.workspace[begin:begin + nbytes].view(dtype).reshape(shape)
+
+    def status(self) -> tuple[int, int]:
+        error, detail = ctypes.c_int32(0), ctypes.c_int32(0)
+        check(load().fmoe_read_status(_ptr(self.workspace), _stream(), ctypes.byref(error), ctypes.byref(detail)))
+        return error.value, detail.value
+
+    def raise_for_status(self) -> None:
+        error, detail = self.status()
+        if error == ERR_EXPERT_ID_RANGE:
+            raise FusedMoEError(error, f"topk expert id is out of range (flat route {detail})")
+        if error != OK:
+            raise FusedMoEError(error, load().fmoe_last_error().decode("utf-8", "replace"))
+
+
+def _require_cuda(name: str, tensor: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if not isinstance(tensor, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if tensor.device.type != "cuda":
+        raise ValueError(f"{name} must be a CUDA tensor (this build has no CPU path)")
+    if tensor.dtype != dtype:
+        raise TypeError(f"{name} must have dtype {dtype}, got {tensor.dtype}")
+    return tensor.contiguous()
+
+
+def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numerics: int = NUMERICS_TORCHREF,
+                gemm_impl: int = GEMM_AUTO, gate_up_tile: int = 0, down_tile: int = 0, swiglu_limit: float | None = None,
+                out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None) -> ForwardResult:
+    """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8."""
+    int8 = w13.dtype == torch.int8
+    x = _require_cuda("input", x, torch.bfloat16)
+    w13 = _require_cuda("w13", w13, torch.int8 if int8 else torch.bfloat16)
+    w2 = _require_cuda("w2", w2, torch.int8 if int8 else torch.bfloat16)
+    topk_weights = _require_cuda("topk_weights", topk_weights, torch.float32)
+    topk_ids = _require_cuda("topk_ids", topk_ids, torch.int64)
+    tokens, hidden = x.shape
+    experts, two_i, _ = w13.shape
+    inter = two_i // 2
+    top_k = topk_ids.shape[1]
+    if int8:
+        s13 = _require_cuda("w13_scale", s13, torch.float32)
+        s2 = _require_cuda("w2_scale", s2, torch.float32)
+    if out is None:
+        out = torch.empty_like(x)
+    layout = workspace_layout(int8, tokens, top_k, experts, hidden, inter)
+    if workspace is None:
+        workspace = get_workspace(layout.total_bytes, x.device)
+    config = Config()
+    config.numerics = numerics
+    config.gemm_impl = gemm_impl
+    config.gate_up_tile = gate_up_tile
+    config.down_tile = down_tile
+    config.swiglu_limit = (10.0 if int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
+    acc1 = acc2 = None
+    if dump:
+        acc_dtype = torch.int32 if int8 else torch.float32
+        acc1 = torch.zeros((max(tokens * top_k, 1), two_i), dtype=acc_dtype, device=x.device)
+        acc2 = torch.zeros((max(tokens * top_k, 1), hidden), dtype=acc_dtype, device=x.device)
+        config.dump_acc1 = acc1.data_ptr()
+        config.dump_acc2 = acc2.data_ptr()
+    lib = load()
+    if int8:
+        code = lib.fmoe_w8a8_forward(_ptr(x), _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2), _ptr(topk_weights), _ptr(topk_ids),
+                                     tokens, top_k, experts, hidden, inter, ctypes.byref(config), _ptr(out),
+                                     _ptr(workspace), workspace.numel(), _stream())
+    else:
+        code = lib.fmoe_bf16_forward(_ptr(x), _ptr(w13), _ptr(w2), _ptr(topk_weights), _ptr(topk_ids), tokens, top_k,
+                                     experts, hidden, inter, ctypes.byref(config), _ptr(out), _ptr(workspace),
+                                     workspace.numel(), _stream())
+    check(code)
+    return ForwardResult(out=out, workspace=workspace, layout=layout, acc1=acc1, acc2=acc2)
+
+
+def quantize_rows(x: torch.Tensor, numerics: int = NUMERICS_TORCHREF, weight_mode: bool = False):
+    """bf16 [rows, cols] -> (int8 [rows, cols], fp32 scale [rows]) on the GPU."""
+    x = _require_cuda("x", x, torch.bfloat16)
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
+    lib = load()
+    if weight_mode:
+        check(lib.fmoe_quantize_weight_rows(_ptr(x), rows, cols, _ptr(q), _ptr(scale), _stream()))
+    else:
+        check(lib.fmoe_quantize_rows(_ptr(x), rows, cols, numerics, _ptr(q), _ptr(scale), _stream()))
+    return q, scale

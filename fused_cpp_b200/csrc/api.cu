@@ -1,0 +1,340 @@
+// C ABI of the library: argument validation, workspace layout and the kernel sequence of each
+// forward call.  See include/fused_moe_b200.h for the contract of every entry point.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* format, ...) {
+  va_list list;
+  va_start(list, format);
+  vsnprintf(g_error, sizeof(g_error), format, list);
+  va_end(list);
+  return code;
+}
+
+int cuda_fail(cudaError_t error, const char* what) {
+  return fail(FMOE_ERR_CUDA, "%s: %s", what, cudaGetErrorString(error));
+}
+
+size_t align_up(size_t value, size_t quantum) { return (value + quantum - 1) / quantum * quantum; }
+
+int check_device() {
+  int device = 0;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return cuda_fail(error, "cudaGetDevice");
+  static thread_local int checked_device = -1;
+  if (checked_device == device) return FMOE_OK;
+  if (!fmoe_device_supported(device)) {
+    return fail(FMOE_ERR_UNSUPPORTED_DEVICE, "device %d is not a compute capability 10.x GPU; this library has no other path", device);
+  }
+  checked_device = device;
+  return FMOE_OK;
+}
+
+int64_t max_items_for(int64_t routes, int experts) {
+  // Upper bound on (expert, row tile) items for any tile height >= 8.
+  return experts + routes / 8 + 1;
+}
+
+int check_shape(int64_t tokens, int top_k, int experts, int hidden, int inter) {
+  if (tokens < 0 || top_k <= 0 || top_k > 32 || experts <= 0 || experts > fmoe::kMaxExperts) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid shape: tokens=%lld top_k=%d (1..32) experts=%d (1..%d)",
+                static_cast<long long>(tokens), top_k, experts, fmoe::kMaxExperts);
+  }
+  if (hidden <= 0 || inter <= 0 || hidden % 16 != 0 || inter % 16 != 0) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "H and I must be positive multiples of 16 (H=%d, I=%d)", hidden, inter);
+  }
+  if (tokens * top_k > (1ll << 30)) return fail(FMOE_ERR_INVALID_ARGUMENT, "too many routes");
+  return FMOE_OK;
+}
+
+int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, int inter, fmoe_workspace_layout* layout) {
+  const int status = check_shape(tokens, top_k, experts, hidden, inter);
+  if (status != FMOE_OK) return status;
+  if (layout == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "layout is null");
+  const size_t routes = static_cast<size_t>(tokens) * top_k;
+  const size_t rows = routes > 0 ? routes : 1;
+  const size_t max_items = static_cast<size_t>(max_items_for(routes, experts));
+  size_t offset = 0;
+  auto take = [&offset](size_t bytes) {
+    const size_t begin = offset;
+    offset = align_up(offset + bytes, 256);
+    return begin;
+  };
+  memset(layout, 0, sizeof(*layout));
+  layout->status = take(sizeof(int) * fmoe::kStatusWords);
+  layout->counts = take(sizeof(int) * experts);
+  layout->offsets = take(sizeof(int) * (experts + 1));
+  layout->sorted_routes = take(sizeof(int) * rows);
+  layout->row_expert = take(sizeof(int) * rows);
+  layout->items = take(sizeof(int) * 4 * max_items * 2);
+  layout->scratch = take(fmoe::route_scratch_bytes(routes, experts));
+  layout->a_rows = take(rows * hidden * (int8 ? 1 : 2));
+  layout->a_scale = take(sizeof(float) * rows);
+  layout->y = take(rows * inter * 2);
+  layout->yq = take(int8 ? rows * inter : 0);
+  layout->y_scale = take(sizeof(float) * rows);
+  layout->route_out = take(sizeof(float) * rows * hidden);
+  layout->total_bytes = offset;
+  return FMOE_OK;
+}
+
+int pick_row_tile(int requested, int64_t routes, int experts, bool umma) {
+  if (!umma) return fmoe::kSimtRowTile;
+  if (requested != 0) return requested;
+  // Expected rows per expert decide the tile: the smallest MMA N that holds a typical expert in one
+  // work item, so each weight byte is streamed once.
+  const int64_t average = (routes + experts - 1) / experts;
+  if (average <= 8) return 16;
+  if (average <= 24) return 32;
+  if (average <= 48) return 64;
+  return 128;
+}
+
+struct Forward {
+  bool int8;
+  const void* x;
+  const void* w13;
+  const float* s13;
+  const void* w2;
+  const float* s2;
+  const float* topk_weights;
+  const int64_t* topk_ids;
+  int64_t tokens;
+  int top_k, experts, hidden, inter;
+};
+
+int run_forward(const Forward& f, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes, void* stream_ptr) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  fmoe_workspace_layout layout;
+  status = make_layout(f.int8, f.tokens, f.top_k, f.experts, f.hidden, f.inter, &layout);
+  if (status != FMOE_OK) return status;
+  if (f.tokens == 0) return FMOE_OK;
+  if (f.x == nullptr || f.w13 == nullptr || f.w2 == nullptr || f.topk_weights == nullptr || f.topk_ids == nullptr || out == nullptr) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
+  }
+  if (f.int8 && (f.s13 == nullptr || f.s2 == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null scale pointer");
+  if (workspace == nullptr || workspace_bytes < layout.total_bytes) {
+    return fail(FMOE_ERR_WORKSPACE, "workspace too small: %zu bytes given, %zu needed", workspace_bytes, layout.total_bytes);
+  }
+  if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(FMOE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  const uintptr_t align_mask = reinterpret_cast<uintptr_t>(f.x) | reinterpret_cast<uintptr_t>(f.w13) |
+                               reinterpret_cast<uintptr_t>(f.w2) | reinterpret_cast<uintptr_t>(out);
+  if (align_mask % 16 != 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "x, w13, w2 and out must be 16-byte aligned");
+
+  fmoe_config defaults;
+  memset(&defaults, 0, sizeof(defaults));
+  defaults.swiglu_limit = f.int8 ? 10.0f : 0.0f;
+  const fmoe_config cfg = config ? *config : defaults;
+  if (f.int8 && cfg.swiglu_limit != 10.0f) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "W8A8 supports only clamped SwiGLU limit 10.0");
+  }
+  if (!f.int8 && cfg.swiglu_limit != 0.0f && cfg.swiglu_limit != 10.0f) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "BF16 supports swiglu_limit 0 (plain SiLU) or 10.0");
+  }
+  if (cfg.numerics != FMOE_NUMERICS_TORCHREF && cfg.numerics != FMOE_NUMERICS_NATIVE) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown numerics %d", cfg.numerics);
+  }
+  if (cfg.gemm_impl < FMOE_GEMM_AUTO || cfg.gemm_impl > FMOE_GEMM_UMMA) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown gemm_impl %d", cfg.gemm_impl);
+  }
+  const bool umma = cfg.gemm_impl != FMOE_GEMM_SIMT;
+  const int64_t routes = f.tokens * f.top_k;
+  const int tile_gu = pick_row_tile(cfg.gate_up_tile, routes, f.experts, umma);
+  const int tile_dn = pick_row_tile(cfg.down_tile, routes, f.experts, umma);
+  if (umma && (!fmoe::umma_row_tile_supported(tile_gu) || !fmoe::umma_row_tile_supported(tile_dn))) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128 or 256 (got %d, %d)", tile_gu, tile_dn);
+  }
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  char* base = static_cast<char*>(workspace);
+  int* status_block = reinterpret_cast<int*>(base + layout.status);
+  int* counts = reinterpret_cast<int*>(base + layout.counts);
+  int* offsets = reinterpret_cast<int*>(base + layout.offsets);
+  int* sorted_routes = reinterpret_cast<int*>(base + layout.sorted_routes);
+  int* row_expert = reinterpret_cast<int*>(base + layout.row_expert);
+  const int max_items = static_cast<int>(max_items_for(routes, f.experts));
+  int* items_gu = reinterpret_cast<int*>(base + layout.items);
+  int* items_dn = items_gu + 4 * static_cast<size_t>(max_items);
+  int* scratch = reinterpret_cast<int*>(base + layout.scratch);
+  float* a_scale = reinterpret_cast<float*>(base + layout.a_scale);
+  uint16_t* y = reinterpret_cast<uint16_t*>(base + layout.y);
+  float* y_scale = reinterpret_cast<float*>(base + layout.y_scale);
+  float* route_out = reinterpret_cast<float*>(base + layout.route_out);
+
+  cudaError_t error = cudaMemsetAsync(status_block, 0, sizeof(int) * fmoe::kStatusWords, stream);
+  if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
+  error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, tile_gu, tile_dn, max_items, status_block, counts, offsets,
+                                   sorted_routes, row_expert, items_gu, items_dn, scratch, stream);
+  if (error != cudaSuccess) return cuda_fail(error, "route build");
+  const int* valid_rows = offsets + f.experts;
+
+  if (f.int8) {
+    error = fmoe::launch_quantize_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden, sorted_routes, f.top_k, valid_rows,
+                                       cfg.numerics, 0, reinterpret_cast<int8_t*>(base + layout.a_rows), a_scale, stream);
+  } else {
+    error = fmoe::launch_gather_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden, sorted_routes, f.top_k, valid_rows,
+                                     reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
+  }
+  if (error != cudaSuccess) return cuda_fail(error, "activation quantise/gather");
+
+  fmoe::GroupedGemmArgs gu;
+  memset(&gu, 0, sizeof(gu));
+  gu.a_rows = base + layout.a_rows;
+  gu.weights = f.w13;
+  gu.a_scale = a_scale;
+  gu.w_scale = f.s13;
+  gu.items = items_gu;
+  gu.status = status_block;
+  gu.status_rw = status_block;
+  gu.item_count_word = fmoe::kStatusItems;
+  gu.max_items = max_items;
+  gu.sorted_routes = sorted_routes;
+  gu.experts = f.experts;
+  gu.k = f.hidden;
+  gu.n_out = f.inter;
+  gu.numerics = cfg.numerics;
+  gu.swiglu_limit = cfg.swiglu_limit;
+  gu.y = y;
+  gu.route_out = nullptr;
+  gu.dump_acc = cfg.dump_acc1;
+  gu.total_rows = routes;
+  gu.row_tile = tile_gu;
+  error = umma ? fmoe::launch_umma_grouped_gemm(gu, f.int8, true, stream) : fmoe::launch_simt_grouped_gemm(gu, f.int8, true, stream);
+  if (error != cudaSuccess) return cuda_fail(error, "gate_up grouped GEMM");
+
+  const void* down_rows = y;
+  if (f.int8) {
+    int8_t* yq = reinterpret_cast<int8_t*>(base + layout.yq);
+    error = fmoe::launch_quantize_rows(y, routes, f.inter, nullptr, 1, valid_rows, cfg.numerics, 0, yq, y_scale, stream);
+    if (error != cudaSuccess) return cuda_fail(error, "intermediate quantise");
+    down_rows = yq;
+  }
+
+  fmoe::GroupedGemmArgs dn = gu;
+  dn.a_rows = down_rows;
+  dn.weights = f.w2;
+  dn.a_scale = y_scale;
+  dn.w_scale = f.s2;
+  dn.items = items_dn;
+  dn.item_count_word = fmoe::kStatusItemsB;
+  dn.k = f.inter;
+  dn.n_out = f.hidden;
+  dn.y = nullptr;
+  dn.route_out = route_out;
+  dn.dump_acc = cfg.dump_acc2;
+  dn.row_tile = tile_dn;
+  error = umma ? fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
+  if (error != cudaSuccess) return cuda_fail(error, "down grouped GEMM");
+
+  error = fmoe::launch_merge(route_out, f.topk_weights, f.tokens, f.top_k, f.hidden, f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream);
+  if (error != cudaSuccess) return cuda_fail(error, "top-k merge");
+  return FMOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fmoe_abi_version(void) { return FMOE_ABI_VERSION; }
+
+const char* fmoe_last_error(void) { return g_error; }
+
+int fmoe_device_supported(int device) {
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return major == 10 ? 1 : 0;
+}
+
+int fmoe_read_status(const void* workspace, void* stream, int32_t* error, int32_t* detail) {
+  if (workspace == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "workspace is null");
+  int words[fmoe::kStatusWords];
+  cudaError_t result = cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (result == cudaSuccess) result = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (result != cudaSuccess) return cuda_fail(result, "reading the status block");
+  if (error) *error = words[fmoe::kStatusError];
+  if (detail) *detail = words[fmoe::kStatusDetail];
+  if (words[fmoe::kStatusError] == FMOE_ERR_EXPERT_ID_RANGE) {
+    fail(FMOE_ERR_EXPERT_ID_RANGE, "topk expert id is out of range at flat route %d", words[fmoe::kStatusDetail]);
+  } else if (words[fmoe::kStatusError] == FMOE_ERR_DEVICE_WAIT) {
+    fail(FMOE_ERR_DEVICE_WAIT, "a bounded device wait gave up (CTA %d, site %d)", words[fmoe::kStatusDetail],
+         words[fmoe::kStatusWaitSite]);
+  }
+  return FMOE_OK;
+}
+
+int fmoe_w8a8_workspace_layout(int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden, int32_t inter,
+                               fmoe_workspace_layout* layout) {
+  return make_layout(true, tokens, top_k, experts, hidden, inter, layout);
+}
+
+int fmoe_bf16_workspace_layout(int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden, int32_t inter,
+                               fmoe_workspace_layout* layout) {
+  return make_layout(false, tokens, top_k, experts, hidden, inter, layout);
+}
+
+int fmoe_w8a8_forward(const void* x, const int8_t* w13, const float* s13, const int8_t* w2, const float* s2,
+                      const float* topk_weights, const int64_t* topk_ids, int64_t tokens, int32_t top_k,
+                      int32_t experts, int32_t hidden, int32_t inter, const fmoe_config* config, void* out,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  const Forward f{true, x, w13, s13, w2, s2, topk_weights, topk_ids, tokens, top_k, experts, hidden, inter};
+  return run_forward(f, config, out, workspace, workspace_bytes, stream);
+}
+
+int fmoe_bf16_forward(const void* x, const void* w13, const void* w2, const float* topk_weights,
+                      const int64_t* topk_ids, int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden,
+                      int32_t inter, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+  const Forward f{false, x, w13, nullptr, w2, nullptr, topk_weights, topk_ids, tokens, top_k, experts, hidden, inter};
+  return run_forward(f, config, out, workspace, workspace_bytes, stream);
+}
+
+int fmoe_quantize_weight_rows(const void* w, int64_t rows, int32_t cols, int8_t* q, float* scale, void* stream) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (rows < 0 || cols <= 0 || cols % 16 != 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "cols must be a positive multiple of 16");
+  if (rows > 0 && (w == nullptr || q == nullptr || scale == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  const cudaError_t error = fmoe::launch_quantize_rows(static_cast<const uint16_t*>(w), rows, cols, nullptr, 1, nullptr,
+                                                       FMOE_NUMERICS_TORCHREF, 1, q, scale, static_cast<cudaStream_t>(stream));
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "weight quantiser");
+}
+
+int fmoe_quantize_rows(const void* x, int64_t rows, int32_t cols, int32_t numerics, int8_t* q, float* scale, void* stream) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (rows < 0 || cols <= 0 || cols % 16 != 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "cols must be a positive multiple of 16");
+  if (numerics != FMOE_NUMERICS_TORCHREF && numerics != FMOE_NUMERICS_NATIVE) return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown numerics");
+  if (rows > 0 && (x == nullptr || q == nullptr || scale == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  const cudaError_t error = fmoe::launch_quantize_rows(static_cast<const uint16_t*>(x), rows, cols, nullptr, 1, nullptr, numerics, 0, q,
+                                                       scale, static_cast<cudaStream_t>(stream));
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "row quantiser");
+}
+
+size_t fmoe_i8gemm_workspace_bytes(int64_t rows, int32_t k, int32_t n) {
+  (void)n;
+  if (rows < 0 || k <= 0) return 0;
+  const size_t k_padded = align_up(static_cast<size_t>(k), 16);
+  return align_up(sizeof(int) * fmoe::kStatusWords, 256) + align_up(static_cast<size_t>(rows > 0 ? rows : 1) * k_padded, 256) +
+         align_up(sizeof(float) * static_cast<size_t>(rows > 0 ? rows : 1), 256) + 256;
+}
+
+int fmoe_i8gemm_dynamic_scaled_mm(const void* x, int32_t x_is_bf16, int64_t rows, int32_t k, const int8_t* w,
+                                  const float* w_scale, const float* bias, int32_t n, void* out, int32_t out_is_bf16,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+  (void)x; (void)x_is_bf16; (void)rows; (void)k; (void)w; (void)w_scale; (void)bias; (void)n; (void)out; (void)out_is_bf16;
+  (void)workspace; (void)workspace_bytes; (void)stream;
+  return fail(FMOE_ERR_INVALID_ARGUMENT, "fmoe_i8gemm_dynamic_scaled_mm is not built yet");
+}
+
+}  // extern "C"

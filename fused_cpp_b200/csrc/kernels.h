@@ -1,0 +1,72 @@
+// Launchers of the individual kernels; the C ABI in api.cu sequences them.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace fmoe {
+
+constexpr int kUnitRoutes = 512;   // routes per warp in the route-build kernels
+constexpr int kMaxExperts = 2048;  // bound of the per-warp shared-memory histograms
+
+// ---- route.cu
+size_t route_scratch_bytes(int64_t routes, int experts);
+cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
+                               int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
+                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream);
+
+// ---- quant.cu
+// Quantise rows of a bf16 matrix to int8 with one fp32 scale per row.  When `sorted_routes` is
+// non-null, output row p reads source row sorted_routes[p] / top_k (gather by token).
+// weight_mode: scale of an all-zero row is 1 and rounding is ties-to-even with division (weight prep).
+// valid_rows (nullable, device): rows at or beyond *valid_rows are skipped (routes dropped for a bad id).
+cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
+                                 const int* valid_rows, int numerics, int weight_mode, int8_t* q, float* scale,
+                                 cudaStream_t stream);
+// Same for fp32 sources (dense linear).  clamp_low is -128 or -127.
+cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int8_t* q,
+                                       float* scale, cudaStream_t stream);
+// Copy bf16 rows into expert-sorted order: out[p] = x[sorted_routes[p] / top_k].
+cudaError_t launch_gather_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
+                               const int* valid_rows, uint16_t* out, cudaStream_t stream);
+
+// ---- merge.cu
+// W8A8: out[t] = bf16( fma chain over slots of route_out[t*K+slot] * w[t,slot] ).
+// BF16: pairwise tree for K in {2,4,6,8}, chain otherwise.
+cudaError_t launch_merge(const float* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
+                         int tree, uint16_t* out, cudaStream_t stream);
+
+// ---- grouped GEMM, shared argument block
+struct GroupedGemmArgs {
+  const void* a_rows;        // [rows, K] int8 or bf16, expert-sorted
+  const void* weights;       // [E, N_total, K] int8 or bf16
+  const float* a_scale;      // [rows] (int8) or null
+  const float* w_scale;      // [E, N_total] (int8) or null
+  const int* items;          // (expert, first row, rows, 0) per work item
+  const int* status;         // status block: item counts are read from it
+  int item_count_word;       // kStatusItems or kStatusItemsB
+  int max_items;
+  const int* sorted_routes;  // down GEMM: flat route id of each sorted row
+  int experts;
+  int k;                     // reduction length (H for gate_up, I for down)
+  int n_out;                 // output channels per row: I (gate_up, gate/up pairs) or H (down)
+  int numerics;
+  float swiglu_limit;
+  uint16_t* y;               // gate_up output bf16 [rows, I]
+  float* route_out;          // down output fp32 [T*K, H], row = flat route id
+  void* dump_acc;            // optional raw accumulators [rows, N_total], sorted-row order
+  int64_t total_rows;
+  int row_tile;              // rows per work item
+  int* status_rw;            // writable status block (device-side error reports)
+};
+
+// ---- simt_gemm.cu: diagnostic CUDA-core grouped GEMM (work items of at most 8 rows)
+constexpr int kSimtRowTile = 8;
+cudaError_t launch_simt_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
+
+// ---- umma_gemm.cu: tcgen05 grouped GEMM
+bool umma_row_tile_supported(int row_tile);
+cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
+
+}  // namespace fmoe

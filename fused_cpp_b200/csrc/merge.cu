@@ -1,0 +1,92 @@
+// Top-k merge: out[t,:] = bf16( sum over slots of route_out[t*K+slot,:] * w[t,slot] ) in the
+// reference's fixed orders, so the result is deterministic and independent of the launch shape.
+//   W8A8: one fused multiply-add chain in slot order starting from zero
+//         (csrc/moe/arm/i8mm_w8a8/kernels.cpp:675-688).
+//   BF16: for K in {2,4,6,8} a pairwise tree over unfused products, split at the largest power of two
+//         below the count; any other K the same chain as W8A8 (csrc/moe/arm/sve_bf16/route_merge.cpp:48-86).
+// route_out rows are indexed by flat route id, so the un-permute already happened in the down GEMM's
+// epilogue; this pass is a pure streaming read of fp32 rows with 16-byte loads.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fmoe {
+
+namespace {
+
+constexpr int kMergeThreads = 256;
+constexpr int kMaxTopK = 32;
+
+template <int Begin, int Count>
+__device__ __forceinline__ float tree_sum(const float* products) {
+  if constexpr (Count == 1) {
+    return products[Begin];
+  } else {
+    constexpr int kLeft = Count > 4 ? 4 : (Count > 2 ? 2 : 1);  // largest power of two below Count (Count <= 8)
+    return __fadd_rn(tree_sum<Begin, kLeft>(products), tree_sum<Begin + kLeft, Count - kLeft>(products));
+  }
+}
+
+template <int TopK>
+__device__ __forceinline__ float merge_fixed(const float* values, const float* weights) {
+  float products[TopK];
+#pragma unroll
+  for (int slot = 0; slot < TopK; ++slot) products[slot] = __fmul_rn(values[slot], weights[slot]);
+  return tree_sum<0, TopK>(products);
+}
+
+__global__ void __launch_bounds__(kMergeThreads)
+merge_kernel(const float* __restrict__ route_out, const float* __restrict__ topk_weights, int top_k, int hidden, int tree,
+             uint16_t* __restrict__ out) {
+  __shared__ float weights[kMaxTopK];
+  const int64_t token = blockIdx.y;
+  if (threadIdx.x < top_k) weights[threadIdx.x] = topk_weights[token * top_k + threadIdx.x];
+  __syncthreads();
+  const int h = (blockIdx.x * kMergeThreads + threadIdx.x) * 4;
+  if (h >= hidden) return;
+  const float* base = route_out + token * top_k * static_cast<int64_t>(hidden) + h;
+  float result[4];
+  const bool fixed = tree && (top_k == 2 || top_k == 4 || top_k == 6 || top_k == 8);
+  if (fixed) {
+    float4 rows[8];
+    for (int slot = 0; slot < top_k; ++slot) rows[slot] = *reinterpret_cast<const float4*>(base + static_cast<int64_t>(slot) * hidden);
+#pragma unroll
+    for (int lane = 0; lane < 4; ++lane) {
+      float values[8];
+#pragma unroll
+      for (int slot = 0; slot < 8; ++slot) values[slot] = reinterpret_cast<const float*>(&rows[slot])[lane];
+      switch (top_k) {
+        case 2: result[lane] = merge_fixed<2>(values, weights); break;
+        case 4: result[lane] = merge_fixed<4>(values, weights); break;
+        case 6: result[lane] = merge_fixed<6>(values, weights); break;
+        default: result[lane] = merge_fixed<8>(values, weights); break;
+      }
+    }
+  } else {
+    result[0] = result[1] = result[2] = result[3] = 0.0f;
+    for (int slot = 0; slot < top_k; ++slot) {
+      const float4 row = *reinterpret_cast<const float4*>(base + static_cast<int64_t>(slot) * hidden);
+      const float w = weights[slot];
+      result[0] = __fmaf_rn(row.x, w, result[0]);
+      result[1] = __fmaf_rn(row.y, w, result[1]);
+      result[2] = __fmaf_rn(row.z, w, result[2]);
+      result[3] = __fmaf_rn(row.w, w, result[3]);
+    }
+  }
+  uint2 packed;
+  packed.x = static_cast<uint32_t>(f32_to_bf16_bits(result[0])) | (static_cast<uint32_t>(f32_to_bf16_bits(result[1])) << 16);
+  packed.y = static_cast<uint32_t>(f32_to_bf16_bits(result[2])) | (static_cast<uint32_t>(f32_to_bf16_bits(result[3])) << 16);
+  *reinterpret_cast<uint2*>(out + token * hidden + h) = packed;
+}
+
+}  // namespace
+
+cudaError_t launch_merge(const float* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
+                         int tree, uint16_t* out, cudaStream_t stream) {
+  if (tokens <= 0) return cudaSuccess;
+  if (top_k > kMaxTopK) return cudaErrorInvalidValue;
+  const dim3 grid((hidden / 4 + kMergeThreads - 1) / kMergeThreads, static_cast<unsigned>(tokens));
+  merge_kernel<<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe

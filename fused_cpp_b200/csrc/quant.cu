@@ -1,0 +1,167 @@
+// Dynamic per-row symmetric int8 quantisation and the row gather of the BF16 path.
+//
+// The reference quantises x[token] once per route into the expert's private buffer
+// (quantize_bf16_row, csrc/moe/arm/i8mm_w8a8/kernels.cpp:211-228, called at :639-644 and :655-656).
+// One CTA handles one output row: pass 1 finds the row's absmax with 16-byte loads and a
+// warp-shuffle/shared-memory reduction, pass 2 re-reads the row (L1/L2 resident) and stores 16 int8
+// per thread as one 16-byte vector.  With `sorted_routes` the source row is the route's token, so
+// the output is already in expert-sorted order for the grouped GEMM (gather and quantise fused).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fmoe {
+
+namespace {
+
+constexpr int kQuantThreads = 256;
+
+__device__ __forceinline__ float block_max(float value, float* smem) {
+  value = warp_max(value);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = value;
+  __syncthreads();
+  float result = lane < (blockDim.x >> 5) ? smem[lane] : 0.0f;
+  result = warp_max(result);
+  __syncthreads();
+  return result;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* out) {
+  const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(words[i] << 16);
+    out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ float amax8(const uint4& v) {
+  float values[8];
+  unpack8(v, values);
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(values[i]));
+  return m;
+}
+
+__device__ __forceinline__ uint32_t pack4(const float* values, float operand, int numerics) {
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int q = quantize_value(values[i], operand, numerics);
+    packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+  }
+  return packed;
+}
+
+// cols % 16 == 0.  One CTA per output row.
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_rows_kernel(const uint16_t* __restrict__ x, int cols, const int* __restrict__ sorted_routes, int top_k,
+                     const int* __restrict__ valid_rows, int numerics, int weight_mode, int8_t* __restrict__ q,
+                     float* __restrict__ scale_out) {
+  __shared__ float smem[32];
+  const int64_t row = blockIdx.x;
+  if (valid_rows && row >= *valid_rows) return;  // rows of dropped (out-of-range) routes
+  const int64_t src_row = sorted_routes ? static_cast<int64_t>(sorted_routes[row] / top_k) : row;
+  const uint4* src = reinterpret_cast<const uint4*>(x + src_row * cols);
+  const int vec16 = cols >> 4;
+  float local = 0.0f;
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    local = fmaxf(local, amax8(src[2 * v]));
+    local = fmaxf(local, amax8(src[2 * v + 1]));
+  }
+  const float amax = block_max(local, smem);
+  float scale;
+  int mode = numerics;
+  if (weight_mode) {
+    scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    mode = FMOE_NUMERICS_TORCHREF;
+  } else {
+    scale = row_scale_from_amax(amax, numerics);
+  }
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  const float operand = quantize_operand(scale, mode);
+  uint4* dst = reinterpret_cast<uint4*>(q + row * cols);
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    float values[16];
+    unpack8(src[2 * v], values);
+    unpack8(src[2 * v + 1], values + 8);
+    uint4 out;
+    out.x = pack4(values, operand, mode);
+    out.y = pack4(values + 4, operand, mode);
+    out.z = pack4(values + 8, operand, mode);
+    out.w = pack4(values + 12, operand, mode);
+    dst[v] = out;
+  }
+}
+
+// Dense linear: arbitrary cols, fp32 or bf16 source, zero-padded to cols_padded, clamp to [-128,127]
+// with division and ties-to-even (csrc/i8gemm.cpp:384-399).
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_rows_dense_kernel(const void* __restrict__ x, int x_is_bf16, int cols, int cols_padded, int8_t* __restrict__ q,
+                           float* __restrict__ scale_out) {
+  __shared__ float smem[32];
+  const int64_t row = blockIdx.x;
+  const float* xf = static_cast<const float*>(x) + row * cols;
+  const uint16_t* xb = static_cast<const uint16_t*>(x) + row * cols;
+  float local = 0.0f;
+  for (int c = threadIdx.x; c < cols; c += kQuantThreads) {
+    const float value = x_is_bf16 ? bf16_bits_to_f32(xb[c]) : xf[c];
+    local = fmaxf(local, fabsf(value));
+  }
+  const float amax = block_max(local, smem);
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  int8_t* dst = q + row * cols_padded;
+  for (int c = threadIdx.x; c < cols_padded; c += kQuantThreads) {
+    int value = 0;
+    if (c < cols) {
+      const float source = x_is_bf16 ? bf16_bits_to_f32(xb[c]) : xf[c];
+      float rounded = rintf(__fdiv_rn(source, scale));
+      rounded = fmaxf(fminf(rounded, 127.0f), -128.0f);
+      value = static_cast<int>(rounded);
+    }
+    dst[c] = static_cast<int8_t>(value);
+  }
+}
+
+// cols % 8 == 0.  out[p] = x[sorted_routes[p] / top_k].
+__global__ void __launch_bounds__(kQuantThreads)
+gather_rows_kernel(const uint16_t* __restrict__ x, int cols, const int* __restrict__ sorted_routes, int top_k,
+                   const int* __restrict__ valid_rows, uint16_t* __restrict__ out) {
+  const int64_t row = blockIdx.x;
+  if (valid_rows && row >= *valid_rows) return;
+  const int64_t src_row = sorted_routes[row] / top_k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + src_row * cols);
+  uint4* dst = reinterpret_cast<uint4*>(out + row * cols);
+  for (int v = threadIdx.x; v < (cols >> 3); v += kQuantThreads) dst[v] = src[v];
+}
+
+}  // namespace
+
+cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
+                                 const int* valid_rows, int numerics, int weight_mode, int8_t* q, float* scale,
+                                 cudaStream_t stream) {
+  if (out_rows <= 0) return cudaSuccess;
+  quantize_rows_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows,
+                                                                                     numerics, weight_mode, q, scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int8_t* q,
+                                       float* scale, cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  quantize_rows_dense_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(x, x_is_bf16, cols, cols_padded, q,
+                                                                                       scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
+                               const int* valid_rows, uint16_t* out, cudaStream_t stream) {
+  if (out_rows <= 0) return cudaSuccess;
+  gather_rows_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows, out);
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe

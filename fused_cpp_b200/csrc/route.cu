@@ -1,0 +1,183 @@
+// Route build: per-expert route lists and the work-item lists of the grouped GEMMs.
+//
+// The reference walks topk_ids once on the calling thread and pushes each flat route id t*K+slot
+// onto its expert's vector (csrc/moe/arm/i8mm_w8a8/kernels.cpp:583-592;
+// csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:6455-6469), i.e. a stable counting sort by expert.
+// Here the same order is produced by three small kernels built on warp primitives:
+//   1. route_hist:    every warp owns a unit of kUnitRoutes consecutive routes and histograms it;
+//   2. route_scan:    one block turns the unit histograms into per-(unit, expert) cursors, the
+//                     per-expert offsets and the (expert, row-tile) work items;
+//   3. route_scatter: every warp replays its unit in order; __match_any_sync ranks equal ids inside
+//                     a 32-route round, so positions are assigned in ascending flat-id order.
+// Ids outside [0, E) raise FMOE_ERR_EXPERT_ID_RANGE in the status block and are dropped.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fmoe {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int experts, int units, int* unit_hist,
+                  int* status) {
+  extern __shared__ int smem_hist[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int unit = blockIdx.x * kWarpsPerBlock + warp;
+  int* hist = smem_hist + warp * experts;
+  for (int e = lane; e < experts; e += 32) hist[e] = 0;
+  __syncwarp();
+  if (unit >= units) return;
+  const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
+  for (int round = 0; round < kUnitRoutes / 32; ++round) {
+    const int64_t route = begin + round * 32 + lane;
+    if (route < routes) {
+      const int64_t id = topk_ids[route];
+      if (id < 0 || id >= experts) {
+        raise_error(status, FMOE_ERR_EXPERT_ID_RANGE, static_cast<int>(route));
+      } else {
+        atomicAdd(hist + id, 1);
+      }
+    }
+  }
+  __syncwarp();
+  for (int e = lane; e < experts; e += 32) unit_hist[static_cast<int64_t>(unit) * experts + e] = hist[e];
+}
+
+// Exclusive scan of `values[0..n)` by one warp, 32 entries per step; returns the total.
+__device__ int warp_exclusive_scan(const int* values, int* out, int n, int lane) {
+  int carry = 0;
+  for (int base = 0; base < n; base += 32) {
+    const int index = base + lane;
+    const int value = index < n ? values[index] : 0;
+    int inclusive = value;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+      if (lane >= offset) inclusive += other;
+    }
+    if (index < n) out[index] = carry + inclusive - value;
+    carry += __shfl_sync(0xffffffffu, inclusive, 31);
+  }
+  return carry;
+}
+
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offsets, int tile_a, int tile_b,
+                  int* items_a, int* items_b, int max_items, int* scan_tmp, int* status) {
+  // Pass 1: per expert, running sum over units (unit_hist becomes the unit's cursor relative to the
+  // expert's first row) and the expert total.
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int running = 0;
+    for (int u = 0; u < units; ++u) {
+      const int64_t index = static_cast<int64_t>(u) * experts + e;
+      const int value = unit_hist[index];
+      unit_hist[index] = running;
+      running += value;
+    }
+    counts[e] = running;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp == 0) {
+    const int total = warp_exclusive_scan(counts, offsets, experts, lane);
+    if (lane == 0) offsets[experts] = total;
+  }
+  __syncthreads();
+  // Work items: (expert, first sorted row, rows, 0) for every row tile of every active expert.
+  // Two lists with independent tile heights (gate_up and down GEMM).  scan_tmp holds tiles per expert.
+  for (int list = 0; list < 2; ++list) {
+    const int tile = list == 0 ? tile_a : tile_b;
+    int* items = list == 0 ? items_a : items_b;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) scan_tmp[e] = (counts[e] + tile - 1) / tile;
+    __syncthreads();
+    if (warp == 0) {
+      const int total = warp_exclusive_scan(scan_tmp, scan_tmp + experts, experts, lane);
+      if (lane == 0) status[list == 0 ? kStatusItems : kStatusItemsB] = total < max_items ? total : max_items;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+      const int tiles = scan_tmp[e];
+      const int first = scan_tmp[experts + e];
+      for (int t = 0; t < tiles && first + t < max_items; ++t) {
+        int* item = items + 4 * static_cast<int64_t>(first + t);
+        item[0] = e;
+        item[1] = offsets[e] + t * tile;
+        item[2] = min(tile, counts[e] - t * tile);
+        item[3] = 0;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    int active = 0;
+    for (int e = 0; e < experts; ++e) active += counts[e] > 0;
+    status[kStatusActive] = active;
+  }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int experts, int units,
+                     const int* __restrict__ unit_hist, const int* __restrict__ offsets, int* sorted_routes,
+                     int* row_expert) {
+  extern __shared__ int smem_cursor[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int unit = blockIdx.x * kWarpsPerBlock + warp;
+  if (unit >= units) return;
+  int* cursor = smem_cursor + warp * experts;
+  for (int e = lane; e < experts; e += 32) cursor[e] = offsets[e] + unit_hist[static_cast<int64_t>(unit) * experts + e];
+  __syncwarp();
+  const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
+  const unsigned lanes_below = (1u << lane) - 1u;
+  for (int round = 0; round < kUnitRoutes / 32; ++round) {
+    const int64_t route = begin + round * 32 + lane;
+    int id = -1;
+    if (route < routes) {
+      const int64_t value = topk_ids[route];
+      if (value >= 0 && value < experts) id = static_cast<int>(value);
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, id);
+    int position = -1;
+    if (id >= 0) position = cursor[id] + __popc(peers & lanes_below);
+    __syncwarp();
+    if (id >= 0 && (peers & lanes_below) == 0) cursor[id] += __popc(peers);
+    __syncwarp();
+    if (id >= 0) {
+      sorted_routes[position] = static_cast<int>(route);
+      row_expert[position] = id;
+    }
+  }
+}
+
+}  // namespace
+
+size_t route_scratch_bytes(int64_t routes, int experts) {
+  const int64_t units = (routes + kUnitRoutes - 1) / kUnitRoutes;
+  return static_cast<size_t>((units > 0 ? units : 1) * experts + 2 * (experts + 1)) * sizeof(int);
+}
+
+cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
+                               int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
+                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream) {
+  const int units = static_cast<int>((routes + kUnitRoutes - 1) / kUnitRoutes);
+  int* unit_hist = scratch;
+  int* scan_tmp = scratch + static_cast<int64_t>(units > 0 ? units : 1) * experts;
+  const size_t smem = static_cast<size_t>(kWarpsPerBlock) * experts * sizeof(int);
+  const int blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (blocks > 0) {
+    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist, status);
+  }
+  route_scan_kernel<<<1, 1024, 0, stream>>>(experts, units, unit_hist, counts, offsets, tile_a, tile_b, items_a, items_b,
+                                            max_items, scan_tmp, status);
+  if (blocks > 0) {
+    route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist,
+                                                                        offsets, sorted_routes, row_expert);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe

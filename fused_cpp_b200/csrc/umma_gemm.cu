@@ -1,0 +1,369 @@
+// Grouped expert GEMM on the sm_100a tensor cores (tcgen05.mma, accumulators in tensor memory,
+// operands staged in shared memory by TMA tiled loads).
+//
+// It does the work of the reference's two `run_stage` sweeps and their epilogues:
+//   gate_up: acc = Xq * W13[e]^T (int8 -> int32, or bf16 -> fp32), then dequant, clamp, SiLU(gate)*up,
+//            bf16 store            (csrc/moe/arm/i8mm_w8a8/kernels.cpp:328-368, 230-246;
+//                                   BF16: csrc/moe/arm/sve_bf16/packing.cpp:51-73)
+//   down:    acc = Yq * W2[e]^T, then route_out[flat route] = f32(acc) * (a2 * s2)  -- the scatter to
+//            the flat route id is the un-permute (csrc/moe/arm/i8mm_w8a8/kernels.cpp:248-257, 659-671)
+//
+// Orientation.  The weight tile is the MMA's A operand (M = 128 output channels) and the expert's
+// token rows are the B operand (N = row tile, 16..256), both K-major exactly as they lie in HBM
+// ([E, N, K] weights, [rows, K] activations).  Every weight byte is therefore read once per
+// (expert, row tile) whatever the number of rows, which is what the weight-streaming (decode)
+// regime needs, and the same kernel covers prefill with a 128/256-row tile.  The accumulator
+// D[channel, token] lives in TMEM: one lane per output channel, one 32-bit column per token.
+// gate_up issues two MMAs per K step (gate rows n and up rows I+n against the same token tile) so
+// that each epilogue thread holds the gate and the up value of the same (token, channel).
+//
+// CTA = 6 warps, persistent over work units (work item x 128-channel block), round-robin:
+//   warp 0      TMA producer: per K block of 128 bytes, one or two weight tiles + the token tile;
+//   warp 1      allocates TMEM, issues tcgen05.mma (one thread), commits to the stage's "empty"
+//               barrier and, per work unit, to the accumulator's "full" barrier;
+//   warps 2..5  epilogue: tcgen05.ld their 32-lane TMEM quarter, apply the epilogue, store.
+// Accumulators are double-buffered in TMEM when two buffers fit in 512 columns, so the epilogue of
+// one unit overlaps the main loop of the next.  No load uses cluster multicast; weight-tile reuse
+// between row tiles of one expert comes from L2 (adjacent work items run concurrently).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace fmoe {
+
+namespace {
+
+constexpr int kBlockM = 128;        // output channels per MMA tile (TMEM lanes)
+constexpr int kBlockKBytes = 128;   // bytes of K per pipeline stage = one 128-byte swizzle row
+constexpr int kUmmaKBytes = 32;     // bytes of K per tcgen05.mma
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarp0 = 2;
+constexpr int kSmemBudget = 200 * 1024;
+
+template <bool kGateUp, int kRowTile>
+struct TileConfig {
+  static constexpr int kWeightTiles = kGateUp ? 2 : 1;
+  static constexpr int kWeightBytes = kWeightTiles * kBlockM * kBlockKBytes;
+  static constexpr int kTokenBytes = kRowTile * kBlockKBytes;
+  static constexpr int kStageBytes = kWeightBytes + kTokenBytes;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAccColumns = kWeightTiles * kRowTile;
+  static constexpr int kAccBuffers = (2 * kAccColumns <= 512) ? 2 : 1;
+  static constexpr int kTmemColumnsRaw = kAccBuffers * kAccColumns;
+  static constexpr int kTmemColumns = kTmemColumnsRaw <= 32 ? 32 : kTmemColumnsRaw <= 64 ? 64 : kTmemColumnsRaw <= 128 ? 128
+                                      : kTmemColumnsRaw <= 256 ? 256 : 512;
+  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes + 256 /*barriers*/;
+  static_assert(kStages >= 2, "pipeline needs at least two stages");
+  static_assert(kAccColumns <= 512, "accumulator does not fit tensor memory");
+};
+
+struct SmemControl {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+template <bool kInt8, bool kGateUp, int kRowTile>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap token_map,
+                         GroupedGemmArgs args) {
+  using Cfg = TileConfig<kGateUp, kRowTile>;
+  constexpr int kElemBytes = kInt8 ? 1 : 2;
+  constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
+  constexpr uint32_t kIdesc = ptx::make_instr_desc(kInt8, kBlockM, kRowTile);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  SmemControl* ctl = reinterpret_cast<SmemControl*>(smem + static_cast<size_t>(Cfg::kStages) * Cfg::kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int* status = args.status_rw;
+
+  const int items = min(args.status[args.item_count_word], args.max_items);
+  const int n_blocks = (args.n_out + kBlockM - 1) / kBlockM;
+  const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
+  const int64_t units = static_cast<int64_t>(items) * n_blocks;
+  const int k_blocks = (args.k + kBlockKElems - 1) / kBlockKElems;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      ptx::mbar_init(&ctl->full[s], 1);
+      ptx::mbar_init(&ctl->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&ctl->acc_full[b], 1);
+      ptx::mbar_init(&ctl->acc_empty[b], 4);
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&ctl->tmem_base, Cfg::kTmemColumns);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&weight_map);
+      ptx::prefetch_tensormap(&token_map);
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+        const int item = static_cast<int>(unit / n_blocks);
+        const int n0 = static_cast<int>(unit % n_blocks) * kBlockM;
+        const int expert = args.items[4 * item + 0];
+        const int row0 = args.items[4 * item + 1];
+        const int weight_row = expert * n_total + n0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
+          uint8_t* stage_base = smem + static_cast<size_t>(stage) * Cfg::kStageBytes;
+          ptx::mbar_arrive_expect_tx(&ctl->full[stage], Cfg::kStageBytes);
+          const int x = kb * kBlockKElems;
+          ptx::tma_load_2d(stage_base, &weight_map, &ctl->full[stage], x, weight_row);
+          if (kGateUp) ptx::tma_load_2d(stage_base + kBlockM * kBlockKBytes, &weight_map, &ctl->full[stage], x, weight_row + args.n_out);
+          ptx::tma_load_2d(stage_base + Cfg::kWeightBytes, &token_map, &ctl->full[stage], x, row0);
+          ++issued;
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // Drain: every load this thread issued must have landed before the CTA may exit.  In a healthy
+      // run the MMA warp has already consumed them; this only matters after an abort.
+      const int pending = issued < Cfg::kStages ? issued : Cfg::kStages;
+      for (int back = 0; back < pending; ++back) {
+        int s = stage - 1 - back;
+        uint32_t p = phase;
+        if (s < 0) {
+          s += Cfg::kStages;
+          p ^= 1u;
+        }
+        const unsigned long long start = ptx::global_timer_ns();
+        while (!ptx::mbar_try_wait(&ctl->full[s], p)) {
+          if (ptx::global_timer_ns() - start > ptx::kWaitLimitNs) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
+        const int buffer = local % Cfg::kAccBuffers;
+        const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
+        ptx::mbar_wait(&ctl->acc_empty[buffer], (use & 1u) ^ 1u, abort_flag, status, 2);
+        ptx::tcgen05_fence_after();
+        const uint32_t acc = tmem_base + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ptx::mbar_wait(&ctl->full[stage], phase, abort_flag, status, 3);
+          ptx::tcgen05_fence_after();
+          const uint32_t stage_addr = ptx::smem_u32(smem + static_cast<size_t>(stage) * Cfg::kStageBytes);
+#pragma unroll
+          for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
+            const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
+            const uint64_t desc_tok = ptx::make_smem_desc_sw128(stage_addr + Cfg::kWeightBytes + ks * kUmmaKBytes);
+            const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+            ptx::umma_ss<kInt8>(acc, desc_gate, desc_tok, kIdesc, accumulate);
+            if (kGateUp) {
+              const uint64_t desc_up = ptx::make_smem_desc_sw128(stage_addr + kBlockM * kBlockKBytes + ks * kUmmaKBytes);
+              ptx::umma_ss<kInt8>(acc + kRowTile, desc_up, desc_tok, kIdesc, accumulate);
+            }
+          }
+          ptx::tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        ptx::tcgen05_commit(&ctl->acc_full[buffer]);  // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;  // the TMEM lanes a warp may read are fixed by warp id % 4
+    const int channel_in_block = quarter * 32 + lane;
+    int local = 0;
+    for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
+      const int buffer = local % Cfg::kAccBuffers;
+      const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
+      const int item = static_cast<int>(unit / n_blocks);
+      const int n = static_cast<int>(unit % n_blocks) * kBlockM + channel_in_block;
+      const int expert = args.items[4 * item + 0];
+      const int row0 = args.items[4 * item + 1];
+      const int rows = args.items[4 * item + 2];
+      const bool channel_ok = n < args.n_out;
+      float scale_gate = 1.0f, scale_up = 1.0f;
+      if (kInt8 && channel_ok) {
+        const float* s = args.w_scale + static_cast<int64_t>(expert) * n_total;
+        scale_gate = s[n];
+        if (kGateUp) scale_up = s[n + args.n_out];
+      }
+      ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 4);
+      ptx::tcgen05_fence_after();
+      const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
+      for (int c0 = 0; c0 < rows; c0 += 8) {
+        uint32_t gate_bits[8];
+        uint32_t up_bits[8];
+        ptx::tmem_ld_x8(acc + c0, gate_bits);
+        if (kGateUp) ptx::tmem_ld_x8(acc + kRowTile + c0, up_bits);
+        ptx::tmem_ld_wait();
+        if (channel_ok) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (c0 + j < rows) {
+              const int64_t row = row0 + c0 + j;
+              if (args.dump_acc) {
+                uint32_t* dump = static_cast<uint32_t*>(args.dump_acc) + row * n_total;
+                dump[n] = gate_bits[j];
+                if (kGateUp) dump[n + args.n_out] = up_bits[j];
+              }
+              if constexpr (kGateUp) {
+                float gate, up;
+                if constexpr (kInt8) {
+                  const float a = args.a_scale[row];
+                  gate = dequantize(static_cast<int>(gate_bits[j]), a, scale_gate, args.numerics);
+                  up = dequantize(static_cast<int>(up_bits[j]), a, scale_up, args.numerics);
+                } else {
+                  gate = __uint_as_float(gate_bits[j]);
+                  up = __uint_as_float(up_bits[j]);
+                }
+                args.y[row * args.n_out + n] = swiglu_to_bf16(gate, up, args.swiglu_limit);
+              } else {
+                float value;
+                if constexpr (kInt8) {
+                  value = dequantize(static_cast<int>(gate_bits[j]), args.a_scale[row], scale_gate, args.numerics);
+                } else {
+                  value = __uint_as_float(gate_bits[j]);
+                }
+                const int64_t flat = args.sorted_routes[row];
+                args.route_out[flat * args.n_out + n] = value;
+              }
+            }
+          }
+        }
+      }
+      ptx::tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&ctl->acc_empty[buffer]);
+    }
+  }
+
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemColumns);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &query) == cudaSuccess &&
+        query == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(symbol);
+    }
+  }
+  return fn;
+}
+
+// 2-D K-major tensor [rows, k] with 128-byte-swizzled boxes of {128 bytes of K, box_rows}.
+bool make_tensor_map(CUtensorMap* map, const void* base, bool int8, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const uint32_t elem_bytes = int8 ? 1 : 2;
+  const cuuint64_t dims[2] = {k, rows};
+  const cuuint64_t strides[1] = {k * elem_bytes};
+  const cuuint32_t box[2] = {kBlockKBytes / elem_bytes, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult result = encode(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                 const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return result == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+template <bool kInt8, bool kGateUp, int kRowTile>
+cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
+  using Cfg = TileConfig<kGateUp, kRowTile>;
+  auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile>;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmemBytes));
+    if (err != cudaSuccess) return err;
+    configured = true;
+  }
+  const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
+  CUtensorMap weight_map, token_map;
+  if (!make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total, args.k, kBlockM) ||
+      !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowTile)) {
+    return cudaErrorInvalidValue;
+  }
+  const int n_blocks = (args.n_out + kBlockM - 1) / kBlockM;
+  int64_t grid = static_cast<int64_t>(args.max_items) * n_blocks;
+  if (grid > sm_count()) grid = sm_count();
+  if (grid <= 0) return cudaSuccess;
+  kernel<<<static_cast<unsigned>(grid), kThreads, Cfg::kSmemBytes, stream>>>(weight_map, token_map, args);
+  return cudaGetLastError();
+}
+
+template <bool kInt8, bool kGateUp>
+cudaError_t launch_tile(const GroupedGemmArgs& args, cudaStream_t stream) {
+  switch (args.row_tile) {
+    case 16: return launch_config<kInt8, kGateUp, 16>(args, stream);
+    case 32: return launch_config<kInt8, kGateUp, 32>(args, stream);
+    case 64: return launch_config<kInt8, kGateUp, 64>(args, stream);
+    case 128: return launch_config<kInt8, kGateUp, 128>(args, stream);
+    case 256: return launch_config<kInt8, kGateUp, 256>(args, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace
+
+bool umma_row_tile_supported(int row_tile) {
+  return row_tile == 16 || row_tile == 32 || row_tile == 64 || row_tile == 128 || row_tile == 256;
+}
+
+cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream) {
+  if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
+  if (int8) return gate_up ? launch_tile<true, true>(args, stream) : launch_tile<true, false>(args, stream);
+  return gate_up ? launch_tile<false, true>(args, stream) : launch_tile<false, false>(args, stream);
+}
+
+}  // namespace fmoe

@@ -1,0 +1,166 @@
+/*
+ * C ABI of the B200 routed-expert MoE library (libfused_moe_b200.so).
+ *
+ * The reference project has no C ABI of its own: its boundary for this path is two pybind11 torch
+ * extensions (fused_cpp._moe_C, csrc/moe/module.cpp:10-264, and the i8gemm_* ops of fused_cpp._C,
+ * csrc/module.cpp:220-233).  Each entry point below names the reference function whose work it does;
+ * the Python package above this ABI (fused_cpp_b200.moe) keeps the reference's op names and
+ * argument lists and forwards device pointers here.
+ *
+ * Conventions
+ *   - every data pointer is a DEVICE pointer on the current CUDA device unless a comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); calls are
+ *     asynchronous: they enqueue kernels and return, no device-wide synchronisation;
+ *   - the library allocates no device memory in the forward calls: the caller passes a workspace of
+ *     at least *_workspace_bytes() bytes, 256-byte aligned, private to one call at a time;
+ *   - return value: FMOE_OK or an FMOE_ERR_* code; fmoe_last_error() gives the text (thread-local);
+ *   - errors that only the device can see (an expert id out of range, a bounded wait that gave up)
+ *     are recorded in the workspace status block and read back with fmoe_read_status();
+ *   - there is no CPU fallback: on a device that is not compute capability 10.x every call fails
+ *     with FMOE_ERR_UNSUPPORTED_DEVICE.
+ *
+ * Tensor layouts (row-major, innermost last): x[T,H] bf16; topk_weights[T,K] fp32; topk_ids[T,K]
+ * int64; W8A8: w13[E,2I,H] int8 (gate rows then up rows), s13[E,2I] fp32, w2[E,H,I] int8, s2[E,H]
+ * fp32; BF16: w13[E,2I,H], w2[E,H,I] bf16; out[T,H] bf16.  H and I must be multiples of 16.
+ */
+#ifndef FUSED_MOE_B200_H_
+#define FUSED_MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FMOE_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define FMOE_API __attribute__((visibility("default")))
+#else
+#define FMOE_API
+#endif
+
+#define FMOE_OK 0
+#define FMOE_ERR_INVALID_ARGUMENT 1
+#define FMOE_ERR_CUDA 2
+#define FMOE_ERR_WORKSPACE 3
+#define FMOE_ERR_EXPERT_ID_RANGE 4   /* device-detected: a topk id outside [0, E) */
+#define FMOE_ERR_DEVICE_WAIT 5       /* device-detected: a bounded barrier wait gave up */
+#define FMOE_ERR_UNSUPPORTED_DEVICE 6
+
+/* Which of the reference's two arithmetic statements the W8A8 path follows. */
+#define FMOE_NUMERICS_TORCHREF 0 /* tests/test_moe_w8a8.py:40-69: x/scale, ties-to-even, (acc*a)*s */
+#define FMOE_NUMERICS_NATIVE 1   /* csrc/moe/arm/i8mm_w8a8/kernels.cpp:211-257: x*(1/scale), ties away, acc*(a*s) */
+
+/* Grouped-GEMM implementation.  AUTO is the product path (tcgen05); SIMT is a diagnostic CUDA-core
+ * kernel kept as a stage-level cross-check, in the spirit of the reference's fused_moe_test_* hooks
+ * (csrc/moe/module.cpp:41-115). */
+#define FMOE_GEMM_AUTO 0
+#define FMOE_GEMM_SIMT 1
+#define FMOE_GEMM_UMMA 2
+
+typedef struct fmoe_config {
+  int32_t numerics;      /* FMOE_NUMERICS_* (W8A8 only) */
+  int32_t gemm_impl;     /* FMOE_GEMM_* */
+  int32_t gate_up_tile;  /* rows of one expert handled per work item in the gate_up GEMM; 0 = auto */
+  int32_t down_tile;     /* same for the down GEMM; 0 = auto */
+  float swiglu_limit;    /* BF16: 0 = plain SiLU, 10 = clamp-10 SwiGLU.  W8A8 requires 10. */
+  int32_t reserved0;
+  int32_t* dump_acc1;    /* optional [T*K, 2I] int32 (W8A8) / fp32 (BF16): raw gate_up accumulators, sorted-row order */
+  int32_t* dump_acc2;    /* optional [T*K, H]: raw down accumulators, sorted-row order */
+} fmoe_config;
+
+/* Byte offsets of the regions of a forward workspace (all 256-byte aligned).  Rows of the
+ * per-route regions are in SORTED order: position p holds flat route sorted_routes[p]. */
+typedef struct fmoe_workspace_layout {
+  size_t total_bytes;
+  size_t status;         /* int32[16]: [0] error, [1] detail, [2] work items, [3] active experts */
+  size_t counts;         /* int32[E]   routes per expert */
+  size_t offsets;        /* int32[E+1] exclusive prefix of counts */
+  size_t sorted_routes;  /* int32[T*K] flat route ids t*K+slot grouped by expert, ascending inside an expert */
+  size_t row_expert;     /* int32[T*K] expert of each sorted row */
+  size_t items;          /* int32[4*max_items] (expert, first row, rows, reserved) per work item; two lists */
+  size_t scratch;        /* route-build scratch */
+  size_t a_rows;         /* W8A8: int8[T*K,H] quantised token rows; BF16: bf16[T*K,H] gathered rows */
+  size_t a_scale;        /* W8A8: fp32[T*K] activation scales */
+  size_t y;              /* bf16[T*K,I] SiLU(gate)*up */
+  size_t yq;             /* W8A8: int8[T*K,I] */
+  size_t y_scale;        /* W8A8: fp32[T*K] */
+  size_t route_out;      /* fp32[T*K,H], row = FLAT route id (already un-permuted) */
+} fmoe_workspace_layout;
+
+/* ---- library state -------------------------------------------------------------------------- */
+
+FMOE_API int fmoe_abi_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+FMOE_API const char* fmoe_last_error(void);
+
+/* 1 if `device` is a compute-capability-10.x GPU this library can run on, else 0. */
+FMOE_API int fmoe_device_supported(int device);
+
+/* Synchronises `stream` and returns the status block of `workspace`: *error is FMOE_OK or the first
+ * device-detected error, *detail its argument (e.g. the offending flat route id). */
+FMOE_API int fmoe_read_status(const void* workspace, void* stream, int32_t* error, int32_t* detail);
+
+/* ---- W8A8 routed-expert MoE ------------------------------------------------------------------ */
+
+/* Workspace size and layout for fmoe_w8a8_forward (the reference keeps the same buffers in a
+ * thread-local RuntimeScratch, csrc/moe/arm/i8mm_w8a8/kernels.cpp:118-182). */
+FMOE_API int fmoe_w8a8_workspace_layout(int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden, int32_t inter,
+                               fmoe_workspace_layout* layout);
+
+/* The W8A8 forward: route lists, per-route int8 activation quantisation, grouped gate_up GEMM with
+ * dequant + clamp-10 SwiGLU + bf16 store, row requantisation, grouped down GEMM with dequant into
+ * fp32 route rows, fixed-order top-k merge.  Replaces fused_moe_w8a8_tiled_async_plan_v2
+ * (csrc/moe/arm/i8mm_w8a8/kernels.cpp:463-694).  `config` may be NULL (defaults). */
+FMOE_API int fmoe_w8a8_forward(const void* x, const int8_t* w13, const float* s13, const int8_t* w2, const float* s2,
+                      const float* topk_weights, const int64_t* topk_ids, int64_t tokens, int32_t top_k,
+                      int32_t experts, int32_t hidden, int32_t inter, const fmoe_config* config, void* out,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Per-output-channel weight quantiser: scale = amax/127 (1 if the row is zero),
+ * q = clamp(round_half_even(w/scale), +-127).  Replaces the quantiser inside
+ * fused_moe_w8a8_tiled_prepare_weights (csrc/moe/arm/i8mm_w8a8/kernels.cpp:446-461).
+ * w[rows, cols] bf16 -> q[rows, cols] int8, scale[rows] fp32. */
+FMOE_API int fmoe_quantize_weight_rows(const void* w, int64_t rows, int32_t cols, int8_t* q, float* scale, void* stream);
+
+/* Row quantiser stage hook: x[rows, cols] bf16 -> q int8 + scale fp32 with the chosen numerics
+ * (quantize_bf16_row, csrc/moe/arm/i8mm_w8a8/kernels.cpp:211-228). */
+FMOE_API int fmoe_quantize_rows(const void* x, int64_t rows, int32_t cols, int32_t numerics, int8_t* q, float* scale,
+                       void* stream);
+
+/* ---- BF16 routed-expert MoE ------------------------------------------------------------------ */
+
+FMOE_API int fmoe_bf16_workspace_layout(int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden, int32_t inter,
+                               fmoe_workspace_layout* layout);
+
+/* The BF16 forward: route lists, row gather, grouped gate_up GEMM (fp32 accumulate) with
+ * SiLU(gate)*up -> bf16, grouped down GEMM into fp32 route rows, tree/chain top-k merge.
+ * Replaces fused_moe_bf16_tiled / fused_moe_bf16_tiled_async_plan_v2
+ * (csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:6376, :9394). */
+FMOE_API int fmoe_bf16_forward(const void* x, const void* w13, const void* w2, const float* topk_weights,
+                      const int64_t* topk_ids, int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden,
+                      int32_t inter, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* ---- dense W8A8 linear ----------------------------------------------------------------------- */
+
+/* Workspace bytes for fmoe_i8gemm_dynamic_scaled_mm. */
+FMOE_API size_t fmoe_i8gemm_workspace_bytes(int64_t rows, int32_t k, int32_t n);
+
+/* out[M,N] = dequant( quant_rows(x[M,K]) @ w[N,K]^T ) (+ bias): per-row dynamic int8 quantisation
+ * (scale = amax/127, 1 for a zero row; q = clamp(nearbyint(x/scale), -128, 127)), int32 accumulate,
+ * value = (acc * x_scale[m]) * w_scale[n] (+ bias[n]).  Replaces i8gemm_dynamic_scaled_mm
+ * (csrc/i8gemm.cpp:318-452, scalar-fallback arithmetic :384-399, :147-165).
+ * x_is_bf16 / out_is_bf16 select bf16 (else fp32) element types; bias may be NULL. */
+FMOE_API int fmoe_i8gemm_dynamic_scaled_mm(const void* x, int32_t x_is_bf16, int64_t rows, int32_t k, const int8_t* w,
+                                  const float* w_scale, const float* bias, int32_t n, void* out,
+                                  int32_t out_is_bf16, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FUSED_MOE_B200_H_ */

@@ -98,9 +98,8 @@ static inline uint16_t swiglu_to_bf16(float gate, float up, float limit) {
 }
 
 static inline float round_half_away(float value) {
-  /* svrinta: ties away from zero.  |value| <= 127 here so truncation is exact. */
-  const float magnitude = floorf(fabsf(value) + 0.5f);
-  return value < 0.0f ? -magnitude : magnitude;
+  /* svrinta: ties away from zero, which is C's roundf. */
+  return roundf(value);
 }
 
 /* One row of bf16 -> int8 + scale. */

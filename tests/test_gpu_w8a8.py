@@ -1,0 +1,146 @@
+"""W8A8 routed-expert MoE on the GPU, through the C ABI, against the CPU oracle and the golden
+outputs of the reference's own Python functions.  Integer and byte results are compared bit-exactly;
+so are the bf16/fp32 stages, because the kernels follow the reference's arithmetic step by step
+with IEEE operations (tolerance 0 everywhere in this file).
+"""
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+
+from fused_cpp_b200 import _lib
+from oracle import oracle
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+IMPLS = {"simt": _lib.GEMM_SIMT, "umma": _lib.GEMM_UMMA}
+
+
+def _to_cuda(case, device):
+    return {k: v.to(device) for k, v in case.items()}
+
+
+def _run(case, device, **kw):
+    c = _to_cuda(case, device)
+    return _lib.moe_forward(c["x"], c["w13"], c["w2"], c["topk_weights"], c["topk_ids"], s13=c["s13"], s2=c["s2"], **kw)
+
+
+def _check_all_stages(case, result, numerics):
+    tokens, hidden = case["x"].shape
+    experts, two_i, _ = case["w13"].shape
+    inter = two_i // 2
+    top_k = case["topk_ids"].shape[1]
+    routes = tokens * top_k
+    out_ref, d = oracle.w8a8_forward(case["x"], case["w13"], case["s13"], case["w2"], case["s2"], case["topk_weights"],
+                                     case["topk_ids"], numerics, dumps=True)
+    counts_ref, offsets_ref, order_ref = oracle.route_build(case["topk_ids"], experts)
+    error, detail = result.status()
+    assert error == 0, (error, detail)
+    order = result.region("sorted_routes", torch.int32, (routes,)).cpu()
+    assert torch.equal(result.region("counts", torch.int32, (experts,)).cpu(), counts_ref)
+    assert torch.equal(result.region("offsets", torch.int32, (experts + 1,)).cpu(), offsets_ref)
+    assert torch.equal(order, order_ref), "route lists differ"
+    assert torch.equal(result.region("row_expert", torch.int32, (routes,)).cpu().long(),
+                       case["topk_ids"].reshape(-1)[order.long()])
+    token_of_row = (order // top_k).long()
+    flat = order.long()
+    assert torch.equal(result.region("a_rows", torch.int8, (routes, hidden)).cpu(), d["xq"][token_of_row]), "xq differs"
+    assert torch.equal(result.region("a_scale", torch.float32, (routes,)).cpu(), d["a"][token_of_row]), "a differs"
+    assert torch.equal(result.acc1.cpu(), d["acc1"][flat]), "gate_up int32 accumulators differ"
+    y = result.region("y", torch.bfloat16, (routes, inter)).cpu()
+    assert torch.equal(y.view(torch.int16), d["y"][flat].view(torch.int16)), "SwiGLU output differs"
+    assert torch.equal(result.region("yq", torch.int8, (routes, inter)).cpu(), d["yq"][flat]), "yq differs"
+    assert torch.equal(result.region("y_scale", torch.float32, (routes,)).cpu(), d["a2"][flat]), "a2 differs"
+    assert torch.equal(result.acc2.cpu(), d["acc2"][flat]), "down int32 accumulators differ"
+    route_out = result.region("route_out", torch.float32, (routes, hidden)).cpu()
+    assert torch.equal(route_out, d["route_out"]), "route_out differs"
+    assert torch.equal(result.out.cpu().view(torch.int16), out_ref.view(torch.int16)), "output differs"
+
+
+@pytest.mark.parametrize("impl", ["simt", "umma"])
+@pytest.mark.parametrize("numerics", [0, 1], ids=["torchref", "native"])
+@pytest.mark.parametrize("name", cases.W8A8_CASES)
+def test_w8a8_every_stage_matches_oracle(cuda_device, name, numerics, impl):
+    case = cases.w8a8_case(name)
+    result = _run(case, cuda_device, numerics=numerics, gemm_impl=IMPLS[impl], dump=True)
+    _check_all_stages(case, result, numerics)
+
+
+@pytest.mark.parametrize("impl", ["simt", "umma"])
+@pytest.mark.parametrize("name", cases.W8A8_CASES)
+def test_w8a8_matches_reference_golden(cuda_device, name, impl):
+    """Golden = tests/test_moe_w8a8.py::_quantize_row/_reference of the reference, run on the same inputs."""
+    case = cases.w8a8_case(name)
+    golden = torch.load(os.path.join(GOLDEN, f"w8a8_{name}.pt"))
+    result = _run(case, cuda_device, numerics=_lib.NUMERICS_TORCHREF, gemm_impl=IMPLS[impl])
+    top_k = case["topk_ids"].shape[1]
+    routes = case["topk_ids"].numel()
+    hidden = case["x"].shape[1]
+    order = result.region("sorted_routes", torch.int32, (routes,)).cpu()
+    token_of_row = (order // top_k).long()
+    assert torch.equal(result.region("a_rows", torch.int8, (routes, hidden)).cpu(), golden["xq"][token_of_row])
+    assert torch.equal(result.region("a_scale", torch.float32, (routes,)).cpu(), golden["a"].float()[token_of_row])
+    # The reference's own native-vs-Python tolerance is atol=3e-6 (tests/test_moe_w8a8.py:225); this path is bit-exact.
+    assert torch.equal(result.out.cpu().view(torch.int16), golden["out"].view(torch.int16))
+
+
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+def test_w8a8_row_tile_does_not_change_results(cuda_device, tile):
+    """Every row-tile configuration of the tcgen05 kernel gives the same bits (the reference's
+    route-slice tests, tests/test_fused_moe_bf16_tiled.py:358-464, recast for tile height)."""
+    case = cases.w8a8_case("wide")
+    result = _run(case, cuda_device, gemm_impl=_lib.GEMM_UMMA, gate_up_tile=tile, down_tile=tile, dump=True)
+    _check_all_stages(case, result, 0)
+
+
+def test_w8a8_repeated_call_is_bit_identical(cuda_device):
+    case = cases.w8a8_case("ragged")
+    first = _run(case, cuda_device).out.clone()
+    second = _run(case, cuda_device).out.clone()
+    assert torch.equal(first.view(torch.int16), second.view(torch.int16))
+
+
+def test_w8a8_identical_rows_give_identical_outputs(cuda_device):
+    """A token's result does not depend on its position in the batch (docs/public_contracts.md:38-42)."""
+    case = cases.w8a8_case("wide")
+    case["x"][57] = case["x"][3]
+    case["topk_ids"][57] = case["topk_ids"][3]
+    case["topk_weights"][57] = case["topk_weights"][3]
+    out = _run(case, cuda_device).out.cpu()
+    assert torch.equal(out[57].view(torch.int16), out[3].view(torch.int16))
+
+
+def test_w8a8_out_of_range_expert_id_is_reported(cuda_device):
+    case = cases.w8a8_case("tiny")
+    case["topk_ids"][2, 1] = 99
+    result = _run(case, cuda_device)
+    error, detail = result.status()
+    assert error == _lib.ERR_EXPERT_ID_RANGE and detail == 2 * case["topk_ids"].shape[1] + 1
+    with pytest.raises(_lib.FusedMoEError, match="out of range"):
+        result.raise_for_status()
+
+
+def test_w8a8_rejects_unclamped_activation(cuda_device):
+    case = cases.w8a8_case("tiny")
+    with pytest.raises(ValueError, match="limit 10.0"):
+        _run(case, cuda_device, swiglu_limit=0.0)
+
+
+def test_w8a8_empty_batch(cuda_device):
+    case = cases.w8a8_case("tiny")
+    case["x"] = case["x"][:0]
+    case["topk_ids"] = case["topk_ids"][:0]
+    case["topk_weights"] = case["topk_weights"][:0]
+    assert _run(case, cuda_device).out.shape == (0, 64)
+
+
+def test_row_quantiser_hook_matches_oracle(cuda_device):
+    x = cases.w8a8_case("cfg1")["x"]
+    for numerics in (0, 1):
+        q, scale = _lib.quantize_rows(x.to(cuda_device), numerics)
+        q_ref, scale_ref = oracle.quantize_rows(x, numerics)
+        assert torch.equal(q.cpu(), q_ref) and torch.equal(scale.cpu(), scale_ref)
