@@ -268,6 +268,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
   ptx::tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     ptx::tcgen05_fence_after();
     ptx::tmem_dealloc(tmem_base, Cfg::kTmemColumns);
   }
