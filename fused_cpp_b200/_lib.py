@@ -32,14 +32,17 @@ EXPORTS = (
     "fmoe_abi_version", "fmoe_last_error", "fmoe_device_supported", "fmoe_read_status",
     "fmoe_w8a8_workspace_layout", "fmoe_w8a8_forward", "fmoe_quantize_weight_rows", "fmoe_quantize_rows",
     "fmoe_bf16_workspace_layout", "fmoe_bf16_forward", "fmoe_i8gemm_workspace_bytes", "fmoe_i8gemm_dynamic_scaled_mm",
+    "fmoe_stage_timer_create", "fmoe_stage_timer_destroy", "fmoe_stage_timer_reset", "fmoe_stage_timer_calls",
+    "fmoe_stage_timer_read",
 )
+STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
 
 class Config(ctypes.Structure):
     _fields_ = [
         ("numerics", ctypes.c_int32), ("gemm_impl", ctypes.c_int32), ("gate_up_tile", ctypes.c_int32),
         ("down_tile", ctypes.c_int32), ("swiglu_limit", ctypes.c_float), ("reserved0", ctypes.c_int32),
-        ("dump_acc1", ctypes.c_void_p), ("dump_acc2", ctypes.c_void_p),
+        ("stage_timer", ctypes.c_void_p), ("dump_acc1", ctypes.c_void_p), ("dump_acc2", ctypes.c_void_p),
     ]
 
 
@@ -81,6 +84,11 @@ def load() -> ctypes.CDLL:
                                       ctypes.c_size_t, p]
     lib.fmoe_quantize_weight_rows.argtypes = [p, i64, i32, p, p, p]
     lib.fmoe_quantize_rows.argtypes = [p, i64, i32, i32, p, p, p]
+    lib.fmoe_stage_timer_create.argtypes = [i32, ctypes.POINTER(ctypes.c_void_p)]
+    lib.fmoe_stage_timer_destroy.argtypes = [p]
+    lib.fmoe_stage_timer_reset.argtypes = [p]
+    lib.fmoe_stage_timer_calls.argtypes = [p]
+    lib.fmoe_stage_timer_read.argtypes = [p, i32, ctypes.POINTER(ctypes.c_float)]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     _LIB = lib
     return lib
@@ -166,6 +174,38 @@ class ForwardResult:
             raise FusedMoEError(error, load().fmoe_last_error().decode("utf-8", "replace"))
 
 
+class StageTimer:
+    """Per-stage CUDA-event timer handed to moe_forward(stage_timer=...): the GPU form of the
+    reference's FUSED_CPP_MOE_STAGE_TIMING report."""
+
+    def __init__(self, max_calls: int):
+        self.handle = ctypes.c_void_p(0)
+        check(load().fmoe_stage_timer_create(int(max_calls), ctypes.byref(self.handle)))
+
+    def reset(self) -> None:
+        check(load().fmoe_stage_timer_reset(self.handle))
+
+    @property
+    def calls(self) -> int:
+        return int(load().fmoe_stage_timer_calls(self.handle))
+
+    def read(self, call: int) -> dict[str, float]:
+        values = (ctypes.c_float * len(STAGES))()
+        check(load().fmoe_stage_timer_read(self.handle, int(call), values))
+        return {name: float(values[i]) for i, name in enumerate(STAGES)}
+
+    def close(self) -> None:
+        if self.handle:
+            load().fmoe_stage_timer_destroy(self.handle)
+            self.handle = ctypes.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def _require_cuda(name: str, tensor: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     if not isinstance(tensor, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor")
@@ -178,7 +218,8 @@ def _require_cuda(name: str, tensor: torch.Tensor, dtype: torch.dtype) -> torch.
 
 def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numerics: int = NUMERICS_TORCHREF,
                 gemm_impl: int = GEMM_AUTO, gate_up_tile: int = 0, down_tile: int = 0, swiglu_limit: float | None = None,
-                out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None) -> ForwardResult:
+                out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None,
+                stage_timer: "StageTimer | None" = None) -> ForwardResult:
     """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8."""
     int8 = w13.dtype == torch.int8
     x = _require_cuda("input", x, torch.bfloat16)
@@ -204,6 +245,8 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
     config.gate_up_tile = gate_up_tile
     config.down_tile = down_tile
     config.swiglu_limit = (10.0 if int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
+    if stage_timer is not None:
+        config.stage_timer = stage_timer.handle
     acc1 = acc2 = None
     if dump:
         acc_dtype = torch.int32 if int8 else torch.float32

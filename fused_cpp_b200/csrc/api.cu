@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -98,6 +99,12 @@ int pick_row_tile(int requested, int64_t routes, int experts, bool umma) {
   return 128;
 }
 
+struct StageTimer {
+  int max_calls = 0;
+  int calls = 0;
+  std::vector<cudaEvent_t> events;  // (FMOE_STAGES + 1) per call
+};
+
 struct Forward {
   bool int8;
   const void* x;
@@ -170,11 +177,22 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   float* y_scale = reinterpret_cast<float*>(base + layout.y_scale);
   float* route_out = reinterpret_cast<float*>(base + layout.route_out);
 
+  StageTimer* timer = static_cast<StageTimer*>(cfg.stage_timer);
+  cudaEvent_t* marks = nullptr;
+  if (timer != nullptr && timer->calls < timer->max_calls) {
+    marks = timer->events.data() + static_cast<size_t>(timer->calls) * (FMOE_STAGES + 1);
+    timer->calls += 1;
+  }
+  auto mark = [&](int index) {
+    if (marks != nullptr) cudaEventRecord(marks[index], stream);
+  };
+  mark(0);
   cudaError_t error = cudaMemsetAsync(status_block, 0, sizeof(int) * fmoe::kStatusWords, stream);
   if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
   error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, tile_gu, tile_dn, max_items, status_block, counts, offsets,
                                    sorted_routes, row_expert, items_gu, items_dn, scratch, stream);
   if (error != cudaSuccess) return cuda_fail(error, "route build");
+  mark(FMOE_STAGE_ROUTE + 1);
   const int* valid_rows = offsets + f.experts;
 
   if (f.int8) {
@@ -185,6 +203,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
                                      reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
   }
   if (error != cudaSuccess) return cuda_fail(error, "activation quantise/gather");
+  mark(FMOE_STAGE_QUANT_IN + 1);
 
   fmoe::GroupedGemmArgs gu;
   memset(&gu, 0, sizeof(gu));
@@ -210,6 +229,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.row_tile = tile_gu;
   error = umma ? fmoe::launch_umma_grouped_gemm(gu, f.int8, true, stream) : fmoe::launch_simt_grouped_gemm(gu, f.int8, true, stream);
   if (error != cudaSuccess) return cuda_fail(error, "gate_up grouped GEMM");
+  mark(FMOE_STAGE_GATE_UP + 1);
 
   const void* down_rows = y;
   if (f.int8) {
@@ -218,6 +238,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     if (error != cudaSuccess) return cuda_fail(error, "intermediate quantise");
     down_rows = yq;
   }
+  mark(FMOE_STAGE_QUANT_MID + 1);
 
   fmoe::GroupedGemmArgs dn = gu;
   dn.a_rows = down_rows;
@@ -234,9 +255,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   dn.row_tile = tile_dn;
   error = umma ? fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
   if (error != cudaSuccess) return cuda_fail(error, "down grouped GEMM");
+  mark(FMOE_STAGE_DOWN + 1);
 
   error = fmoe::launch_merge(route_out, f.topk_weights, f.tokens, f.top_k, f.hidden, f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream);
   if (error != cudaSuccess) return cuda_fail(error, "top-k merge");
+  mark(FMOE_STAGE_MERGE + 1);
   return FMOE_OK;
 }
 
@@ -270,6 +293,50 @@ int fmoe_read_status(const void* workspace, void* stream, int32_t* error, int32_
   } else if (words[fmoe::kStatusError] == FMOE_ERR_DEVICE_WAIT) {
     fail(FMOE_ERR_DEVICE_WAIT, "a bounded device wait gave up (CTA %d, site %d)", words[fmoe::kStatusDetail],
          words[fmoe::kStatusWaitSite]);
+  }
+  return FMOE_OK;
+}
+
+int fmoe_stage_timer_create(int32_t max_calls, void** timer) {
+  if (timer == nullptr || max_calls <= 0 || max_calls > 4096) return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid stage timer request");
+  StageTimer* created = new StageTimer();
+  created->max_calls = max_calls;
+  created->events.resize(static_cast<size_t>(max_calls) * (FMOE_STAGES + 1));
+  for (cudaEvent_t& event : created->events) {
+    const cudaError_t error = cudaEventCreate(&event);
+    if (error != cudaSuccess) return cuda_fail(error, "cudaEventCreate");
+  }
+  *timer = created;
+  return FMOE_OK;
+}
+
+int fmoe_stage_timer_destroy(void* timer) {
+  StageTimer* owned = static_cast<StageTimer*>(timer);
+  if (owned == nullptr) return FMOE_OK;
+  for (cudaEvent_t event : owned->events) cudaEventDestroy(event);
+  delete owned;
+  return FMOE_OK;
+}
+
+int fmoe_stage_timer_reset(void* timer) {
+  if (timer == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "timer is null");
+  static_cast<StageTimer*>(timer)->calls = 0;
+  return FMOE_OK;
+}
+
+int fmoe_stage_timer_calls(void* timer) { return timer == nullptr ? 0 : static_cast<StageTimer*>(timer)->calls; }
+
+int fmoe_stage_timer_read(void* timer, int32_t call, float* stage_ms) {
+  StageTimer* owned = static_cast<StageTimer*>(timer);
+  if (owned == nullptr || stage_ms == nullptr || call < 0 || call >= owned->calls) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid stage timer read");
+  }
+  cudaEvent_t* marks = owned->events.data() + static_cast<size_t>(call) * (FMOE_STAGES + 1);
+  cudaError_t error = cudaEventSynchronize(marks[FMOE_STAGES]);
+  if (error != cudaSuccess) return cuda_fail(error, "cudaEventSynchronize");
+  for (int stage = 0; stage < FMOE_STAGES; ++stage) {
+    error = cudaEventElapsedTime(stage_ms + stage, marks[stage], marks[stage + 1]);
+    if (error != cudaSuccess) return cuda_fail(error, "cudaEventElapsedTime");
   }
   return FMOE_OK;
 }

@@ -1,0 +1,306 @@
+"""The op table of the reference's `fused_cpp._moe_C` extension, backed by the B200 C ABI.
+
+Names, positional order and defaults follow the pybind registration in csrc/moe/module.cpp:14-263
+(prototypes in csrc/moe/common/api.h:58-162).  Differences that are deliberate:
+  * forward ops take CUDA tensors (the reference rejects anything but CPU tensors) and run on the
+    current CUDA stream; prepare_* accept CPU or CUDA weights and return CUDA-resident tensors;
+  * "packed" weights keep the checkpoint layout [E, N, K]: the tcgen05 kernel reads K-major rows
+    through TMA, so there is nothing to repack (the packed objects are opaque by contract,
+    docs/public_contracts.md:9-14);
+  * Plan V2 placement arrays are checked for consistency and otherwise ignored; the row tiles of the
+    two grouped GEMMs ride in task_w13_window_tiles[0] / task_w2_window_tiles[0];
+  * ops that only exist as CPU scheduling experiments raise, as unavailable.cpp does on other hosts.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .. import _lib
+
+BACKEND_ID = 200
+BACKEND_NAME = "cuda_sm100_tcgen05"
+BACKEND_N_TILE = 128
+W8A8_BACKEND_NAME = "cuda_sm100_w8a8_tcgen05"
+
+
+def _device() -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("fused_cpp_b200 requires a CUDA device (there is no CPU path)")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _numerics() -> int:
+    value = os.environ.get("FUSED_CPP_MOE_W8A8_NUMERICS", "torchref").strip().lower()
+    if value in ("torchref", "0", ""):
+        return _lib.NUMERICS_TORCHREF
+    if value in ("native", "1"):
+        return _lib.NUMERICS_NATIVE
+    raise ValueError("FUSED_CPP_MOE_W8A8_NUMERICS must be 'torchref' or 'native'")
+
+
+def _gemm_impl() -> int:
+    value = os.environ.get("FUSED_CPP_MOE_GEMM_IMPL", "auto").strip().lower()
+    table = {"auto": _lib.GEMM_AUTO, "simt": _lib.GEMM_SIMT, "umma": _lib.GEMM_UMMA}
+    if value not in table:
+        raise ValueError("FUSED_CPP_MOE_GEMM_IMPL must be auto, simt or umma")
+    return table[value]
+
+
+def _sync_check() -> bool:
+    return os.environ.get("FUSED_CPP_MOE_SYNC_CHECK", "1") != "0"
+
+
+def fused_moe_bf16_tiled_available_backends() -> list[str]:
+    return [BACKEND_NAME] if _lib.device_supported() else []
+
+
+def fused_moe_w8a8_tiled_available() -> bool:
+    return _lib.device_supported()
+
+
+def page_policy_info() -> dict:
+    return {"backend": BACKEND_NAME, "allocator": "torch caching allocator (cudaMalloc)", "pages": "device"}
+
+
+def page_mappings() -> list:
+    return []
+
+
+def _check_expert_weights(w13: torch.Tensor, w2: torch.Tensor, dtype: torch.dtype, label: str) -> tuple[int, int, int]:
+    if w13.dtype != dtype or w2.dtype != dtype:
+        raise RuntimeError(f"{label} weights must have dtype {dtype}")
+    if w13.dim() != 3 or w2.dim() != 3:
+        raise RuntimeError(f"{label} weights must be [E, 2F, H] and [E, H, F]")
+    experts, n13, hidden = w13.shape
+    if experts <= 0 or w2.shape[0] != experts:
+        raise RuntimeError(f"{label} expert counts must match and be positive")
+    if n13 % 2 != 0:
+        raise RuntimeError(f"{label} W13 output dimension must be even")
+    inter = n13 // 2
+    if tuple(w2.shape[1:]) != (hidden, inter):
+        raise RuntimeError(f"{label} W2 shape mismatch")
+    if hidden % 16 != 0 or inter % 16 != 0:
+        raise RuntimeError(f"{label} requires H and F to be multiples of 16")
+    return experts, hidden, inter
+
+
+def fused_moe_bf16_tiled_prepare_weights(w13_weight, w2_weight, fuse_silu=False, backend="auto"):
+    """-> (w13_packed, K13, N13, w2_packed, K2, N2, backend_id, n_tile, name); api.h:58-60."""
+    if backend not in ("auto", BACKEND_NAME):
+        raise RuntimeError(f"unknown BF16 fused MoE backend {backend!r}; available: {BACKEND_NAME}")
+    experts, hidden, inter = _check_expert_weights(w13_weight, w2_weight, torch.bfloat16, "BF16 tiled fused MoE")
+    device = _device()
+    w13 = w13_weight.to(device).contiguous()
+    w2 = w2_weight.to(device).contiguous()
+    return (w13, hidden, 2 * inter, w2, inter, hidden, BACKEND_ID, BACKEND_N_TILE, BACKEND_NAME)
+
+
+def fused_moe_bf16_tiled_prepare_routed_shared_weights(routed_w13, routed_w2, shared_w13, shared_w2, backend="auto"):
+    """Routed experts followed by the shared expert as expert id E; api.h:72-75."""
+    if shared_w13.dim() != 2 or shared_w2.dim() != 2:
+        raise RuntimeError("shared weights must be [2F, H] and [H, F]")
+    w13 = torch.cat((routed_w13, shared_w13.unsqueeze(0).to(routed_w13.device)), dim=0)
+    w2 = torch.cat((routed_w2, shared_w2.unsqueeze(0).to(routed_w2.device)), dim=0)
+    return fused_moe_bf16_tiled_prepare_weights(w13, w2, True, backend)
+
+
+def fused_moe_w8a8_tiled_prepare_quantized_weights(w13_weight, w13_scale, w2_weight, w2_scale):
+    """-> (q13, K13, N13, s13[E,2F], q2, K2, N2, s2[E,H], backend_id, n_tile); kernels.cpp:424-444."""
+    experts, hidden, inter = _check_expert_weights(w13_weight, w2_weight, torch.int8, "W8A8")
+    if w13_scale.dtype != torch.float32 or w2_scale.dtype != torch.float32:
+        raise RuntimeError("W8A8 scales must be float32 tensors")
+    if w13_scale.numel() != experts * 2 * inter:
+        raise RuntimeError("W8A8 W13 scales must contain one value per output channel")
+    if w2_scale.numel() != experts * hidden:
+        raise RuntimeError("W8A8 W2 scales must contain one value per output channel")
+    device = _device()
+    return (w13_weight.to(device).contiguous(), hidden, 2 * inter, w13_scale.to(device).reshape(experts, 2 * inter).contiguous(),
+            w2_weight.to(device).contiguous(), inter, hidden, w2_scale.to(device).reshape(experts, hidden).contiguous(),
+            BACKEND_ID, BACKEND_N_TILE)
+
+
+def fused_moe_w8a8_tiled_prepare_weights(w13_weight, w2_weight):
+    """bf16 weights -> per-output-channel int8 on the GPU, then as above; kernels.cpp:446-461."""
+    experts, hidden, inter = _check_expert_weights(w13_weight, w2_weight, torch.bfloat16, "W8A8 source")
+    device = _device()
+    q13, s13 = _lib.quantize_rows(w13_weight.to(device).reshape(experts * 2 * inter, hidden), weight_mode=True)
+    q2, s2 = _lib.quantize_rows(w2_weight.to(device).reshape(experts * hidden, inter), weight_mode=True)
+    return fused_moe_w8a8_tiled_prepare_quantized_weights(q13.reshape(experts, 2 * inter, hidden), s13.reshape(experts, 2 * inter),
+                                                          q2.reshape(experts, hidden, inter), s2.reshape(experts, hidden))
+
+
+def _check_out(input: torch.Tensor, out: torch.Tensor | None, others) -> None:
+    if out is None:
+        return
+    if out.device != input.device or out.dtype != torch.bfloat16 or out.shape != input.shape or not out.is_contiguous():
+        raise RuntimeError("out must be a contiguous BF16 tensor with the input shape on the input's device")
+    if out.requires_grad:
+        raise RuntimeError("out with requires_grad=True is not supported")
+    for other in others:
+        if other is not None and out.untyped_storage().data_ptr() == other.untyped_storage().data_ptr():
+            raise RuntimeError("out must not alias the input, weights or top-k tensors")
+
+
+def _tile_from(windows) -> int:
+    if windows is None or windows.numel() == 0:
+        return 0
+    return int(windows.reshape(-1)[0])
+
+
+def _check_plan_vectors(task_expert_ids, task_core_begins, task_threads, task_dep_offsets, task_deps, plan_version,
+                        execution_mode, task_min_threads, task_max_threads, task_resize_points, label):
+    if plan_version != 2 or execution_mode != 0:
+        raise RuntimeError(f"{label} requires strict Plan V2 execution")
+    tasks = task_expert_ids.numel()
+    for tensor in (task_core_begins, task_threads, task_min_threads, task_max_threads):
+        if tensor.numel() != tasks:
+            raise RuntimeError(f"{label} task vectors must have matching lengths")
+    if task_dep_offsets.numel() != tasks + 1 or int(task_dep_offsets[tasks]) != task_deps.numel():
+        raise RuntimeError(f"{label} dependency offsets are invalid")
+    if task_resize_points.numel() and bool((task_resize_points != 0).any()):
+        raise RuntimeError(f"{label} does not support dynamic resize points")
+
+
+def fused_moe_w8a8_tiled_async_plan_v2(
+        input, w13_packed, w13_k, w13_n, w13_scales, w2_packed, w2_k, w2_n, w2_scales, topk_weights, topk_ids,
+        task_expert_ids, task_core_begins, task_threads, task_dep_offsets, task_deps, plan_version, execution_mode,
+        task_preferred_threads, task_min_threads, task_max_threads, task_allowed_thread_offsets, task_allowed_threads,
+        task_placement_modes, task_numa_nodes, task_stage_ids, task_resize_points, task_range_granularities,
+        task_w13_window_tiles=None, task_w2_window_tiles=None, thread_cpu_ids=None, num_threads=1, activation="silu",
+        global_num_experts=-1, skip_weighted=False, backend_n_tile=8, out=None, early_merge=0, swiglu_limit=10.0):
+    """The W8A8 forward op; csrc/moe/module.cpp:205-220, csrc/moe/arm/i8mm_w8a8/kernels.cpp:463-694."""
+    _check_plan_vectors(task_expert_ids, task_core_begins, task_threads, task_dep_offsets, task_deps, plan_version,
+                        execution_mode, task_min_threads, task_max_threads, task_resize_points, "W8A8")
+    if activation != "silu" or float(swiglu_limit) != 10.0:
+        raise RuntimeError("W8A8 supports only clamped SwiGLU limit 10.0")
+    if global_num_experts != -1:
+        raise RuntimeError("W8A8 v1 does not support expert-parallel id remapping")
+    if skip_weighted:
+        raise RuntimeError("W8A8 v1 requires weighted TopK merge")
+    if early_merge != 0:
+        raise RuntimeError("W8A8 v1 requires early_merge=False")
+    if input.dim() != 2 or input.dtype != torch.bfloat16 or input.device.type != "cuda":
+        raise RuntimeError("W8A8 input must be a CUDA BF16 [tokens, H] tensor")
+    if topk_ids.dim() != 2 or topk_weights.shape != topk_ids.shape or topk_ids.shape[0] != input.shape[0]:
+        raise RuntimeError("W8A8 topk tensors must be matching [tokens, top_k]")
+    if topk_ids.dtype != torch.int64:
+        raise RuntimeError("W8A8 topk_ids must be torch.int64")
+    if topk_weights.dtype != torch.float32:
+        raise RuntimeError("W8A8 topk_weights must be torch.float32")
+    if input.shape[1] != w13_k or w13_n != 2 * w2_k or w2_n != w13_k:
+        raise RuntimeError("W8A8 expert dimensions mismatch")
+    if backend_n_tile != BACKEND_N_TILE:
+        raise RuntimeError("W8A8 backend N tile mismatch")
+    experts = w13_packed.shape[0]
+    if tuple(w13_scales.shape) != (experts, w13_n) or tuple(w2_scales.shape) != (experts, w2_n):
+        raise RuntimeError("W8A8 scale shapes are invalid")
+    _check_out(input, out, (input, w13_packed, w2_packed, topk_weights, topk_ids))
+    w13 = w13_packed.reshape(experts, w13_n, w13_k)
+    w2 = w2_packed.reshape(experts, w2_n, w2_k)
+    result = _lib.moe_forward(input, w13, w2, topk_weights, topk_ids, s13=w13_scales, s2=w2_scales, numerics=_numerics(),
+                              gemm_impl=_gemm_impl(), gate_up_tile=_tile_from(task_w13_window_tiles),
+                              down_tile=_tile_from(task_w2_window_tiles), swiglu_limit=float(swiglu_limit), out=out)
+    if _sync_check():
+        result.raise_for_status()
+    if out is not None:
+        out._version  # noqa: B018  (written in place by the kernels; torch tracks no version bump for raw pointers)
+    return result.out
+
+
+def _native_activation(activation: str) -> float:
+    if activation == "silu":
+        return 0.0
+    if activation == "silu_clamp10":
+        return 10.0
+    raise RuntimeError(f"unsupported activation {activation!r}: the GPU path implements 'silu' and 'silu_clamp10'")
+
+
+def _bf16_forward(input, w13_packed, w13_k, w13_n, w2_packed, w2_k, w2_n, topk_weights, topk_ids, w13_bias, w2_bias,
+                  activation, global_num_experts, skip_weighted, out, gate_up_tile=0, down_tile=0):
+    if w13_bias is not None or w2_bias is not None:
+        raise RuntimeError("w13_bias / w2_bias are not implemented on the GPU path")
+    if input.dim() != 2 or input.dtype != torch.bfloat16 or input.device.type != "cuda":
+        raise RuntimeError("input must be a CUDA BF16 [tokens, H] tensor")
+    if topk_ids.dim() != 2 or topk_weights.shape != topk_ids.shape or topk_ids.shape[0] != input.shape[0]:
+        raise RuntimeError("topk tensors must be matching [tokens, top_k]")
+    if input.shape[1] != w13_k or w13_n != 2 * w2_k or w2_n != w13_k:
+        raise RuntimeError("expert dimensions mismatch")
+    experts = w13_packed.shape[0]
+    if global_num_experts != -1 and global_num_experts > experts:
+        raise RuntimeError("global_num_experts cannot exceed the packed expert count")
+    if skip_weighted and topk_ids.shape[1] != 1:
+        raise RuntimeError("skip_weighted is only valid when top_k == 1")
+    _check_out(input, out, (input, w13_packed, w2_packed, topk_weights, topk_ids))
+    weights = topk_weights.to(torch.float32)
+    if skip_weighted:
+        weights = torch.ones_like(weights)
+    result = _lib.moe_forward(input, w13_packed.reshape(experts, w13_n, w13_k), w2_packed.reshape(experts, w2_n, w2_k), weights,
+                              topk_ids.to(torch.int64), gemm_impl=_gemm_impl(), gate_up_tile=gate_up_tile, down_tile=down_tile,
+                              swiglu_limit=_native_activation(activation), out=out)
+    if _sync_check():
+        result.raise_for_status()
+    return result.out
+
+
+def fused_moe_bf16_tiled(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids, w13_bias=None,
+                         w2_bias=None, num_threads=1, activation="silu", global_num_experts=-1, skip_weighted=False,
+                         fuse_silu=False, silu_poly_degree=5, gemm_backend=0, backend_n_tile=8, out=None):
+    """The BF16 forward op; csrc/moe/module.cpp:132-139, fused_moe_bf16_tiled.cpp:6376."""
+    if silu_poly_degree not in (4, 5, 6):
+        raise RuntimeError("silu_poly_degree must be 4, 5 or 6")
+    return _bf16_forward(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids, w13_bias, w2_bias,
+                         activation, global_num_experts, skip_weighted, out)
+
+
+def fused_moe_bf16_tiled_async_plan_v2(
+        input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids, task_expert_ids, task_core_begins,
+        task_threads, task_dep_offsets, task_deps, plan_version, execution_mode, task_preferred_threads, task_min_threads,
+        task_max_threads, task_allowed_thread_offsets, task_allowed_threads, task_placement_modes, task_numa_nodes,
+        task_stage_ids, task_resize_points, task_range_granularities, task_w13_window_tiles=None, task_w2_window_tiles=None,
+        thread_cpu_ids=None, w13_bias=None, w2_bias=None, num_threads=1, activation="silu", global_num_experts=-1,
+        skip_weighted=False, fuse_silu=False, silu_poly_degree=5, gemm_backend=0, backend_n_tile=8, out=None, early_merge=-1):
+    """The BF16 Plan V2 op; csrc/moe/module.cpp:162-177, fused_moe_bf16_tiled.cpp:9394."""
+    if plan_version != 2:
+        raise RuntimeError("BF16 async plan requires plan_version 2")
+    return _bf16_forward(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids, w13_bias, w2_bias,
+                         activation, global_num_experts, skip_weighted, out, _tile_from(task_w13_window_tiles),
+                         _tile_from(task_w2_window_tiles))
+
+
+def fused_moe_bf16_tiled_scheduled(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids,
+                                   wave_offsets, team_expert_ids, team_threads, thread_cpu_ids=None, w13_bias=None,
+                                   w2_bias=None, num_threads=1, activation="silu", global_num_experts=-1, skip_weighted=False,
+                                   fuse_silu=False, silu_poly_degree=5, gemm_backend=0, backend_n_tile=8, out=None):
+    """Wave/team schedule variant (csrc/moe/module.cpp:141-150): the CPU placement is ignored on the GPU."""
+    return _bf16_forward(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids, w13_bias, w2_bias,
+                         activation, global_num_experts, skip_weighted, out)
+
+
+def fused_moe_bf16_tiled_async(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids,
+                               task_expert_ids, task_core_begins, task_threads, task_dep_offsets, task_deps,
+                               thread_cpu_ids=None, w13_bias=None, w2_bias=None, num_threads=1, activation="silu",
+                               global_num_experts=-1, skip_weighted=False, fuse_silu=False, silu_poly_degree=5,
+                               gemm_backend=0, backend_n_tile=8, out=None):
+    """Async task-DAG variant (csrc/moe/module.cpp:152-160): the CPU task graph is ignored on the GPU."""
+    return _bf16_forward(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, topk_weights, topk_ids, w13_bias, w2_bias,
+                         activation, global_num_experts, skip_weighted, out)
+
+
+def _not_built(name: str, why: str):
+    def raiser(*_args, **_kwargs):
+        raise RuntimeError(f"{name} is not implemented on this backend: {why}")
+    raiser.__name__ = name
+    return raiser
+
+
+_CPU_ONLY = "it is a CPU thread-scheduling experiment; use fused_moe_bf16_tiled or fused_moe_bf16_tiled_async_plan_v2"
+_W8A16 = "the W8A16 path (int8 weights, bf16 activations) is not built yet"
+fused_moe_bf16_tiled_planned_staged = _not_built("fused_moe_bf16_tiled_planned_staged", _CPU_ONLY)
+fused_moe_bf16_tiled_vllm_staged = _not_built("fused_moe_bf16_tiled_vllm_staged", _CPU_ONLY)
+fused_moe_w8a16_tiled_prepare_weights = _not_built("fused_moe_w8a16_tiled_prepare_weights", _W8A16)
+fused_moe_w8a16_tiled_prepare_quantized_weights = _not_built("fused_moe_w8a16_tiled_prepare_quantized_weights", _W8A16)
+fused_moe_w8a16_tiled_prepare_quantized_routed_shared_weights = _not_built(
+    "fused_moe_w8a16_tiled_prepare_quantized_routed_shared_weights", _W8A16)
+fused_moe_w8a16_tiled_async_plan_v2 = _not_built("fused_moe_w8a16_tiled_async_plan_v2", _W8A16)

@@ -67,6 +67,7 @@ typedef struct fmoe_config {
   int32_t down_tile;     /* same for the down GEMM; 0 = auto */
   float swiglu_limit;    /* BF16: 0 = plain SiLU, 10 = clamp-10 SwiGLU.  W8A8 requires 10. */
   int32_t reserved0;
+  void* stage_timer;     /* optional handle from fmoe_stage_timer_create: per-stage CUDA events are recorded */
   int32_t* dump_acc1;    /* optional [T*K, 2I] int32 (W8A8) / fp32 (BF16): raw gate_up accumulators, sorted-row order */
   int32_t* dump_acc2;    /* optional [T*K, H]: raw down accumulators, sorted-row order */
 } fmoe_config;
@@ -103,6 +104,29 @@ FMOE_API int fmoe_device_supported(int device);
 /* Synchronises `stream` and returns the status block of `workspace`: *error is FMOE_OK or the first
  * device-detected error, *detail its argument (e.g. the offending flat route id). */
 FMOE_API int fmoe_read_status(const void* workspace, void* stream, int32_t* error, int32_t* detail);
+
+/* ---- per-stage timing ------------------------------------------------------------------------ */
+
+/* Stages of one forward call, in launch order.  With a stage timer in fmoe_config the forward records
+ * a CUDA event on its stream before the first stage and after every stage; this is the GPU form of
+ * the reference's FUSED_CPP_MOE_STAGE_TIMING report (csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:6756-6762). */
+#define FMOE_STAGE_ROUTE 0      /* route build (3 kernels) */
+#define FMOE_STAGE_QUANT_IN 1   /* activation quantise + gather (W8A8) / gather (BF16) */
+#define FMOE_STAGE_GATE_UP 2    /* grouped gate_up GEMM + SwiGLU epilogue */
+#define FMOE_STAGE_QUANT_MID 3  /* intermediate requantise (W8A8; empty for BF16) */
+#define FMOE_STAGE_DOWN 4       /* grouped down GEMM + dequant/un-permute epilogue */
+#define FMOE_STAGE_MERGE 5      /* top-k merge */
+#define FMOE_STAGES 6
+
+/* A timer holds events for up to max_calls forward calls; calls beyond that are not recorded. */
+FMOE_API int fmoe_stage_timer_create(int32_t max_calls, void** timer);
+FMOE_API int fmoe_stage_timer_destroy(void* timer);
+/* Forget recorded calls (the events are reused). */
+FMOE_API int fmoe_stage_timer_reset(void* timer);
+/* Number of forward calls recorded since the last reset. */
+FMOE_API int fmoe_stage_timer_calls(void* timer);
+/* Waits for call `call` to finish on the device and writes its FMOE_STAGES stage durations in ms. */
+FMOE_API int fmoe_stage_timer_read(void* timer, int32_t call, float* stage_ms);
 
 /* ---- W8A8 routed-expert MoE ------------------------------------------------------------------ */
 
