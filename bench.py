@@ -371,6 +371,7 @@ def run_multi_gpu(args) -> None:
 
 
 def main() -> None:
+    global E
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
@@ -382,7 +383,6 @@ def main() -> None:
     parser.add_argument("--skip-e2e", action="store_true", help="profiling captures only")
     parser.add_argument("--skip-cpu", action="store_true", help="profiling captures only")
     args = parser.parse_args()
-    global E
     E = args.experts
     if args.warmup < 3:
         args.warmup = 3
