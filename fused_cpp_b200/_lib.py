@@ -33,7 +33,7 @@ EXPORTS = (
     "fmoe_w8a8_workspace_layout", "fmoe_w8a8_forward", "fmoe_quantize_weight_rows", "fmoe_quantize_rows",
     "fmoe_bf16_workspace_layout", "fmoe_bf16_forward", "fmoe_i8gemm_workspace_bytes", "fmoe_i8gemm_dynamic_scaled_mm",
     "fmoe_stage_timer_create", "fmoe_stage_timer_destroy", "fmoe_stage_timer_reset", "fmoe_stage_timer_calls",
-    "fmoe_stage_timer_read",
+    "fmoe_stage_timer_read", "fmoe_route_build_noalloc",
 )
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
@@ -89,6 +89,7 @@ def load() -> ctypes.CDLL:
     lib.fmoe_stage_timer_reset.argtypes = [p]
     lib.fmoe_stage_timer_calls.argtypes = [p]
     lib.fmoe_stage_timer_read.argtypes = [p, i32, ctypes.POINTER(ctypes.c_float)]
+    lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     _LIB = lib
     return lib
@@ -279,3 +280,23 @@ def quantize_rows(x: torch.Tensor, numerics: int = NUMERICS_TORCHREF, weight_mod
     else:
         check(lib.fmoe_quantize_rows(_ptr(x), rows, cols, numerics, _ptr(q), _ptr(scale), _stream()))
     return q, scale
+
+
+def route_build_noalloc(topk_ids: torch.Tensor, experts: int):
+    """Route lists through the allocation-free entry point (scratch inside the library, nothing allocated by it).
+
+    For hosts that cannot allocate device memory while serving.  The output tensors here are the caller's
+    (this helper makes them with torch for convenience); limits: T*K <= 131072, experts <= 512.
+    Returns (counts[E], offsets[E+1], sorted_routes[T*K], row_expert[T*K], status[2]) on the device.
+    """
+    topk_ids = _require_cuda("topk_ids", topk_ids, torch.int64)
+    tokens, top_k = topk_ids.shape
+    device = topk_ids.device
+    counts = torch.empty(experts, dtype=torch.int32, device=device)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=device)
+    order = torch.empty(max(tokens * top_k, 1), dtype=torch.int32, device=device)
+    row_expert = torch.empty(max(tokens * top_k, 1), dtype=torch.int32, device=device)
+    status = torch.empty(2, dtype=torch.int32, device=device)
+    check(load().fmoe_route_build_noalloc(_ptr(topk_ids), tokens, top_k, experts, _ptr(counts), _ptr(offsets), _ptr(order),
+                                          _ptr(row_expert), _ptr(status), _stream()))
+    return counts, offsets, order[: tokens * top_k], row_expert[: tokens * top_k], status

@@ -265,6 +265,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
 
 }  // namespace
 
+namespace fmoe {
+// Lets entry points defined in other translation units set the thread's error text.
+int report_error(int code, const char* text) { return fail(code, "%s", text); }
+}  // namespace fmoe
+
 extern "C" {
 
 int fmoe_abi_version(void) { return FMOE_ABI_VERSION; }

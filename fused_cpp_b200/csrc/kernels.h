@@ -10,6 +10,9 @@ namespace fmoe {
 constexpr int kUnitRoutes = 512;   // routes per warp in the route-build kernels
 constexpr int kMaxExperts = 2048;  // bound of the per-warp shared-memory histograms
 
+// ---- api.cu
+int report_error(int code, const char* text);
+
 // ---- route.cu
 size_t route_scratch_bytes(int64_t routes, int experts);
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,

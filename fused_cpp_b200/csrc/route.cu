@@ -10,6 +10,9 @@
 //   3. route_scatter: every warp replays its unit in order; __match_any_sync ranks equal ids inside
 //                     a 32-route round, so positions are assigned in ascending flat-id order.
 // Ids outside [0, E) raise FMOE_ERR_EXPERT_ID_RANGE in the status block and are dropped.
+#include <cstdio>
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -180,4 +183,92 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
   return cudaGetLastError();
 }
 
+// ---- allocation-free route build ---------------------------------------------------------------
+//
+// Some hosts of this library must not allocate device memory once they are serving: an inference
+// server that handed the whole HBM budget to its KV-cache pool at start-up has nothing left for a
+// cudaMalloc to take, and a runtime whose memory plan is frozen after warm-up treats any later
+// allocation as a bug.  For them the route build is also offered with its scratch (the per-unit
+// histograms, the scan temporaries and the status block) in a fixed array that lives in the
+// library's device image, so the call needs no workspace and performs no allocation of any kind.
+// The price is a fixed ceiling on the problem size and one array shared by every call.
+
+namespace {
+
+constexpr int64_t kStaticMaxRoutes = 131072;  // tokens * top_k
+constexpr int kStaticMaxExperts = 512;
+constexpr size_t kStaticScratchInts = fmoe::kStatusWords + static_cast<size_t>(kStaticMaxRoutes / fmoe::kUnitRoutes) * kStaticMaxExperts +
+                                      2 * (kStaticMaxExperts + 1);
+constexpr int kStaticMaxDevices = 64;
+
+// 528 KB per GPU, held from the moment the library is loaded on that GPU until the process exits.
+static __device__ __align__(256) int g_static_route_scratch[kStaticScratchInts];
+
+// In host code the array's name only stands for the symbol; the address a kernel can use has to be
+// asked for, per device, with that device current.
+int* static_scratch_for_current_device(cudaError_t* error) {
+  static std::mutex guard;
+  static int* address[kStaticMaxDevices] = {};
+  int device = 0;
+  *error = cudaGetDevice(&device);
+  if (*error != cudaSuccess) return nullptr;
+  if (device < 0 || device >= kStaticMaxDevices) {
+    *error = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(guard);
+  if (address[device] == nullptr) {
+    int* pointer = nullptr;
+    *error = cudaGetSymbolAddress(reinterpret_cast<void**>(&pointer), g_static_route_scratch);
+    if (*error != cudaSuccess) return nullptr;
+    address[device] = pointer;
+  }
+  return address[device];
+}
+
+}  // namespace
+
 }  // namespace fmoe
+
+extern "C" int fmoe_route_build_noalloc(const int64_t* topk_ids, int64_t tokens, int32_t top_k, int32_t experts, int32_t* counts,
+                                        int32_t* offsets, int32_t* sorted_routes, int32_t* row_expert, int32_t* status_out,
+                                        void* stream_ptr) {
+  char text[256];
+  if (tokens < 0 || top_k <= 0 || experts <= 0) return fmoe::report_error(FMOE_ERR_INVALID_ARGUMENT, "invalid route-build shape");
+  const int64_t routes = tokens * top_k;
+  if (routes > fmoe::kStaticMaxRoutes || experts > fmoe::kStaticMaxExperts) {
+    snprintf(text, sizeof(text),
+             "fmoe_route_build_noalloc: %lld routes x %d experts exceeds the static scratch (at most %lld routes and %d experts); "
+             "use fmoe_w8a8_forward / fmoe_bf16_forward with a caller workspace for larger problems",
+             static_cast<long long>(routes), experts, static_cast<long long>(fmoe::kStaticMaxRoutes), fmoe::kStaticMaxExperts);
+    return fmoe::report_error(FMOE_ERR_INVALID_ARGUMENT, text);
+  }
+  if (counts == nullptr || offsets == nullptr || status_out == nullptr ||
+      (routes > 0 && (topk_ids == nullptr || sorted_routes == nullptr || row_expert == nullptr))) {
+    return fmoe::report_error(FMOE_ERR_INVALID_ARGUMENT, "fmoe_route_build_noalloc: null pointer");
+  }
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || !fmoe_device_supported(device)) {
+    return fmoe::report_error(FMOE_ERR_UNSUPPORTED_DEVICE, "fmoe_route_build_noalloc: the current device is not a compute capability 10.x GPU");
+  }
+  cudaError_t error = cudaSuccess;
+  int* scratch = fmoe::static_scratch_for_current_device(&error);
+  if (scratch == nullptr) {
+    snprintf(text, sizeof(text), "fmoe_route_build_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(error));
+    return fmoe::report_error(FMOE_ERR_CUDA, text);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  int* status = scratch;                       // kStatusWords ints: must start at zero, the kernels only ever raise it
+  int* work = scratch + fmoe::kStatusWords;    // histograms + scan temporaries: fully rewritten by every call
+  error = cudaMemsetAsync(status, 0, sizeof(int) * fmoe::kStatusWords, stream);
+  if (error == cudaSuccess) {
+    error = fmoe::launch_route_build(topk_ids, routes, experts, 16, 16, 0, status, counts, offsets, sorted_routes, row_expert, nullptr,
+                                     nullptr, work, stream);
+  }
+  if (error == cudaSuccess) error = cudaMemcpyAsync(status_out, status, 2 * sizeof(int), cudaMemcpyDeviceToDevice, stream);
+  if (error != cudaSuccess) {
+    snprintf(text, sizeof(text), "fmoe_route_build_noalloc: %s", cudaGetErrorString(error));
+    return fmoe::report_error(FMOE_ERR_CUDA, text);
+  }
+  return FMOE_OK;
+}

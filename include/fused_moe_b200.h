@@ -155,6 +155,22 @@ FMOE_API int fmoe_quantize_weight_rows(const void* w, int64_t rows, int32_t cols
 FMOE_API int fmoe_quantize_rows(const void* x, int64_t rows, int32_t cols, int32_t numerics, int8_t* q, float* scale,
                        void* stream);
 
+/* Route build without any allocation or caller workspace.  It has no counterpart in the reference, whose
+ * route lists are std::vectors grown on the calling thread.  It exists for hosts that must not allocate
+ * device memory while serving -- a server that gave all of HBM to its KV-cache pool, a runtime with a frozen
+ * memory plan -- and so cannot provide the forward calls' workspace: the histograms and scan temporaries
+ * live in a 528 KB array inside the library's device image (one per GPU that loads the library, held until
+ * the process exits).  Limits: tokens * top_k <= 131072 and experts <= 512; larger requests are refused
+ * with FMOE_ERR_INVALID_ARGUMENT.  The first call on each device looks the array's device address up
+ * (cudaGetSymbolAddress); make that first call during start-up, before any stream capture.  Every call
+ * uses the same array, so two calls that overlap on the GPU (different streams, or threads) race: issue
+ * them on one stream.  Inputs and outputs are the caller's: counts[E], offsets[E+1], sorted_routes[T*K],
+ * row_expert[T*K] as in fmoe_workspace_layout, status_out[2] = (error code, detail) as fmoe_read_status
+ * would report them.  No cudaMalloc, cudaFree or other allocating call is made. */
+FMOE_API int fmoe_route_build_noalloc(const int64_t* topk_ids, int64_t tokens, int32_t top_k, int32_t experts,
+                                      int32_t* counts, int32_t* offsets, int32_t* sorted_routes, int32_t* row_expert,
+                                      int32_t* status_out, void* stream);
+
 /* ---- BF16 routed-expert MoE ------------------------------------------------------------------ */
 
 FMOE_API int fmoe_bf16_workspace_layout(int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden, int32_t inter,
