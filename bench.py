@@ -43,6 +43,7 @@ WORKLOADS = {
     "w8a8_prefill_v3_T8192": {"kind": "int8", "tokens": 8192, "skew": False},
     "w8a8_prefill_v3_T16384": {"kind": "int8", "tokens": 16384, "skew": False},
     "bf16_prefill_v3_T8192": {"kind": "bf16", "tokens": 8192, "skew": False},
+    "w8a8_ep_shared_v3_T16384": {"kind": "int8", "tokens": 16384, "skew": False, "shared": True},
 }
 DEFAULT_WORKLOAD = "bf16_decode_v3_T64"
 EXTRA_POINTS = ["bf16_decode_v3_T1", "bf16_decode_v3_T8", "bf16_decode_v3_T32", "w8a8_decode_v3_T64", "w8a8_prefill_v3_T8192"]
@@ -367,6 +368,8 @@ def run_single_gpu(args) -> None:
 def run_multi_gpu(args) -> None:
     from fused_cpp_b200 import ep
 
+    args.hidden, args.inter, args.top_k = H, I, K
+    args.ep_points = ["w8a8_ep_shared_v3_T16384"]
     ep.bench_main(args, WORKLOADS, SEED, measured_peaks())
 
 

@@ -33,7 +33,8 @@ EXPORTS = (
     "fmoe_w8a8_workspace_layout", "fmoe_w8a8_forward", "fmoe_quantize_weight_rows", "fmoe_quantize_rows",
     "fmoe_bf16_workspace_layout", "fmoe_bf16_forward", "fmoe_i8gemm_workspace_bytes", "fmoe_i8gemm_dynamic_scaled_mm",
     "fmoe_stage_timer_create", "fmoe_stage_timer_destroy", "fmoe_stage_timer_reset", "fmoe_stage_timer_calls",
-    "fmoe_stage_timer_read", "fmoe_route_build_noalloc",
+    "fmoe_stage_timer_read", "fmoe_route_build_noalloc", "fmoe_ep_dispatch_workspace_bytes", "fmoe_ep_dispatch_prepare",
+    "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
 )
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
@@ -89,6 +90,13 @@ def load() -> ctypes.CDLL:
     lib.fmoe_stage_timer_reset.argtypes = [p]
     lib.fmoe_stage_timer_calls.argtypes = [p]
     lib.fmoe_stage_timer_read.argtypes = [p, i32, ctypes.POINTER(ctypes.c_float)]
+    lib.fmoe_ep_dispatch_workspace_bytes.restype = ctypes.c_size_t
+    lib.fmoe_ep_dispatch_workspace_bytes.argtypes = [i64, i32, i32]
+    lib.fmoe_ep_dispatch_prepare.argtypes = [p, p, i64, i32, i32, i32, i32, i32, i32, i32, p, p, p, p, p, p, ctypes.c_size_t, p]
+    lib.fmoe_w8a8_expert_rows_forward.argtypes = [p, p, p, i64, p, p, p, p, i32, i32, i32, ctypes.POINTER(Config), p, p,
+                                                  ctypes.c_size_t, p]
+    lib.fmoe_bf16_expert_rows_forward.argtypes = [p, p, i64, p, p, i32, i32, i32, ctypes.POINTER(Config), p, p, ctypes.c_size_t, p]
+    lib.fmoe_ep_combine_finish.argtypes = [p, p, p, i64, i32, i32, i32, p, p, p]
     lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     _LIB = lib
@@ -300,3 +308,84 @@ def route_build_noalloc(topk_ids: torch.Tensor, experts: int):
     check(load().fmoe_route_build_noalloc(_ptr(topk_ids), tokens, top_k, experts, _ptr(counts), _ptr(offsets), _ptr(order),
                                           _ptr(row_expert), _ptr(status), _stream()))
     return counts, offsets, order[: tokens * top_k], row_expert[: tokens * top_k], status
+
+
+# ---- expert-parallel building blocks (used by fused_cpp_b200.ep) ---------------------------------
+
+def ep_dispatch_prepare(x, topk_ids, experts_global: int, world: int, shared_rank: int, int8: bool,
+                        numerics: int = NUMERICS_TORCHREF):
+    """Sort this rank's routes by destination rank and lay out the payload (fmoe_ep_dispatch_prepare).
+
+    Returns dict(dest_counts int32[W], send_order int32[TK], send_rows [TK,H] int8|bf16, send_scale f32[TK]|None,
+    send_expert int64[TK], workspace)."""
+    x = _require_cuda("input", x, torch.bfloat16)
+    topk_ids = _require_cuda("topk_ids", topk_ids, torch.int64)
+    tokens, hidden = x.shape
+    top_k = topk_ids.shape[1]
+    routes = tokens * top_k
+    device = x.device
+    lib = load()
+    workspace = torch.empty(lib.fmoe_ep_dispatch_workspace_bytes(tokens, top_k, world) + 256, dtype=torch.uint8, device=device)
+    offset = (-workspace.data_ptr()) % 256
+    ws = workspace[offset:]
+    out = {
+        "dest_counts": torch.empty(world, dtype=torch.int32, device=device),
+        "send_order": torch.empty(max(routes, 1), dtype=torch.int32, device=device),
+        "send_rows": torch.empty((max(routes, 1), hidden), dtype=torch.int8 if int8 else torch.bfloat16, device=device),
+        "send_scale": torch.empty(max(routes, 1), dtype=torch.float32, device=device) if int8 else None,
+        "send_expert": torch.empty(max(routes, 1), dtype=torch.int64, device=device),
+        "workspace": ws,
+    }
+    check(lib.fmoe_ep_dispatch_prepare(_ptr(x), _ptr(topk_ids), tokens, top_k, experts_global, world, shared_rank, hidden,
+                                       1 if int8 else 0, numerics, _ptr(out["dest_counts"]), _ptr(out["send_order"]),
+                                       _ptr(out["send_rows"]), _ptr(out["send_scale"]), _ptr(out["send_expert"]), _ptr(ws),
+                                       ws.numel(), _stream()))
+    for name in ("send_order", "send_rows", "send_scale", "send_expert"):
+        if out[name] is not None:
+            out[name] = out[name][:routes]
+    return out
+
+
+def expert_rows_forward(rows, rows_scale, rows_expert, w13, w2, s13=None, s2=None, *, numerics: int = NUMERICS_TORCHREF,
+                        gemm_impl: int = GEMM_AUTO, gate_up_tile: int = 0, down_tile: int = 0, swiglu_limit: float | None = None):
+    """Grouped GEMMs over received rows (fmoe_*_expert_rows_forward).  Returns route_out fp32 [R, H] in row order."""
+    int8 = w13.dtype == torch.int8
+    count = rows.shape[0]
+    experts, two_i, hidden = w13.shape
+    inter = two_i // 2
+    device = w13.device
+    route_out = torch.empty((count, hidden), dtype=torch.float32, device=device)
+    if count == 0:
+        return route_out
+    layout = workspace_layout(int8, count, 1, experts, hidden, inter)
+    workspace = get_workspace(layout.total_bytes, device)
+    config = Config()
+    config.numerics = numerics
+    config.gemm_impl = gemm_impl
+    config.gate_up_tile = gate_up_tile
+    config.down_tile = down_tile
+    config.swiglu_limit = (10.0 if int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
+    lib = load()
+    rows = rows.contiguous()
+    rows_expert = rows_expert.contiguous()
+    if int8:
+        code = lib.fmoe_w8a8_expert_rows_forward(_ptr(rows), _ptr(rows_scale.contiguous()), _ptr(rows_expert), count, _ptr(w13), _ptr(s13),
+                                                 _ptr(w2), _ptr(s2), experts, hidden, inter, ctypes.byref(config), _ptr(route_out),
+                                                 _ptr(workspace), workspace.numel(), _stream())
+    else:
+        code = lib.fmoe_bf16_expert_rows_forward(_ptr(rows), _ptr(rows_expert), count, _ptr(w13), _ptr(w2), experts, hidden, inter,
+                                                 ctypes.byref(config), _ptr(route_out), _ptr(workspace), workspace.numel(), _stream())
+    check(code)
+    return route_out
+
+
+def ep_combine_finish(returned_rows, send_order, topk_weights, tokens: int, top_k: int, tree_merge: bool, out=None):
+    """Scatter the returned fp32 route rows to flat-route order and merge (fmoe_ep_combine_finish)."""
+    hidden = returned_rows.shape[1]
+    device = returned_rows.device
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device)
+    route_out = torch.empty((max(tokens * top_k, 1), hidden), dtype=torch.float32, device=device)
+    check(load().fmoe_ep_combine_finish(_ptr(returned_rows.contiguous()), _ptr(send_order), _ptr(topk_weights.contiguous()), tokens, top_k,
+                                        hidden, 1 if tree_merge else 0, _ptr(route_out), _ptr(out), _stream()))
+    return out

@@ -116,6 +116,12 @@ struct Forward {
   const int64_t* topk_ids;
   int64_t tokens;
   int top_k, experts, hidden, inter;
+  // Expert-rows mode (expert-parallel receive side): `x` holds rows that are already quantised (int8, with
+  // rows_scale) or gathered (bf16), one route per row, topk_ids[R,1] = the row's local expert; the merge is
+  // skipped and the fp32 route rows go to route_out_override in the order the rows were given.
+  const float* rows_scale = nullptr;
+  float* route_out_override = nullptr;
+  bool rows_mode = false;
 };
 
 int run_forward(const Forward& f, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes, void* stream_ptr) {
@@ -125,8 +131,12 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   status = make_layout(f.int8, f.tokens, f.top_k, f.experts, f.hidden, f.inter, &layout);
   if (status != FMOE_OK) return status;
   if (f.tokens == 0) return FMOE_OK;
-  if (f.x == nullptr || f.w13 == nullptr || f.w2 == nullptr || f.topk_weights == nullptr || f.topk_ids == nullptr || out == nullptr) {
+  if (f.x == nullptr || f.w13 == nullptr || f.w2 == nullptr || f.topk_ids == nullptr) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
+  }
+  if (!f.rows_mode && (f.topk_weights == nullptr || out == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
+  if (f.rows_mode && (f.route_out_override == nullptr || (f.int8 && f.rows_scale == nullptr) || f.top_k != 1)) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "expert-rows mode needs route_out, row scales (int8) and one route per row");
   }
   if (f.int8 && (f.s13 == nullptr || f.s2 == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null scale pointer");
   if (workspace == nullptr || workspace_bytes < layout.total_bytes) {
@@ -134,8 +144,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   }
   if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(FMOE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
   const uintptr_t align_mask = reinterpret_cast<uintptr_t>(f.x) | reinterpret_cast<uintptr_t>(f.w13) |
-                               reinterpret_cast<uintptr_t>(f.w2) | reinterpret_cast<uintptr_t>(out);
-  if (align_mask % 16 != 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "x, w13, w2 and out must be 16-byte aligned");
+                               reinterpret_cast<uintptr_t>(f.w2) | reinterpret_cast<uintptr_t>(out) |
+                               reinterpret_cast<uintptr_t>(f.route_out_override);
+  if (align_mask % 16 != 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "x, w13, w2, out and route_out must be 16-byte aligned");
 
   fmoe_config defaults;
   memset(&defaults, 0, sizeof(defaults));
@@ -175,7 +186,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   float* a_scale = reinterpret_cast<float*>(base + layout.a_scale);
   uint16_t* y = reinterpret_cast<uint16_t*>(base + layout.y);
   float* y_scale = reinterpret_cast<float*>(base + layout.y_scale);
-  float* route_out = reinterpret_cast<float*>(base + layout.route_out);
+  float* route_out = f.rows_mode ? f.route_out_override : reinterpret_cast<float*>(base + layout.route_out);
 
   StageTimer* timer = static_cast<StageTimer*>(cfg.stage_timer);
   cudaEvent_t* marks = nullptr;
@@ -195,7 +206,12 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   mark(FMOE_STAGE_ROUTE + 1);
   const int* valid_rows = offsets + f.experts;
 
-  if (f.int8) {
+  if (f.rows_mode && f.int8) {
+    // int8 rows travel as H bytes: gather them as H/2 16-bit words, then their scales.
+    error = fmoe::launch_gather_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden / 2, sorted_routes, 1, valid_rows,
+                                     reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
+    if (error == cudaSuccess) error = fmoe::launch_gather_scalars(f.rows_scale, routes, sorted_routes, valid_rows, a_scale, stream);
+  } else if (f.int8) {
     error = fmoe::launch_quantize_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden, sorted_routes, f.top_k, valid_rows,
                                        cfg.numerics, 0, reinterpret_cast<int8_t*>(base + layout.a_rows), a_scale, stream);
   } else {
@@ -257,8 +273,10 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (error != cudaSuccess) return cuda_fail(error, "down grouped GEMM");
   mark(FMOE_STAGE_DOWN + 1);
 
-  error = fmoe::launch_merge(route_out, f.topk_weights, f.tokens, f.top_k, f.hidden, f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream);
-  if (error != cudaSuccess) return cuda_fail(error, "top-k merge");
+  if (!f.rows_mode) {
+    error = fmoe::launch_merge(route_out, f.topk_weights, f.tokens, f.top_k, f.hidden, f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream);
+    if (error != cudaSuccess) return cuda_fail(error, "top-k merge");
+  }
   mark(FMOE_STAGE_MERGE + 1);
   return FMOE_OK;
 }
@@ -370,6 +388,109 @@ int fmoe_bf16_forward(const void* x, const void* w13, const void* w2, const floa
                       void* stream) {
   const Forward f{false, x, w13, nullptr, w2, nullptr, topk_weights, topk_ids, tokens, top_k, experts, hidden, inter};
   return run_forward(f, config, out, workspace, workspace_bytes, stream);
+}
+
+int fmoe_w8a8_expert_rows_forward(const int8_t* rows_q, const float* rows_scale, const int64_t* rows_expert, int64_t rows,
+                                  const int8_t* w13, const float* s13, const int8_t* w2, const float* s2, int32_t experts,
+                                  int32_t hidden, int32_t inter, const fmoe_config* config, float* route_out, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+  Forward f{true, rows_q, w13, s13, w2, s2, nullptr, rows_expert, rows, 1, experts, hidden, inter};
+  f.rows_scale = rows_scale;
+  f.route_out_override = route_out;
+  f.rows_mode = true;
+  return run_forward(f, config, nullptr, workspace, workspace_bytes, stream);
+}
+
+int fmoe_bf16_expert_rows_forward(const void* rows, const int64_t* rows_expert, int64_t row_count, const void* w13, const void* w2,
+                                  int32_t experts, int32_t hidden, int32_t inter, const fmoe_config* config, float* route_out,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+  Forward f{false, rows, w13, nullptr, w2, nullptr, nullptr, rows_expert, row_count, 1, experts, hidden, inter};
+  f.route_out_override = route_out;
+  f.rows_mode = true;
+  return run_forward(f, config, nullptr, workspace, workspace_bytes, stream);
+}
+
+size_t fmoe_ep_dispatch_workspace_bytes(int64_t tokens, int32_t top_k, int32_t world) {
+  if (tokens < 0 || top_k <= 0 || world <= 0) return 0;
+  const size_t routes = static_cast<size_t>(tokens) * top_k;
+  return align_up(sizeof(int) * fmoe::kStatusWords, 256) + align_up(sizeof(int64_t) * (routes > 0 ? routes : 1), 256) +
+         align_up(sizeof(int) * (world + 1), 256) + align_up(sizeof(int) * (routes > 0 ? routes : 1), 256) +
+         align_up(fmoe::route_scratch_bytes(routes, world), 256) + 256;
+}
+
+int fmoe_ep_dispatch_prepare(const void* x, const int64_t* topk_ids, int64_t tokens, int32_t top_k, int32_t experts_global,
+                             int32_t world, int32_t shared_rank, int32_t hidden, int32_t int8, int32_t numerics, int32_t* dest_counts,
+                             int32_t* send_order, void* send_rows, float* send_scale, int64_t* send_expert, void* workspace,
+                             size_t workspace_bytes, void* stream_ptr) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (tokens < 0 || top_k <= 0 || top_k > 32 || world <= 0 || world > fmoe::kMaxExperts || experts_global <= 0 ||
+      experts_global % world != 0 || hidden <= 0 || hidden % 16 != 0 || shared_rank >= world) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid dispatch shape (experts must divide evenly over the ranks, H %% 16 == 0)");
+  }
+  if (dest_counts == nullptr || workspace == nullptr || workspace_bytes < fmoe_ep_dispatch_workspace_bytes(tokens, top_k, world)) {
+    return fail(FMOE_ERR_WORKSPACE, "dispatch workspace missing or too small");
+  }
+  const int64_t routes = tokens * top_k;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  char* cursor = static_cast<char*>(workspace);
+  auto take = [&cursor](size_t bytes) {
+    char* begin = cursor;
+    cursor += align_up(bytes, 256);
+    return begin;
+  };
+  int* status_block = reinterpret_cast<int*>(take(sizeof(int) * fmoe::kStatusWords));
+  int64_t* dest = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * (routes > 0 ? routes : 1)));
+  int* offsets = reinterpret_cast<int*>(take(sizeof(int) * (world + 1)));
+  int* row_rank = reinterpret_cast<int*>(take(sizeof(int) * (routes > 0 ? routes : 1)));
+  int* scratch = reinterpret_cast<int*>(take(fmoe::route_scratch_bytes(routes, world)));
+  cudaError_t error = cudaMemsetAsync(status_block, 0, sizeof(int) * fmoe::kStatusWords, stream);
+  if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
+  if (routes == 0) {
+    error = cudaMemsetAsync(dest_counts, 0, sizeof(int) * world, stream);
+    return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "cudaMemsetAsync(counts)");
+  }
+  if (x == nullptr || topk_ids == nullptr || send_order == nullptr || send_rows == nullptr || send_expert == nullptr ||
+      (int8 && send_scale == nullptr)) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  }
+  error = fmoe::launch_dest_ranks(topk_ids, routes, experts_global, experts_global / world, shared_rank, dest, stream);
+  if (error == cudaSuccess) {
+    // A stable counting sort of the routes by destination rank: the same kernels as the per-expert route build.
+    error = fmoe::launch_route_build(dest, routes, world, 16, 16, 0, status_block, dest_counts, offsets, send_order, row_rank,
+                                     nullptr, nullptr, scratch, stream);
+  }
+  const int* valid_rows = offsets + world;
+  if (error == cudaSuccess) {
+    if (int8) {
+      error = fmoe::launch_quantize_rows(static_cast<const uint16_t*>(x), routes, hidden, send_order, top_k, valid_rows, numerics, 0,
+                                         static_cast<int8_t*>(send_rows), send_scale, stream);
+    } else {
+      error = fmoe::launch_gather_rows(static_cast<const uint16_t*>(x), routes, hidden, send_order, top_k, valid_rows,
+                                       static_cast<uint16_t*>(send_rows), stream);
+    }
+  }
+  if (error == cudaSuccess) {
+    error = fmoe::launch_local_experts(topk_ids, send_order, routes, valid_rows, experts_global, experts_global / world, send_expert, stream);
+  }
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "expert-parallel dispatch");
+}
+
+int fmoe_ep_combine_finish(const float* returned_rows, const int32_t* send_order, const float* topk_weights, int64_t tokens,
+                           int32_t top_k, int32_t hidden, int32_t tree_merge, float* route_out, void* out, void* stream_ptr) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (tokens < 0 || top_k <= 0 || top_k > 32 || hidden <= 0 || hidden % 16 != 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid combine shape");
+  if (tokens == 0) return FMOE_OK;
+  if (returned_rows == nullptr || send_order == nullptr || topk_weights == nullptr || route_out == nullptr || out == nullptr) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  cudaError_t error = fmoe::launch_scatter_rows_f32(returned_rows, send_order, tokens * top_k, nullptr, hidden, route_out, stream);
+  if (error == cudaSuccess) {
+    error = fmoe::launch_merge(route_out, topk_weights, tokens, top_k, hidden, tree_merge, static_cast<uint16_t*>(out), stream);
+  }
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "expert-parallel combine");
 }
 
 int fmoe_quantize_weight_rows(const void* w, int64_t rows, int32_t cols, int8_t* q, float* scale, void* stream) {

@@ -34,6 +34,22 @@ cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t row
 cudaError_t launch_gather_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
                                const int* valid_rows, uint16_t* out, cudaStream_t stream);
 
+// out[i] = in[index[i]] for fp32 scalars (activation scales following their rows).
+cudaError_t launch_gather_scalars(const float* in, int64_t n, const int* index, const int* valid_rows, float* out,
+                                  cudaStream_t stream);
+
+// ---- ep.cu: helpers of the expert-parallel dispatch / combine
+// dest[i] = ids[i] / experts_per_rank as int64 (ids outside [0, experts_global) become -1).  With
+// shared_rank >= 0 the id experts_global (the replicated shared expert) maps to shared_rank.
+cudaError_t launch_dest_ranks(const int64_t* ids, int64_t n, int experts_global, int experts_per_rank, int shared_rank,
+                              int64_t* dest, cudaStream_t stream);
+// local[p] = ids[order[p]] % experts_per_rank (experts_per_rank for the shared expert) for the first *valid_rows positions.
+cudaError_t launch_local_experts(const int64_t* ids, const int* order, int64_t n, const int* valid_rows, int experts_global,
+                                 int experts_per_rank, int64_t* local, cudaStream_t stream);
+// route_out[order[p], :] = rows[p, :] (fp32 rows of `hidden` columns).
+cudaError_t launch_scatter_rows_f32(const float* rows, const int* order, int64_t n, const int* valid_rows, int hidden,
+                                    float* route_out, cudaStream_t stream);
+
 // ---- merge.cu
 // W8A8: out[t] = bf16( fma chain over slots of route_out[t*K+slot] * w[t,slot] ).
 // BF16: pairwise tree for K in {2,4,6,8}, chain otherwise.

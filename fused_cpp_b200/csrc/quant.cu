@@ -138,7 +138,21 @@ gather_rows_kernel(const uint16_t* __restrict__ x, int cols, const int* __restri
   for (int v = threadIdx.x; v < (cols >> 3); v += kQuantThreads) dst[v] = src[v];
 }
 
+__global__ void gather_scalars_kernel(const float* __restrict__ in, int64_t n, const int* __restrict__ index,
+                                      const int* __restrict__ valid_rows, float* __restrict__ out) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i >= n || (valid_rows && i >= *valid_rows)) return;
+  out[i] = in[index[i]];
+}
+
 }  // namespace
+
+cudaError_t launch_gather_scalars(const float* in, int64_t n, const int* index, const int* valid_rows, float* out,
+                                  cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  gather_scalars_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(in, n, index, valid_rows, out);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
                                  const int* valid_rows, int numerics, int weight_mode, int8_t* q, float* scale,

@@ -1,0 +1,256 @@
+"""Expert-parallel routed-expert MoE over one NVLink/NVSwitch box.
+
+One process per GPU (torch.distributed, NCCL).  Rank r owns experts [r*E/W, (r+1)*E/W) and, if there is
+one, a replica of the shared expert; tokens stay data-parallel.  One forward is
+
+    source rank : quantise / copy each route's token row, sort routes by destination rank   (CUDA)
+    exchange    : counts, then rows + (scale, local expert id) by all-to-all-v               (NCCL)
+    expert rank : grouped gate_up / down GEMMs over the received rows -> fp32 route rows      (CUDA, tcgen05)
+    exchange    : fp32 route rows back by the mirrored all-to-all-v                           (NCCL)
+    source rank : scatter to flat-route order, merge in the reference's slot order            (CUDA)
+
+Each route keeps the single-GPU arithmetic and the merge order is unchanged, so the sharded result is
+bit-identical to the single-GPU one (int8 path and bf16 path alike).  The reference has no expert
+parallelism to be compatible with (csrc/moe/arm/i8mm_w8a8/kernels.cpp:488 rejects it).
+
+The device steps sit behind a small backend object so that the exchange logic can be tested with CPU
+ranks (gloo) and a stand-in backend; the product backend is CudaBackend and nothing else is shipped.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+class CudaBackend:
+    """The three device steps through the C ABI (fused_cpp_b200._lib)."""
+
+    def __init__(self, numerics: int = 0, gate_up_tile: int = 0, down_tile: int = 0):
+        self.numerics = numerics
+        self.gate_up_tile = gate_up_tile
+        self.down_tile = down_tile
+
+    def dispatch_prepare(self, x, topk_ids, experts_global, world, shared_rank, int8):
+        from . import _lib
+
+        return _lib.ep_dispatch_prepare(x, topk_ids, experts_global, world, shared_rank, int8, self.numerics)
+
+    def expert_rows_forward(self, rows, scale, expert, weights, swiglu_limit):
+        from . import _lib
+
+        return _lib.expert_rows_forward(rows, scale, expert, weights["w13"], weights["w2"], weights.get("s13"), weights.get("s2"),
+                                        numerics=self.numerics, gate_up_tile=self.gate_up_tile, down_tile=self.down_tile,
+                                        swiglu_limit=swiglu_limit)
+
+    def combine_finish(self, returned, send_order, topk_weights, tokens, top_k, tree_merge, out):
+        from . import _lib
+
+        return _lib.ep_combine_finish(returned, send_order, topk_weights, tokens, top_k, tree_merge, out)
+
+
+def validate_expert_split(experts_global: int, world: int, local_experts: int, has_shared: bool) -> int:
+    """Experts per rank, after checking that every rank holds the same contiguous share."""
+    if world <= 0 or experts_global <= 0 or experts_global % world != 0:
+        raise ValueError(f"{experts_global} experts do not split evenly over {world} ranks")
+    per_rank = experts_global // world
+    expected = per_rank + (1 if has_shared else 0)
+    if local_experts != expected:
+        raise ValueError(f"this rank holds {local_experts} expert weight blocks, expected {expected} "
+                         f"({per_rank} routed{' + 1 shared' if has_shared else ''})")
+    return per_rank
+
+
+@dataclass
+class ExchangePlan:
+    send_splits: list
+    recv_splits: list
+
+    @property
+    def received(self) -> int:
+        return sum(self.recv_splits)
+
+
+def exchange_counts(dest_counts: torch.Tensor, expected_routes: int, group) -> ExchangePlan:
+    """All-to-all of the per-destination route counts; the split sizes are needed on the host.
+
+    Every rank also tells every other whether its dispatch dropped routes (an expert id out of range), so
+    that all ranks raise together before the row exchange instead of one rank leaving the others waiting.
+    """
+    send = dest_counts.to(torch.int64)
+    dropped = (send.sum() != expected_routes).to(torch.int64)
+    message = torch.stack((send, dropped.expand_as(send)), dim=1).contiguous()
+    reply = torch.empty_like(message)
+    dist.all_to_all_single(reply, message, group=group)
+    send_splits = [int(v) for v in send.tolist()]
+    recv_splits = [int(v) for v in reply[:, 0].tolist()]
+    failed = [rank for rank, flag in enumerate(reply[:, 1].tolist()) if flag]
+    if sum(send_splits) != expected_routes and dist.get_rank(group) not in failed:
+        failed.append(dist.get_rank(group))
+    if failed:
+        raise RuntimeError(f"expert-parallel dispatch dropped routes on rank(s) {sorted(failed)}: an expert id was out of range")
+    return ExchangePlan(send_splits, recv_splits)
+
+
+def _all_to_all_rows(rows: torch.Tensor, out_rows: int, send_splits, recv_splits, group) -> torch.Tensor:
+    received = torch.empty((out_rows,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    dist.all_to_all_single(received, rows.contiguous(), output_split_sizes=recv_splits, input_split_sizes=send_splits, group=group)
+    return received
+
+
+class ExpertParallelMoE:
+    """Routed (+ optional shared) expert layer sharded by expert over the ranks of `group`.
+
+    weights: dict with this rank's blocks w13[E/W (+1), 2I, H], w2[E/W (+1), H, I] (int8 or bf16) and, for int8,
+    s13 / s2; when has_shared the shared expert is the last local block.
+    """
+
+    def __init__(self, weights: dict, experts_global: int, *, has_shared: bool = False, group=None, backend=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.weights = weights
+        self.int8 = weights["w13"].dtype == torch.int8
+        self.has_shared = bool(has_shared)
+        self.experts_global = int(experts_global)
+        self.per_rank = validate_expert_split(self.experts_global, self.world, int(weights["w13"].shape[0]), self.has_shared)
+        self.backend = backend if backend is not None else CudaBackend()
+        self.last_exchange: ExchangePlan | None = None
+
+    def forward(self, x, topk_weights, topk_ids, *, routed_scaling_factor: float = 1.0, swiglu_limit: float | None = None, out=None):
+        tokens = x.shape[0]
+        if self.has_shared:
+            # The reference's convention: the shared expert is expert id E, appended as route K with weight 1.
+            shared = torch.full((tokens, 1), self.experts_global, dtype=topk_ids.dtype, device=topk_ids.device)
+            topk_ids = torch.cat((topk_ids, shared), dim=1).contiguous()
+            ones = torch.ones((tokens, 1), dtype=topk_weights.dtype, device=topk_weights.device)
+            topk_weights = torch.cat((topk_weights * routed_scaling_factor, ones), dim=1).contiguous()
+        elif routed_scaling_factor != 1.0:
+            topk_weights = topk_weights * routed_scaling_factor
+        top_k = topk_ids.shape[1]
+        prepared = self.backend.dispatch_prepare(x, topk_ids, self.experts_global, self.world,
+                                                 self.rank if self.has_shared else -1, self.int8)
+        plan = exchange_counts(prepared["dest_counts"], tokens * top_k, self.group)
+        self.last_exchange = plan
+        rows = _all_to_all_rows(prepared["send_rows"], plan.received, plan.send_splits, plan.recv_splits, self.group)
+        meta = prepared["send_expert"].reshape(-1, 1)
+        if self.int8:
+            meta = torch.cat((meta, prepared["send_scale"].view(torch.int32).to(torch.int64).reshape(-1, 1)), dim=1)
+        meta = _all_to_all_rows(meta.contiguous(), plan.received, plan.send_splits, plan.recv_splits, self.group)
+        expert = meta[:, 0].contiguous()
+        scale = meta[:, 1].to(torch.int32).view(torch.float32).contiguous() if self.int8 else None
+        route_rows = self.backend.expert_rows_forward(rows, scale, expert, self.weights, swiglu_limit)
+        returned = _all_to_all_rows(route_rows, tokens * top_k, plan.recv_splits, plan.send_splits, self.group)
+        return self.backend.combine_finish(returned, prepared["send_order"], topk_weights.to(torch.float32), tokens, top_k,
+                                           not self.int8, out)
+
+    __call__ = forward
+
+
+def shard_rows(total: int, world: int, rank: int) -> slice:
+    """Contiguous even split of `total` tokens (the first total % world ranks take one more)."""
+    base, extra = divmod(total, world)
+    begin = rank * base + min(rank, extra)
+    return slice(begin, begin + base + (1 if rank < extra else 0))
+
+
+# ---- multi-GPU benchmark leg (called by bench.py under torchrun) -----------------------------------
+
+def bench_main(args, workloads: dict, seed: int, peaks: dict) -> None:
+    from . import _lib, synthetic
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", device_id=device)
+    try:
+        if not _lib.device_supported():
+            raise SystemExit("bench.py needs compute-capability-10.x GPUs")
+        hidden, inter, experts, top_k = args.hidden, args.inter, args.experts, args.top_k
+        lines = []
+        for name in [args.workload] + ([] if args.no_points else list(args.ep_points)):
+            spec = workloads[name]
+            lines.append(_bench_one(name, spec, args, rank, world, device, hidden, inter, experts, top_k, seed, peaks,
+                                    has_shared=spec.get("shared", False)))
+        if rank == 0:
+            head = lines[0]
+            head["points"] = lines[1:]
+            print(json.dumps(head), flush=True)
+    finally:
+        dist.destroy_process_group()
+
+
+def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, top_k, seed, peaks, has_shared):
+    from . import synthetic
+
+    kind, tokens = spec["kind"], spec["tokens"]
+    per_rank = experts // world
+    generator = torch.Generator(device=device).manual_seed(seed + 2 + rank)
+    local = per_rank + (1 if has_shared else 0)
+    if kind == "int8":
+        weights = {"w13": torch.randint(-127, 128, (local, 2 * inter, hidden), generator=generator, dtype=torch.int8, device=device),
+                   "w2": torch.randint(-127, 128, (local, hidden, inter), generator=generator, dtype=torch.int8, device=device),
+                   "s13": (torch.rand((local, 2 * inter), generator=generator, device=device) * 1.5 + 0.5) / (127.0 * hidden ** 0.5),
+                   "s2": (torch.rand((local, hidden), generator=generator, device=device) * 1.5 + 0.5) / (127.0 * inter ** 0.5)}
+    else:
+        weights = {"w13": torch.empty((local, 2 * inter, hidden), dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=generator),
+                   "w2": torch.empty((local, hidden, inter), dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=generator)}
+    topk_w, topk_ids = synthetic.make_routing(tokens, experts, top_k, seed, spec.get("skew", False))
+    x = synthetic.make_activations(tokens, hidden, seed + 1)
+    mine = shard_rows(tokens, world, rank)
+    x_host, w_host, ids_host = x[mine].contiguous(), topk_w[mine].contiguous(), topk_ids[mine].contiguous()
+    xd, wd, idd = x_host.to(device), w_host.to(device), ids_host.to(device)
+    layer = ExpertParallelMoE(weights, experts, has_shared=has_shared)
+    kwargs = {"swiglu_limit": 10.0} if kind == "int8" else {}
+
+    def step():
+        return layer(xd, wd, idd, **kwargs)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        return float(elapsed.item())
+
+    ms = timed(step, args.steps, args.warmup)
+
+    x_pin, w_pin, ids_pin = x_host.pin_memory(), w_host.pin_memory(), ids_host.pin_memory()
+    out_pin = torch.empty((x_host.shape[0], hidden), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        out = layer(x_pin.to(device, non_blocking=True), w_pin.to(device, non_blocking=True), ids_pin.to(device, non_blocking=True), **kwargs)
+        out_pin.copy_(out, non_blocking=True)
+
+    e2e_ms = timed(e2e_step, args.steps, args.warmup)
+    local_tokens = x_host.shape[0]
+    work = synthetic.algorithmic_work(synthetic.MoEShape(tokens, hidden, inter, experts, top_k), topk_ids, 1 if kind == "int8" else 2,
+                                      shared=has_shared)
+    return {
+        "metric": "moe_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16" if kind == "bf16" else "int8(w8a8)", "data": "synthetic",
+        "config": {"workload": name, "tokens": tokens, "hidden": hidden, "inter": inter, "experts": experts, "top_k": top_k,
+                   "shared_expert": has_shared, "parallelism": f"ep{world}: experts and tokens split evenly, NCCL all-to-all dispatch/combine",
+                   "l2": "inputs larger than L2: every rank streams its experts' weights each step"},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": local_tokens * hidden * 2 + local_tokens * top_k * 12,
+                "d2h_bytes_per_step": local_tokens * hidden * 2},
+        "gpu_launches": (14 if kind == "int8" else 13) * args.steps,
+        "layer": {"algorithmic_bytes": work["bytes"], "ops": work["ops"],
+                  "hbm_gbs_aggregate": work["bytes"] / (ms * 1e-3) / 1e9, "tops_aggregate": work["ops"] / (ms * 1e-3) / 1e12},
+    }

@@ -185,6 +185,51 @@ FMOE_API int fmoe_bf16_forward(const void* x, const void* w13, const void* w2, c
                       int32_t inter, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/* ---- expert-parallel building blocks ------------------------------------------------------------
+ *
+ * The reference has no expert parallelism (it rejects expert id remapping,
+ * csrc/moe/arm/i8mm_w8a8/kernels.cpp:488): these entry points have no counterpart there.  Ranks own
+ * contiguous blocks of experts_global / world experts; tokens stay data-parallel.  The exchange itself
+ * (two all-to-all-v) is the caller's: NCCL through torch.distributed in fused_cpp_b200/ep.py.  Every route
+ * keeps the single-GPU arithmetic -- quantised where its token lives (quantize_bf16_row,
+ * kernels.cpp:211-228), multiplied where its expert lives (run_stage + epilogues, :328-368, :230-257),
+ * merged in slot order where its token lives (:675-688) -- so a sharded call returns the same bits. */
+
+FMOE_API size_t fmoe_ep_dispatch_workspace_bytes(int64_t tokens, int32_t top_k, int32_t world);
+
+/* Source side, before the exchange: sort this rank's T*K routes by destination rank (stable), and lay the
+ * payload out in that order: send_rows[T*K, H] (int8 quantised per route when int8 != 0, else bf16 copies),
+ * send_scale[T*K] (int8 only), send_expert[T*K] = expert id local to the destination, send_order[T*K] = the
+ * flat route id t*K+slot of each send position, dest_counts[world] = routes per destination.
+ * shared_rank >= 0: the id experts_global names a shared expert replicated on every rank (the reference's
+ * synthetic expert E, src/fused_cpp/moe/bf16_tiled.py:1007-1013); those routes stay on shared_rank (the
+ * caller's own rank) with local expert id experts_global / world.  shared_rank = -1: no shared expert. */
+FMOE_API int fmoe_ep_dispatch_prepare(const void* x, const int64_t* topk_ids, int64_t tokens, int32_t top_k,
+                                      int32_t experts_global, int32_t world, int32_t shared_rank, int32_t hidden, int32_t int8,
+                                      int32_t numerics, int32_t* dest_counts, int32_t* send_order, void* send_rows,
+                                      float* send_scale, int64_t* send_expert, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
+/* Expert side: the grouped gate_up / down GEMMs over received rows (one route per row, rows_expert = local
+ * expert id); route_out[R, H] fp32 comes back in the order the rows were given.  Workspace as
+ * fmoe_*_workspace_layout(tokens = R, top_k = 1, experts = local experts). */
+FMOE_API int fmoe_w8a8_expert_rows_forward(const int8_t* rows_q, const float* rows_scale, const int64_t* rows_expert,
+                                           int64_t rows, const int8_t* w13, const float* s13, const int8_t* w2,
+                                           const float* s2, int32_t experts, int32_t hidden, int32_t inter,
+                                           const fmoe_config* config, float* route_out, void* workspace,
+                                           size_t workspace_bytes, void* stream);
+FMOE_API int fmoe_bf16_expert_rows_forward(const void* rows, const int64_t* rows_expert, int64_t row_count,
+                                           const void* w13, const void* w2, int32_t experts, int32_t hidden,
+                                           int32_t inter, const fmoe_config* config, float* route_out,
+                                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* Source side, after the exchange back: returned_rows[T*K, H] fp32 in send order are scattered to
+ * route_out[flat route] (scratch of T*K*H floats) and merged with topk_weights into out[T, H] bf16;
+ * tree_merge = 1 selects the BF16 path's pairwise order, 0 the W8A8 fused chain. */
+FMOE_API int fmoe_ep_combine_finish(const float* returned_rows, const int32_t* send_order, const float* topk_weights,
+                                    int64_t tokens, int32_t top_k, int32_t hidden, int32_t tree_merge,
+                                    float* route_out, void* out, void* stream);
+
 /* ---- dense W8A8 linear ----------------------------------------------------------------------- */
 
 /* Workspace bytes for fmoe_i8gemm_dynamic_scaled_mm. */

@@ -248,6 +248,66 @@ int fmoe_oracle_w8a8_forward(const uint16_t* x, const int8_t* w13, const float* 
   return 0;
 }
 
+/*
+ * Expert-side half of the W8A8 forward for rows that are already quantised (one route per row):
+ * gate_up dot products, dequant + clamp-10 SwiGLU + bf16, requantise, down dot products, dequant.
+ * Same statements as the per-route loop of fmoe_oracle_w8a8_forward (kernels.cpp:646-671); used to
+ * check the expert-parallel split, where quantisation and GEMMs run on different ranks.
+ */
+int fmoe_oracle_w8a8_route_rows(const int8_t* rows_q, const float* rows_scale, const int64_t* rows_expert, int64_t rows,
+                                const int8_t* w13, const float* s13, const int8_t* w2, const float* s2, int experts,
+                                int hidden, int inter, int numerics, float* route_out) {
+  for (int64_t row = 0; row < rows; ++row) {
+    if (rows_expert[row] < 0 || rows_expert[row] >= experts) return -1;
+  }
+#pragma omp parallel
+  {
+    int32_t* acc1 = (int32_t*)malloc(sizeof(int32_t) * 2 * (size_t)inter);
+    uint16_t* y = (uint16_t*)malloc(sizeof(uint16_t) * (size_t)inter);
+    int8_t* yq = (int8_t*)malloc((size_t)inter);
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t row = 0; row < rows; ++row) {
+      const int64_t expert = rows_expert[row];
+      const int8_t* xrow = rows_q + row * hidden;
+      const int8_t* w13_e = w13 + expert * 2 * (int64_t)inter * hidden;
+      const float* s13_e = s13 + expert * 2 * (int64_t)inter;
+      for (int n = 0; n < 2 * inter; ++n) acc1[n] = dot_i8(xrow, w13_e + (int64_t)n * hidden, hidden);
+      for (int j = 0; j < inter; ++j) {
+        const float gate = dequantize(acc1[j], rows_scale[row], s13_e[j], numerics);
+        const float up = dequantize(acc1[inter + j], rows_scale[row], s13_e[inter + j], numerics);
+        y[j] = swiglu_to_bf16(gate, up, 10.0f);
+      }
+      float a2;
+      quantize_row(y, inter, numerics, yq, &a2);
+      const int8_t* w2_e = w2 + expert * (int64_t)hidden * inter;
+      const float* s2_e = s2 + expert * (int64_t)hidden;
+      for (int h = 0; h < hidden; ++h) {
+        route_out[row * hidden + h] = dequantize(dot_i8(yq, w2_e + (int64_t)h * inter, inter), a2, s2_e[h], numerics);
+      }
+    }
+    free(acc1);
+    free(y);
+    free(yq);
+  }
+  return 0;
+}
+
+/* W8A8 merge alone (kernels.cpp:675-688): fused chain in slot order from zero, bf16 store. */
+void fmoe_oracle_merge_w8a8_path(const float* route_out, const float* topk_w, int64_t tokens, int top_k, int hidden,
+                                 uint16_t* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t token = 0; token < tokens; ++token) {
+    for (int h = 0; h < hidden; ++h) {
+      float accumulator = 0.0f;
+      for (int slot = 0; slot < top_k; ++slot) {
+        const int64_t route = token * top_k + slot;
+        accumulator = fmaf(route_out[route * hidden + h], topk_w[route], accumulator);
+      }
+      out[token * hidden + h] = fmoe_oracle_f32_to_bf16(accumulator);
+    }
+  }
+}
+
 /* route_merge.cpp:48-69: split at the largest power of two below count; leaves are w*route. */
 static float merge_tree(const float* route_out, const float* weights, int64_t hidden, int h, int begin, int count) {
   if (count == 1) return route_out[(int64_t)begin * hidden + h] * weights[begin];

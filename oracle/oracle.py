@@ -152,3 +152,27 @@ def i8gemm_dynamic(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Te
         _ptr(None if bias is None else bias.to(torch.float32).contiguous()), _ptr(out),
         ctypes.c_int(1 if out_dtype == torch.bfloat16 else 0))
     return out
+
+
+def w8a8_route_rows(rows_q, rows_scale, rows_expert, w13, s13, w2, s2, numerics: int = NUMERICS_TORCHREF) -> torch.Tensor:
+    """fmoe_oracle_w8a8_route_rows: pre-quantised rows [R,H] + scales + expert ids -> route_out fp32 [R,H]."""
+    rows, hidden = rows_q.shape
+    experts, two_i, _ = w13.shape
+    out = torch.empty((rows, hidden), dtype=torch.float32)
+    status = lib().fmoe_oracle_w8a8_route_rows(
+        _ptr(rows_q.contiguous()), _ptr(rows_scale.to(torch.float32).contiguous()), _ptr(rows_expert.to(torch.int64).contiguous()),
+        ctypes.c_int64(rows), _ptr(w13.contiguous()), _ptr(s13.to(torch.float32).reshape(experts, two_i).contiguous()),
+        _ptr(w2.contiguous()), _ptr(s2.to(torch.float32).reshape(experts, hidden).contiguous()), ctypes.c_int(experts),
+        ctypes.c_int(hidden), ctypes.c_int(two_i // 2), ctypes.c_int(numerics), _ptr(out))
+    if status != 0:
+        raise ValueError("row expert id is out of range")
+    return out
+
+
+def merge_w8a8_path(route_out: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+    """fmoe_oracle_merge_w8a8_path: route_out fp32 [T,K,H] + weights [T,K] -> bf16 [T,H]."""
+    tokens, top_k, hidden = route_out.shape
+    out = torch.empty((tokens, hidden), dtype=torch.bfloat16)
+    lib().fmoe_oracle_merge_w8a8_path(_ptr(route_out.contiguous()), _ptr(topk_w.to(torch.float32).contiguous()),
+                                      ctypes.c_int64(tokens), ctypes.c_int(top_k), ctypes.c_int(hidden), _ptr(out))
+    return out
