@@ -35,6 +35,7 @@ EXPORTS = (
     "fmoe_stage_timer_create", "fmoe_stage_timer_destroy", "fmoe_stage_timer_reset", "fmoe_stage_timer_calls",
     "fmoe_stage_timer_read", "fmoe_route_build_noalloc", "fmoe_ep_dispatch_workspace_bytes", "fmoe_ep_dispatch_prepare",
     "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
+    "fmoe_i8gemm_dynamic_scaled_mm_pair",
 )
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
@@ -99,6 +100,7 @@ def load() -> ctypes.CDLL:
     lib.fmoe_ep_combine_finish.argtypes = [p, p, p, i64, i32, i32, i32, p, p, p]
     lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
+    lib.fmoe_i8gemm_dynamic_scaled_mm_pair.argtypes = [p, i64, i32, p, p, i32, p, p, p, i32, p, p, ctypes.c_size_t, p]
     _LIB = lib
     return lib
 
@@ -369,7 +371,8 @@ def expert_rows_forward(rows, rows_scale, rows_expert, w13, w2, s13=None, s2=Non
     rows = rows.contiguous()
     rows_expert = rows_expert.contiguous()
     if int8:
-        code = lib.fmoe_w8a8_expert_rows_forward(_ptr(rows), _ptr(rows_scale.contiguous()), _ptr(rows_expert), count, _ptr(w13), _ptr(s13),
+        rows_scale = rows_scale.contiguous()
+        code = lib.fmoe_w8a8_expert_rows_forward(_ptr(rows), _ptr(rows_scale), _ptr(rows_expert), count, _ptr(w13), _ptr(s13),
                                                  _ptr(w2), _ptr(s2), experts, hidden, inter, ctypes.byref(config), _ptr(route_out),
                                                  _ptr(workspace), workspace.numel(), _stream())
     else:
@@ -386,6 +389,7 @@ def ep_combine_finish(returned_rows, send_order, topk_weights, tokens: int, top_
     if out is None:
         out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device)
     route_out = torch.empty((max(tokens * top_k, 1), hidden), dtype=torch.float32, device=device)
-    check(load().fmoe_ep_combine_finish(_ptr(returned_rows.contiguous()), _ptr(send_order), _ptr(topk_weights.contiguous()), tokens, top_k,
+    returned_rows, topk_weights = returned_rows.contiguous(), topk_weights.contiguous()
+    check(load().fmoe_ep_combine_finish(_ptr(returned_rows), _ptr(send_order), _ptr(topk_weights), tokens, top_k,
                                         hidden, 1 if tree_merge else 0, _ptr(route_out), _ptr(out), _stream()))
     return out

@@ -514,20 +514,129 @@ int fmoe_quantize_rows(const void* x, int64_t rows, int32_t cols, int32_t numeri
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "row quantiser");
 }
 
+namespace {
+struct DenseLayout {
+  size_t status, items, xq, scale, total;
+  int max_items;
+  int k_padded;
+};
+
+DenseLayout dense_layout(int64_t rows, int k) {
+  DenseLayout d;
+  d.k_padded = static_cast<int>(align_up(static_cast<size_t>(k), 16));
+  d.max_items = static_cast<int>(rows / 16 + 2);
+  size_t offset = 0;
+  auto take = [&offset](size_t bytes) {
+    const size_t begin = offset;
+    offset = align_up(offset + bytes, 256);
+    return begin;
+  };
+  const size_t r = static_cast<size_t>(rows > 0 ? rows : 1);
+  d.status = take(sizeof(int) * fmoe::kStatusWords);
+  d.items = take(sizeof(int) * 4 * static_cast<size_t>(d.max_items));
+  d.xq = take(r * d.k_padded);
+  d.scale = take(sizeof(float) * r);
+  d.total = offset;
+  return d;
+}
+
+int dense_row_tile(int64_t rows) {
+  if (rows <= 16) return 16;
+  if (rows <= 32) return 32;
+  if (rows <= 64) return 64;
+  return 128;
+}
+
+// One int8 GEMM with the dense epilogue over already-quantised rows.
+cudaError_t dense_gemm(const DenseLayout& d, char* base, int64_t rows, const int8_t* w, const float* w_scale, const float* bias,
+                       int n, void* out, int out_is_bf16, int row_tile, cudaStream_t stream) {
+  fmoe::GroupedGemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.a_rows = base + d.xq;
+  args.weights = w;
+  args.a_scale = reinterpret_cast<const float*>(base + d.scale);
+  args.w_scale = w_scale;
+  args.items = reinterpret_cast<const int*>(base + d.items);
+  args.status = reinterpret_cast<const int*>(base + d.status);
+  args.status_rw = reinterpret_cast<int*>(base + d.status);
+  args.item_count_word = fmoe::kStatusItems;
+  args.max_items = d.max_items;
+  args.experts = 1;
+  args.k = d.k_padded;
+  args.n_out = n;
+  args.numerics = FMOE_NUMERICS_TORCHREF;  // (acc * x_scale) * w_scale, csrc/i8gemm.cpp:157
+  args.total_rows = rows;
+  args.row_tile = row_tile;
+  args.dense_out = out;
+  args.dense_out_bf16 = out_is_bf16;
+  args.bias = bias;
+  return fmoe::launch_umma_grouped_gemm(args, true, false, stream);
+}
+
+int dense_prologue(const void* x, int x_is_bf16, int64_t rows, int k, int clamp_low, void* workspace, size_t workspace_bytes,
+                   DenseLayout* layout, int* row_tile, cudaStream_t stream) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (rows < 0 || k <= 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "i8gemm: rows must be >= 0 and K positive");
+  *layout = dense_layout(rows, k);
+  if (rows == 0) return FMOE_OK;
+  if (x == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "i8gemm: null input");
+  if (workspace == nullptr || workspace_bytes < layout->total || reinterpret_cast<uintptr_t>(workspace) % 256 != 0) {
+    return fail(FMOE_ERR_WORKSPACE, "i8gemm: workspace missing, misaligned or too small (%zu bytes needed)", layout->total);
+  }
+  char* base = static_cast<char*>(workspace);
+  *row_tile = dense_row_tile(rows);
+  cudaError_t error = cudaMemsetAsync(base + layout->status, 0, sizeof(int) * fmoe::kStatusWords, stream);
+  if (error == cudaSuccess) {
+    error = fmoe::launch_quantize_rows_dense(x, x_is_bf16, rows, k, layout->k_padded, clamp_low, reinterpret_cast<int8_t*>(base + layout->xq),
+                                             reinterpret_cast<float*>(base + layout->scale), stream);
+  }
+  if (error == cudaSuccess) {
+    error = fmoe::launch_dense_items(rows, *row_tile, layout->max_items, reinterpret_cast<int*>(base + layout->items),
+                                     reinterpret_cast<int*>(base + layout->status), stream);
+  }
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm activation quantisation");
+}
+}  // namespace
+
 size_t fmoe_i8gemm_workspace_bytes(int64_t rows, int32_t k, int32_t n) {
   (void)n;
   if (rows < 0 || k <= 0) return 0;
-  const size_t k_padded = align_up(static_cast<size_t>(k), 16);
-  return align_up(sizeof(int) * fmoe::kStatusWords, 256) + align_up(static_cast<size_t>(rows > 0 ? rows : 1) * k_padded, 256) +
-         align_up(sizeof(float) * static_cast<size_t>(rows > 0 ? rows : 1), 256) + 256;
+  return dense_layout(rows, k).total;
 }
 
 int fmoe_i8gemm_dynamic_scaled_mm(const void* x, int32_t x_is_bf16, int64_t rows, int32_t k, const int8_t* w,
                                   const float* w_scale, const float* bias, int32_t n, void* out, int32_t out_is_bf16,
-                                  void* workspace, size_t workspace_bytes, void* stream) {
-  (void)x; (void)x_is_bf16; (void)rows; (void)k; (void)w; (void)w_scale; (void)bias; (void)n; (void)out; (void)out_is_bf16;
-  (void)workspace; (void)workspace_bytes; (void)stream;
-  return fail(FMOE_ERR_INVALID_ARGUMENT, "fmoe_i8gemm_dynamic_scaled_mm is not built yet");
+                                  void* workspace, size_t workspace_bytes, void* stream_ptr) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  DenseLayout layout;
+  int row_tile = 16;
+  if (n <= 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "i8gemm: N must be positive");
+  const int status = dense_prologue(x, x_is_bf16, rows, k, -128, workspace, workspace_bytes, &layout, &row_tile, stream);
+  if (status != FMOE_OK || rows == 0) return status;
+  if (w == nullptr || w_scale == nullptr || out == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "i8gemm: null pointer");
+  const cudaError_t error = dense_gemm(layout, static_cast<char*>(workspace), rows, w, w_scale, bias, n, out, out_is_bf16, row_tile, stream);
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm GEMM");
+}
+
+int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows, int32_t k, const int8_t* first_w, const float* first_scale,
+                                       int32_t first_n, void* first_out, const int8_t* second_w, const float* second_scale,
+                                       int32_t second_n, void* second_out, void* workspace, size_t workspace_bytes,
+                                       void* stream_ptr) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  DenseLayout layout;
+  int row_tile = 16;
+  if (first_n <= 0 || second_n <= 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "i8gemm pair: N must be positive");
+  const int status = dense_prologue(x_bf16, 1, rows, k, -127, workspace, workspace_bytes, &layout, &row_tile, stream);
+  if (status != FMOE_OK || rows == 0) return status;
+  if (first_w == nullptr || second_w == nullptr || first_scale == nullptr || second_scale == nullptr || first_out == nullptr ||
+      second_out == nullptr) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "i8gemm pair: null pointer");
+  }
+  char* base = static_cast<char*>(workspace);
+  cudaError_t error = dense_gemm(layout, base, rows, first_w, first_scale, nullptr, first_n, first_out, 1, row_tile, stream);
+  if (error == cudaSuccess) error = dense_gemm(layout, base, rows, second_w, second_scale, nullptr, second_n, second_out, 1, row_tile, stream);
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm pair GEMM");
 }
 
 }  // extern "C"

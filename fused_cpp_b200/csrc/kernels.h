@@ -19,6 +19,9 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
                                int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream);
 
+// Work items of a dense [rows, K] x [N, K]^T product: one "expert", consecutive row tiles.
+cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream);
+
 // ---- quant.cu
 // Quantise rows of a bf16 matrix to int8 with one fp32 scale per row.  When `sorted_routes` is
 // non-null, output row p reads source row sorted_routes[p] / top_k (gather by token).
@@ -28,8 +31,8 @@ cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, 
                                  const int* valid_rows, int numerics, int weight_mode, int8_t* q, float* scale,
                                  cudaStream_t stream);
 // Same for fp32 sources (dense linear).  clamp_low is -128 or -127.
-cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int8_t* q,
-                                       float* scale, cudaStream_t stream);
+cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
+                                       int8_t* q, float* scale, cudaStream_t stream);
 // Copy bf16 rows into expert-sorted order: out[p] = x[sorted_routes[p] / top_k].
 cudaError_t launch_gather_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
                                const int* valid_rows, uint16_t* out, cudaStream_t stream);
@@ -78,6 +81,10 @@ struct GroupedGemmArgs {
   int64_t total_rows;
   int row_tile;              // rows per work item
   int* status_rw;            // writable status block (device-side error reports)
+  // Dense-linear mode of the down epilogue: out[row, n] = dequant (+ bias[n]) as fp32 or bf16, no scatter.
+  void* dense_out;
+  int dense_out_bf16;
+  const float* bias;
 };
 
 // ---- simt_gemm.cu: diagnostic CUDA-core grouped GEMM (work items of at most 8 rows)

@@ -97,10 +97,10 @@ quantize_rows_kernel(const uint16_t* __restrict__ x, int cols, const int* __rest
 }
 
 // Dense linear: arbitrary cols, fp32 or bf16 source, zero-padded to cols_padded, clamp to [-128,127]
-// with division and ties-to-even (csrc/i8gemm.cpp:384-399).
+// (single GEMM) or [-127,127] (paired GEMMs) with division and ties-to-even (csrc/i8gemm.cpp:384-399, :492-506).
 __global__ void __launch_bounds__(kQuantThreads)
-quantize_rows_dense_kernel(const void* __restrict__ x, int x_is_bf16, int cols, int cols_padded, int8_t* __restrict__ q,
-                           float* __restrict__ scale_out) {
+quantize_rows_dense_kernel(const void* __restrict__ x, int x_is_bf16, int cols, int cols_padded, float clamp_low,
+                           int8_t* __restrict__ q, float* __restrict__ scale_out) {
   __shared__ float smem[32];
   const int64_t row = blockIdx.x;
   const float* xf = static_cast<const float*>(x) + row * cols;
@@ -119,7 +119,7 @@ quantize_rows_dense_kernel(const void* __restrict__ x, int x_is_bf16, int cols, 
     if (c < cols) {
       const float source = x_is_bf16 ? bf16_bits_to_f32(xb[c]) : xf[c];
       float rounded = rintf(__fdiv_rn(source, scale));
-      rounded = fmaxf(fminf(rounded, 127.0f), -128.0f);
+      rounded = fmaxf(fminf(rounded, 127.0f), clamp_low);
       value = static_cast<int>(rounded);
     }
     dst[c] = static_cast<int8_t>(value);
@@ -163,11 +163,11 @@ cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, 
   return cudaGetLastError();
 }
 
-cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int8_t* q,
-                                       float* scale, cudaStream_t stream) {
+cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
+                                       int8_t* q, float* scale, cudaStream_t stream) {
   if (rows <= 0) return cudaSuccess;
-  quantize_rows_dense_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(x, x_is_bf16, cols, cols_padded, q,
-                                                                                       scale);
+  quantize_rows_dense_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(
+      x, x_is_bf16, cols, cols_padded, static_cast<float>(clamp_low), q, scale);
   return cudaGetLastError();
 }
 

@@ -183,6 +183,29 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
   return cudaGetLastError();
 }
 
+namespace {
+__global__ void dense_items_kernel(int64_t rows, int row_tile, int max_items, int* items, int* status) {
+  const int tiles = static_cast<int>((rows + row_tile - 1) / row_tile);
+  const int count = tiles < max_items ? tiles : max_items;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < count; t += gridDim.x * blockDim.x) {
+    items[4 * t + 0] = 0;
+    items[4 * t + 1] = t * row_tile;
+    items[4 * t + 2] = static_cast<int>(min(static_cast<int64_t>(row_tile), rows - static_cast<int64_t>(t) * row_tile));
+    items[4 * t + 3] = 0;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    status[kStatusItems] = count;
+    status[kStatusItemsB] = count;
+    status[kStatusActive] = rows > 0 ? 1 : 0;
+  }
+}
+}  // namespace
+
+cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream) {
+  dense_items_kernel<<<8, 256, 0, stream>>>(rows, row_tile, max_items, items, status);
+  return cudaGetLastError();
+}
+
 // ---- allocation-free route build ---------------------------------------------------------------
 //
 // Some hosts of this library must not allocate device memory once they are serving: an inference

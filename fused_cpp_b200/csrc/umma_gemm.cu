@@ -252,8 +252,17 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                 } else {
                   value = __uint_as_float(gate_bits[j]);
                 }
-                const int64_t flat = args.sorted_routes[row];
-                args.route_out[flat * args.n_out + n] = value;
+                if (args.dense_out != nullptr) {
+                  if (args.bias != nullptr) value = __fadd_rn(value, args.bias[n]);
+                  if (args.dense_out_bf16) {
+                    static_cast<uint16_t*>(args.dense_out)[row * args.n_out + n] = f32_to_bf16_bits(value);
+                  } else {
+                    static_cast<float*>(args.dense_out)[row * args.n_out + n] = value;
+                  }
+                } else {
+                  const int64_t flat = args.sorted_routes[row];
+                  args.route_out[flat * args.n_out + n] = value;
+                }
               }
             }
           }

@@ -232,17 +232,26 @@ FMOE_API int fmoe_ep_combine_finish(const float* returned_rows, const int32_t* s
 
 /* ---- dense W8A8 linear ----------------------------------------------------------------------- */
 
-/* Workspace bytes for fmoe_i8gemm_dynamic_scaled_mm. */
+/* Workspace bytes for the dense calls below (quantised rows, scales, work items, status block). */
 FMOE_API size_t fmoe_i8gemm_workspace_bytes(int64_t rows, int32_t k, int32_t n);
 
-/* out[M,N] = dequant( quant_rows(x[M,K]) @ w[N,K]^T ) (+ bias): per-row dynamic int8 quantisation
- * (scale = amax/127, 1 for a zero row; q = clamp(nearbyint(x/scale), -128, 127)), int32 accumulate,
- * value = (acc * x_scale[m]) * w_scale[n] (+ bias[n]).  Replaces i8gemm_dynamic_scaled_mm
- * (csrc/i8gemm.cpp:318-452, scalar-fallback arithmetic :384-399, :147-165).
- * x_is_bf16 / out_is_bf16 select bf16 (else fp32) element types; bias may be NULL. */
+/* out[M,N] = dequant( quant_rows(x[M,K]) @ w^T ) (+ bias): per-row dynamic int8 quantisation
+ * (scale = amax/127, 1 for a zero row; q = clamp(nearbyint(x/scale), -128, 127)), int32 accumulate on
+ * the tensor cores, value = (acc * x_scale[m]) * w_scale[n] (+ bias[n]).  Replaces i8gemm_dynamic_scaled_mm
+ * (csrc/i8gemm.cpp:318-452; scalar-fallback arithmetic :384-399, :147-165).
+ * w is [N, Kp] int8 with Kp = K rounded up to 16 and the padding zero (what i8gemm_prepare's packed
+ * weight is on this backend, csrc/i8gemm.cpp:280-316); w_scale[N] and bias[N] fp32, bias may be NULL;
+ * x_is_bf16 / out_is_bf16 select bf16 (else fp32) element types. */
 FMOE_API int fmoe_i8gemm_dynamic_scaled_mm(const void* x, int32_t x_is_bf16, int64_t rows, int32_t k, const int8_t* w,
-                                  const float* w_scale, const float* bias, int32_t n, void* out,
-                                  int32_t out_is_bf16, void* workspace, size_t workspace_bytes, void* stream);
+                                           const float* w_scale, const float* bias, int32_t n, void* out,
+                                           int32_t out_is_bf16, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Two bf16-output GEMMs over one shared activation quantisation (clamp +-127, no bias).  Replaces
+ * i8gemm_dynamic_scaled_mm_pair (csrc/i8gemm.cpp:454-570; scalar arithmetic :492-506). */
+FMOE_API int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows, int32_t k, const int8_t* first_w,
+                                                const float* first_scale, int32_t first_n, void* first_out,
+                                                const int8_t* second_w, const float* second_scale, int32_t second_n,
+                                                void* second_out, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -397,7 +397,7 @@ int fmoe_oracle_bf16_forward(const uint16_t* x, const uint16_t* w13, const uint1
  * out_bf16 != 0 stores bf16 (nearest-even), else fp32.
  */
 void fmoe_oracle_i8gemm_dynamic(const float* x, int64_t rows, int k, const int8_t* weight, const float* weight_scale,
-                                int n, const float* bias, void* out, int out_bf16) {
+                                int n, const float* bias, void* out, int out_bf16, int clamp_low) {
 #pragma omp parallel
   {
     int8_t* q = (int8_t*)malloc((size_t)k);
@@ -409,7 +409,7 @@ void fmoe_oracle_i8gemm_dynamic(const float* x, int64_t rows, int k, const int8_
       const float scale = maximum > 0.0f ? maximum / 127.0f : 1.0f;
       for (int i = 0; i < k; ++i) {
         float value = rintf(xrow[i] / scale);
-        value = fmaxf(fminf(value, 127.0f), -128.0f);
+        value = fmaxf(fminf(value, 127.0f), (float)clamp_low); /* -128 single GEMM (:395), -127 paired (:505) */
         q[i] = (int8_t)value;
       }
       for (int column = 0; column < n; ++column) {

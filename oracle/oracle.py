@@ -121,9 +121,10 @@ def bf16_forward(x, w13, w2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps:
     if dumps:
         d = {"y": torch.empty((routes, inter), dtype=torch.bfloat16),
              "route_out": torch.empty((routes, hidden), dtype=torch.float32)}
+    x, w13, w2 = x.contiguous(), w13.contiguous(), w2.contiguous()
+    topk_w, topk_ids = topk_w.to(torch.float32).contiguous(), topk_ids.to(torch.int64).contiguous()
     status = lib().fmoe_oracle_bf16_forward(
-        _ptr(x.contiguous()), _ptr(w13.contiguous()), _ptr(w2.contiguous()),
-        _ptr(topk_w.to(torch.float32).contiguous()), _ptr(topk_ids.to(torch.int64).contiguous()),
+        _ptr(x), _ptr(w13), _ptr(w2), _ptr(topk_w), _ptr(topk_ids),
         ctypes.c_int64(tokens), ctypes.c_int(top_k), ctypes.c_int(experts), ctypes.c_int(hidden), ctypes.c_int(inter),
         ctypes.c_float(swiglu_limit), _ptr(out), _ptr(d.get("y")), _ptr(d.get("route_out")))
     if status != 0:
@@ -135,22 +136,26 @@ def merge_bf16_path(route_out: torch.Tensor, topk_w: torch.Tensor) -> torch.Tens
     """fmoe_oracle_merge_bf16_path: route_out fp32 [T,K,H] + weights [T,K] -> bf16 [T,H]."""
     tokens, top_k, hidden = route_out.shape
     out = torch.empty((tokens, hidden), dtype=torch.bfloat16)
-    lib().fmoe_oracle_merge_bf16_path(_ptr(route_out.contiguous()), _ptr(topk_w.to(torch.float32).contiguous()),
+    route_out, topk_w = route_out.contiguous(), topk_w.to(torch.float32).contiguous()
+    lib().fmoe_oracle_merge_bf16_path(_ptr(route_out), _ptr(topk_w),
                                       ctypes.c_int64(tokens), ctypes.c_int(top_k), ctypes.c_int(hidden), _ptr(out))
     return out
 
 
 def i8gemm_dynamic(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, bias=None,
-                   out_dtype=torch.float32) -> torch.Tensor:
+                   out_dtype=torch.float32, clamp_low: int = -128) -> torch.Tensor:
     """fmoe_oracle_i8gemm_dynamic: dense dynamic-quant W8A8 linear (scalar-fallback arithmetic)."""
     rows, k = x.shape
     n = weight.shape[0]
     out = torch.empty((rows, n), dtype=out_dtype)
-    lib().fmoe_oracle_i8gemm_dynamic(
-        _ptr(x.to(torch.float32).contiguous()), ctypes.c_int64(rows), ctypes.c_int(k), _ptr(weight.contiguous()),
-        _ptr(weight_scale.to(torch.float32).contiguous()), ctypes.c_int(n),
-        _ptr(None if bias is None else bias.to(torch.float32).contiguous()), _ptr(out),
-        ctypes.c_int(1 if out_dtype == torch.bfloat16 else 0))
+    # keep every converted operand alive until the call returns
+    x32 = x.to(torch.float32).contiguous()
+    w = weight.contiguous()
+    scale = weight_scale.to(torch.float32).reshape(-1).expand(n).contiguous()
+    bias32 = None if bias is None else bias.to(torch.float32).contiguous()
+    lib().fmoe_oracle_i8gemm_dynamic(_ptr(x32), ctypes.c_int64(rows), ctypes.c_int(k), _ptr(w), _ptr(scale), ctypes.c_int(n),
+                                     _ptr(bias32), _ptr(out), ctypes.c_int(1 if out_dtype == torch.bfloat16 else 0),
+                                     ctypes.c_int(clamp_low))
     return out
 
 
@@ -159,10 +164,13 @@ def w8a8_route_rows(rows_q, rows_scale, rows_expert, w13, s13, w2, s2, numerics:
     rows, hidden = rows_q.shape
     experts, two_i, _ = w13.shape
     out = torch.empty((rows, hidden), dtype=torch.float32)
+    rows_q, rows_scale = rows_q.contiguous(), rows_scale.to(torch.float32).contiguous()
+    rows_expert, w13, w2 = rows_expert.to(torch.int64).contiguous(), w13.contiguous(), w2.contiguous()
+    s13 = s13.to(torch.float32).reshape(experts, two_i).contiguous()
+    s2 = s2.to(torch.float32).reshape(experts, hidden).contiguous()
     status = lib().fmoe_oracle_w8a8_route_rows(
-        _ptr(rows_q.contiguous()), _ptr(rows_scale.to(torch.float32).contiguous()), _ptr(rows_expert.to(torch.int64).contiguous()),
-        ctypes.c_int64(rows), _ptr(w13.contiguous()), _ptr(s13.to(torch.float32).reshape(experts, two_i).contiguous()),
-        _ptr(w2.contiguous()), _ptr(s2.to(torch.float32).reshape(experts, hidden).contiguous()), ctypes.c_int(experts),
+        _ptr(rows_q), _ptr(rows_scale), _ptr(rows_expert), ctypes.c_int64(rows), _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2),
+        ctypes.c_int(experts),
         ctypes.c_int(hidden), ctypes.c_int(two_i // 2), ctypes.c_int(numerics), _ptr(out))
     if status != 0:
         raise ValueError("row expert id is out of range")
@@ -173,6 +181,7 @@ def merge_w8a8_path(route_out: torch.Tensor, topk_w: torch.Tensor) -> torch.Tens
     """fmoe_oracle_merge_w8a8_path: route_out fp32 [T,K,H] + weights [T,K] -> bf16 [T,H]."""
     tokens, top_k, hidden = route_out.shape
     out = torch.empty((tokens, hidden), dtype=torch.bfloat16)
-    lib().fmoe_oracle_merge_w8a8_path(_ptr(route_out.contiguous()), _ptr(topk_w.to(torch.float32).contiguous()),
+    route_out, topk_w = route_out.contiguous(), topk_w.to(torch.float32).contiguous()
+    lib().fmoe_oracle_merge_w8a8_path(_ptr(route_out), _ptr(topk_w),
                                       ctypes.c_int64(tokens), ctypes.c_int(top_k), ctypes.c_int(hidden), _ptr(out))
     return out

@@ -62,3 +62,27 @@ def bf16_case(name: str) -> dict:
     std = 0.05 if shape.hidden <= 256 else 0.02
     return synthetic.make_bf16_case(shape, seed=synthetic.SEED_BASE + 5000 + 1000 * BF16_CASES.index(name),
                                     skew=(name == "ragged"), std=std)
+
+
+# Dense W8A8 linear cases: (M, K, N, x dtype, out dtype, bias).  The first three are the shapes of the
+# reference's own test (tests/test_i8gemm.py:41-47); the others add tile tails and a larger K.
+I8GEMM_CASES = {
+    "m1": (1, 7, 5, torch.bfloat16, torch.float32, True),
+    "m4": (4, 16, 8, torch.bfloat16, torch.bfloat16, True),
+    "m9": (9, 31, 13, torch.bfloat16, torch.bfloat16, True),
+    "f32": (24, 64, 96, torch.float32, torch.float32, False),
+    "wide": (150, 300, 200, torch.bfloat16, torch.bfloat16, False),
+    "deep": (40, 2048, 272, torch.bfloat16, torch.float32, True),
+}
+
+
+def i8gemm_case(name: str) -> dict:
+    m, k, n, x_dtype, out_dtype, with_bias = I8GEMM_CASES[name]
+    generator = torch.Generator().manual_seed(7000 + sorted(I8GEMM_CASES).index(name))
+    weight = torch.randint(-16, 17, (n, k), dtype=torch.int8, generator=generator)
+    weight_scale = torch.rand(n, generator=generator) * 0.05 + 0.01
+    bias = torch.randn(n, generator=generator).to(torch.bfloat16) if with_bias else None
+    x = torch.randn((m, k), generator=generator).to(x_dtype)
+    if name == "wide":
+        x[5].zero_()
+    return {"x": x, "weight": weight, "weight_scale": weight_scale, "bias": bias, "out_dtype": out_dtype}

@@ -7,6 +7,7 @@ Run in a container that has the reference checkout:
 It imports, unmodified,
   * tests/test_moe_w8a8.py::_quantize_row and ::_reference   (the W8A8 per-token reference), and
   * src/fused_cpp/moe/naive.py::fused_moe_naive               (the BF16 reference),
+  * tests/test_i8gemm.py::_reference_dynamic_scaled_mm        (the dense W8A8 linear reference),
 runs them on seeded inputs from fused_cpp_b200.synthetic (plus the input recipe of the reference's
 own W8A8 test), and stores ONLY their outputs (inputs are regenerated from the seeds by the tests).
 The reference cannot travel to the GPU machine; these files can.
@@ -35,11 +36,14 @@ def _load_reference():
     module = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(module)
     from fused_cpp.moe.naive import fused_moe_naive
-    return module._quantize_row, module._reference, fused_moe_naive
+    spec = importlib.util.spec_from_file_location("ref_test_i8gemm", os.path.join(root, "tests", "test_i8gemm.py"))
+    dense = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(dense)
+    return module._quantize_row, module._reference, fused_moe_naive, dense._reference_dynamic_scaled_mm
 
 
 def main() -> None:
-    quantize_row, reference, fused_moe_naive = _load_reference()
+    quantize_row, reference, fused_moe_naive, dense_reference = _load_reference()
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for name in cases.W8A8_CASES:
         case = cases.w8a8_case(name)
@@ -58,6 +62,14 @@ def main() -> None:
                               case["topk_ids"]).to(torch.bfloat16)
         torch.save({"out": out}, os.path.join(HERE, f"bf16_{name}.pt"))
         print("bf16", name, tuple(out.shape))
+
+
+    # appended: dense W8A8 linear, tests/test_i8gemm.py::_reference_dynamic_scaled_mm of the reference
+    for name in cases.I8GEMM_CASES:
+        case = cases.i8gemm_case(name)
+        out = dense_reference(case["x"], case["weight"], case["weight_scale"], bias=case["bias"], out_dtype=case["out_dtype"])
+        torch.save({"out": out}, os.path.join(HERE, f"i8gemm_{name}.pt"))
+        print("i8gemm", name, tuple(out.shape))
 
 
 if __name__ == "__main__":
