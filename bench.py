@@ -74,47 +74,61 @@ def ncu_traffic_bytes(workload: str) -> float | None:
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and clock-event reasons through NVML from a thread while the timed region runs
+    (the region lasts tens of milliseconds, too short for a polling nvidia-smi process)."""
 
-    def __init__(self, device_index: int):
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+
+    def __init__(self, device_index: int, period_s: float = 0.004):
         self.device_index = device_index
-        self.process = None
+        self.period_s = period_s
+        self.thread = None
+        self.stop_flag = False
+        self.clocks: list[int] = []
+        self.reason_bits = 0
+        self.max_clock = None
+        self.error = None
+
+    def _run(self, handle, nvml) -> None:
+        while not self.stop_flag:
+            try:
+                self.clocks.append(int(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+            except Exception as error:  # noqa: BLE001
+                self.error = repr(error)
+                return
+            time.sleep(self.period_s)
 
     def start(self) -> None:
+        import threading
+
         try:
-            self.process = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                             "-lms", "100", "-i", str(self.device_index)], stdout=subprocess.PIPE,
-                                            stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.process = None
+            import pynvml as nvml
+
+            nvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
+            try:
+                handle = nvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode() if not uuid.startswith("GPU-") else uuid.encode())
+            except Exception:  # noqa: BLE001
+                handle = nvml.nvmlDeviceGetHandleByIndex(self.device_index)
+            self.max_clock = int(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+            self.stop_flag = False
+            self.thread = threading.Thread(target=self._run, args=(handle, nvml), daemon=True)
+            self.thread.start()
+        except Exception as error:  # noqa: BLE001
+            self.error = repr(error)
+            self.thread = None
 
     def stop(self) -> dict:
-        if self.process is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.process.terminate()
-        try:
-            text, _ = self.process.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.process.kill()
-            text, _ = self.process.communicate()
-        clocks, max_clock, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in text.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                clocks.append(float(parts[1]))
-                max_clock = float(parts[2])
-            except ValueError:
-                continue
-            for name, value in zip(names, parts[5:9]):
-                if value.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock, "reasons": sorted(reasons),
-                "samples": len(clocks)}
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        reasons = sorted(name for bit, name in self.REASONS.items() if self.reason_bits & bit)
+        result = {"sm_mhz": statistics.median(self.clocks) if self.clocks else None, "sm_max_mhz": self.max_clock,
+                  "reasons": reasons, "samples": len(self.clocks), "source": "nvml"}
+        if self.error:
+            result["error"] = self.error
+        return result
 
 
 def make_layer(kind: str, device: torch.device, seed: int, experts: int | None = None):
@@ -378,7 +392,7 @@ def main() -> None:
     global E
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
