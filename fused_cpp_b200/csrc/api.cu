@@ -169,8 +169,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   const int tile_gu = pick_row_tile(cfg.gate_up_tile, routes, f.experts, umma);
   const int tile_dn = pick_row_tile(cfg.down_tile, routes, f.experts, umma);
   if (umma && (!fmoe::umma_row_tile_supported(tile_gu) || !fmoe::umma_row_tile_supported(tile_dn))) {
-    return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128 or 256 (got %d, %d)", tile_gu, tile_dn);
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128, 256 or 512 = two-SM pairs (got %d, %d)", tile_gu, tile_dn);
   }
+  // Tile 512 selects the two-SM kernel, whose work items hold up to 256 rows.
+  const int item_rows_gu = tile_gu == fmoe::kPairRowTile ? 256 : tile_gu;
+  const int item_rows_dn = tile_dn == fmoe::kPairRowTile ? 256 : tile_dn;
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   char* base = static_cast<char*>(workspace);
@@ -200,7 +203,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   mark(0);
   cudaError_t error = cudaMemsetAsync(status_block, 0, sizeof(int) * fmoe::kStatusWords, stream);
   if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
-  error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, tile_gu, tile_dn, max_items, status_block, counts, offsets,
+  error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, item_rows_gu, item_rows_dn, max_items, status_block, counts, offsets,
                                    sorted_routes, row_expert, items_gu, items_dn, scratch, stream);
   if (error != cudaSuccess) return cuda_fail(error, "route build");
   mark(FMOE_STAGE_ROUTE + 1);

@@ -95,4 +95,8 @@ cudaError_t launch_simt_grouped_gemm(const GroupedGemmArgs& args, bool int8, boo
 bool umma_row_tile_supported(int row_tile);
 cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
 
+// ---- umma2_gemm.cu: two-SM (cta_group::2) grouped GEMM, 256-row work items.  Selected by row tile 512.
+constexpr int kPairRowTile = 512;
+cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
+
 }  // namespace fmoe

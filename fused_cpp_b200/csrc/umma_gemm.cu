@@ -40,7 +40,7 @@ constexpr int kBlockKBytes = 128;   // bytes of K per pipeline stage = one 128-b
 constexpr int kUmmaKBytes = 32;     // bytes of K per tcgen05.mma
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarp0 = 2;
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kSmemBudget = 196 * 1024;
 
 template <bool kGateUp, int kRowTile>
 struct TileConfig {
@@ -55,9 +55,16 @@ struct TileConfig {
   static constexpr int kTmemColumnsRaw = kAccBuffers * kAccColumns;
   static constexpr int kTmemColumns = kTmemColumnsRaw <= 32 ? 32 : kTmemColumnsRaw <= 64 ? 64 : kTmemColumnsRaw <= 128 ? 128
                                       : kTmemColumnsRaw <= 256 ? 256 : 512;
-  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes + 256 /*barriers*/;
+  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes + 4608 /*control block*/;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
   static_assert(kAccColumns <= 512, "accumulator does not fit tensor memory");
+};
+
+// Per-column (= per token row) values of the current work unit, staged once by the epilogue warps so that the
+// element loop reads shared memory instead of issuing a dependent global load per element.
+struct ColumnMeta {
+  float scale[256];  // activation scale of the row (int8)
+  int target[256];   // output row: the flat route id (down), else the sorted row itself
 };
 
 struct SmemControl {
@@ -67,9 +74,10 @@ struct SmemControl {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
+  ColumnMeta meta[2];
 };
 
-template <bool kInt8, bool kGateUp, int kRowTile>
+template <bool kInt8, bool kGateUp, int kRowTile, bool kDense>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap token_map,
                          GroupedGemmArgs args) {
@@ -199,6 +207,11 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;  // the TMEM lanes a warp may read are fixed by warp id % 4
     const int channel_in_block = quarter * 32 + lane;
+    const int epilogue_thread = static_cast<int>(threadIdx.x) - kEpilogueWarp0 * 32;
+    const int n_out = args.n_out;
+    const int numerics = args.numerics;
+    const float limit = args.swiglu_limit;
+    uint32_t* const dump = static_cast<uint32_t*>(args.dump_acc);
     int local = 0;
     for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
       const int buffer = local % Cfg::kAccBuffers;
@@ -208,13 +221,21 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       const int expert = args.items[4 * item + 0];
       const int row0 = args.items[4 * item + 1];
       const int rows = args.items[4 * item + 2];
-      const bool channel_ok = n < args.n_out;
+      const bool channel_ok = n < n_out;
+      ColumnMeta* meta = &ctl->meta[local & 1];
+      for (int c = epilogue_thread; c < rows; c += 128) {
+        if (kInt8) meta->scale[c] = args.a_scale[row0 + c];
+        meta->target[c] = (kGateUp || kDense) ? row0 + c : args.sorted_routes[row0 + c];
+      }
       float scale_gate = 1.0f, scale_up = 1.0f;
       if (kInt8 && channel_ok) {
         const float* s = args.w_scale + static_cast<int64_t>(expert) * n_total;
         scale_gate = s[n];
-        if (kGateUp) scale_up = s[n + args.n_out];
+        if (kGateUp) scale_up = s[n + n_out];
       }
+      float bias = 0.0f;
+      if (kDense && channel_ok && args.bias != nullptr) bias = args.bias[n];
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // metadata visible to the four epilogue warps
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 4);
       ptx::tcgen05_fence_after();
       const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
@@ -228,40 +249,39 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (c0 + j < rows) {
-              const int64_t row = row0 + c0 + j;
-              if (args.dump_acc) {
-                uint32_t* dump = static_cast<uint32_t*>(args.dump_acc) + row * n_total;
-                dump[n] = gate_bits[j];
-                if (kGateUp) dump[n + args.n_out] = up_bits[j];
+              const int64_t target = meta->target[c0 + j];
+              if (dump != nullptr) {
+                uint32_t* out = dump + static_cast<int64_t>(row0 + c0 + j) * n_total;
+                out[n] = gate_bits[j];
+                if (kGateUp) out[n + n_out] = up_bits[j];
               }
               if constexpr (kGateUp) {
                 float gate, up;
                 if constexpr (kInt8) {
-                  const float a = args.a_scale[row];
-                  gate = dequantize(static_cast<int>(gate_bits[j]), a, scale_gate, args.numerics);
-                  up = dequantize(static_cast<int>(up_bits[j]), a, scale_up, args.numerics);
+                  const float a = meta->scale[c0 + j];
+                  gate = dequantize(static_cast<int>(gate_bits[j]), a, scale_gate, numerics);
+                  up = dequantize(static_cast<int>(up_bits[j]), a, scale_up, numerics);
                 } else {
                   gate = __uint_as_float(gate_bits[j]);
                   up = __uint_as_float(up_bits[j]);
                 }
-                args.y[row * args.n_out + n] = swiglu_to_bf16(gate, up, args.swiglu_limit);
+                args.y[target * n_out + n] = swiglu_to_bf16(gate, up, limit);
               } else {
                 float value;
                 if constexpr (kInt8) {
-                  value = dequantize(static_cast<int>(gate_bits[j]), args.a_scale[row], scale_gate, args.numerics);
+                  value = dequantize(static_cast<int>(gate_bits[j]), meta->scale[c0 + j], scale_gate, numerics);
                 } else {
                   value = __uint_as_float(gate_bits[j]);
                 }
-                if (args.dense_out != nullptr) {
-                  if (args.bias != nullptr) value = __fadd_rn(value, args.bias[n]);
+                if constexpr (kDense) {
+                  value = __fadd_rn(value, bias);
                   if (args.dense_out_bf16) {
-                    static_cast<uint16_t*>(args.dense_out)[row * args.n_out + n] = f32_to_bf16_bits(value);
+                    static_cast<uint16_t*>(args.dense_out)[target * n_out + n] = f32_to_bf16_bits(value);
                   } else {
-                    static_cast<float*>(args.dense_out)[row * args.n_out + n] = value;
+                    static_cast<float*>(args.dense_out)[target * n_out + n] = value;
                   }
                 } else {
-                  const int64_t flat = args.sorted_routes[row];
-                  args.route_out[flat * args.n_out + n] = value;
+                  args.route_out[target * n_out + n] = value;
                 }
               }
             }
@@ -328,10 +348,10 @@ int sm_count() {
   return count;
 }
 
-template <bool kInt8, bool kGateUp, int kRowTile>
+template <bool kInt8, bool kGateUp, int kRowTile, bool kDense>
 cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   using Cfg = TileConfig<kGateUp, kRowTile>;
-  auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile>;
+  auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile, kDense>;
   static bool configured = false;
   if (!configured) {
     const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmemBytes));
@@ -352,14 +372,14 @@ cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-template <bool kInt8, bool kGateUp>
+template <bool kInt8, bool kGateUp, bool kDense>
 cudaError_t launch_tile(const GroupedGemmArgs& args, cudaStream_t stream) {
   switch (args.row_tile) {
-    case 16: return launch_config<kInt8, kGateUp, 16>(args, stream);
-    case 32: return launch_config<kInt8, kGateUp, 32>(args, stream);
-    case 64: return launch_config<kInt8, kGateUp, 64>(args, stream);
-    case 128: return launch_config<kInt8, kGateUp, 128>(args, stream);
-    case 256: return launch_config<kInt8, kGateUp, 256>(args, stream);
+    case 16: return launch_config<kInt8, kGateUp, 16, kDense>(args, stream);
+    case 32: return launch_config<kInt8, kGateUp, 32, kDense>(args, stream);
+    case 64: return launch_config<kInt8, kGateUp, 64, kDense>(args, stream);
+    case 128: return launch_config<kInt8, kGateUp, 128, kDense>(args, stream);
+    case 256: return launch_config<kInt8, kGateUp, 256, kDense>(args, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -367,13 +387,18 @@ cudaError_t launch_tile(const GroupedGemmArgs& args, cudaStream_t stream) {
 }  // namespace
 
 bool umma_row_tile_supported(int row_tile) {
-  return row_tile == 16 || row_tile == 32 || row_tile == 64 || row_tile == 128 || row_tile == 256;
+  return row_tile == 16 || row_tile == 32 || row_tile == 64 || row_tile == 128 || row_tile == 256 || row_tile == kPairRowTile;
 }
 
 cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream) {
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
-  if (int8) return gate_up ? launch_tile<true, true>(args, stream) : launch_tile<true, false>(args, stream);
-  return gate_up ? launch_tile<false, true>(args, stream) : launch_tile<false, false>(args, stream);
+  if (args.row_tile == kPairRowTile) return launch_umma_pair_grouped_gemm(args, int8, gate_up, stream);
+  if (args.dense_out != nullptr) {
+    if (!int8 || gate_up) return cudaErrorInvalidValue;  // the dense epilogue exists for the int8 single-stage GEMM
+    return launch_tile<true, false, true>(args, stream);
+  }
+  if (int8) return gate_up ? launch_tile<true, true, false>(args, stream) : launch_tile<true, false, false>(args, stream);
+  return gate_up ? launch_tile<false, true, false>(args, stream) : launch_tile<false, false, false>(args, stream);
 }
 
 }  // namespace fmoe

@@ -31,7 +31,7 @@ from .plan import AsyncMoEPlanV2, gpu_placeholder_plan
 
 DEFAULT_MOE_COST_CACHE_DIR = Path(os.environ.get("FUSED_CPP_MOE_COST_CACHE_DIR", Path.home() / ".cache" / "fused_cpp_b200" / "moe"))
 ROUTE_BUCKETS = (1, 2, 4, 8, 12, 24, 48, 96, 192, 384, 768, 1536, 2040, 4096, 8192)
-CANDIDATE_TILES = (16, 32, 64, 128, 256)
+CANDIDATE_TILES = (16, 32, 64, 128, 256, 512)  # 512 = the two-SM (cta_group::2) kernel with 256-row items
 PROFILE_SCHEMA = 1
 
 

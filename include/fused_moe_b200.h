@@ -63,7 +63,7 @@ extern "C" {
 typedef struct fmoe_config {
   int32_t numerics;      /* FMOE_NUMERICS_* (W8A8 only) */
   int32_t gemm_impl;     /* FMOE_GEMM_* */
-  int32_t gate_up_tile;  /* rows of one expert handled per work item in the gate_up GEMM; 0 = auto */
+  int32_t gate_up_tile;  /* rows of one expert per work item in the gate_up GEMM: 16..256, 512 = two-SM pairs of 256 rows; 0 = auto */
   int32_t down_tile;     /* same for the down GEMM; 0 = auto */
   float swiglu_limit;    /* BF16: 0 = plain SiLU, 10 = clamp-10 SwiGLU.  W8A8 requires 10. */
   int32_t reserved0;

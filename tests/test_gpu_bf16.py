@@ -85,7 +85,7 @@ def test_bf16_umma_matches_simt_route_rows(cuda_device):
     assert float((rows_umma - rows_simt).norm() / rows_simt.norm()) <= 1e-3
 
 
-@pytest.mark.parametrize("tile", [16, 64, 256])
+@pytest.mark.parametrize("tile", [16, 64, 256, 512])
 def test_bf16_repeat_and_tile_invariance(cuda_device, tile):
     """Same bits on a repeated call; per-row results do not depend on the row tile because each output
     element is one MMA column whose K order is fixed."""

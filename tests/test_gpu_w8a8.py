@@ -88,6 +88,14 @@ def test_w8a8_matches_reference_golden(cuda_device, name, impl):
     assert torch.equal(result.out.cpu().view(torch.int16), golden["out"].view(torch.int16))
 
 
+@pytest.mark.parametrize("name", ["wide", "cfg1", "ragged"])
+def test_w8a8_two_sm_pair_kernel_matches_oracle(cuda_device, name):
+    """Row tile 512 selects the cta_group::2 kernel (256-row work items, a cluster of two CTAs per tile)."""
+    case = cases.w8a8_case(name)
+    result = _run(case, cuda_device, gemm_impl=_lib.GEMM_UMMA, gate_up_tile=512, down_tile=512, dump=True)
+    _check_all_stages(case, result, 0)
+
+
 @pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
 def test_w8a8_row_tile_does_not_change_results(cuda_device, tile):
     """Every row-tile configuration of the tcgen05 kernel gives the same bits (the reference's
