@@ -35,7 +35,7 @@ EXPORTS = (
     "fmoe_stage_timer_create", "fmoe_stage_timer_destroy", "fmoe_stage_timer_reset", "fmoe_stage_timer_calls",
     "fmoe_stage_timer_read", "fmoe_route_build_noalloc", "fmoe_ep_dispatch_workspace_bytes", "fmoe_ep_dispatch_prepare",
     "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
-    "fmoe_i8gemm_dynamic_scaled_mm_pair",
+    "fmoe_i8gemm_dynamic_scaled_mm_pair", "fmoe_probe_mma_rate",
 )
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
@@ -51,7 +51,7 @@ class Config(ctypes.Structure):
 class WorkspaceLayout(ctypes.Structure):
     _fields_ = [(name, ctypes.c_size_t) for name in (
         "total_bytes", "status", "counts", "offsets", "sorted_routes", "row_expert", "items", "scratch", "a_rows",
-        "a_scale", "y", "yq", "y_scale", "route_out")]
+        "a_scale", "y", "yq", "y_scale", "route_out", "route_pos")]
 
 
 class FusedMoEError(RuntimeError):
@@ -98,6 +98,7 @@ def load() -> ctypes.CDLL:
                                                   ctypes.c_size_t, p]
     lib.fmoe_bf16_expert_rows_forward.argtypes = [p, p, i64, p, p, i32, i32, i32, ctypes.POINTER(Config), p, p, ctypes.c_size_t, p]
     lib.fmoe_ep_combine_finish.argtypes = [p, p, p, i64, i32, i32, i32, p, p, p]
+    lib.fmoe_probe_mma_rate.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_float)]
     lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm_pair.argtypes = [p, i64, i32, p, p, i32, p, p, p, i32, p, p, ctypes.c_size_t, p]
@@ -250,6 +251,9 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
     layout = workspace_layout(int8, tokens, top_k, experts, hidden, inter)
     if workspace is None:
         workspace = get_workspace(layout.total_bytes, x.device)
+    forced = os.environ.get("FUSED_CPP_MOE_FORCE_TILES")  # "gate_up,down": diagnostic override of the row tiles
+    if forced and gate_up_tile == 0 and down_tile == 0:
+        gate_up_tile, down_tile = (int(v) for v in forced.split(","))
     config = Config()
     config.numerics = numerics
     config.gemm_impl = gemm_impl
@@ -393,3 +397,10 @@ def ep_combine_finish(returned_rows, send_order, topk_weights, tokens: int, top_
     check(load().fmoe_ep_combine_finish(_ptr(returned_rows), _ptr(send_order), _ptr(topk_weights), tokens, top_k,
                                         hidden, 1 if tree_merge else 0, _ptr(route_out), _ptr(out), _stream()))
     return out
+
+
+def probe_mma_rate(int8: bool, n: int = 256, iterations: int = 20000) -> float:
+    """Measured dense tensor-core peak (tera-ops/s) for a 128 x n MMA tile on the current GPU."""
+    value = ctypes.c_float(0.0)
+    check(load().fmoe_probe_mma_rate(1 if int8 else 0, n, iterations, ctypes.byref(value)))
+    return float(value.value)

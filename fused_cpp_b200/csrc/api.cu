@@ -83,6 +83,7 @@ int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, i
   layout->yq = take(int8 ? rows * inter : 0);
   layout->y_scale = take(sizeof(float) * rows);
   layout->route_out = take(sizeof(float) * rows * hidden);
+  layout->route_pos = take(sizeof(int) * rows);
   layout->total_bytes = offset;
   return FMOE_OK;
 }
@@ -204,7 +205,8 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   cudaError_t error = cudaMemsetAsync(status_block, 0, sizeof(int) * fmoe::kStatusWords, stream);
   if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
   error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, item_rows_gu, item_rows_dn, max_items, status_block, counts, offsets,
-                                   sorted_routes, row_expert, items_gu, items_dn, scratch, stream);
+                                   sorted_routes, row_expert, items_gu, items_dn, scratch, stream,
+                                   reinterpret_cast<int*>(base + layout.route_pos));
   if (error != cudaSuccess) return cuda_fail(error, "route build");
   mark(FMOE_STAGE_ROUTE + 1);
   const int* valid_rows = offsets + f.experts;
@@ -215,8 +217,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
                                      reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
     if (error == cudaSuccess) error = fmoe::launch_gather_scalars(f.rows_scale, routes, sorted_routes, valid_rows, a_scale, stream);
   } else if (f.int8) {
-    error = fmoe::launch_quantize_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden, sorted_routes, f.top_k, valid_rows,
-                                       cfg.numerics, 0, reinterpret_cast<int8_t*>(base + layout.a_rows), a_scale, stream);
+    error = fmoe::launch_quantize_tokens_scatter(static_cast<const uint16_t*>(f.x), f.tokens, f.hidden, f.top_k,
+                                                 reinterpret_cast<const int*>(base + layout.route_pos), cfg.numerics,
+                                                 reinterpret_cast<int8_t*>(base + layout.a_rows), a_scale, stream);
   } else {
     error = fmoe::launch_gather_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden, sorted_routes, f.top_k, valid_rows,
                                      reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
@@ -640,6 +643,41 @@ int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows, int32_t
   cudaError_t error = dense_gemm(layout, base, rows, first_w, first_scale, nullptr, first_n, first_out, 1, row_tile, stream);
   if (error == cudaSuccess) error = dense_gemm(layout, base, rows, second_w, second_scale, nullptr, second_n, second_out, 1, row_tile, stream);
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm pair GEMM");
+}
+
+int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, float* tera_ops_per_s) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (tera_ops_per_s == nullptr || iterations <= 0 || n < 16 || n > 256 || n % 16 != 0) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "probe: n must be a multiple of 16 in [16, 256] and iterations positive");
+  }
+  int device = 0, sms = 0;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  int* status_block = nullptr;
+  cudaEvent_t begin = nullptr, end = nullptr;
+  cudaError_t error = cudaMalloc(&status_block, sizeof(int) * fmoe::kStatusWords);
+  if (error == cudaSuccess) error = cudaMemset(status_block, 0, sizeof(int) * fmoe::kStatusWords);
+  if (error == cudaSuccess) error = cudaEventCreate(&begin);
+  if (error == cudaSuccess) error = cudaEventCreate(&end);
+  float best_ms = 0.0f;
+  for (int round = 0; round < 4 && error == cudaSuccess; ++round) {
+    cudaEventRecord(begin, nullptr);
+    error = fmoe::launch_mma_rate_probe(int8 != 0, n, iterations, sms, status_block, nullptr);
+    cudaEventRecord(end, nullptr);
+    if (error == cudaSuccess) error = cudaEventSynchronize(end);
+    float ms = 0.0f;
+    if (error == cudaSuccess) error = cudaEventElapsedTime(&ms, begin, end);
+    if (round > 0 && (best_ms == 0.0f || ms < best_ms)) best_ms = ms;
+  }
+  if (begin) cudaEventDestroy(begin);
+  if (end) cudaEventDestroy(end);
+  if (status_block) cudaFree(status_block);
+  if (error != cudaSuccess) return cuda_fail(error, "MMA rate probe");
+  const double elements_k = int8 ? 32.0 : 16.0;
+  const double ops = 2.0 * 128.0 * n * elements_k * static_cast<double>(iterations) * sms;
+  *tera_ops_per_s = static_cast<float>(ops / (best_ms * 1e-3) / 1e12);
+  return FMOE_OK;
 }
 
 }  // extern "C"

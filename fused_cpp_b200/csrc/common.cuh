@@ -30,6 +30,20 @@ __device__ __forceinline__ void raise_error(int* status, int code, int detail) {
   if (atomicCAS(status + kStatusError, 0, code) == 0) status[kStatusDetail] = detail;
 }
 
+// Work unit -> (work item, channel block).  Items are sorted by (expert, row tile); units are ordered so that,
+// inside one expert, the row tiles of a channel block are adjacent: CTAs that run side by side then read the
+// same weight tile at the same time and the second read is served by L2 instead of HBM.  items[4*i+3] packs
+// the first item of the item's expert (20 bits) and that expert's tile count.
+__device__ __forceinline__ void decode_unit(const int* __restrict__ items, int64_t unit, int n_blocks, int* item, int* block) {
+  const int guess = static_cast<int>(unit / n_blocks);
+  const int packed = items[4 * guess + 3];
+  const int first = packed & 0xfffff;
+  const int tiles = packed >> 20;
+  const int64_t local = unit - static_cast<int64_t>(first) * n_blocks;
+  *block = static_cast<int>(local / tiles);
+  *item = first + static_cast<int>(local % tiles);
+}
+
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t bits) { return __uint_as_float(static_cast<uint32_t>(bits) << 16); }
 
 // Nearest-even bf16 by adding 0x7fff + lsb, like the reference's store_bf16.

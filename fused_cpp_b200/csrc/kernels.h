@@ -17,7 +17,8 @@ int report_error(int code, const char* text);
 size_t route_scratch_bytes(int64_t routes, int experts);
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
-                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream);
+                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream,
+                               int* route_pos = nullptr);
 
 // Work items of a dense [rows, K] x [N, K]^T product: one "expert", consecutive row tiles.
 cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream);
@@ -30,6 +31,10 @@ cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* i
 cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
                                  const int* valid_rows, int numerics, int weight_mode, int8_t* q, float* scale,
                                  cudaStream_t stream);
+// Quantise every token row once and write it to the sorted positions of its top_k routes
+// (route_pos[t*top_k+slot], -1 = dropped): same bits as quantising per route, one read of x per token.
+cudaError_t launch_quantize_tokens_scatter(const uint16_t* x, int64_t tokens, int cols, int top_k, const int* route_pos,
+                                           int numerics, int8_t* q, float* scale, cudaStream_t stream);
 // Same for fp32 sources (dense linear).  clamp_low is -128 or -127.
 cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
                                        int8_t* q, float* scale, cudaStream_t stream);
@@ -98,5 +103,8 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, boo
 // ---- umma2_gemm.cu: two-SM (cta_group::2) grouped GEMM, 256-row work items.  Selected by row tile 512.
 constexpr int kPairRowTile = 512;
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
+
+// ---- probe.cu: tcgen05.mma issue-rate probe (128 x n x 32-byte MMAs back to back on every CTA)
+cudaError_t launch_mma_rate_probe(bool int8, int n, int iterations, int blocks, int* status, cudaStream_t stream);
 
 }  // namespace fmoe

@@ -96,6 +96,42 @@ quantize_rows_kernel(const uint16_t* __restrict__ x, int cols, const int* __rest
   }
 }
 
+// cols % 16 == 0, top_k <= 32.  One CTA per token: the row is quantised once and stored to each of its routes'
+// sorted positions (the reference re-quantises the token for every route, kernels.cpp:639-644; the bits are the same).
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_tokens_scatter_kernel(const uint16_t* __restrict__ x, int cols, int top_k, const int* __restrict__ route_pos,
+                               int numerics, int8_t* __restrict__ q, float* __restrict__ scale_out) {
+  __shared__ float smem[32];
+  __shared__ int positions[32];
+  const int64_t token = blockIdx.x;
+  if (threadIdx.x < top_k) positions[threadIdx.x] = route_pos[token * top_k + threadIdx.x];
+  const uint4* src = reinterpret_cast<const uint4*>(x + token * cols);
+  const int vec16 = cols >> 4;
+  float local = 0.0f;
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    local = fmaxf(local, amax8(src[2 * v]));
+    local = fmaxf(local, amax8(src[2 * v + 1]));
+  }
+  const float amax = block_max(local, smem);  // its barriers also publish positions[]
+  const float scale = row_scale_from_amax(amax, numerics);
+  if (threadIdx.x < top_k && positions[threadIdx.x] >= 0) scale_out[positions[threadIdx.x]] = scale;
+  const float operand = quantize_operand(scale, numerics);
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    float values[16];
+    unpack8(src[2 * v], values);
+    unpack8(src[2 * v + 1], values + 8);
+    uint4 out;
+    out.x = pack4(values, operand, numerics);
+    out.y = pack4(values + 4, operand, numerics);
+    out.z = pack4(values + 8, operand, numerics);
+    out.w = pack4(values + 12, operand, numerics);
+    for (int slot = 0; slot < top_k; ++slot) {
+      const int position = positions[slot];
+      if (position >= 0) reinterpret_cast<uint4*>(q + static_cast<int64_t>(position) * cols)[v] = out;
+    }
+  }
+}
+
 // Dense linear: arbitrary cols, fp32 or bf16 source, zero-padded to cols_padded, clamp to [-128,127]
 // (single GEMM) or [-127,127] (paired GEMMs) with division and ties-to-even (csrc/i8gemm.cpp:384-399, :492-506).
 __global__ void __launch_bounds__(kQuantThreads)
@@ -160,6 +196,14 @@ cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, 
   if (out_rows <= 0) return cudaSuccess;
   quantize_rows_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows,
                                                                                      numerics, weight_mode, q, scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_tokens_scatter(const uint16_t* x, int64_t tokens, int cols, int top_k, const int* route_pos,
+                                           int numerics, int8_t* q, float* scale, cudaStream_t stream) {
+  if (tokens <= 0) return cudaSuccess;
+  quantize_tokens_scatter_kernel<<<static_cast<unsigned>(tokens), kQuantThreads, 0, stream>>>(x, cols, top_k, route_pos, numerics, q,
+                                                                                             scale);
   return cudaGetLastError();
 }
 

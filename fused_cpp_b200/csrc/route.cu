@@ -110,7 +110,9 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
         item[0] = e;
         item[1] = offsets[e] + t * tile;
         item[2] = min(tile, counts[e] - t * tile);
-        item[3] = 0;
+        // Group key for the unit order of the grouped GEMM: first item of this expert and its tile count, so
+        // that the row tiles of one (expert, channel block) are consecutive work units (see decode_unit).
+        item[3] = tiles < 2048 ? (first | (tiles << 20)) : ((first + t) | (1 << 20));
       }
     }
     __syncthreads();
@@ -125,7 +127,7 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int experts, int units,
                      const int* __restrict__ unit_hist, const int* __restrict__ offsets, int* sorted_routes,
-                     int* row_expert) {
+                     int* row_expert, int* route_pos) {
   extern __shared__ int smem_cursor[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -153,6 +155,8 @@ route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int e
       sorted_routes[position] = static_cast<int>(route);
       row_expert[position] = id;
     }
+    // Inverse permutation: sorted position of every flat route (-1 for a dropped route).
+    if (route_pos != nullptr && route < routes) route_pos[route] = position;
   }
 }
 
@@ -165,7 +169,7 @@ size_t route_scratch_bytes(int64_t routes, int experts) {
 
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
-                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream) {
+                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos) {
   const int units = static_cast<int>((routes + kUnitRoutes - 1) / kUnitRoutes);
   int* unit_hist = scratch;
   int* scan_tmp = scratch + static_cast<int64_t>(units > 0 ? units : 1) * experts;
@@ -178,7 +182,7 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
                                             max_items, scan_tmp, status);
   if (blocks > 0) {
     route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist,
-                                                                        offsets, sorted_routes, row_expert);
+                                                                        offsets, sorted_routes, row_expert, route_pos);
   }
   return cudaGetLastError();
 }
@@ -191,7 +195,7 @@ __global__ void dense_items_kernel(int64_t rows, int row_tile, int max_items, in
     items[4 * t + 0] = 0;
     items[4 * t + 1] = t * row_tile;
     items[4 * t + 2] = static_cast<int>(min(static_cast<int64_t>(row_tile), rows - static_cast<int64_t>(t) * row_tile));
-    items[4 * t + 3] = 0;
+    items[4 * t + 3] = count < 2048 ? (0 | (count << 20)) : (t | (1 << 20));
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     status[kStatusItems] = count;

@@ -139,7 +139,6 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
   constexpr int kChannelsPerUnit = kGateUp ? 128 : 256;  // output channels one pair finishes per work unit
-  constexpr uint32_t kIdesc = ptx::make_instr_desc(kInt8, 2 * kRowsPerCta, kPairTokens);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -191,11 +190,15 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       uint32_t phase = 0;
       int issued = 0;
       for (int64_t unit = first_unit; unit < units; unit += unit_stride) {
-        const int item = static_cast<int>(unit / n_blocks);
-        const int c0 = static_cast<int>(unit % n_blocks) * kChannelsPerUnit;
+        int item, block;
+        decode_unit(args.items, unit, n_blocks, &item, &block);
+        const int c0 = block * kChannelsPerUnit;
         const int expert = args.items[4 * item + 0];
         const int row0 = args.items[4 * item + 1];
         const int weight_row = expert * n_total + c0;
+        // The MMA takes the first N/2 token rows from the leader's tile and the other N/2 from the follower's.
+        const int mma_n = min(kPairTokens, (args.items[4 * item + 2] + 31) & ~31);
+        const int token_row = row0 + (mma_n / 2) * static_cast<int>(cta);
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 11);
           uint8_t* stage_base = smem + static_cast<size_t>(stage) * kStageBytes;
@@ -208,7 +211,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
           } else {
             tma_load_2d_pair(stage_base, &weight_map, full_leader, x, weight_row + kRowsPerCta * static_cast<int>(cta));
           }
-          tma_load_2d_pair(stage_base + kRowsPerCta * kBlockKBytes, &token_map, full_leader, x, row0 + kRowsPerCta * static_cast<int>(cta));
+          tma_load_2d_pair(stage_base + kRowsPerCta * kBlockKBytes, &token_map, full_leader, x, token_row);
           ++issued;
           if (++stage == kStages) {
             stage = 0;
@@ -242,6 +245,12 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       for (int64_t unit = first_unit; unit < units; unit += unit_stride, ++local) {
         const int buffer = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1);
+        // N follows the rows this unit really has (a multiple of 32 for two-SM MMAs).
+        int item, block;
+        decode_unit(args.items, unit, n_blocks, &item, &block);
+        const int item_rows = args.items[4 * item + 2];
+        const int mma_n = min(kPairTokens, (item_rows + 31) & ~31);
+        const uint32_t idesc = ptx::make_instr_desc(kInt8, 2 * kRowsPerCta, mma_n);
         ptx::mbar_wait(&ctl->acc_empty[buffer], (use & 1u) ^ 1u, abort_flag, status, 12);
         ptx::tcgen05_fence_after();
         const uint32_t acc = tmem_base + static_cast<uint32_t>(buffer * kAccColumns);
@@ -253,7 +262,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
           for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
             const uint64_t desc_a = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
             const uint64_t desc_b = ptx::make_smem_desc_sw128(stage_addr + kRowsPerCta * kBlockKBytes + ks * kUmmaKBytes);
-            umma_pair<kInt8>(acc, desc_a, desc_b, kIdesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            umma_pair<kInt8>(acc, desc_a, desc_b, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
           }
           const uint32_t empty_local = ptx::smem_u32(&ctl->empty[stage]);
           tcgen05_commit_pair(map_to_cta(empty_local, 0));
@@ -282,8 +291,9 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
     for (int64_t unit = first_unit; unit < units; unit += unit_stride, ++local) {
       const int buffer = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
-      const int item = static_cast<int>(unit / n_blocks);
-      const int c0 = static_cast<int>(unit % n_blocks) * kChannelsPerUnit;
+      int item, block;
+      decode_unit(args.items, unit, n_blocks, &item, &block);
+      const int c0 = block * kChannelsPerUnit;
       const int expert = args.items[4 * item + 0];
       const int row0 = args.items[4 * item + 1];
       const int rows = args.items[4 * item + 2];

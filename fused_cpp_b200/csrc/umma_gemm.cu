@@ -84,7 +84,6 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
   using Cfg = TileConfig<kGateUp, kRowTile>;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
-  constexpr uint32_t kIdesc = ptx::make_instr_desc(kInt8, kBlockM, kRowTile);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -131,8 +130,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       uint32_t phase = 0;
       int issued = 0;
       for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
-        const int item = static_cast<int>(unit / n_blocks);
-        const int n0 = static_cast<int>(unit % n_blocks) * kBlockM;
+        int item, block;
+        decode_unit(args.items, unit, n_blocks, &item, &block);
+        const int n0 = block * kBlockM;
         const int expert = args.items[4 * item + 0];
         const int row0 = args.items[4 * item + 1];
         const int weight_row = expert * n_total + n0;
@@ -176,6 +176,13 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
         const int buffer = local % Cfg::kAccBuffers;
         const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
+        // The MMA's N follows the rows this unit really has (multiple of 16): a tail item of a few rows costs a
+        // few columns of tensor-core time, not a full tile.  Unused accumulator columns are never read.
+        int item, block;
+        decode_unit(args.items, unit, n_blocks, &item, &block);
+        const int item_rows = args.items[4 * item + 2];
+        const int mma_n = min(kRowTile, (item_rows + 15) & ~15);
+        const uint32_t idesc = ptx::make_instr_desc(kInt8, kBlockM, mma_n);
         ptx::mbar_wait(&ctl->acc_empty[buffer], (use & 1u) ^ 1u, abort_flag, status, 2);
         ptx::tcgen05_fence_after();
         const uint32_t acc = tmem_base + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
@@ -188,10 +195,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
             const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
             const uint64_t desc_tok = ptx::make_smem_desc_sw128(stage_addr + Cfg::kWeightBytes + ks * kUmmaKBytes);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
-            ptx::umma_ss<kInt8>(acc, desc_gate, desc_tok, kIdesc, accumulate);
+            ptx::umma_ss<kInt8>(acc, desc_gate, desc_tok, idesc, accumulate);
             if (kGateUp) {
               const uint64_t desc_up = ptx::make_smem_desc_sw128(stage_addr + kBlockM * kBlockKBytes + ks * kUmmaKBytes);
-              ptx::umma_ss<kInt8>(acc + kRowTile, desc_up, desc_tok, kIdesc, accumulate);
+              ptx::umma_ss<kInt8>(acc + kRowTile, desc_up, desc_tok, idesc, accumulate);
             }
           }
           ptx::tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs have read it
@@ -216,8 +223,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
     for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
       const int buffer = local % Cfg::kAccBuffers;
       const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
-      const int item = static_cast<int>(unit / n_blocks);
-      const int n = static_cast<int>(unit % n_blocks) * kBlockM + channel_in_block;
+      int item, block;
+      decode_unit(args.items, unit, n_blocks, &item, &block);
+      const int n = block * kBlockM + channel_in_block;
       const int expert = args.items[4 * item + 0];
       const int row0 = args.items[4 * item + 1];
       const int rows = args.items[4 * item + 2];

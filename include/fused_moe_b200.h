@@ -89,6 +89,7 @@ typedef struct fmoe_workspace_layout {
   size_t yq;             /* W8A8: int8[T*K,I] */
   size_t y_scale;        /* W8A8: fp32[T*K] */
   size_t route_out;      /* fp32[T*K,H], row = FLAT route id (already un-permuted) */
+  size_t route_pos;      /* int32[T*K] sorted position of every flat route (-1 = dropped): inverse of sorted_routes */
 } fmoe_workspace_layout;
 
 /* ---- library state -------------------------------------------------------------------------- */
@@ -252,6 +253,15 @@ FMOE_API int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows
                                                 const float* first_scale, int32_t first_n, void* first_out,
                                                 const int8_t* second_w, const float* second_scale, int32_t second_n,
                                                 void* second_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- measurement helper ---------------------------------------------------------------------- */
+
+/* Dense tensor-core peak of the current GPU for one MMA shape: every SM issues `iterations` back-to-back
+ * tcgen05.mma of 128 x n x 32 bytes (kind::i8 when int8 != 0, else kind::f16 with bf16 operands) on zeroed
+ * shared memory; returns tera-operations per second (2 per multiply-add), best of three timed launches.
+ * No counterpart in the reference (its ceilings are per-core SMMLA/BFMMLA rates,
+ * docs/agent_performance_references.md:85-91).  Allocates a few bytes and synchronises: not for hot paths. */
+FMOE_API int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, float* tera_ops_per_s);
 
 #ifdef __cplusplus
 }

@@ -48,6 +48,8 @@ def _check_all_stages(case, result, numerics):
                        case["topk_ids"].reshape(-1)[order.long()])
     token_of_row = (order // top_k).long()
     flat = order.long()
+    route_pos = result.region("route_pos", torch.int32, (routes,)).cpu().long()
+    assert torch.equal(route_pos[flat], torch.arange(routes)), "route_pos is not the inverse of sorted_routes"
     assert torch.equal(result.region("a_rows", torch.int8, (routes, hidden)).cpu(), d["xq"][token_of_row]), "xq differs"
     assert torch.equal(result.region("a_scale", torch.float32, (routes,)).cpu(), d["a"][token_of_row]), "a differs"
     assert torch.equal(result.acc1.cpu(), d["acc1"][flat]), "gate_up int32 accumulators differ"
