@@ -45,9 +45,14 @@ WORKLOADS = {
     "bf16_prefill_v3_T8192": {"kind": "bf16", "tokens": 8192, "skew": False},
     "w8a8_ep_shared_v3_T16384": {"kind": "int8", "tokens": 16384, "skew": False, "shared": True},
     "w8a8_prefill_v3_T2048": {"kind": "int8", "tokens": 2048, "skew": False},
+    # Zipf-biased router logits (a few experts take most routes): the compute-bound prefill configuration.
+    "w8a8_prefill_zipf_v3_T8192": {"kind": "int8", "tokens": 8192, "skew": True},
+    "w8a8_prefill_zipf_v3_T2048": {"kind": "int8", "tokens": 2048, "skew": True},
+    "bf16_prefill_zipf_v3_T8192": {"kind": "bf16", "tokens": 8192, "skew": True},
 }
 DEFAULT_WORKLOAD = "bf16_decode_v3_T64"
-EXTRA_POINTS = ["bf16_decode_v3_T1", "bf16_decode_v3_T8", "bf16_decode_v3_T32", "w8a8_decode_v3_T64", "w8a8_prefill_v3_T8192"]
+EXTRA_POINTS = ["bf16_decode_v3_T1", "bf16_decode_v3_T8", "bf16_decode_v3_T32", "w8a8_decode_v3_T64", "w8a8_prefill_zipf_v3_T8192",
+                "w8a8_prefill_v3_T8192"]
 CPU_SAMPLE_TOKENS = 16
 SEED = 20260101
 

@@ -98,7 +98,7 @@ def load() -> ctypes.CDLL:
                                                   ctypes.c_size_t, p]
     lib.fmoe_bf16_expert_rows_forward.argtypes = [p, p, i64, p, p, i32, i32, i32, ctypes.POINTER(Config), p, p, ctypes.c_size_t, p]
     lib.fmoe_ep_combine_finish.argtypes = [p, p, p, i64, i32, i32, i32, p, p, p]
-    lib.fmoe_probe_mma_rate.argtypes = [i32, i32, i32, ctypes.POINTER(ctypes.c_float)]
+    lib.fmoe_probe_mma_rate.argtypes = [i32, i32, i32, i32, ctypes.POINTER(ctypes.c_float)]
     lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm_pair.argtypes = [p, i64, i32, p, p, i32, p, p, p, i32, p, p, ctypes.c_size_t, p]
@@ -399,8 +399,10 @@ def ep_combine_finish(returned_rows, send_order, topk_weights, tokens: int, top_
     return out
 
 
-def probe_mma_rate(int8: bool, n: int = 256, iterations: int = 20000) -> float:
-    """Measured dense tensor-core peak (tera-ops/s) for a 128 x n MMA tile on the current GPU."""
+def probe_mma_rate(int8: bool, n: int = 256, iterations: int = 20000, *, nonzero: bool = False, commit_every: int = 0) -> float:
+    """Measured dense tensor-core peak (tera-ops/s) for a 128 x n MMA tile on the current GPU.
+
+    nonzero: operands hold a non-zero pattern instead of zeros; commit_every: a tcgen05.commit after every c MMAs."""
     value = ctypes.c_float(0.0)
-    check(load().fmoe_probe_mma_rate(1 if int8 else 0, n, iterations, ctypes.byref(value)))
+    check(load().fmoe_probe_mma_rate(1 if int8 else 0, n, iterations, (1 if nonzero else 0) | (commit_every << 8), ctypes.byref(value)))
     return float(value.value)

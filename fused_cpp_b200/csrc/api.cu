@@ -97,7 +97,8 @@ int pick_row_tile(int requested, int64_t routes, int experts, bool umma) {
   if (average <= 8) return 16;
   if (average <= 24) return 32;
   if (average <= 48) return 64;
-  return 128;
+  if (average <= 160) return 128;
+  return fmoe::kPairRowTile;  // hundreds of rows per expert: the two-SM kernel (256-row work items)
 }
 
 struct StageTimer {
@@ -645,7 +646,7 @@ int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows, int32_t
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm pair GEMM");
 }
 
-int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, float* tera_ops_per_s) {
+int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mode, float* tera_ops_per_s) {
   int status = check_device();
   if (status != FMOE_OK) return status;
   if (tera_ops_per_s == nullptr || iterations <= 0 || n < 16 || n > 256 || n % 16 != 0) {
@@ -663,7 +664,7 @@ int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, float* tera
   float best_ms = 0.0f;
   for (int round = 0; round < 4 && error == cudaSuccess; ++round) {
     cudaEventRecord(begin, nullptr);
-    error = fmoe::launch_mma_rate_probe(int8 != 0, n, iterations, sms, status_block, nullptr);
+    error = fmoe::launch_mma_rate_probe(int8 != 0, n, iterations, mode, sms, status_block, nullptr);
     cudaEventRecord(end, nullptr);
     if (error == cudaSuccess) error = cudaEventSynchronize(end);
     float ms = 0.0f;

@@ -66,8 +66,10 @@ __device__ __constant__ const uint32_t kExp2Table[64] = {
 };
 
 // exp(-gate) with the reference's FEXPA evaluator: range reduction to multiples of 1/64 in the
-// exponent, a table significand and a degree-2 correction.
-__device__ __forceinline__ float expneg(float gate) {
+// exponent, a table significand and a degree-2 correction.  `table` is kExp2Table or a copy of it in
+// shared memory: lanes index it with different values, which the constant cache serialises (one
+// address per pass) while shared memory serves 32 banks at once.
+__device__ __forceinline__ float expneg_with(float gate, const uint32_t* table) {
   float x = -gate;
   x = fminf(x, 87.0f);
   x = fmaxf(x, -87.0f);
@@ -76,20 +78,26 @@ __device__ __forceinline__ float expneg(float gate) {
   float residual = __fmaf_rn(-k, 0.693145751953125f, x);
   residual = __fmaf_rn(-k, 1.428606765330187e-06f, residual);
   const uint32_t enc_bits = __float_as_uint(encoded);
-  const uint32_t scale_bits = (((enc_bits >> 6) & 0xffu) << 23) | (kExp2Table[enc_bits & 63u] & 0x007fffffu);
+  const uint32_t scale_bits = (((enc_bits >> 6) & 0xffu) << 23) | (table[enc_bits & 63u] & 0x007fffffu);
   const float scale = __uint_as_float(scale_bits);
   const float polynomial = __fmaf_rn(residual, 0.5000003576278687f, 1.000003695487976f);
   return __fmaf_rn(scale, __fmul_rn(polynomial, residual), scale);
 }
 
+__device__ __forceinline__ float expneg(float gate) { return expneg_with(gate, kExp2Table); }
+
 // (gate*up)/(exp(-gate)+1) -> bf16, with the optional +-limit clamp (limit <= 0: none).
-__device__ __forceinline__ uint16_t swiglu_to_bf16(float gate, float up, float limit) {
+__device__ __forceinline__ uint16_t swiglu_to_bf16_with(float gate, float up, float limit, const uint32_t* table) {
   if (limit > 0.0f) {
     gate = fminf(gate, limit);
     up = fmaxf(fminf(up, limit), -limit);
   }
-  const float value = __fdiv_rn(__fmul_rn(gate, up), __fadd_rn(expneg(gate), 1.0f));
+  const float value = __fdiv_rn(__fmul_rn(gate, up), __fadd_rn(expneg_with(gate, table), 1.0f));
   return f32_to_bf16_bits(value);
+}
+
+__device__ __forceinline__ uint16_t swiglu_to_bf16(float gate, float up, float limit) {
+  return swiglu_to_bf16_with(gate, up, limit, kExp2Table);
 }
 
 // int32 accumulator -> fp32 with the activation and per-channel weight scale.

@@ -90,6 +90,9 @@ struct GroupedGemmArgs {
   void* dense_out;
   int dense_out_bf16;
   const float* bias;
+  // Performance diagnosis only (environment FUSED_CPP_MOE_GEMM_DIAG, 0 in production; results are meaningless otherwise):
+  // bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.
+  int diag;
 };
 
 // ---- simt_gemm.cu: diagnostic CUDA-core grouped GEMM (work items of at most 8 rows)
@@ -102,9 +105,10 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, boo
 
 // ---- umma2_gemm.cu: two-SM (cta_group::2) grouped GEMM, 256-row work items.  Selected by row tile 512.
 constexpr int kPairRowTile = 512;
+bool umma_pair_supported(bool gate_up, int n_out);  // gate_up needs n_out % 16 == 0 (16-channel TMA groups)
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
 
 // ---- probe.cu: tcgen05.mma issue-rate probe (128 x n x 32-byte MMAs back to back on every CTA)
-cudaError_t launch_mma_rate_probe(bool int8, int n, int iterations, int blocks, int* status, cudaStream_t stream);
+cudaError_t launch_mma_rate_probe(bool int8, int n, int iterations, int mode, int blocks, int* status, cudaStream_t stream);
 
 }  // namespace fmoe

@@ -3,18 +3,22 @@
 //
 // Same work as umma_gemm.cu (the reference's two run_stage sweeps and their epilogues,
 // csrc/moe/arm/i8mm_w8a8/kernels.cpp:328-368, 230-257) for the prefill regime, where an expert has
-// hundreds of rows and the one-SM kernel is limited by operand delivery from L2: a 128x128 tile needs
-// 96 bytes of shared-memory fill per tensor-core clock, this one needs 64, and every weight byte is
-// read once per 256 rows instead of once per 128.
+// hundreds of rows.  Three things bound that regime and shape this kernel:
+//   * one thread issues every MMA, and a dependent instruction costs it several clocks: a 128 x 128 x 32-byte
+//     MMA runs 66 clocks, so anything beyond a dozen instructions per MMA starves the tensor pipe.  The pair
+//     issues 256 x 256 MMAs (132 clocks each) from a loop that only adds constants to descriptor words;
+//   * a 128 x 128 tile reads 8 KB of shared memory per 66 clocks, the full shared-memory bandwidth; here
+//     each SM reads 4 + 4 KB per 132 clocks;
+//   * the epilogue handles 128 x 256 accumulators per CTA per unit: eight warps, 32-column tensor-memory
+//     loads, per-column metadata fetched one unit ahead, no block-wide barrier inside a unit.
 //
 // Pair layout.  CTA r of the pair (r = 0 leads) stages its own halves: 128 A rows (weight channels)
 // and 128 B rows (tokens); the MMA reads A rows 0..127 from CTA 0 and 128..255 from CTA 1, B likewise,
 // and leaves D rows 128r..128r+127 x 256 token columns in CTA r's tensor memory.
 //   down:    A rows of CTA r = channels n0 + 128 r .. + 127.
-//   gate_up: A rows of CTA r = gate channels c0 + 64 r .. + 63 followed by the up channels of the same
-//            indices (two 64-row TMA loads), so each CTA holds gate and up of its 64 channels; the
-//            epilogue's gate warps (TMEM lanes 0..63) and up warps (lanes 64..127) swap half of their
-//            columns through shared memory and each finish half of the SwiGLU outputs.
+//   gate_up: A rows of CTA r = channels c0 + 64 r .. + 63 as four groups of [16 gate rows | 16 up rows]
+//            (one 5-D TMA box: {K bytes, 16 rows, gate/up, 4 groups, expert}), so lanes l and l + 16 of every
+//            epilogue warp hold gate and up of the same channel and swap them with one shuffle.
 // Barriers.  Both producers signal the leader's "full" barrier (TMA complete_tx through the cluster
 // address), the leader's single MMA thread commits to the "empty" and "accumulator full" barriers of
 // both CTAs, and the follower's epilogue warps arrive on the leader's "accumulator empty" barrier
@@ -33,17 +37,19 @@ constexpr int kRowsPerCta = 128;    // A rows and B rows staged by one CTA
 constexpr int kPairTokens = 256;    // MMA N
 constexpr int kBlockKBytes = 128;
 constexpr int kUmmaKBytes = 32;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kThreads = 64 + kEpilogueThreads;
 constexpr int kStages = 6;
 constexpr int kStageBytes = 2 * kRowsPerCta * kBlockKBytes;  // 32 KB
 constexpr int kAccColumns = kPairTokens;                     // one accumulator: 256 columns
 constexpr int kTmemColumns = 512;                            // two accumulators
 constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + 8192;
 
-// Per-column values of the current work unit, staged once so that the element loop reads shared memory.
+// Per-column values of a work unit, staged one unit ahead so that the element loop reads shared memory.
 struct ColumnMeta {
-  float scale[256];
-  int target[256];
+  float scale[256];      // activation scale of the row (int8)
+  int64_t offset[256];   // element offset of the output row: target row * n_out
 };
 
 struct PairControl {
@@ -53,9 +59,10 @@ struct PairControl {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
-  uint32_t exchange[2][64][4];  // [gate->up | up->gate][channel][column]
+  uint32_t exp_table[64];  // copy of kExp2Table: divergent lookups are served by 32 banks
   ColumnMeta meta[2];
 };
+static_assert(sizeof(PairControl) <= 8192, "control block exceeds its shared-memory reservation");
 
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t rank;
@@ -78,12 +85,21 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_address) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
 }
 
-// TMA tiled load whose completion bytes go to an mbarrier given by its cluster address (the leader's).
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_address, int x, int y) {
+// TMA tiled loads whose completion bytes go to an mbarrier given by its cluster address (the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster_address, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       :
-      : "r"(ptx::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_address), "r"(x), "r"(y)
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_address), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster_address, int c0, int c1,
+                                                 int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_address), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
 
@@ -105,32 +121,75 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t cluster_address) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_address) : "memory");
 }
 
+// D[tmem] (+)= A * B with the descriptors given as their 32-bit halves: the high word is the same for every
+// operand tile of this kernel and the low word only ever has constants added to it, so the issuing thread
+// spends one integer add per operand per MMA.
 template <bool kInt8>
-__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                          uint32_t accumulate) {
   if constexpr (kInt8) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, p;\n\t"
         "}"
         :
-        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t"
         "}"
         :
-        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }
 
-__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// 32 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld_x32(uint32_t address, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
+      "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(address)
+      : "memory");
+}
+
+__device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory"); }
+
+// Work unit -> (work item, channel block), item-major: the units of one item (same token rows, successive
+// channel blocks) are adjacent, and the same channel block of the next row tile of an expert is n_blocks
+// units further, i.e. in flight on another pair at about the same time, so its weight tile comes from L2.
+struct UnitInfo {
+  int expert, row0, rows, block;
+};
+
+__device__ __forceinline__ UnitInfo load_unit(const int* __restrict__ items, int64_t unit, int64_t units, int n_blocks) {
+  UnitInfo info = {0, 0, 0, 0};
+  if (unit < units) {
+    const int item = static_cast<int>(unit / n_blocks);
+    const int4 packed = __ldg(reinterpret_cast<const int4*>(items) + item);
+    info.expert = packed.x;
+    info.row0 = packed.y;
+    info.rows = packed.z;
+    info.block = static_cast<int>(unit - static_cast<int64_t>(item) * n_blocks);
+  }
+  return info;
+}
 
 template <bool kInt8, bool kGateUp, bool kDense>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -165,11 +224,12 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&ctl->acc_full[b], 1);
-      ptx::mbar_init(&ctl->acc_empty[b], 8);  // four epilogue warps in each CTA of the pair
+      ptx::mbar_init(&ctl->acc_empty[b], 2 * kEpilogueWarps);  // the epilogue warps of both CTAs
     }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
   }
+  if (threadIdx.x >= 64 && threadIdx.x < 128) ctl->exp_table[threadIdx.x - 64] = kExp2Table[threadIdx.x - 64];
   if (warp == 1) {
     tmem_alloc_pair(&ctl->tmem_base, kTmemColumns);
     tmem_relinquish_pair();
@@ -180,44 +240,51 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
+  const uint32_t smem_base = ptx::smem_u32(smem);
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       ptx::prefetch_tensormap(&weight_map);
       ptx::prefetch_tensormap(&token_map);
+      const uint32_t full_leader0 = map_to_cta(ptx::smem_u32(&ctl->full[0]), 0);
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
+      UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks);
       for (int64_t unit = first_unit; unit < units; unit += unit_stride) {
-        int item, block;
-        decode_unit(args.items, unit, n_blocks, &item, &block);
-        const int c0 = block * kChannelsPerUnit;
-        const int expert = args.items[4 * item + 0];
-        const int row0 = args.items[4 * item + 1];
-        const int weight_row = expert * n_total + c0;
+        const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks);  // in flight during this unit
         // The MMA takes the first N/2 token rows from the leader's tile and the other N/2 from the follower's.
-        const int mma_n = min(kPairTokens, (args.items[4 * item + 2] + 31) & ~31);
-        const int token_row = row0 + (mma_n / 2) * static_cast<int>(cta);
+        const int mma_n = min(kPairTokens, (cur.rows + 31) & ~31);
+        const int token_row = cur.row0 + (mma_n / 2) * static_cast<int>(cta);
+        const int channel0 = cur.block * kChannelsPerUnit + (kChannelsPerUnit / 2) * static_cast<int>(cta);
+        const int weight_row = cur.expert * n_total + channel0;  // down
+        const int group = channel0 >> 4;                         // gate_up: 16-channel group
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 11);
-          uint8_t* stage_base = smem + static_cast<size_t>(stage) * kStageBytes;
-          const uint32_t full_leader = map_to_cta(ptx::smem_u32(&ctl->full[stage]), 0);
-          if (leader) ptx::mbar_arrive_expect_tx(&ctl->full[stage], 2 * kStageBytes);
-          const int x = kb * kBlockKElems;
-          if (kGateUp) {
-            tma_load_2d_pair(stage_base, &weight_map, full_leader, x, weight_row + 64 * static_cast<int>(cta));
-            tma_load_2d_pair(stage_base + 64 * kBlockKBytes, &weight_map, full_leader, x, weight_row + args.n_out + 64 * static_cast<int>(cta));
+          if (args.diag & 2) {
+            if (leader) ptx::mbar_arrive(&ctl->full[stage]);
           } else {
-            tma_load_2d_pair(stage_base, &weight_map, full_leader, x, weight_row + kRowsPerCta * static_cast<int>(cta));
+            const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes;
+            const uint32_t bar = full_leader0 + 8u * static_cast<uint32_t>(stage);
+            if (leader) ptx::mbar_arrive_expect_tx(&ctl->full[stage], 2 * kStageBytes);
+            const int x = kb * kBlockKElems;
+            if constexpr (kGateUp) {
+              // Four boxes of [16 gate rows | 16 up rows]: tensor dimensions {K, row in group, group, gate/up, expert}.
+#pragma unroll
+              for (int g = 0; g < 4; ++g) tma_load_5d_pair(dst + g * 32 * kBlockKBytes, &weight_map, bar, x, 0, group + g, 0, cur.expert);
+            } else {
+              tma_load_2d_pair(dst, &weight_map, bar, x, weight_row);
+            }
+            tma_load_2d_pair(dst + kRowsPerCta * kBlockKBytes, &token_map, bar, x, token_row);
           }
-          tma_load_2d_pair(stage_base + kRowsPerCta * kBlockKBytes, &token_map, full_leader, x, token_row);
           ++issued;
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
+        cur = next;
       }
       if (leader) {
         // Drain: the leader's full barriers count both CTAs' bytes, so this also covers the follower's loads.
@@ -239,147 +306,180 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (leader && lane == 0) {
+      // Descriptor words (see ptx::make_smem_desc_sw128): the low word holds the start address >> 4 and the
+      // ignored leading offset, the high word the 1024-byte group stride, version 1 and SWIZZLE_128B.
+      const uint32_t desc_hi = static_cast<uint32_t>(1024 >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t a_lo_stage0 = ((smem_base & 0x3ffffu) >> 4) | (1u << 16);
+      constexpr uint32_t kStageStep = kStageBytes >> 4;
+      constexpr uint32_t kTokenStep = (kRowsPerCta * kBlockKBytes) >> 4;
+      const uint32_t empty_c0 = map_to_cta(ptx::smem_u32(&ctl->empty[0]), 0);
+      const uint32_t empty_c1 = map_to_cta(ptx::smem_u32(&ctl->empty[0]), 1);
+      const uint32_t accfull_c0 = map_to_cta(ptx::smem_u32(&ctl->acc_full[0]), 0);
+      const uint32_t accfull_c1 = map_to_cta(ptx::smem_u32(&ctl->acc_full[0]), 1);
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t a_lo = a_lo_stage0;
       int local = 0;
+      UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks);
       for (int64_t unit = first_unit; unit < units; unit += unit_stride, ++local) {
-        const int buffer = local & 1;
-        const uint32_t use = static_cast<uint32_t>(local >> 1);
+        const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks);
+        const uint32_t buffer = static_cast<uint32_t>(local) & 1u;
+        const uint32_t use = static_cast<uint32_t>(local) >> 1;
         // N follows the rows this unit really has (a multiple of 32 for two-SM MMAs).
-        int item, block;
-        decode_unit(args.items, unit, n_blocks, &item, &block);
-        const int item_rows = args.items[4 * item + 2];
-        const int mma_n = min(kPairTokens, (item_rows + 31) & ~31);
+        const int mma_n = min(kPairTokens, (cur.rows + 31) & ~31);
         const uint32_t idesc = ptx::make_instr_desc(kInt8, 2 * kRowsPerCta, mma_n);
         ptx::mbar_wait(&ctl->acc_empty[buffer], (use & 1u) ^ 1u, abort_flag, status, 12);
         ptx::tcgen05_fence_after();
-        const uint32_t acc = tmem_base + static_cast<uint32_t>(buffer * kAccColumns);
+        const uint32_t acc = tmem_base + buffer * kAccColumns;
+        uint32_t accumulate = 0;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->full[stage], phase, abort_flag, status, 13);
           ptx::tcgen05_fence_after();
-          const uint32_t stage_addr = ptx::smem_u32(smem + static_cast<size_t>(stage) * kStageBytes);
+          if (!(args.diag & 4)) {
 #pragma unroll
-          for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
-            const uint64_t desc_a = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
-            const uint64_t desc_b = ptx::make_smem_desc_sw128(stage_addr + kRowsPerCta * kBlockKBytes + ks * kUmmaKBytes);
-            umma_pair<kInt8>(acc, desc_a, desc_b, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            for (uint32_t ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
+              umma_pair<kInt8>(acc, a_lo + 2u * ks, a_lo + kTokenStep + 2u * ks, desc_hi, idesc, accumulate);
+              accumulate = 1;
+            }
           }
-          const uint32_t empty_local = ptx::smem_u32(&ctl->empty[stage]);
-          tcgen05_commit_pair(map_to_cta(empty_local, 0));
-          tcgen05_commit_pair(map_to_cta(empty_local, 1));
+          tcgen05_commit_pair(empty_c0 + 8u * static_cast<uint32_t>(stage));
+          tcgen05_commit_pair(empty_c1 + 8u * static_cast<uint32_t>(stage));
+          a_lo += kStageStep;
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
+            a_lo = a_lo_stage0;
           }
         }
-        const uint32_t full_local = ptx::smem_u32(&ctl->acc_full[buffer]);
-        tcgen05_commit_pair(map_to_cta(full_local, 0));
-        tcgen05_commit_pair(map_to_cta(full_local, 1));
+        tcgen05_commit_pair(accfull_c0 + 8u * buffer);
+        tcgen05_commit_pair(accfull_c1 + 8u * buffer);
+        cur = next;
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
-    const int quarter = warp & 3;
+    // ---------------- epilogue (warps 2..9 of both CTAs) ----------------
+    const int quarter = warp & 3;            // the TMEM lanes a warp may read are fixed by warp id % 4
+    const int chunk_parity = (warp - 2) >> 2;  // warps 2..5 take the even 32-column chunks, warps 6..9 the odd ones
     const int lane_in_tile = quarter * 32 + lane;  // TMEM lane = A row of this CTA
-    const int epilogue_thread = static_cast<int>(threadIdx.x) - 64;
+    const int tid = static_cast<int>(threadIdx.x) - 64;  // the column whose metadata this thread stages
     const int n_out = args.n_out;
     const int numerics = args.numerics;
     const float limit = args.swiglu_limit;
     uint32_t* const dump = static_cast<uint32_t*>(args.dump_acc);
-    const bool up_half = kGateUp && lane_in_tile >= 64;
+    const bool low = lane < 16;  // gate_up: lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same channels
+    // Output channel of this thread inside the unit's channel block.
+    const int channel_in_unit = kGateUp ? 64 * static_cast<int>(cta) + 16 * quarter + (lane & 15)
+                                        : kRowsPerCta * static_cast<int>(cta) + lane_in_tile;
+    const uint32_t acc_empty_leader = map_to_cta(ptx::smem_u32(&ctl->acc_empty[0]), 0);
+    const uint32_t acc_lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+
+    // Per-unit values: the column metadata in shared memory and this thread's weight scales in registers.  Both
+    // are fetched while the previous unit is being finished.
+    struct ThreadUnit {
+      float column_scale;     // of column `tid`
+      int64_t column_offset;  // of column `tid`
+      float scale_gate, scale_up, bias;
+    };
+    auto fetch = [&](const UnitInfo& info, bool valid) {
+      ThreadUnit t = {0.0f, 0, 1.0f, 1.0f, 0.0f};
+      if (!valid) return t;
+      if (tid < info.rows) {
+        const int row = info.row0 + tid;
+        if (kInt8) t.column_scale = args.a_scale[row];
+        const int target = (kGateUp || kDense) ? row : args.sorted_routes[row];
+        t.column_offset = static_cast<int64_t>(target) * n_out;
+      }
+      const int n = info.block * kChannelsPerUnit + channel_in_unit;
+      if (n < n_out) {
+        if (kInt8) {
+          const float* s = args.w_scale + static_cast<int64_t>(info.expert) * n_total;
+          t.scale_gate = s[n];
+          if (kGateUp) t.scale_up = s[n + n_out];
+        }
+        if (kDense && args.bias != nullptr) t.bias = args.bias[n];
+      }
+      return t;
+    };
+
+    UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks);
+    UnitInfo next = load_unit(args.items, first_unit + unit_stride, units, n_blocks);
+    ThreadUnit mine = fetch(cur, first_unit < units);
+    ctl->meta[0].scale[tid] = mine.column_scale;
+    ctl->meta[0].offset[tid] = mine.column_offset;
+    epilogue_bar_sync();
+
     int local = 0;
     for (int64_t unit = first_unit; unit < units; unit += unit_stride, ++local) {
-      const int buffer = local & 1;
-      const uint32_t use = static_cast<uint32_t>(local >> 1);
-      int item, block;
-      decode_unit(args.items, unit, n_blocks, &item, &block);
-      const int c0 = block * kChannelsPerUnit;
-      const int expert = args.items[4 * item + 0];
-      const int row0 = args.items[4 * item + 1];
-      const int rows = args.items[4 * item + 2];
-      // Output channel this thread finishes.
-      const int n = kGateUp ? c0 + 64 * static_cast<int>(cta) + (lane_in_tile & 63) : c0 + kRowsPerCta * static_cast<int>(cta) + lane_in_tile;
+      const uint32_t buffer = static_cast<uint32_t>(local) & 1u;
+      const uint32_t use = static_cast<uint32_t>(local) >> 1;
+      // Loads for the next unit (and the work item of the one after) are issued now and consumed after this unit.
+      const ThreadUnit upcoming = fetch(next, unit + unit_stride < units);
+      const UnitInfo after = load_unit(args.items, unit + 2 * unit_stride, units, n_blocks);
+
+      const int rows = cur.rows;
+      const int row0 = cur.row0;
+      const int n = cur.block * kChannelsPerUnit + channel_in_unit;
       const bool channel_ok = n < n_out;
-      ColumnMeta* meta = &ctl->meta[local & 1];
-      for (int c = epilogue_thread; c < rows; c += 128) {
-        if (kInt8) meta->scale[c] = args.a_scale[row0 + c];
-        meta->target[c] = (kGateUp || kDense) ? row0 + c : args.sorted_routes[row0 + c];
-      }
-      float scale_gate = 1.0f, scale_up = 1.0f;
-      if (kInt8 && channel_ok) {
-        const float* s = args.w_scale + static_cast<int64_t>(expert) * n_total;
-        scale_gate = s[n];
-        if (kGateUp) scale_up = s[n + n_out];
-      }
-      float bias = 0.0f;
-      if (kDense && channel_ok && args.bias != nullptr) bias = args.bias[n];
-      epilogue_bar_sync();  // metadata visible to the four epilogue warps
+      const ColumnMeta* meta = &ctl->meta[local & 1];
+      const int chunks = (args.diag & 1) ? 0 : (rows + 31) >> 5;
+
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 14);
       ptx::tcgen05_fence_after();
-      const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * kAccColumns);
-      for (int col0 = 0; col0 < rows; col0 += 8) {
-        uint32_t bits[8];
-        ptx::tmem_ld_x8(acc + col0, bits);
+      const uint32_t acc = acc_lane_base + buffer * kAccColumns;
+      for (int chunk = chunk_parity; chunk < chunks; chunk += 2) {
+        uint32_t v[32];
+        tmem_ld_x32(acc + static_cast<uint32_t>(chunk * 32), v);
         ptx::tmem_ld_wait();
+        const int col0 = chunk * 32;
         if constexpr (kGateUp) {
-          // Gate threads finish columns 0..3 of the chunk, up threads columns 4..7; each sends the other half.
-          const int channel = lane_in_tile & 63;
-          uint32_t* send = ctl->exchange[up_half ? 1 : 0][channel];
+          // Lanes l (gate) and l + 16 (up) hold the same channel: the gate lane finishes the even columns, the
+          // up lane the odd ones, each receiving the other's value of that column.
 #pragma unroll
-          for (int j = 0; j < 4; ++j) send[j] = bits[up_half ? j : 4 + j];
-          epilogue_bar_sync();
-          const uint32_t* receive = ctl->exchange[up_half ? 0 : 1][channel];
-          uint32_t other[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) other[j] = receive[j];
-          epilogue_bar_sync();
-          if (channel_ok) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int column = col0 + (up_half ? 4 + j : j);
-              if (column < rows) {
-                const int64_t row = meta->target[column];
-                const uint32_t gate_bits = up_half ? other[j] : bits[j];
-                const uint32_t up_bits = up_half ? bits[4 + j] : other[j];
-                if (dump != nullptr) {
-                  uint32_t* out = dump + row * n_total;
-                  out[n] = gate_bits;
-                  out[n + n_out] = up_bits;
-                }
-                float gate, up;
-                if constexpr (kInt8) {
-                  const float a = meta->scale[column];
-                  gate = dequantize(static_cast<int>(gate_bits), a, scale_gate, numerics);
-                  up = dequantize(static_cast<int>(up_bits), a, scale_up, numerics);
-                } else {
-                  gate = __uint_as_float(gate_bits);
-                  up = __uint_as_float(up_bits);
-                }
-                args.y[row * n_out + n] = swiglu_to_bf16(gate, up, limit);
+          for (int p = 0; p < 16; ++p) {
+            const uint32_t received = __shfl_xor_sync(0xffffffffu, low ? v[2 * p + 1] : v[2 * p], 16);
+            const uint32_t gate_bits = low ? v[2 * p] : received;
+            const uint32_t up_bits = low ? received : v[2 * p + 1];
+            const int column = col0 + 2 * p + (low ? 0 : 1);
+            if (column < rows && channel_ok) {
+              if (dump != nullptr) {
+                uint32_t* out = dump + static_cast<int64_t>(row0 + column) * n_total;
+                out[n] = gate_bits;
+                out[n + n_out] = up_bits;
               }
+              float gate, up;
+              if constexpr (kInt8) {
+                const float a = meta->scale[column];
+                gate = dequantize(static_cast<int>(gate_bits), a, mine.scale_gate, numerics);
+                up = dequantize(static_cast<int>(up_bits), a, mine.scale_up, numerics);
+              } else {
+                gate = __uint_as_float(gate_bits);
+                up = __uint_as_float(up_bits);
+              }
+              args.y[meta->offset[column] + n] = swiglu_to_bf16_with(gate, up, limit, ctl->exp_table);
             }
           }
-        } else if (channel_ok) {
+        } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (col0 + j < rows) {
-              const int64_t target = meta->target[col0 + j];
-              if (dump != nullptr) dump[static_cast<int64_t>(row0 + col0 + j) * n_total + n] = bits[j];
+          for (int j = 0; j < 32; ++j) {
+            const int column = col0 + j;
+            if (column < rows && channel_ok) {
+              if (dump != nullptr) dump[static_cast<int64_t>(row0 + column) * n_total + n] = v[j];
               float value;
               if constexpr (kInt8) {
-                value = dequantize(static_cast<int>(bits[j]), meta->scale[col0 + j], scale_gate, numerics);
+                value = dequantize(static_cast<int>(v[j]), meta->scale[column], mine.scale_gate, numerics);
               } else {
-                value = __uint_as_float(bits[j]);
+                value = __uint_as_float(v[j]);
               }
+              const int64_t index = meta->offset[column] + n;
               if constexpr (kDense) {
-                value = __fadd_rn(value, bias);
+                value = __fadd_rn(value, mine.bias);
                 if (args.dense_out_bf16) {
-                  static_cast<uint16_t*>(args.dense_out)[target * n_out + n] = f32_to_bf16_bits(value);
+                  static_cast<uint16_t*>(args.dense_out)[index] = f32_to_bf16_bits(value);
                 } else {
-                  static_cast<float*>(args.dense_out)[target * n_out + n] = value;
+                  static_cast<float*>(args.dense_out)[index] = value;
                 }
               } else {
-                args.route_out[target * n_out + n] = value;
+                args.route_out[index] = value;
               }
             }
           }
@@ -387,7 +487,17 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       }
       ptx::tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&ctl->acc_empty[buffer]), 0));
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8u * buffer);
+
+      // Publish the next unit's column metadata.  Nobody still reads that buffer: it belonged to the previous
+      // unit, which every warp left before the barrier at the end of the previous iteration.
+      ColumnMeta* meta_next = &ctl->meta[(local + 1) & 1];
+      meta_next->scale[tid] = upcoming.column_scale;
+      meta_next->offset[tid] = upcoming.column_offset;
+      epilogue_bar_sync();
+      mine = upcoming;
+      cur = next;
+      next = after;
     }
   }
 
@@ -418,6 +528,7 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// 2-D K-major tensor [rows, k] with 128-byte-swizzled boxes of {128 bytes of K, box_rows}.
 bool make_tensor_map(CUtensorMap* map, const void* base, bool int8, uint64_t rows, uint64_t k, uint32_t box_rows) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
@@ -427,6 +538,22 @@ bool make_tensor_map(CUtensorMap* map, const void* base, bool int8, uint64_t row
   const cuuint32_t box[2] = {kBlockKBytes / elem_bytes, box_rows};
   const cuuint32_t elem_strides[2] = {1, 1};
   return encode(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// gate_up weights [E, 2I, K] seen as {K, 16 rows, I/16 groups, gate|up, E}: one box is the 16 gate rows of a
+// channel group followed by its 16 up rows.
+bool make_gate_up_map(CUtensorMap* map, const void* base, bool int8, uint64_t experts, uint64_t inter, uint64_t k) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const uint64_t elem_bytes = int8 ? 1 : 2;
+  const uint64_t row_bytes = k * elem_bytes;
+  const cuuint64_t dims[5] = {k, 16, inter / 16, 2, experts};
+  const cuuint64_t strides[4] = {row_bytes, 16 * row_bytes, inter * row_bytes, 2 * inter * row_bytes};
+  const cuuint32_t box[5] = {static_cast<cuuint32_t>(kBlockKBytes / elem_bytes), 16, 1, 2, 1};
+  const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  return encode(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides,
                 box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -442,8 +569,10 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
   }
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   CUtensorMap weight_map, token_map;
-  if (!make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total, args.k, kGateUp ? 64 : kRowsPerCta) ||
-      !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowsPerCta)) {
+  const bool weights_ok = kGateUp ? make_gate_up_map(&weight_map, args.weights, kInt8, args.experts, args.n_out, args.k)
+                                  : make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total,
+                                                    args.k, kRowsPerCta);
+  if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowsPerCta)) {
     return cudaErrorInvalidValue;
   }
   int device = 0, sms = 148;
@@ -460,8 +589,11 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
 
 }  // namespace
 
+bool umma_pair_supported(bool gate_up, int n_out) { return !gate_up || n_out % 16 == 0; }
+
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream) {
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
+  if (!umma_pair_supported(gate_up, args.n_out)) return cudaErrorInvalidValue;
   if (args.dense_out != nullptr) {
     if (!int8 || gate_up) return cudaErrorInvalidValue;
     return launch_pair<true, false, true>(args, stream);

@@ -26,6 +26,7 @@
 // one unit overlaps the main loop of the next.  No load uses cluster multicast; weight-tile reuse
 // between row tiles of one expert comes from L2 (adjacent work items run concurrently).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -74,6 +75,7 @@ struct SmemControl {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
+  uint32_t exp_table[64];  // copy of kExp2Table: divergent lookups are served by 32 banks
   ColumnMeta meta[2];
 };
 
@@ -111,6 +113,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
   }
+  if (threadIdx.x >= 64 && threadIdx.x < 128) ctl->exp_table[threadIdx.x - 64] = kExp2Table[threadIdx.x - 64];
   if (warp == 1) {
     ptx::tmem_alloc(&ctl->tmem_base, Cfg::kTmemColumns);
     ptx::tmem_relinquish();
@@ -139,11 +142,15 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
           uint8_t* stage_base = smem + static_cast<size_t>(stage) * Cfg::kStageBytes;
-          ptx::mbar_arrive_expect_tx(&ctl->full[stage], Cfg::kStageBytes);
-          const int x = kb * kBlockKElems;
-          ptx::tma_load_2d(stage_base, &weight_map, &ctl->full[stage], x, weight_row);
-          if (kGateUp) ptx::tma_load_2d(stage_base + kBlockM * kBlockKBytes, &weight_map, &ctl->full[stage], x, weight_row + args.n_out);
-          ptx::tma_load_2d(stage_base + Cfg::kWeightBytes, &token_map, &ctl->full[stage], x, row0);
+          if (args.diag & 2) {
+            ptx::mbar_arrive(&ctl->full[stage]);
+          } else {
+            ptx::mbar_arrive_expect_tx(&ctl->full[stage], Cfg::kStageBytes);
+            const int x = kb * kBlockKElems;
+            ptx::tma_load_2d(stage_base, &weight_map, &ctl->full[stage], x, weight_row);
+            if (kGateUp) ptx::tma_load_2d(stage_base + kBlockM * kBlockKBytes, &weight_map, &ctl->full[stage], x, weight_row + args.n_out);
+            ptx::tma_load_2d(stage_base + Cfg::kWeightBytes, &token_map, &ctl->full[stage], x, row0);
+          }
           ++issued;
           if (++stage == Cfg::kStages) {
             stage = 0;
@@ -192,6 +199,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
           const uint32_t stage_addr = ptx::smem_u32(smem + static_cast<size_t>(stage) * Cfg::kStageBytes);
 #pragma unroll
           for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
+            if (args.diag & 4) break;
             const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
             const uint64_t desc_tok = ptx::make_smem_desc_sw128(stage_addr + Cfg::kWeightBytes + ks * kUmmaKBytes);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
@@ -247,7 +255,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 4);
       ptx::tcgen05_fence_after();
       const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
-      for (int c0 = 0; c0 < rows; c0 += 8) {
+      for (int c0 = 0; c0 < ((args.diag & 1) ? 0 : rows); c0 += 8) {
         uint32_t gate_bits[8];
         uint32_t up_bits[8];
         ptx::tmem_ld_x8(acc + c0, gate_bits);
@@ -273,7 +281,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                   gate = __uint_as_float(gate_bits[j]);
                   up = __uint_as_float(up_bits[j]);
                 }
-                args.y[target * n_out + n] = swiglu_to_bf16(gate, up, limit);
+                args.y[target * n_out + n] = swiglu_to_bf16_with(gate, up, limit, ctl->exp_table);
               } else {
                 float value;
                 if constexpr (kInt8) {
@@ -398,9 +406,15 @@ bool umma_row_tile_supported(int row_tile) {
   return row_tile == 16 || row_tile == 32 || row_tile == 64 || row_tile == 128 || row_tile == 256 || row_tile == kPairRowTile;
 }
 
-cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream) {
+cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& caller_args, bool int8, bool gate_up, cudaStream_t stream) {
+  GroupedGemmArgs args = caller_args;
+  const char* diag = getenv("FUSED_CPP_MOE_GEMM_DIAG");
+  args.diag = diag ? atoi(diag) : 0;
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
-  if (args.row_tile == kPairRowTile) return launch_umma_pair_grouped_gemm(args, int8, gate_up, stream);
+  if (args.row_tile == kPairRowTile) {
+    if (umma_pair_supported(gate_up, args.n_out)) return launch_umma_pair_grouped_gemm(args, int8, gate_up, stream);
+    args.row_tile = 256;  // same 256-row work items, one-SM kernel
+  }
   if (args.dense_out != nullptr) {
     if (!int8 || gate_up) return cudaErrorInvalidValue;  // the dense epilogue exists for the int8 single-stage GEMM
     return launch_tile<true, false, true>(args, stream);

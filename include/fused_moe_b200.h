@@ -257,11 +257,13 @@ FMOE_API int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows
 /* ---- measurement helper ---------------------------------------------------------------------- */
 
 /* Dense tensor-core peak of the current GPU for one MMA shape: every SM issues `iterations` back-to-back
- * tcgen05.mma of 128 x n x 32 bytes (kind::i8 when int8 != 0, else kind::f16 with bf16 operands) on zeroed
- * shared memory; returns tera-operations per second (2 per multiply-add), best of three timed launches.
+ * tcgen05.mma of 128 x n x 32 bytes (kind::i8 when int8 != 0, else kind::f16 with bf16 operands) on shared
+ * memory that is zeroed (mode bit 0 clear) or filled with a non-zero pattern (bit 0 set: zero operands draw
+ * less power than real data and give the rate at full clock); mode >> 8 = c > 0 adds a tcgen05.commit after
+ * every c MMAs.  Returns tera-operations per second (2 per multiply-add), best of three timed launches.
  * No counterpart in the reference (its ceilings are per-core SMMLA/BFMMLA rates,
  * docs/agent_performance_references.md:85-91).  Allocates a few bytes and synchronises: not for hot paths. */
-FMOE_API int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, float* tera_ops_per_s);
+FMOE_API int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mode, float* tera_ops_per_s);
 
 #ifdef __cplusplus
 }
