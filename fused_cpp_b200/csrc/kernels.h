@@ -105,7 +105,7 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& args, bool int8, boo
 
 // ---- umma2_gemm.cu: two-SM (cta_group::2) grouped GEMM, 256-row work items.  Selected by row tile 512.
 constexpr int kPairRowTile = 512;
-bool umma_pair_supported(bool gate_up, int n_out);  // gate_up needs n_out % 16 == 0 (16-channel TMA groups)
+bool umma_pair_supported(bool gate_up, int n_out, int64_t output_rows);  // else callers use the one-SM kernel on the same items
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
 
 // ---- probe.cu: tcgen05.mma issue-rate probe (128 x n x 32-byte MMAs back to back on every CTA)

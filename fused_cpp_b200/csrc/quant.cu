@@ -96,6 +96,61 @@ quantize_rows_kernel(const uint16_t* __restrict__ x, int cols, const int* __rest
   }
 }
 
+// Same work, one warp per output row, for rows of at most 32 * 16 * kVectors columns: the row is read once
+// into registers (kVectors 32-byte pieces per lane), the absmax is a shuffle reduction, no block barrier.
+// Rows of a few KB (the 2048-column intermediate of the W8A8 layer) are too short to keep a 256-thread CTA busy.
+template <int kVectors>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_rows_warp_kernel(const uint16_t* __restrict__ x, int64_t out_rows, int cols, const int* __restrict__ sorted_routes, int top_k,
+                          const int* __restrict__ valid_rows, int numerics, int weight_mode, int8_t* __restrict__ q,
+                          float* __restrict__ scale_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kQuantThreads / 32) + (threadIdx.x >> 5);
+  if (row >= out_rows) return;
+  if (valid_rows && row >= *valid_rows) return;
+  const int64_t src_row = sorted_routes ? static_cast<int64_t>(sorted_routes[row] / top_k) : row;
+  const uint4* src = reinterpret_cast<const uint4*>(x + src_row * cols);
+  const int vec16 = cols >> 4;
+  uint4 held[kVectors][2];
+  float local = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kVectors; ++i) {
+    const int v = lane + 32 * i;
+    if (v < vec16) {
+      held[i][0] = src[2 * v];
+      held[i][1] = src[2 * v + 1];
+      local = fmaxf(local, fmaxf(amax8(held[i][0]), amax8(held[i][1])));
+    }
+  }
+  const float amax = warp_max(local);
+  float scale;
+  int mode = numerics;
+  if (weight_mode) {
+    scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    mode = FMOE_NUMERICS_TORCHREF;
+  } else {
+    scale = row_scale_from_amax(amax, numerics);
+  }
+  if (lane == 0) scale_out[row] = scale;
+  const float operand = quantize_operand(scale, mode);
+  uint4* dst = reinterpret_cast<uint4*>(q + row * cols);
+#pragma unroll
+  for (int i = 0; i < kVectors; ++i) {
+    const int v = lane + 32 * i;
+    if (v < vec16) {
+      float values[16];
+      unpack8(held[i][0], values);
+      unpack8(held[i][1], values + 8);
+      uint4 out;
+      out.x = pack4(values, operand, mode);
+      out.y = pack4(values + 4, operand, mode);
+      out.z = pack4(values + 8, operand, mode);
+      out.w = pack4(values + 12, operand, mode);
+      dst[v] = out;
+    }
+  }
+}
+
 // cols % 16 == 0, top_k <= 32.  One CTA per token: the row is quantised once and stored to each of its routes'
 // sorted positions (the reference re-quantises the token for every route, kernels.cpp:639-644; the bits are the same).
 __global__ void __launch_bounds__(kQuantThreads)
@@ -194,8 +249,18 @@ cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, 
                                  const int* valid_rows, int numerics, int weight_mode, int8_t* q, float* scale,
                                  cudaStream_t stream) {
   if (out_rows <= 0) return cudaSuccess;
-  quantize_rows_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows,
-                                                                                     numerics, weight_mode, q, scale);
+  const int vec16 = cols >> 4;
+  const unsigned warp_blocks = static_cast<unsigned>((out_rows + kQuantThreads / 32 - 1) / (kQuantThreads / 32));
+  if (vec16 <= 64) {
+    quantize_rows_warp_kernel<2><<<warp_blocks, kQuantThreads, 0, stream>>>(x, out_rows, cols, sorted_routes, top_k, valid_rows, numerics,
+                                                                             weight_mode, q, scale);
+  } else if (vec16 <= 128) {
+    quantize_rows_warp_kernel<4><<<warp_blocks, kQuantThreads, 0, stream>>>(x, out_rows, cols, sorted_routes, top_k, valid_rows, numerics,
+                                                                             weight_mode, q, scale);
+  } else {
+    quantize_rows_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows,
+                                                                                       numerics, weight_mode, q, scale);
+  }
   return cudaGetLastError();
 }
 

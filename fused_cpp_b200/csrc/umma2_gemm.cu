@@ -37,7 +37,10 @@ constexpr int kRowsPerCta = 128;    // A rows and B rows staged by one CTA
 constexpr int kPairTokens = 256;    // MMA N
 constexpr int kBlockKBytes = 128;
 constexpr int kUmmaKBytes = 32;
-constexpr int kEpilogueWarps = 8;
+#ifndef FMOE_PAIR_EPILOGUE_WARPS
+#define FMOE_PAIR_EPILOGUE_WARPS 8
+#endif
+constexpr int kEpilogueWarps = FMOE_PAIR_EPILOGUE_WARPS;  // a multiple of 4: every TMEM lane quarter gets the same number
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kThreads = 64 + kEpilogueThreads;
 constexpr int kStages = 6;
@@ -49,10 +52,11 @@ constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes 
 // Per-column values of a work unit, staged one unit ahead so that the element loop reads shared memory.
 struct ColumnMeta {
   float scale[256];      // activation scale of the row (int8)
-  int64_t offset[256];   // element offset of the output row: target row * n_out
+  uint32_t offset[256];  // element offset of the output row: target row * n_out
 };
 
 struct PairControl {
+  ColumnMeta meta[2];  // first: its arrays are read with 16-byte loads
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t acc_full[2];
@@ -60,7 +64,6 @@ struct PairControl {
   uint32_t tmem_base;
   volatile int abort_flag;
   uint32_t exp_table[64];  // copy of kExp2Table: divergent lookups are served by 32 banks
-  ColumnMeta meta[2];
 };
 static_assert(sizeof(PairControl) <= 8192, "control block exceeds its shared-memory reservation");
 
@@ -174,6 +177,13 @@ __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 
 // Work unit -> (work item, channel block), item-major: the units of one item (same token rows, successive
 // channel blocks) are adjacent, and the same channel block of the next row tile of an expert is n_blocks
 // units further, i.e. in flight on another pair at about the same time, so its weight tile comes from L2.
+struct TrueTag {
+  static constexpr bool value = true;
+};
+struct FalseTag {
+  static constexpr bool value = false;
+};
+
 struct UnitInfo {
   int expert, row0, rows, block;
 };
@@ -357,13 +367,14 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..9 of both CTAs) ----------------
-    const int quarter = warp & 3;            // the TMEM lanes a warp may read are fixed by warp id % 4
-    const int chunk_parity = (warp - 2) >> 2;  // warps 2..5 take the even 32-column chunks, warps 6..9 the odd ones
-    const int lane_in_tile = quarter * 32 + lane;  // TMEM lane = A row of this CTA
-    const int tid = static_cast<int>(threadIdx.x) - 64;  // the column whose metadata this thread stages
+    // ---------------- epilogue (warps 2.. of both CTAs) ----------------
+    const int quarter = warp & 3;                    // the TMEM lanes a warp may read are fixed by warp id % 4
+    const int chunk_first = (warp - 2) >> 2;         // warps sharing a lane quarter take 32-column chunks round-robin
+    constexpr int kChunkStep = kEpilogueWarps / 4;
+    const int lane_in_tile = quarter * 32 + lane;    // TMEM lane = A row of this CTA
+    const int tid = static_cast<int>(threadIdx.x) - 64;  // threads 0..255 each stage the metadata of one column
     const int n_out = args.n_out;
-    const int numerics = args.numerics;
+    const bool native = args.numerics == FMOE_NUMERICS_NATIVE;
     const float limit = args.swiglu_limit;
     uint32_t* const dump = static_cast<uint32_t*>(args.dump_acc);
     const bool low = lane < 16;  // gate_up: lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same channels
@@ -372,22 +383,23 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
                                         : kRowsPerCta * static_cast<int>(cta) + lane_in_tile;
     const uint32_t acc_empty_leader = map_to_cta(ptx::smem_u32(&ctl->acc_empty[0]), 0);
     const uint32_t acc_lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t* exp_table = ctl->exp_table;
 
     // Per-unit values: the column metadata in shared memory and this thread's weight scales in registers.  Both
     // are fetched while the previous unit is being finished.
     struct ThreadUnit {
-      float column_scale;     // of column `tid`
-      int64_t column_offset;  // of column `tid`
+      float column_scale;      // of column `tid`
+      uint32_t column_offset;  // of column `tid`: output row * n_out (the launcher checks that it fits 32 bits)
       float scale_gate, scale_up, bias;
     };
     auto fetch = [&](const UnitInfo& info, bool valid) {
-      ThreadUnit t = {0.0f, 0, 1.0f, 1.0f, 0.0f};
+      ThreadUnit t = {0.0f, 0u, 1.0f, 1.0f, 0.0f};
       if (!valid) return t;
       if (tid < info.rows) {
         const int row = info.row0 + tid;
         if (kInt8) t.column_scale = args.a_scale[row];
         const int target = (kGateUp || kDense) ? row : args.sorted_routes[row];
-        t.column_offset = static_cast<int64_t>(target) * n_out;
+        t.column_offset = static_cast<uint32_t>(target) * static_cast<uint32_t>(n_out);
       }
       const int n = info.block * kChannelsPerUnit + channel_in_unit;
       if (n < n_out) {
@@ -401,11 +413,43 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       return t;
     };
 
+    // One accumulator value -> fp32 (int8: the reference's two multiplication orders, chosen at compile time).
+    auto to_float = [&](auto native_tag, uint32_t bits, float a, float s) {
+      if constexpr (kInt8) {
+        const float value = static_cast<float>(static_cast<int>(bits));
+        if constexpr (decltype(native_tag)::value) {
+          return __fmul_rn(value, __fmul_rn(a, s));
+        } else {
+          return __fmul_rn(__fmul_rn(value, a), s);
+        }
+      } else {
+        return __uint_as_float(bits);
+      }
+    };
+    // Calls body(fast, native) with both flags turned into types: four instances of the element loop, one branch.
+    auto dispatch = [&](bool fast, auto&& body) {
+      if (fast) {
+        if (native) {
+          body(TrueTag{}, TrueTag{});
+        } else {
+          body(TrueTag{}, FalseTag{});
+        }
+      } else {
+        if (native) {
+          body(FalseTag{}, TrueTag{});
+        } else {
+          body(FalseTag{}, FalseTag{});
+        }
+      }
+    };
+
     UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks);
     UnitInfo next = load_unit(args.items, first_unit + unit_stride, units, n_blocks);
     ThreadUnit mine = fetch(cur, first_unit < units);
-    ctl->meta[0].scale[tid] = mine.column_scale;
-    ctl->meta[0].offset[tid] = mine.column_offset;
+    if (tid < 256) {
+      ctl->meta[0].scale[tid] = mine.column_scale;
+      ctl->meta[0].offset[tid] = mine.column_offset;
+    }
     epilogue_bar_sync();
 
     int local = 0;
@@ -420,69 +464,91 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       const int row0 = cur.row0;
       const int n = cur.block * kChannelsPerUnit + channel_in_unit;
       const bool channel_ok = n < n_out;
+      const bool block_full = (cur.block + 1) * kChannelsPerUnit <= n_out;  // every thread's channel exists
       const ColumnMeta* meta = &ctl->meta[local & 1];
       const int chunks = (args.diag & 1) ? 0 : (rows + 31) >> 5;
 
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 14);
       ptx::tcgen05_fence_after();
       const uint32_t acc = acc_lane_base + buffer * kAccColumns;
-      for (int chunk = chunk_parity; chunk < chunks; chunk += 2) {
+      for (int chunk = chunk_first; chunk < chunks; chunk += kChunkStep) {
         uint32_t v[32];
         tmem_ld_x32(acc + static_cast<uint32_t>(chunk * 32), v);
         ptx::tmem_ld_wait();
         const int col0 = chunk * 32;
+        const bool fast = block_full && col0 + 32 <= rows && dump == nullptr;  // warp-uniform
         if constexpr (kGateUp) {
           // Lanes l (gate) and l + 16 (up) hold the same channel: the gate lane finishes the even columns, the
-          // up lane the odd ones, each receiving the other's value of that column.
+          // up lane the odd ones, each receiving the other's value of that column.  Output rows are the sorted
+          // rows themselves: row0 + column.
+          uint16_t* const out0 = args.y + (static_cast<int64_t>(row0 + col0 + (low ? 0 : 1)) * n_out + n);
+          const uint32_t pair_stride = 2u * static_cast<uint32_t>(n_out);
+          const float4* scale4 = reinterpret_cast<const float4*>(meta->scale + col0);
+          auto body = [&](auto fast_tag, auto native_tag) {
+            constexpr bool kFast = decltype(fast_tag)::value;
 #pragma unroll
-          for (int p = 0; p < 16; ++p) {
-            const uint32_t received = __shfl_xor_sync(0xffffffffu, low ? v[2 * p + 1] : v[2 * p], 16);
-            const uint32_t gate_bits = low ? v[2 * p] : received;
-            const uint32_t up_bits = low ? received : v[2 * p + 1];
-            const int column = col0 + 2 * p + (low ? 0 : 1);
-            if (column < rows && channel_ok) {
-              if (dump != nullptr) {
-                uint32_t* out = dump + static_cast<int64_t>(row0 + column) * n_total;
-                out[n] = gate_bits;
-                out[n + n_out] = up_bits;
-              }
-              float gate, up;
-              if constexpr (kInt8) {
-                const float a = meta->scale[column];
-                gate = dequantize(static_cast<int>(gate_bits), a, mine.scale_gate, numerics);
-                up = dequantize(static_cast<int>(up_bits), a, mine.scale_up, numerics);
-              } else {
-                gate = __uint_as_float(gate_bits);
-                up = __uint_as_float(up_bits);
-              }
-              args.y[meta->offset[column] + n] = swiglu_to_bf16_with(gate, up, limit, ctl->exp_table);
-            }
-          }
-        } else {
+            for (int q = 0; q < 8; ++q) {
+              const float4 s4 = scale4[q];  // the scales of columns 4q .. 4q+3 (one broadcast load)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int column = col0 + j;
-            if (column < rows && channel_ok) {
-              if (dump != nullptr) dump[static_cast<int64_t>(row0 + column) * n_total + n] = v[j];
-              float value;
-              if constexpr (kInt8) {
-                value = dequantize(static_cast<int>(v[j]), meta->scale[column], mine.scale_gate, numerics);
-              } else {
-                value = __uint_as_float(v[j]);
-              }
-              const int64_t index = meta->offset[column] + n;
-              if constexpr (kDense) {
-                value = __fadd_rn(value, mine.bias);
-                if (args.dense_out_bf16) {
-                  static_cast<uint16_t*>(args.dense_out)[index] = f32_to_bf16_bits(value);
-                } else {
-                  static_cast<float*>(args.dense_out)[index] = value;
+              for (int h = 0; h < 2; ++h) {
+                const int p = 2 * q + h;
+                const uint32_t received = __shfl_xor_sync(0xffffffffu, low ? v[2 * p + 1] : v[2 * p], 16);
+                const uint32_t gate_bits = low ? v[2 * p] : received;
+                const uint32_t up_bits = low ? received : v[2 * p + 1];
+                const float a = h == 0 ? (low ? s4.x : s4.y) : (low ? s4.z : s4.w);
+                if constexpr (!kFast) {
+                  const int column = col0 + 2 * p + (low ? 0 : 1);
+                  if (column >= rows || !channel_ok) continue;
+                  if (dump != nullptr) {
+                    uint32_t* out = dump + static_cast<int64_t>(row0 + column) * n_total;
+                    out[n] = gate_bits;
+                    out[n + n_out] = up_bits;
+                  }
                 }
-              } else {
-                args.route_out[index] = value;
+                const float gate = to_float(native_tag, gate_bits, a, mine.scale_gate);
+                const float up = to_float(native_tag, up_bits, a, mine.scale_up);
+                out0[static_cast<uint32_t>(p) * pair_stride] = swiglu_to_bf16_with(gate, up, limit, exp_table);
               }
             }
-          }
+          };
+          dispatch(fast, body);
+        } else {
+          const float4* scale4 = reinterpret_cast<const float4*>(meta->scale + col0);
+          const uint4* offset4 = reinterpret_cast<const uint4*>(meta->offset + col0);
+          float* const out_f32 = (kDense ? static_cast<float*>(args.dense_out) : args.route_out) + n;
+          uint16_t* const out_bf16 = static_cast<uint16_t*>(args.dense_out) + n;
+          const bool bf16_out = kDense && args.dense_out_bf16;
+          auto body = [&](auto fast_tag, auto native_tag) {
+            constexpr bool kFast = decltype(fast_tag)::value;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 s4 = scale4[q];
+              const uint4 o4 = offset4[q];
+              const float scales[4] = {s4.x, s4.y, s4.z, s4.w};
+              const uint32_t offsets[4] = {o4.x, o4.y, o4.z, o4.w};
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                const int j = 4 * q + h;
+                if constexpr (!kFast) {
+                  const int column = col0 + j;
+                  if (column >= rows || !channel_ok) continue;
+                  if (dump != nullptr) dump[static_cast<int64_t>(row0 + column) * n_total + n] = v[j];
+                }
+                float value = to_float(native_tag, v[j], scales[h], mine.scale_gate);
+                if constexpr (kDense) {
+                  value = __fadd_rn(value, mine.bias);
+                  if (bf16_out) {
+                    out_bf16[offsets[h]] = f32_to_bf16_bits(value);
+                  } else {
+                    out_f32[offsets[h]] = value;
+                  }
+                } else {
+                  out_f32[offsets[h]] = value;
+                }
+              }
+            }
+          };
+          dispatch(fast, body);
         }
       }
       ptx::tcgen05_fence_before();
@@ -491,9 +557,11 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
 
       // Publish the next unit's column metadata.  Nobody still reads that buffer: it belonged to the previous
       // unit, which every warp left before the barrier at the end of the previous iteration.
-      ColumnMeta* meta_next = &ctl->meta[(local + 1) & 1];
-      meta_next->scale[tid] = upcoming.column_scale;
-      meta_next->offset[tid] = upcoming.column_offset;
+      if (tid < 256) {
+        ColumnMeta* meta_next = &ctl->meta[(local + 1) & 1];
+        meta_next->scale[tid] = upcoming.column_scale;
+        meta_next->offset[tid] = upcoming.column_offset;
+      }
       epilogue_bar_sync();
       mine = upcoming;
       cur = next;
@@ -589,11 +657,15 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
 
 }  // namespace
 
-bool umma_pair_supported(bool gate_up, int n_out) { return !gate_up || n_out % 16 == 0; }
+// gate_up stages 16-channel groups; the epilogue addresses output rows with 32-bit element offsets.
+bool umma_pair_supported(bool gate_up, int n_out, int64_t output_rows) {
+  if (gate_up && n_out % 16 != 0) return false;
+  return output_rows * static_cast<int64_t>(n_out) < (static_cast<int64_t>(1) << 32);
+}
 
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream) {
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
-  if (!umma_pair_supported(gate_up, args.n_out)) return cudaErrorInvalidValue;
+  if (!umma_pair_supported(gate_up, args.n_out, args.total_rows)) return cudaErrorInvalidValue;
   if (args.dense_out != nullptr) {
     if (!int8 || gate_up) return cudaErrorInvalidValue;
     return launch_pair<true, false, true>(args, stream);

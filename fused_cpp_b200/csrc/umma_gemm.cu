@@ -412,7 +412,7 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& caller_args, bool in
   args.diag = diag ? atoi(diag) : 0;
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
   if (args.row_tile == kPairRowTile) {
-    if (umma_pair_supported(gate_up, args.n_out)) return launch_umma_pair_grouped_gemm(args, int8, gate_up, stream);
+    if (umma_pair_supported(gate_up, args.n_out, args.total_rows)) return launch_umma_pair_grouped_gemm(args, int8, gate_up, stream);
     args.row_tile = 256;  // same 256-row work items, one-SM kernel
   }
   if (args.dense_out != nullptr) {
