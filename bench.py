@@ -437,6 +437,8 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--no-points", action="store_true", help="skip the extra single-GPU points")
+    parser.add_argument("--ep-impl", default="peer", choices=["peer", "nccl"],
+                        help="N > 1: row exchange by the kernels over peer memory (default) or by NCCL all-to-all")
     parser.add_argument("--experts", type=int, default=E, help="shrink the layer (profiling captures only)")
     parser.add_argument("--skip-e2e", action="store_true", help="profiling captures only")
     parser.add_argument("--skip-cpu", action="store_true", help="profiling captures only")

@@ -36,6 +36,8 @@ EXPORTS = (
     "fmoe_stage_timer_read", "fmoe_route_build_noalloc", "fmoe_ep_dispatch_workspace_bytes", "fmoe_ep_dispatch_prepare",
     "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
     "fmoe_i8gemm_dynamic_scaled_mm_pair", "fmoe_probe_mma_rate",
+    "fmoe_ep_peer_create", "fmoe_ep_peer_handle", "fmoe_ep_peer_connect", "fmoe_ep_peer_destroy", "fmoe_ep_peer_slab_bytes",
+    "fmoe_ep_peer_route", "fmoe_ep_peer_dispatch", "fmoe_ep_peer_experts", "fmoe_ep_peer_combine", "fmoe_ep_peer_read_status",
 )
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
@@ -102,6 +104,18 @@ def load() -> ctypes.CDLL:
     lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm_pair.argtypes = [p, i64, i32, p, p, i32, p, p, p, i32, p, p, ctypes.c_size_t, p]
+    lib.fmoe_ep_peer_create.argtypes = [i32, i32, i64, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_void_p)]
+    lib.fmoe_ep_peer_handle.argtypes = [p, p]
+    lib.fmoe_ep_peer_connect.argtypes = [p, p]
+    lib.fmoe_ep_peer_destroy.argtypes = [p]
+    lib.fmoe_ep_peer_destroy.restype = None
+    lib.fmoe_ep_peer_slab_bytes.argtypes = [p]
+    lib.fmoe_ep_peer_slab_bytes.restype = ctypes.c_int64
+    lib.fmoe_ep_peer_route.argtypes = [p, p, i64, i32, i32, p, p]
+    lib.fmoe_ep_peer_dispatch.argtypes = [p, p, p, i64, i32, i32, p, p]
+    lib.fmoe_ep_peer_experts.argtypes = [p, p, p, p, p, ctypes.POINTER(Config), p]
+    lib.fmoe_ep_peer_combine.argtypes = [p, p, i64, i32, p, p]
+    lib.fmoe_ep_peer_read_status.argtypes = [p, p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
     _LIB = lib
     return lib
 
@@ -397,6 +411,64 @@ def ep_combine_finish(returned_rows, send_order, topk_weights, tokens: int, top_
     check(load().fmoe_ep_combine_finish(_ptr(returned_rows), _ptr(send_order), _ptr(topk_weights), tokens, top_k,
                                         hidden, 1 if tree_merge else 0, _ptr(route_out), _ptr(out), _stream()))
     return out
+
+
+class PeerContext:
+    """One rank's side of the peer-memory expert-parallel exchange (fmoe_ep_peer_*): owns the slab that the other
+    ranks write into.  The caller exchanges the 64-byte handles and provides the collectives between the stages."""
+
+    def __init__(self, world: int, rank: int, tokens_max: int, top_k: int, hidden: int, inter: int, local_experts: int, int8: bool):
+        self.world, self.rank, self.top_k, self.hidden, self.int8 = world, rank, top_k, hidden, int8
+        self.tokens_max = tokens_max
+        handle = ctypes.c_void_p()
+        check(load().fmoe_ep_peer_create(world, rank, tokens_max, top_k, hidden, inter, local_experts, 1 if int8 else 0,
+                                         ctypes.byref(handle)))
+        self.handle = handle
+
+    def ipc_handle(self) -> bytes:
+        buffer = ctypes.create_string_buffer(64)
+        check(load().fmoe_ep_peer_handle(self.handle, buffer))
+        return buffer.raw
+
+    def connect(self, handles: list) -> None:
+        blob = b"".join(bytes(h) for h in handles)
+        if len(blob) != 64 * self.world:
+            raise ValueError("expected one 64-byte handle per rank")
+        check(load().fmoe_ep_peer_connect(self.handle, ctypes.create_string_buffer(blob, len(blob))))
+
+    @property
+    def slab_bytes(self) -> int:
+        return int(load().fmoe_ep_peer_slab_bytes(self.handle))
+
+    def route(self, topk_ids, experts_global: int, shared_rank: int, dest_counts) -> None:
+        check(load().fmoe_ep_peer_route(self.handle, _ptr(topk_ids), topk_ids.shape[0], experts_global, shared_rank, _ptr(dest_counts),
+                                        _stream()))
+
+    def dispatch(self, x, topk_ids, experts_global: int, numerics: int, count_matrix) -> None:
+        check(load().fmoe_ep_peer_dispatch(self.handle, _ptr(x), _ptr(topk_ids), x.shape[0], experts_global, numerics, _ptr(count_matrix),
+                                           _stream()))
+
+    def experts(self, w13, s13, w2, s2, config: "Config") -> None:
+        check(load().fmoe_ep_peer_experts(self.handle, _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2), ctypes.byref(config), _stream()))
+
+    def combine(self, topk_weights, tokens: int, tree_merge: bool, out) -> None:
+        check(load().fmoe_ep_peer_combine(self.handle, _ptr(topk_weights), tokens, 1 if tree_merge else 0, _ptr(out), _stream()))
+
+    def read_status(self) -> tuple[int, int]:
+        first, second = ctypes.c_int32(0), ctypes.c_int32(0)
+        check(load().fmoe_ep_peer_read_status(self.handle, _stream(), ctypes.byref(first), ctypes.byref(second)))
+        return int(first.value), int(second.value)
+
+    def close(self) -> None:
+        if self.handle:
+            load().fmoe_ep_peer_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def probe_mma_rate(int8: bool, n: int = 256, iterations: int = 20000, *, nonzero: bool = False, commit_every: int = 0) -> float:

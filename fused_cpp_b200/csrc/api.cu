@@ -56,7 +56,10 @@ int check_shape(int64_t tokens, int top_k, int experts, int hidden, int inter) {
   return FMOE_OK;
 }
 
-int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, int inter, fmoe_workspace_layout* layout) {
+// with_route_out = false (peer-memory expert stage): the fp32 route rows live elsewhere and the region only
+// holds one 8-byte output address per row.
+int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, int inter, fmoe_workspace_layout* layout,
+                bool with_route_out = true) {
   const int status = check_shape(tokens, top_k, experts, hidden, inter);
   if (status != FMOE_OK) return status;
   if (layout == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "layout is null");
@@ -82,7 +85,7 @@ int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, i
   layout->y = take(rows * inter * 2);
   layout->yq = take(int8 ? rows * inter : 0);
   layout->y_scale = take(sizeof(float) * rows);
-  layout->route_out = take(sizeof(float) * rows * hidden);
+  layout->route_out = take(with_route_out ? sizeof(float) * rows * hidden : sizeof(uint64_t) * rows);
   layout->route_pos = take(sizeof(int) * rows);
   layout->total_bytes = offset;
   return FMOE_OK;
@@ -124,20 +127,34 @@ struct Forward {
   const float* rows_scale = nullptr;
   float* route_out_override = nullptr;
   bool rows_mode = false;
+  // Peer-memory expert stage: `tokens` is the capacity of the row list, *rows_valid_count (device) how many rows
+  // it holds, rows_source[row] = (source rank, flat route) and every result row is stored into the source rank's
+  // slab at peer_slabs[rank] + peer_route_out_offset.
+  const int* rows_valid_count = nullptr;
+  const void* rows_source = nullptr;
+  const uint64_t* peer_slabs = nullptr;
+  size_t peer_route_out_offset = 0;
 };
 
 int run_forward(const Forward& f, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes, void* stream_ptr) {
   int status = check_device();
   if (status != FMOE_OK) return status;
   fmoe_workspace_layout layout;
-  status = make_layout(f.int8, f.tokens, f.top_k, f.experts, f.hidden, f.inter, &layout);
+  const bool peer = f.peer_slabs != nullptr;
+  status = make_layout(f.int8, f.tokens, f.top_k, f.experts, f.hidden, f.inter, &layout, !peer);
   if (status != FMOE_OK) return status;
   if (f.tokens == 0) return FMOE_OK;
   if (f.x == nullptr || f.w13 == nullptr || f.w2 == nullptr || f.topk_ids == nullptr) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
   }
   if (!f.rows_mode && (f.topk_weights == nullptr || out == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
-  if (f.rows_mode && (f.route_out_override == nullptr || (f.int8 && f.rows_scale == nullptr) || f.top_k != 1)) {
+  if (peer && (!f.rows_mode || f.rows_valid_count == nullptr || f.rows_source == nullptr)) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "peer-memory mode needs expert rows with a device-side count and their sources");
+  }
+  if (peer && config != nullptr && config->gemm_impl == FMOE_GEMM_SIMT) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "peer-memory mode runs on the tensor-core GEMMs only");
+  }
+  if (f.rows_mode && ((f.route_out_override == nullptr && !peer) || (f.int8 && f.rows_scale == nullptr) || f.top_k != 1)) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "expert-rows mode needs route_out, row scales (int8) and one route per row");
   }
   if (f.int8 && (f.s13 == nullptr || f.s2 == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null scale pointer");
@@ -207,8 +224,15 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
   error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, item_rows_gu, item_rows_dn, max_items, status_block, counts, offsets,
                                    sorted_routes, row_expert, items_gu, items_dn, scratch, stream,
-                                   reinterpret_cast<int*>(base + layout.route_pos));
+                                   reinterpret_cast<int*>(base + layout.route_pos), f.rows_valid_count);
   if (error != cudaSuccess) return cuda_fail(error, "route build");
+  uint64_t* row_out_ptrs = nullptr;
+  if (peer) {
+    row_out_ptrs = reinterpret_cast<uint64_t*>(base + layout.route_out);
+    error = fmoe::launch_peer_row_ptrs(sorted_routes, offsets + f.experts, routes, f.rows_source, f.peer_slabs, f.peer_route_out_offset,
+                                       f.hidden, row_out_ptrs, stream);
+    if (error != cudaSuccess) return cuda_fail(error, "peer output addresses");
+  }
   mark(FMOE_STAGE_ROUTE + 1);
   const int* valid_rows = offsets + f.experts;
 
@@ -274,6 +298,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   dn.n_out = f.hidden;
   dn.y = nullptr;
   dn.route_out = route_out;
+  dn.row_out_ptrs = row_out_ptrs;
   dn.dump_acc = cfg.dump_acc2;
   dn.row_tile = tile_dn;
   error = umma ? fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
@@ -679,6 +704,252 @@ int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mod
   const double ops = 2.0 * 128.0 * n * elements_k * static_cast<double>(iterations) * sms;
   *tera_ops_per_s = static_cast<float>(ops / (best_ms * 1e-3) / 1e12);
   return FMOE_OK;
+}
+
+}  // extern "C"
+
+/* ---- expert parallelism over peer memory ---------------------------------------------------------- */
+
+struct fmoe_ep_peer_context {
+  int world = 0, rank = 0, top_k = 0, hidden = 0, inter = 0, local_experts = 0, int8 = 0;
+  int64_t tokens_max = 0, capacity = 0;
+  fmoe::PeerSlabLayout slab{};
+  char* slab_base = nullptr;          // this rank's slab (cudaMalloc, exported by IPC handle)
+  std::vector<void*> opened;          // peers' slabs as mapped here (null for this rank)
+  uint64_t* peer_slabs_dev = nullptr; // [world] device table of slab addresses
+  bool connected = false;
+  // Local scratch of the dispatch and of the expert stage.
+  char* dispatch_ws = nullptr;
+  size_t dispatch_ws_bytes = 0;
+  char* expert_ws = nullptr;
+  size_t expert_ws_bytes = 0;
+  int* base_at_dest = nullptr;        // [world]
+  int* received = nullptr;            // [1]
+};
+
+namespace {
+
+struct DispatchScratch {
+  int* status;
+  int64_t* dest;
+  int* offsets;
+  int* row_rank;
+  int* send_order;
+  int* route_pos;
+  int* scratch;
+};
+
+size_t dispatch_scratch_bytes(int64_t routes, int world) {
+  const size_t r = static_cast<size_t>(routes > 0 ? routes : 1);
+  return align_up(sizeof(int) * fmoe::kStatusWords, 256) + align_up(sizeof(int64_t) * r, 256) + align_up(sizeof(int) * (world + 1), 256) +
+         3 * align_up(sizeof(int) * r, 256) + align_up(fmoe::route_scratch_bytes(routes, world), 256);
+}
+
+DispatchScratch carve_dispatch(char* base, int64_t routes, int world) {
+  const size_t r = static_cast<size_t>(routes > 0 ? routes : 1);
+  char* cursor = base;
+  auto take = [&cursor](size_t bytes) {
+    char* begin = cursor;
+    cursor += align_up(bytes, 256);
+    return begin;
+  };
+  DispatchScratch d;
+  d.status = reinterpret_cast<int*>(take(sizeof(int) * fmoe::kStatusWords));
+  d.dest = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * r));
+  d.offsets = reinterpret_cast<int*>(take(sizeof(int) * (world + 1)));
+  d.row_rank = reinterpret_cast<int*>(take(sizeof(int) * r));
+  d.send_order = reinterpret_cast<int*>(take(sizeof(int) * r));
+  d.route_pos = reinterpret_cast<int*>(take(sizeof(int) * r));
+  d.scratch = reinterpret_cast<int*>(take(fmoe::route_scratch_bytes(routes, world)));
+  return d;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t top_k, int32_t hidden, int32_t inter,
+                        int32_t local_experts, int32_t int8, fmoe_ep_peer_context** out) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (out == nullptr || world <= 0 || world > 64 || rank < 0 || rank >= world || tokens_max <= 0 || top_k <= 0 || top_k > 32 ||
+      local_experts <= 0) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid peer context shape");
+  }
+  status = check_shape(tokens_max, top_k, local_experts, hidden, inter);
+  if (status != FMOE_OK) return status;
+  fmoe_ep_peer_context* ctx = new fmoe_ep_peer_context();
+  ctx->world = world;
+  ctx->rank = rank;
+  ctx->top_k = top_k;
+  ctx->hidden = hidden;
+  ctx->inter = inter;
+  ctx->local_experts = local_experts;
+  ctx->int8 = int8 ? 1 : 0;
+  ctx->tokens_max = tokens_max;
+  // Worst case: every route of every rank lands here.
+  ctx->capacity = static_cast<int64_t>(world) * tokens_max * top_k;
+  const size_t capacity = static_cast<size_t>(ctx->capacity);
+  size_t offset = 0;
+  auto take = [&offset](size_t bytes) {
+    const size_t begin = offset;
+    offset = align_up(offset + bytes, 256);
+    return begin;
+  };
+  ctx->slab.rows = take(capacity * hidden * (int8 ? 1 : 2));
+  ctx->slab.expert = take(capacity * sizeof(int64_t));
+  ctx->slab.scale = take(capacity * sizeof(float));
+  ctx->slab.source = take(capacity * 2 * sizeof(int));
+  ctx->slab.route_out = take(static_cast<size_t>(tokens_max) * top_k * hidden * sizeof(float));
+  ctx->slab.total = offset;
+  fmoe_workspace_layout layout;
+  status = make_layout(int8 != 0, ctx->capacity, 1, local_experts, hidden, inter, &layout, false);
+  if (status != FMOE_OK) {
+    delete ctx;
+    return status;
+  }
+  ctx->expert_ws_bytes = layout.total_bytes;
+  ctx->dispatch_ws_bytes = dispatch_scratch_bytes(tokens_max * top_k, world);
+  cudaError_t error = cudaMalloc(&ctx->slab_base, ctx->slab.total);
+  if (error == cudaSuccess) error = cudaMalloc(&ctx->expert_ws, ctx->expert_ws_bytes);
+  if (error == cudaSuccess) error = cudaMalloc(&ctx->dispatch_ws, ctx->dispatch_ws_bytes);
+  if (error == cudaSuccess) error = cudaMalloc(&ctx->peer_slabs_dev, sizeof(uint64_t) * world);
+  if (error == cudaSuccess) error = cudaMalloc(&ctx->base_at_dest, sizeof(int) * (world + 1));
+  if (error != cudaSuccess) {
+    fmoe_ep_peer_destroy(ctx);
+    return cuda_fail(error, "peer context allocation");
+  }
+  ctx->received = ctx->base_at_dest + world;
+  ctx->opened.assign(world, nullptr);
+  *out = ctx;
+  return FMOE_OK;
+}
+
+int fmoe_ep_peer_handle(fmoe_ep_peer_context* ctx, void* handle64) {
+  if (ctx == nullptr || handle64 == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t handle;
+  const cudaError_t error = cudaIpcGetMemHandle(&handle, ctx->slab_base);
+  if (error != cudaSuccess) return cuda_fail(error, "cudaIpcGetMemHandle");
+  memcpy(handle64, &handle, sizeof(handle));
+  return FMOE_OK;
+}
+
+int fmoe_ep_peer_connect(fmoe_ep_peer_context* ctx, const void* handles) {
+  if (ctx == nullptr || (handles == nullptr && ctx->world > 1)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  if (ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context is already connected");
+  std::vector<uint64_t> table(ctx->world, 0);
+  for (int r = 0; r < ctx->world; ++r) {
+    if (r == ctx->rank) {
+      table[r] = reinterpret_cast<uint64_t>(ctx->slab_base);
+      continue;
+    }
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, static_cast<const char*>(handles) + static_cast<size_t>(r) * sizeof(handle), sizeof(handle));
+    void* mapped = nullptr;
+    const cudaError_t error = cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess);
+    if (error != cudaSuccess) return cuda_fail(error, "cudaIpcOpenMemHandle");
+    ctx->opened[r] = mapped;
+    table[r] = reinterpret_cast<uint64_t>(mapped);
+  }
+  const cudaError_t error = cudaMemcpy(ctx->peer_slabs_dev, table.data(), sizeof(uint64_t) * ctx->world, cudaMemcpyHostToDevice);
+  if (error != cudaSuccess) return cuda_fail(error, "peer table upload");
+  ctx->connected = true;
+  return FMOE_OK;
+}
+
+void fmoe_ep_peer_destroy(fmoe_ep_peer_context* ctx) {
+  if (ctx == nullptr) return;
+  for (void* mapped : ctx->opened) {
+    if (mapped != nullptr) cudaIpcCloseMemHandle(mapped);
+  }
+  if (ctx->slab_base) cudaFree(ctx->slab_base);
+  if (ctx->expert_ws) cudaFree(ctx->expert_ws);
+  if (ctx->dispatch_ws) cudaFree(ctx->dispatch_ws);
+  if (ctx->peer_slabs_dev) cudaFree(ctx->peer_slabs_dev);
+  if (ctx->base_at_dest) cudaFree(ctx->base_at_dest);
+  delete ctx;
+}
+
+int64_t fmoe_ep_peer_slab_bytes(const fmoe_ep_peer_context* ctx) { return ctx ? static_cast<int64_t>(ctx->slab.total) : 0; }
+
+int fmoe_ep_peer_route(fmoe_ep_peer_context* ctx, const int64_t* topk_ids, int64_t tokens, int32_t experts_global, int32_t shared_rank,
+                       int32_t* dest_counts, void* stream_ptr) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
+  if (tokens < 0 || tokens > ctx->tokens_max || experts_global <= 0 || experts_global % ctx->world != 0 || shared_rank >= ctx->world ||
+      dest_counts == nullptr || (tokens > 0 && topk_ids == nullptr)) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid peer route arguments (tokens within the context's maximum, experts divisible by the ranks)");
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const int64_t routes = tokens * ctx->top_k;
+  const DispatchScratch d = carve_dispatch(ctx->dispatch_ws, ctx->tokens_max * ctx->top_k, ctx->world);
+  cudaError_t error = cudaMemsetAsync(d.status, 0, sizeof(int) * fmoe::kStatusWords, stream);
+  if (error == cudaSuccess && routes == 0) error = cudaMemsetAsync(dest_counts, 0, sizeof(int) * ctx->world, stream);
+  if (error == cudaSuccess && routes > 0) {
+    error = fmoe::launch_dest_ranks(topk_ids, routes, experts_global, experts_global / ctx->world, shared_rank, d.dest, stream);
+  }
+  if (error == cudaSuccess && routes > 0) {
+    error = fmoe::launch_route_build(d.dest, routes, ctx->world, 16, 16, 0, d.status, dest_counts, d.offsets, d.send_order, d.row_rank,
+                                     nullptr, nullptr, d.scratch, stream, d.route_pos);
+  }
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer route");
+}
+
+int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* ctx, const void* x, const int64_t* topk_ids, int64_t tokens, int32_t experts_global,
+                          int32_t numerics, const int32_t* count_matrix, void* stream_ptr) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
+  if (tokens < 0 || tokens > ctx->tokens_max || count_matrix == nullptr || (tokens > 0 && (x == nullptr || topk_ids == nullptr))) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid peer dispatch arguments");
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const DispatchScratch d = carve_dispatch(ctx->dispatch_ws, ctx->tokens_max * ctx->top_k, ctx->world);
+  cudaError_t error = fmoe::launch_peer_offsets(count_matrix, ctx->world, ctx->rank, ctx->base_at_dest, ctx->received, stream);
+  if (error == cudaSuccess) {
+    error = fmoe::launch_peer_dispatch(ctx->int8 != 0, static_cast<const uint16_t*>(x), topk_ids, tokens, ctx->hidden, ctx->top_k, d.dest,
+                                       d.route_pos, d.offsets, ctx->base_at_dest, ctx->slab, ctx->peer_slabs_dev, ctx->rank, experts_global,
+                                       experts_global / ctx->world, numerics, stream);
+  }
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer dispatch");
+}
+
+int fmoe_ep_peer_experts(fmoe_ep_peer_context* ctx, const void* w13, const float* s13, const void* w2, const float* s2,
+                         const fmoe_config* config, void* stream) {
+  if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
+  Forward f{ctx->int8 != 0, ctx->slab_base + ctx->slab.rows, w13, s13, w2, s2, nullptr,
+            reinterpret_cast<const int64_t*>(ctx->slab_base + ctx->slab.expert), ctx->capacity, 1, ctx->local_experts, ctx->hidden, ctx->inter};
+  f.rows_scale = reinterpret_cast<const float*>(ctx->slab_base + ctx->slab.scale);
+  f.rows_mode = true;
+  f.rows_valid_count = ctx->received;
+  f.rows_source = ctx->slab_base + ctx->slab.source;
+  f.peer_slabs = ctx->peer_slabs_dev;
+  f.peer_route_out_offset = ctx->slab.route_out;
+  return run_forward(f, config, nullptr, ctx->expert_ws, ctx->expert_ws_bytes, stream);
+}
+
+int fmoe_ep_peer_combine(fmoe_ep_peer_context* ctx, const float* topk_weights, int64_t tokens, int32_t tree_merge, void* out,
+                         void* stream_ptr) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
+  if (tokens < 0 || tokens > ctx->tokens_max) return fail(FMOE_ERR_INVALID_ARGUMENT, "tokens exceed the context's maximum");
+  if (tokens == 0) return FMOE_OK;
+  if (topk_weights == nullptr || out == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  const cudaError_t error = fmoe::launch_merge(reinterpret_cast<const float*>(ctx->slab_base + ctx->slab.route_out), topk_weights, tokens,
+                                               ctx->top_k, ctx->hidden, tree_merge, static_cast<uint16_t*>(out),
+                                               static_cast<cudaStream_t>(stream_ptr));
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer combine");
+}
+
+int fmoe_ep_peer_read_status(fmoe_ep_peer_context* ctx, void* stream, int32_t* dispatch_error, int32_t* expert_error) {
+  if (ctx == nullptr || dispatch_error == nullptr || expert_error == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  int32_t detail = 0;
+  int status = fmoe_read_status(ctx->dispatch_ws, stream, dispatch_error, &detail);
+  if (status != FMOE_OK) return status;
+  return fmoe_read_status(ctx->expert_ws, stream, expert_error, &detail);
 }
 
 }  // extern "C"

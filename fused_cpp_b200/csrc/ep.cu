@@ -40,7 +40,169 @@ __global__ void scatter_rows_f32_kernel(const float* __restrict__ rows, const in
   for (int v = threadIdx.x; v < (hidden >> 2); v += blockDim.x) dst[v] = src[v];
 }
 
+// ---- peer-memory path: rows go straight into the expert rank's receive slab, results straight back ----
+
+// From the gathered count matrix C[source][destination] (world x world): where this rank's rows start in every
+// destination's slab (the rows of lower source ranks come first) and how many rows this rank receives.
+__global__ void peer_offsets_kernel(const int* __restrict__ count_matrix, int world, int rank, int* __restrict__ base_at_dest,
+                                    int* __restrict__ received) {
+  const int d = threadIdx.x;
+  if (d < world) {
+    int base = 0;
+    for (int s = 0; s < rank; ++s) base += count_matrix[s * world + d];
+    base_at_dest[d] = base;
+  }
+  if (threadIdx.x == 0) {
+    int total = 0;
+    for (int s = 0; s < world; ++s) total += count_matrix[s * world + rank];
+    *received = total;
+  }
+}
+
+__device__ __forceinline__ void unpack8_bf16(const uint4& v, float* out) {
+  const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(words[i] << 16);
+    out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+  }
+}
+
+// One CTA per token.  The token row is quantised once (int8) or taken as it is (bf16) and stored, with plain
+// 16-byte stores, into the receive slab of the rank that owns each of its routes' experts, together with the
+// route's scale, local expert id and return address (source rank, flat route).  Same bits as
+// quantize_tokens_scatter / gather_rows on one GPU.
+template <bool kInt8>
+__global__ void __launch_bounds__(256)
+peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__ topk_ids, int cols, int top_k,
+                     const int64_t* __restrict__ dest, const int* __restrict__ route_pos, const int* __restrict__ dest_offsets,
+                     const int* __restrict__ base_at_dest, PeerSlabLayout slab, const uint64_t* __restrict__ peer_slabs, int rank,
+                     int experts_global, int experts_per_rank, int numerics) {
+  __shared__ float reduce[32];
+  __shared__ int64_t slot_row[32];    // row index in the destination slab, -1 = dropped
+  __shared__ uint64_t slot_slab[32];  // base address of the destination slab
+  const int64_t token = blockIdx.x;
+  if (threadIdx.x < top_k) {
+    const int64_t route = token * top_k + threadIdx.x;
+    const int64_t d = dest[route];
+    const int position = route_pos[route];
+    int64_t row = -1;
+    uint64_t base = 0;
+    if (d >= 0 && position >= 0) {
+      row = base_at_dest[d] + (position - dest_offsets[d]);
+      base = peer_slabs[d];
+    }
+    slot_row[threadIdx.x] = row;
+    slot_slab[threadIdx.x] = base;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + token * cols);
+  const int vec16 = cols >> 4;
+  float scale = 1.0f;
+  float operand = 1.0f;
+  if constexpr (kInt8) {
+    float local = 0.0f;
+    for (int v = threadIdx.x; v < vec16; v += blockDim.x) {
+      float values[16];
+      unpack8_bf16(src[2 * v], values);
+      unpack8_bf16(src[2 * v + 1], values + 8);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) local = fmaxf(local, fabsf(values[i]));
+    }
+    local = warp_max(local);
+    if ((threadIdx.x & 31) == 0) reduce[threadIdx.x >> 5] = local;
+    __syncthreads();
+    float amax = (threadIdx.x & 31) < (blockDim.x >> 5) ? reduce[threadIdx.x & 31] : 0.0f;
+    amax = warp_max(amax);
+    scale = row_scale_from_amax(amax, numerics);
+    operand = quantize_operand(scale, numerics);
+  } else {
+    __syncthreads();
+  }
+  if (threadIdx.x < top_k && slot_row[threadIdx.x] >= 0) {
+    const int64_t route = token * top_k + threadIdx.x;
+    const int64_t row = slot_row[threadIdx.x];
+    const uint64_t base = slot_slab[threadIdx.x];
+    const int64_t id = topk_ids[route];
+    reinterpret_cast<int64_t*>(base + slab.expert)[row] = id >= experts_global ? experts_per_rank : id % experts_per_rank;
+    if (kInt8) reinterpret_cast<float*>(base + slab.scale)[row] = scale;
+    reinterpret_cast<int2*>(base + slab.source)[row] = make_int2(rank, static_cast<int>(route));
+  }
+  const int64_t row_bytes = static_cast<int64_t>(cols) * (kInt8 ? 1 : 2);
+  for (int v = threadIdx.x; v < vec16; v += blockDim.x) {
+    const uint4 a = src[2 * v];
+    const uint4 b = src[2 * v + 1];
+    uint4 packed = make_uint4(0, 0, 0, 0);
+    if constexpr (kInt8) {
+      float values[16];
+      unpack8_bf16(a, values);
+      unpack8_bf16(b, values + 8);
+      uint32_t words[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) word |= (static_cast<uint32_t>(quantize_value(values[4 * w + i], operand, numerics)) & 0xffu) << (8 * i);
+        words[w] = word;
+      }
+      packed = make_uint4(words[0], words[1], words[2], words[3]);
+    }
+    for (int slot = 0; slot < top_k; ++slot) {
+      const int64_t row = slot_row[slot];
+      if (row < 0) continue;
+      uint8_t* out = reinterpret_cast<uint8_t*>(slot_slab[slot] + slab.rows) + row * row_bytes;
+      if constexpr (kInt8) {
+        reinterpret_cast<uint4*>(out)[v] = packed;
+      } else {
+        reinterpret_cast<uint4*>(out)[2 * v] = a;
+        reinterpret_cast<uint4*>(out)[2 * v + 1] = b;
+      }
+    }
+  }
+}
+
+// After the expert rank's route build: the byte address of the fp32 result row of every sorted row, in the
+// memory of the rank the route came from.
+__global__ void peer_row_ptrs_kernel(const int* __restrict__ sorted_routes, const int* __restrict__ valid_rows, int64_t capacity,
+                                     const int2* __restrict__ source, const uint64_t* __restrict__ peer_slabs, size_t route_out_offset,
+                                     int hidden, uint64_t* __restrict__ row_out_ptrs) {
+  const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (p >= capacity || p >= *valid_rows) return;
+  const int2 from = source[sorted_routes[p]];
+  row_out_ptrs[p] = peer_slabs[from.x] + route_out_offset + static_cast<uint64_t>(from.y) * hidden * sizeof(float);
+}
+
 }  // namespace
+
+cudaError_t launch_peer_offsets(const int* count_matrix, int world, int rank, int* base_at_dest, int* received, cudaStream_t stream) {
+  peer_offsets_kernel<<<1, world < 32 ? 32 : ((world + 31) / 32) * 32, 0, stream>>>(count_matrix, world, rank, base_at_dest, received);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
+                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, const int* base_at_dest,
+                                 const PeerSlabLayout& slab, const uint64_t* peer_slabs, int rank, int experts_global,
+                                 int experts_per_rank, int numerics, cudaStream_t stream) {
+  if (tokens <= 0) return cudaSuccess;
+  if (int8) {
+    peer_dispatch_kernel<true><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, dest, route_pos, dest_offsets,
+                                                                                  base_at_dest, slab, peer_slabs, rank, experts_global,
+                                                                                  experts_per_rank, numerics);
+  } else {
+    peer_dispatch_kernel<false><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, dest, route_pos, dest_offsets,
+                                                                                   base_at_dest, slab, peer_slabs, rank, experts_global,
+                                                                                   experts_per_rank, numerics);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows, int64_t capacity, const void* source,
+                                 const uint64_t* peer_slabs, size_t route_out_offset, int hidden, uint64_t* row_out_ptrs,
+                                 cudaStream_t stream) {
+  if (capacity <= 0) return cudaSuccess;
+  peer_row_ptrs_kernel<<<static_cast<unsigned>((capacity + 255) / 256), 256, 0, stream>>>(
+      sorted_routes, valid_rows, capacity, static_cast<const int2*>(source), peer_slabs, route_out_offset, hidden, row_out_ptrs);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_dest_ranks(const int64_t* ids, int64_t n, int experts_global, int experts_per_rank, int shared_rank,
                               int64_t* dest, cudaStream_t stream) {

@@ -15,10 +15,11 @@ int report_error(int code, const char* text);
 
 // ---- route.cu
 size_t route_scratch_bytes(int64_t routes, int experts);
+// valid_count (nullable, device): entries at or beyond *valid_count are padding and skipped silently.
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
                                int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream,
-                               int* route_pos = nullptr);
+                               int* route_pos = nullptr, const int* valid_count = nullptr);
 
 // Work items of a dense [rows, K] x [N, K]^T product: one "expert", consecutive row tiles.
 cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream);
@@ -58,6 +59,25 @@ cudaError_t launch_local_experts(const int64_t* ids, const int* order, int64_t n
 cudaError_t launch_scatter_rows_f32(const float* rows, const int* order, int64_t n, const int* valid_rows, int hidden,
                                     float* route_out, cudaStream_t stream);
 
+// Peer-memory path.  Every rank owns one slab with the same layout (byte offsets below); peer_slabs[r] is the
+// address of rank r's slab as mapped into this process.
+struct PeerSlabLayout {
+  size_t rows;       // [capacity, H] int8 or bf16: received rows, grouped by source rank
+  size_t expert;     // [capacity] int64: local expert id of each received row
+  size_t scale;      // [capacity] fp32: activation scale of each received row (int8)
+  size_t source;     // [capacity] int2: (source rank, flat route id at the source)
+  size_t route_out;  // [local routes, H] fp32: result rows of this rank's own routes, written by the expert ranks
+  size_t total;
+};
+cudaError_t launch_peer_offsets(const int* count_matrix, int world, int rank, int* base_at_dest, int* received, cudaStream_t stream);
+cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
+                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, const int* base_at_dest,
+                                 const PeerSlabLayout& slab, const uint64_t* peer_slabs, int rank, int experts_global,
+                                 int experts_per_rank, int numerics, cudaStream_t stream);
+cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows, int64_t capacity, const void* source,
+                                 const uint64_t* peer_slabs, size_t route_out_offset, int hidden, uint64_t* row_out_ptrs,
+                                 cudaStream_t stream);
+
 // ---- merge.cu
 // W8A8: out[t] = bf16( fma chain over slots of route_out[t*K+slot] * w[t,slot] ).
 // BF16: pairwise tree for K in {2,4,6,8}, chain otherwise.
@@ -90,6 +110,9 @@ struct GroupedGemmArgs {
   void* dense_out;
   int dense_out_bf16;
   const float* bias;
+  // Down GEMM, optional: byte address of the fp32 output row of every sorted row.  Overrides route_out +
+  // sorted_routes; the rows may lie in another GPU's memory (expert-parallel return path, plain stores).
+  const uint64_t* row_out_ptrs;
   // Performance diagnosis only (environment FUSED_CPP_MOE_GEMM_DIAG, 0 in production; results are meaningless otherwise):
   // bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.
   int diag;

@@ -23,8 +23,8 @@ namespace {
 constexpr int kWarpsPerBlock = 4;
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int experts, int units, int* unit_hist,
-                  int* status) {
+route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int experts, int units,
+                  int* unit_hist, int* status) {
   extern __shared__ int smem_hist[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -33,6 +33,8 @@ route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int expe
   for (int e = lane; e < experts; e += 32) hist[e] = 0;
   __syncwarp();
   if (unit >= units) return;
+  // With a device-side count, entries at or beyond it are padding of a fixed-capacity list: skipped, not an error.
+  if (valid_count != nullptr) routes = min(routes, static_cast<int64_t>(*valid_count));
   const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
   for (int round = 0; round < kUnitRoutes / 32; ++round) {
     const int64_t route = begin + round * 32 + lane;
@@ -70,21 +72,28 @@ __device__ int warp_exclusive_scan(const int* values, int* out, int n, int lane)
 __global__ void __launch_bounds__(1024)
 route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offsets, int tile_a, int tile_b,
                   int* items_a, int* items_b, int max_items, int* scan_tmp, int* status) {
-  // Pass 1: per expert, running sum over units (unit_hist becomes the unit's cursor relative to the
-  // expert's first row) and the expert total.
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-    int running = 0;
-    for (int u = 0; u < units; ++u) {
-      const int64_t index = static_cast<int64_t>(u) * experts + e;
-      const int value = unit_hist[index];
-      unit_hist[index] = running;
-      running += value;
-    }
-    counts[e] = running;
-  }
-  __syncthreads();
+  // Pass 1: per expert, exclusive scan over units (unit_hist becomes the unit's cursor relative to the
+  // expert's first row) and the expert total.  One warp per expert, 32 units per step.
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  for (int e = warp; e < experts; e += blockDim.x >> 5) {
+    int carry = 0;
+    for (int base = 0; base < units; base += 32) {
+      const int u = base + lane;
+      const int64_t index = static_cast<int64_t>(u) * experts + e;
+      const int value = u < units ? unit_hist[index] : 0;
+      int inclusive = value;
+#pragma unroll
+      for (int offset = 1; offset < 32; offset <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+        if (lane >= offset) inclusive += other;
+      }
+      if (u < units) unit_hist[index] = carry + inclusive - value;
+      carry += __shfl_sync(0xffffffffu, inclusive, 31);
+    }
+    if (lane == 0) counts[e] = carry;
+  }
+  __syncthreads();
   if (warp == 0) {
     const int total = warp_exclusive_scan(counts, offsets, experts, lane);
     if (lane == 0) offsets[experts] = total;
@@ -125,7 +134,7 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int experts, int units,
+route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int experts, int units,
                      const int* __restrict__ unit_hist, const int* __restrict__ offsets, int* sorted_routes,
                      int* row_expert, int* route_pos) {
   extern __shared__ int smem_cursor[];
@@ -136,6 +145,8 @@ route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int e
   int* cursor = smem_cursor + warp * experts;
   for (int e = lane; e < experts; e += 32) cursor[e] = offsets[e] + unit_hist[static_cast<int64_t>(unit) * experts + e];
   __syncwarp();
+  const int64_t listed = routes;
+  if (valid_count != nullptr) routes = min(routes, static_cast<int64_t>(*valid_count));
   const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
   const unsigned lanes_below = (1u << lane) - 1u;
   for (int round = 0; round < kUnitRoutes / 32; ++round) {
@@ -156,7 +167,7 @@ route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int e
       row_expert[position] = id;
     }
     // Inverse permutation: sorted position of every flat route (-1 for a dropped route).
-    if (route_pos != nullptr && route < routes) route_pos[route] = position;
+    if (route_pos != nullptr && route < listed) route_pos[route] = position;
   }
 }
 
@@ -169,19 +180,20 @@ size_t route_scratch_bytes(int64_t routes, int experts) {
 
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
-                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos) {
+                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos,
+                               const int* valid_count) {
   const int units = static_cast<int>((routes + kUnitRoutes - 1) / kUnitRoutes);
   int* unit_hist = scratch;
   int* scan_tmp = scratch + static_cast<int64_t>(units > 0 ? units : 1) * experts;
   const size_t smem = static_cast<size_t>(kWarpsPerBlock) * experts * sizeof(int);
   const int blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (blocks > 0) {
-    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist, status);
+    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, experts, units, unit_hist, status);
   }
   route_scan_kernel<<<1, 1024, 0, stream>>>(experts, units, unit_hist, counts, offsets, tile_a, tile_b, items_a, items_b,
                                             max_items, scan_tmp, status);
   if (blocks > 0) {
-    route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist,
+    route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, experts, units, unit_hist,
                                                                         offsets, sorted_routes, row_expert, route_pos);
   }
   return cudaGetLastError();

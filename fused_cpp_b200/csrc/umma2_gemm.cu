@@ -52,7 +52,7 @@ constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes 
 // Per-column values of a work unit, staged one unit ahead so that the element loop reads shared memory.
 struct ColumnMeta {
   float scale[256];      // activation scale of the row (int8)
-  uint32_t offset[256];  // element offset of the output row: target row * n_out
+  uint64_t rowptr[256];  // byte address of the output row (down / dense; may be peer memory)
 };
 
 struct PairControl {
@@ -389,17 +389,22 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
     // are fetched while the previous unit is being finished.
     struct ThreadUnit {
       float column_scale;      // of column `tid`
-      uint32_t column_offset;  // of column `tid`: output row * n_out (the launcher checks that it fits 32 bits)
+      uint64_t column_rowptr;  // of column `tid`: byte address of its output row (down / dense)
       float scale_gate, scale_up, bias;
     };
     auto fetch = [&](const UnitInfo& info, bool valid) {
-      ThreadUnit t = {0.0f, 0u, 1.0f, 1.0f, 0.0f};
+      ThreadUnit t = {0.0f, 0ull, 1.0f, 1.0f, 0.0f};
       if (!valid) return t;
       if (tid < info.rows) {
         const int row = info.row0 + tid;
         if (kInt8) t.column_scale = args.a_scale[row];
-        const int target = (kGateUp || kDense) ? row : args.sorted_routes[row];
-        t.column_offset = static_cast<uint32_t>(target) * static_cast<uint32_t>(n_out);
+        if constexpr (kDense) {
+          t.column_rowptr = reinterpret_cast<uint64_t>(args.dense_out) + static_cast<uint64_t>(row) * n_out * (args.dense_out_bf16 ? 2 : 4);
+        } else if constexpr (!kGateUp) {
+          t.column_rowptr = args.row_out_ptrs != nullptr
+                                ? args.row_out_ptrs[row]
+                                : reinterpret_cast<uint64_t>(args.route_out + static_cast<int64_t>(args.sorted_routes[row]) * n_out);
+        }
       }
       const int n = info.block * kChannelsPerUnit + channel_in_unit;
       if (n < n_out) {
@@ -448,7 +453,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
     ThreadUnit mine = fetch(cur, first_unit < units);
     if (tid < 256) {
       ctl->meta[0].scale[tid] = mine.column_scale;
-      ctl->meta[0].offset[tid] = mine.column_offset;
+      ctl->meta[0].rowptr[tid] = mine.column_rowptr;
     }
     epilogue_bar_sync();
 
@@ -514,18 +519,18 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
           dispatch(fast, body);
         } else {
           const float4* scale4 = reinterpret_cast<const float4*>(meta->scale + col0);
-          const uint4* offset4 = reinterpret_cast<const uint4*>(meta->offset + col0);
-          float* const out_f32 = (kDense ? static_cast<float*>(args.dense_out) : args.route_out) + n;
-          uint16_t* const out_bf16 = static_cast<uint16_t*>(args.dense_out) + n;
+          const ulonglong2* rowptr2 = reinterpret_cast<const ulonglong2*>(meta->rowptr + col0);
           const bool bf16_out = kDense && args.dense_out_bf16;
+          const uint64_t n_bytes = static_cast<uint64_t>(n) * (bf16_out ? 2 : 4);
           auto body = [&](auto fast_tag, auto native_tag) {
             constexpr bool kFast = decltype(fast_tag)::value;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const float4 s4 = scale4[q];
-              const uint4 o4 = offset4[q];
+              const ulonglong2 p01 = rowptr2[2 * q];
+              const ulonglong2 p23 = rowptr2[2 * q + 1];
               const float scales[4] = {s4.x, s4.y, s4.z, s4.w};
-              const uint32_t offsets[4] = {o4.x, o4.y, o4.z, o4.w};
+              const uint64_t rowptrs[4] = {p01.x, p01.y, p23.x, p23.y};
 #pragma unroll
               for (int h = 0; h < 4; ++h) {
                 const int j = 4 * q + h;
@@ -538,12 +543,12 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
                 if constexpr (kDense) {
                   value = __fadd_rn(value, mine.bias);
                   if (bf16_out) {
-                    out_bf16[offsets[h]] = f32_to_bf16_bits(value);
+                    *reinterpret_cast<uint16_t*>(rowptrs[h] + n_bytes) = f32_to_bf16_bits(value);
                   } else {
-                    out_f32[offsets[h]] = value;
+                    *reinterpret_cast<float*>(rowptrs[h] + n_bytes) = value;
                   }
                 } else {
-                  out_f32[offsets[h]] = value;
+                  *reinterpret_cast<float*>(rowptrs[h] + n_bytes) = value;
                 }
               }
             }
@@ -560,7 +565,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       if (tid < 256) {
         ColumnMeta* meta_next = &ctl->meta[(local + 1) & 1];
         meta_next->scale[tid] = upcoming.column_scale;
-        meta_next->offset[tid] = upcoming.column_offset;
+        meta_next->rowptr[tid] = upcoming.column_rowptr;
       }
       epilogue_bar_sync();
       mine = upcoming;
@@ -657,10 +662,10 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
 
 }  // namespace
 
-// gate_up stages 16-channel groups; the epilogue addresses output rows with 32-bit element offsets.
+// gate_up stages 16-channel groups through its 5-D tensor map.
 bool umma_pair_supported(bool gate_up, int n_out, int64_t output_rows) {
-  if (gate_up && n_out % 16 != 0) return false;
-  return output_rows * static_cast<int64_t>(n_out) < (static_cast<int64_t>(1) << 32);
+  (void)output_rows;
+  return !gate_up || n_out % 16 == 0;
 }
 
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream) {

@@ -56,7 +56,7 @@ struct TileConfig {
   static constexpr int kTmemColumnsRaw = kAccBuffers * kAccColumns;
   static constexpr int kTmemColumns = kTmemColumnsRaw <= 32 ? 32 : kTmemColumnsRaw <= 64 ? 64 : kTmemColumnsRaw <= 128 ? 128
                                       : kTmemColumnsRaw <= 256 ? 256 : 512;
-  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes + 4608 /*control block*/;
+  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes + 7168 /*control block*/;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
   static_assert(kAccColumns <= 512, "accumulator does not fit tensor memory");
 };
@@ -64,8 +64,8 @@ struct TileConfig {
 // Per-column (= per token row) values of the current work unit, staged once by the epilogue warps so that the
 // element loop reads shared memory instead of issuing a dependent global load per element.
 struct ColumnMeta {
-  float scale[256];  // activation scale of the row (int8)
-  int target[256];   // output row: the flat route id (down), else the sorted row itself
+  float scale[256];      // activation scale of the row (int8)
+  uint64_t rowptr[256];  // down / dense: byte address of the output row (may be peer memory)
 };
 
 struct SmemControl {
@@ -78,6 +78,8 @@ struct SmemControl {
   uint32_t exp_table[64];  // copy of kExp2Table: divergent lookups are served by 32 banks
   ColumnMeta meta[2];
 };
+
+static_assert(sizeof(SmemControl) <= 7168, "control block exceeds its shared-memory reservation");
 
 template <bool kInt8, bool kGateUp, int kRowTile, bool kDense>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -241,7 +243,13 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       ColumnMeta* meta = &ctl->meta[local & 1];
       for (int c = epilogue_thread; c < rows; c += 128) {
         if (kInt8) meta->scale[c] = args.a_scale[row0 + c];
-        meta->target[c] = (kGateUp || kDense) ? row0 + c : args.sorted_routes[row0 + c];
+        if constexpr (kDense) {
+          meta->rowptr[c] = reinterpret_cast<uint64_t>(args.dense_out) + static_cast<uint64_t>(row0 + c) * n_out * (args.dense_out_bf16 ? 2 : 4);
+        } else if constexpr (!kGateUp) {
+          meta->rowptr[c] = args.row_out_ptrs != nullptr
+                                ? args.row_out_ptrs[row0 + c]
+                                : reinterpret_cast<uint64_t>(args.route_out + static_cast<int64_t>(args.sorted_routes[row0 + c]) * n_out);
+        }
       }
       float scale_gate = 1.0f, scale_up = 1.0f;
       if (kInt8 && channel_ok) {
@@ -265,7 +273,6 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if (c0 + j < rows) {
-              const int64_t target = meta->target[c0 + j];
               if (dump != nullptr) {
                 uint32_t* out = dump + static_cast<int64_t>(row0 + c0 + j) * n_total;
                 out[n] = gate_bits[j];
@@ -281,7 +288,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                   gate = __uint_as_float(gate_bits[j]);
                   up = __uint_as_float(up_bits[j]);
                 }
-                args.y[target * n_out + n] = swiglu_to_bf16_with(gate, up, limit, ctl->exp_table);
+                args.y[static_cast<int64_t>(row0 + c0 + j) * n_out + n] = swiglu_to_bf16_with(gate, up, limit, ctl->exp_table);
               } else {
                 float value;
                 if constexpr (kInt8) {
@@ -289,15 +296,16 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                 } else {
                   value = __uint_as_float(gate_bits[j]);
                 }
+                const uint64_t rowptr = meta->rowptr[c0 + j];
                 if constexpr (kDense) {
                   value = __fadd_rn(value, bias);
                   if (args.dense_out_bf16) {
-                    static_cast<uint16_t*>(args.dense_out)[target * n_out + n] = f32_to_bf16_bits(value);
+                    reinterpret_cast<uint16_t*>(rowptr)[n] = f32_to_bf16_bits(value);
                   } else {
-                    static_cast<float*>(args.dense_out)[target * n_out + n] = value;
+                    reinterpret_cast<float*>(rowptr)[n] = value;
                   }
                 } else {
-                  args.route_out[target * n_out + n] = value;
+                  reinterpret_cast<float*>(rowptr)[n] = value;
                 }
               }
             }

@@ -150,6 +150,93 @@ class ExpertParallelMoE:
     __call__ = forward
 
 
+class PeerMemoryExpertParallelMoE:
+    """The same sharded layer with the row exchanges done by the kernels over peer memory (fmoe_ep_peer_*).
+
+    Each rank owns a slab that every other rank of the box maps: the dispatch kernel stores quantised rows straight
+    into the expert ranks' slabs and the down GEMM's epilogue stores the fp32 result rows straight back, so no
+    payload goes through a collective; three small collectives (an all-gather of W counts and two barriers) order
+    the stages, all on the stream, with no host synchronisation.  Bit-identical to ExpertParallelMoE and to the
+    single-GPU forward.  tokens_max bounds the tokens any rank passes to forward().
+    """
+
+    def __init__(self, weights: dict, experts_global: int, *, tokens_max: int, top_k: int, has_shared: bool = False, group=None,
+                 numerics: int = 0, gate_up_tile: int = 0, down_tile: int = 0):
+        from . import _lib
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.weights = weights
+        self.int8 = weights["w13"].dtype == torch.int8
+        self.has_shared = bool(has_shared)
+        self.experts_global = int(experts_global)
+        local_experts, two_inter, hidden = (int(v) for v in weights["w13"].shape)
+        self.per_rank = validate_expert_split(self.experts_global, self.world, local_experts, self.has_shared)
+        self.top_k = int(top_k) + (1 if self.has_shared else 0)
+        self.hidden = hidden
+        self.numerics = numerics
+        self.tiles = (gate_up_tile, down_tile)
+        device = weights["w13"].device
+        self.context = _lib.PeerContext(self.world, self.rank, int(tokens_max), self.top_k, hidden, two_inter // 2, local_experts, self.int8)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.context.ipc_handle(), group=group)
+        self.context.connect(handles)
+        self.dest_counts = torch.zeros(self.world, dtype=torch.int32, device=device)
+        self.count_matrix = torch.zeros(self.world * self.world, dtype=torch.int32, device=device)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.barrier(group=group)  # every rank has mapped every slab before anyone writes
+
+    def _barrier(self) -> None:
+        dist.all_reduce(self.flag, group=self.group)
+
+    def forward(self, x, topk_weights, topk_ids, *, routed_scaling_factor: float = 1.0, swiglu_limit: float | None = None, out=None):
+        from . import _lib
+
+        tokens = x.shape[0]
+        if self.has_shared:
+            shared = torch.full((tokens, 1), self.experts_global, dtype=topk_ids.dtype, device=topk_ids.device)
+            topk_ids = torch.cat((topk_ids, shared), dim=1)
+            ones = torch.ones((tokens, 1), dtype=topk_weights.dtype, device=topk_weights.device)
+            topk_weights = torch.cat((topk_weights * routed_scaling_factor, ones), dim=1)
+        elif routed_scaling_factor != 1.0:
+            topk_weights = topk_weights * routed_scaling_factor
+        if topk_ids.shape[1] != self.top_k:
+            raise ValueError(f"top_k is {topk_ids.shape[1]}, the context was built for {self.top_k}")
+        x = x.contiguous()
+        topk_ids = topk_ids.contiguous()
+        topk_weights = topk_weights.to(torch.float32).contiguous()
+        if out is None:
+            out = torch.empty((tokens, self.hidden), dtype=torch.bfloat16, device=x.device)
+        config = _lib.Config()
+        config.numerics = self.numerics
+        config.gate_up_tile, config.down_tile = self.tiles
+        config.swiglu_limit = (10.0 if self.int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
+        context = self.context
+        context.route(topk_ids, self.experts_global, self.rank if self.has_shared else -1, self.dest_counts)
+        dist.all_gather_into_tensor(self.count_matrix, self.dest_counts, group=self.group)
+        context.dispatch(x, topk_ids, self.experts_global, self.numerics, self.count_matrix)
+        self._barrier()
+        context.experts(self.weights["w13"], self.weights.get("s13"), self.weights["w2"], self.weights.get("s2"), config)
+        self._barrier()
+        context.combine(topk_weights, tokens, not self.int8, out)
+        return out
+
+    __call__ = forward
+
+    def raise_for_status(self) -> None:
+        """Synchronises; raises if the last forward dropped a route (expert id out of range) or a kernel gave up a wait."""
+        from . import _lib
+
+        dispatch_error, expert_error = self.context.read_status()
+        for where, code in (("dispatch", dispatch_error), ("expert stage", expert_error)):
+            if code != 0:
+                raise _lib.FusedMoEError(code, f"expert-parallel {where} reported device-side error {code} on rank {self.rank}")
+
+    def close(self) -> None:
+        self.context.close()
+
+
 def shard_rows(total: int, world: int, rank: int) -> slice:
     """Contiguous even split of `total` tokens (the first total % world ranks take one more)."""
     base, extra = divmod(total, world)
@@ -205,7 +292,13 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
     mine = shard_rows(tokens, world, rank)
     x_host, w_host, ids_host = x[mine].contiguous(), topk_w[mine].contiguous(), topk_ids[mine].contiguous()
     xd, wd, idd = x_host.to(device), w_host.to(device), ids_host.to(device)
-    layer = ExpertParallelMoE(weights, experts, has_shared=has_shared)
+    local_max = (tokens + world - 1) // world
+    if getattr(args, "ep_impl", "peer") == "peer":
+        layer = PeerMemoryExpertParallelMoE(weights, experts, tokens_max=local_max, top_k=top_k, has_shared=has_shared)
+        exchange = "rows stored by the dispatch kernel and the down-GEMM epilogue into peer memory over NVLink; NCCL only for W counts and two barriers"
+    else:
+        layer = ExpertParallelMoE(weights, experts, has_shared=has_shared)
+        exchange = "NCCL all-to-all dispatch/combine"
     kwargs = {"swiglu_limit": 10.0} if kind == "int8" else {}
 
     def step():
@@ -246,7 +339,7 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16" if kind == "bf16" else "int8(w8a8)", "data": "synthetic",
         "config": {"workload": name, "tokens": tokens, "hidden": hidden, "inter": inter, "experts": experts, "top_k": top_k,
-                   "shared_expert": has_shared, "parallelism": f"ep{world}: experts and tokens split evenly, NCCL all-to-all dispatch/combine",
+                   "shared_expert": has_shared, "parallelism": f"ep{world}: experts and tokens split evenly, {exchange}",
                    "l2": "inputs larger than L2: every rank streams its experts' weights each step"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": local_tokens * hidden * 2 + local_tokens * top_k * 12,
                 "d2h_bytes_per_step": local_tokens * hidden * 2},

@@ -1,5 +1,5 @@
-"""Expert-parallel layer on GPUs: the CUDA dispatch / expert-rows / combine entry points against the
-single-GPU forward (bit-exact), on a one-rank NCCL group always and on two GPUs when the box has them."""
+"""Expert-parallel layer on GPUs, both exchanges (NCCL all-to-all and the kernels' own stores into peer memory)
+against the single-GPU forward (bit-exact), on a one-rank NCCL group always and on two GPUs when the box has them."""
 from __future__ import annotations
 
 import datetime
@@ -40,7 +40,7 @@ def _single_gpu(case, device, shared=None, scaling=1.0):
     return _lib.moe_forward(c["x"], w13, w2, w.contiguous(), ids.contiguous(), s13=s13, s2=s2).out
 
 
-def _ep_worker(rank, world, port, kind, with_shared, queue):
+def _ep_worker(rank, world, port, kind, with_shared, impl, queue):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         device = torch.device("cuda", rank)
@@ -68,11 +68,22 @@ def _ep_worker(rank, world, port, kind, with_shared, queue):
         if shared is not None:
             weights = {k: torch.cat((weights[k], shared[k][None].to(device))) for k in keys}
         rows = ep.shard_rows(case["x"].shape[0], world, rank)
-        layer = ep.ExpertParallelMoE(weights, experts, has_shared=with_shared)
-        out = layer(case["x"][rows].to(device), case["topk_weights"][rows].to(device), case["topk_ids"][rows].to(device),
-                    routed_scaling_factor=1.5 if with_shared else 1.0)
+        if impl == "peer":
+            most = max(ep.shard_rows(case["x"].shape[0], world, r).stop - ep.shard_rows(case["x"].shape[0], world, r).start for r in range(world))
+            layer = ep.PeerMemoryExpertParallelMoE(weights, experts, tokens_max=most, top_k=case["topk_ids"].shape[1], has_shared=with_shared)
+        else:
+            layer = ep.ExpertParallelMoE(weights, experts, has_shared=with_shared)
         expected = _single_gpu(case, device, shared, 1.5)[rows]
-        same = torch.equal(out.view(torch.int16), expected.view(torch.int16))
+        same = True
+        for _ in range(2 if impl == "peer" else 1):  # the second call reuses the slabs
+            out = layer(case["x"][rows].to(device), case["topk_weights"][rows].to(device), case["topk_ids"][rows].to(device),
+                        routed_scaling_factor=1.5 if with_shared else 1.0)
+            same = same and torch.equal(out.view(torch.int16), expected.view(torch.int16))
+        if impl == "peer":
+            layer.raise_for_status()
+            torch.cuda.synchronize()
+            dist.barrier()
+            layer.close()
         queue.put((rank, "ok" if same else "mismatch", float((out.float() - expected.float()).abs().max())))
     except Exception as error:  # noqa: BLE001
         queue.put((rank, "error", f"{type(error).__name__}: {error}\n{traceback.format_exc()[-800:]}"))
@@ -81,11 +92,11 @@ def _ep_worker(rank, world, port, kind, with_shared, queue):
             dist.destroy_process_group()
 
 
-def _run_ep(world, kind, with_shared):
+def _run_ep(world, kind, with_shared, impl="nccl"):
     context = mp.get_context("spawn")
     queue = context.Queue()
     port = _free_port()
-    procs = [context.Process(target=_ep_worker, args=(r, world, port, kind, with_shared, queue)) for r in range(world)]
+    procs = [context.Process(target=_ep_worker, args=(r, world, port, kind, with_shared, impl, queue)) for r in range(world)]
     for p in procs:
         p.start()
     results = [queue.get(timeout=300) for _ in procs]
@@ -95,16 +106,18 @@ def _run_ep(world, kind, with_shared):
         assert status == "ok", (rank, status, detail)
 
 
+@pytest.mark.parametrize("impl", ["nccl", "peer"])
 @pytest.mark.parametrize("kind", ["int8", "bf16"])
 @pytest.mark.parametrize("with_shared", [False, True], ids=["routed", "routed+shared"])
-def test_ep_one_rank_equals_plain_forward(cuda_device, kind, with_shared):
+def test_ep_one_rank_equals_plain_forward(cuda_device, kind, with_shared, impl):
     """World size 1: every route is 'sent' to the own rank, so this isolates the CUDA entry points."""
-    _run_ep(1, kind, with_shared)
+    _run_ep(1, kind, with_shared, impl)
 
 
+@pytest.mark.parametrize("impl", ["nccl", "peer"])
 @pytest.mark.parametrize("kind", ["int8", "bf16"])
 @pytest.mark.parametrize("with_shared", [False, True], ids=["routed", "routed+shared"])
-def test_ep_two_gpus_equal_single_gpu(cuda_device, kind, with_shared):
+def test_ep_two_gpus_equal_single_gpu(cuda_device, kind, with_shared, impl):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    _run_ep(2, kind, with_shared)
+    _run_ep(2, kind, with_shared, impl)
