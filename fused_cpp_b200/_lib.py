@@ -37,7 +37,7 @@ EXPORTS = (
     "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
     "fmoe_i8gemm_dynamic_scaled_mm_pair", "fmoe_probe_mma_rate",
     "fmoe_ep_peer_create", "fmoe_ep_peer_handle", "fmoe_ep_peer_connect", "fmoe_ep_peer_destroy", "fmoe_ep_peer_slab_bytes",
-    "fmoe_ep_peer_route", "fmoe_ep_peer_dispatch", "fmoe_ep_peer_experts", "fmoe_ep_peer_combine", "fmoe_ep_peer_read_status",
+    "fmoe_ep_peer_dispatch", "fmoe_ep_peer_experts", "fmoe_ep_peer_combine", "fmoe_ep_peer_read_status",
 )
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
@@ -111,8 +111,7 @@ def load() -> ctypes.CDLL:
     lib.fmoe_ep_peer_destroy.restype = None
     lib.fmoe_ep_peer_slab_bytes.argtypes = [p]
     lib.fmoe_ep_peer_slab_bytes.restype = ctypes.c_int64
-    lib.fmoe_ep_peer_route.argtypes = [p, p, i64, i32, i32, p, p]
-    lib.fmoe_ep_peer_dispatch.argtypes = [p, p, p, i64, i32, i32, p, p]
+    lib.fmoe_ep_peer_dispatch.argtypes = [p, p, p, i64, i32, i32, i32, p]
     lib.fmoe_ep_peer_experts.argtypes = [p, p, p, p, p, ctypes.POINTER(Config), p]
     lib.fmoe_ep_peer_combine.argtypes = [p, p, i64, i32, p, p]
     lib.fmoe_ep_peer_read_status.argtypes = [p, p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
@@ -440,12 +439,8 @@ class PeerContext:
     def slab_bytes(self) -> int:
         return int(load().fmoe_ep_peer_slab_bytes(self.handle))
 
-    def route(self, topk_ids, experts_global: int, shared_rank: int, dest_counts) -> None:
-        check(load().fmoe_ep_peer_route(self.handle, _ptr(topk_ids), topk_ids.shape[0], experts_global, shared_rank, _ptr(dest_counts),
-                                        _stream()))
-
-    def dispatch(self, x, topk_ids, experts_global: int, numerics: int, count_matrix) -> None:
-        check(load().fmoe_ep_peer_dispatch(self.handle, _ptr(x), _ptr(topk_ids), x.shape[0], experts_global, numerics, _ptr(count_matrix),
+    def dispatch(self, x, topk_ids, experts_global: int, shared_rank: int, numerics: int) -> None:
+        check(load().fmoe_ep_peer_dispatch(self.handle, _ptr(x), _ptr(topk_ids), x.shape[0], experts_global, shared_rank, numerics,
                                            _stream()))
 
     def experts(self, w13, s13, w2, s2, config: "Config") -> None:

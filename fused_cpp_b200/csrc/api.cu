@@ -2,6 +2,7 @@
 // forward call.  See include/fused_moe_b200.h for the contract of every entry point.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -127,10 +128,11 @@ struct Forward {
   const float* rows_scale = nullptr;
   float* route_out_override = nullptr;
   bool rows_mode = false;
-  // Peer-memory expert stage: `tokens` is the capacity of the row list, *rows_valid_count (device) how many rows
-  // it holds, rows_source[row] = (source rank, flat route) and every result row is stored into the source rank's
-  // slab at peer_slabs[rank] + peer_route_out_offset.
+  // Peer-memory expert stage: `tokens` is the capacity of the row list, made of regions of rows_region rows of
+  // which rows_valid_count[r] (device) are filled; rows_source[row] = (source rank, flat route) and every result
+  // row is stored into the source rank's slab at peer_slabs[rank] + peer_route_out_offset.
   const int* rows_valid_count = nullptr;
+  int rows_region = 0;
   const void* rows_source = nullptr;
   const uint64_t* peer_slabs = nullptr;
   size_t peer_route_out_offset = 0;
@@ -224,7 +226,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
   error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, item_rows_gu, item_rows_dn, max_items, status_block, counts, offsets,
                                    sorted_routes, row_expert, items_gu, items_dn, scratch, stream,
-                                   reinterpret_cast<int*>(base + layout.route_pos), f.rows_valid_count);
+                                   reinterpret_cast<int*>(base + layout.route_pos), f.rows_valid_count, f.rows_region);
   if (error != cudaSuccess) return cuda_fail(error, "route build");
   uint64_t* row_out_ptrs = nullptr;
   if (peer) {
@@ -723,8 +725,9 @@ struct fmoe_ep_peer_context {
   size_t dispatch_ws_bytes = 0;
   char* expert_ws = nullptr;
   size_t expert_ws_bytes = 0;
-  int* base_at_dest = nullptr;        // [world]
-  int* received = nullptr;            // [1]
+  int* dest_counts = nullptr;         // [world] rows this rank sends to every rank (last dispatch)
+  unsigned* epoch = nullptr;          // [1] barrier epoch of this rank
+  unsigned long long wait_limit_ns = 5000000000ull;  // bound of the barrier wait (FUSED_CPP_MOE_EP_WAIT_MS)
 };
 
 namespace {
@@ -801,7 +804,13 @@ int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t
   ctx->slab.scale = take(capacity * sizeof(float));
   ctx->slab.source = take(capacity * 2 * sizeof(int));
   ctx->slab.route_out = take(static_cast<size_t>(tokens_max) * top_k * hidden * sizeof(float));
+  ctx->slab.counts = take(sizeof(int) * world);
+  ctx->slab.flags = take(sizeof(unsigned) * world);
   ctx->slab.total = offset;
+  if (const char* limit = getenv("FUSED_CPP_MOE_EP_WAIT_MS")) {
+    const long long ms = atoll(limit);
+    if (ms > 0) ctx->wait_limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
+  }
   fmoe_workspace_layout layout;
   status = make_layout(int8 != 0, ctx->capacity, 1, local_experts, hidden, inter, &layout, false);
   if (status != FMOE_OK) {
@@ -814,12 +823,14 @@ int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t
   if (error == cudaSuccess) error = cudaMalloc(&ctx->expert_ws, ctx->expert_ws_bytes);
   if (error == cudaSuccess) error = cudaMalloc(&ctx->dispatch_ws, ctx->dispatch_ws_bytes);
   if (error == cudaSuccess) error = cudaMalloc(&ctx->peer_slabs_dev, sizeof(uint64_t) * world);
-  if (error == cudaSuccess) error = cudaMalloc(&ctx->base_at_dest, sizeof(int) * (world + 1));
+  if (error == cudaSuccess) error = cudaMalloc(&ctx->dest_counts, sizeof(int) * (world + 1));
+  if (error == cudaSuccess) error = cudaMemset(ctx->dest_counts, 0, sizeof(int) * (world + 1));
+  if (error == cudaSuccess) error = cudaMemset(ctx->slab_base + ctx->slab.counts, 0, ctx->slab.total - ctx->slab.counts);
   if (error != cudaSuccess) {
     fmoe_ep_peer_destroy(ctx);
     return cuda_fail(error, "peer context allocation");
   }
-  ctx->received = ctx->base_at_dest + world;
+  ctx->epoch = reinterpret_cast<unsigned*>(ctx->dest_counts + world);
   ctx->opened.assign(world, nullptr);
   *out = ctx;
   return FMOE_OK;
@@ -867,51 +878,45 @@ void fmoe_ep_peer_destroy(fmoe_ep_peer_context* ctx) {
   if (ctx->expert_ws) cudaFree(ctx->expert_ws);
   if (ctx->dispatch_ws) cudaFree(ctx->dispatch_ws);
   if (ctx->peer_slabs_dev) cudaFree(ctx->peer_slabs_dev);
-  if (ctx->base_at_dest) cudaFree(ctx->base_at_dest);
+  if (ctx->dest_counts) cudaFree(ctx->dest_counts);
   delete ctx;
 }
 
 int64_t fmoe_ep_peer_slab_bytes(const fmoe_ep_peer_context* ctx) { return ctx ? static_cast<int64_t>(ctx->slab.total) : 0; }
 
-int fmoe_ep_peer_route(fmoe_ep_peer_context* ctx, const int64_t* topk_ids, int64_t tokens, int32_t experts_global, int32_t shared_rank,
-                       int32_t* dest_counts, void* stream_ptr) {
+int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* ctx, const void* x, const int64_t* topk_ids, int64_t tokens, int32_t experts_global,
+                          int32_t shared_rank, int32_t numerics, void* stream_ptr) {
   int status = check_device();
   if (status != FMOE_OK) return status;
   if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
   if (tokens < 0 || tokens > ctx->tokens_max || experts_global <= 0 || experts_global % ctx->world != 0 || shared_rank >= ctx->world ||
-      dest_counts == nullptr || (tokens > 0 && topk_ids == nullptr)) {
-    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid peer route arguments (tokens within the context's maximum, experts divisible by the ranks)");
+      (tokens > 0 && (x == nullptr || topk_ids == nullptr))) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid peer dispatch arguments (tokens within the context's maximum, experts divisible by the ranks)");
   }
+  if (numerics != FMOE_NUMERICS_TORCHREF && numerics != FMOE_NUMERICS_NATIVE) return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown numerics");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const int64_t routes = tokens * ctx->top_k;
+  const int region = static_cast<int>(ctx->tokens_max * ctx->top_k);
   const DispatchScratch d = carve_dispatch(ctx->dispatch_ws, ctx->tokens_max * ctx->top_k, ctx->world);
   cudaError_t error = cudaMemsetAsync(d.status, 0, sizeof(int) * fmoe::kStatusWords, stream);
-  if (error == cudaSuccess && routes == 0) error = cudaMemsetAsync(dest_counts, 0, sizeof(int) * ctx->world, stream);
+  if (error == cudaSuccess && routes == 0) error = cudaMemsetAsync(ctx->dest_counts, 0, sizeof(int) * ctx->world, stream);
   if (error == cudaSuccess && routes > 0) {
     error = fmoe::launch_dest_ranks(topk_ids, routes, experts_global, experts_global / ctx->world, shared_rank, d.dest, stream);
   }
   if (error == cudaSuccess && routes > 0) {
-    error = fmoe::launch_route_build(d.dest, routes, ctx->world, 16, 16, 0, d.status, dest_counts, d.offsets, d.send_order, d.row_rank,
+    // A stable counting sort of the routes by destination rank: the same kernels as the per-expert route build.
+    error = fmoe::launch_route_build(d.dest, routes, ctx->world, 16, 16, 0, d.status, ctx->dest_counts, d.offsets, d.send_order, d.row_rank,
                                      nullptr, nullptr, d.scratch, stream, d.route_pos);
   }
-  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer route");
-}
-
-int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* ctx, const void* x, const int64_t* topk_ids, int64_t tokens, int32_t experts_global,
-                          int32_t numerics, const int32_t* count_matrix, void* stream_ptr) {
-  int status = check_device();
-  if (status != FMOE_OK) return status;
-  if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
-  if (tokens < 0 || tokens > ctx->tokens_max || count_matrix == nullptr || (tokens > 0 && (x == nullptr || topk_ids == nullptr))) {
-    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid peer dispatch arguments");
-  }
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  const DispatchScratch d = carve_dispatch(ctx->dispatch_ws, ctx->tokens_max * ctx->top_k, ctx->world);
-  cudaError_t error = fmoe::launch_peer_offsets(count_matrix, ctx->world, ctx->rank, ctx->base_at_dest, ctx->received, stream);
   if (error == cudaSuccess) {
     error = fmoe::launch_peer_dispatch(ctx->int8 != 0, static_cast<const uint16_t*>(x), topk_ids, tokens, ctx->hidden, ctx->top_k, d.dest,
-                                       d.route_pos, d.offsets, ctx->base_at_dest, ctx->slab, ctx->peer_slabs_dev, ctx->rank, experts_global,
+                                       d.route_pos, d.offsets, region, ctx->slab, ctx->peer_slabs_dev, ctx->rank, experts_global,
                                        experts_global / ctx->world, numerics, stream);
+  }
+  if (error == cudaSuccess) {
+    // Row counts to the destinations, then the barrier: after it every rank's region of this slab is complete.
+    error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, ctx->dest_counts, ctx->world, ctx->rank, ctx->epoch, d.status,
+                                      ctx->wait_limit_ns, stream);
   }
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer dispatch");
 }
@@ -923,11 +928,18 @@ int fmoe_ep_peer_experts(fmoe_ep_peer_context* ctx, const void* w13, const float
             reinterpret_cast<const int64_t*>(ctx->slab_base + ctx->slab.expert), ctx->capacity, 1, ctx->local_experts, ctx->hidden, ctx->inter};
   f.rows_scale = reinterpret_cast<const float*>(ctx->slab_base + ctx->slab.scale);
   f.rows_mode = true;
-  f.rows_valid_count = ctx->received;
+  f.rows_valid_count = reinterpret_cast<const int*>(ctx->slab_base + ctx->slab.counts);
+  f.rows_region = static_cast<int>(ctx->tokens_max * ctx->top_k);
   f.rows_source = ctx->slab_base + ctx->slab.source;
   f.peer_slabs = ctx->peer_slabs_dev;
   f.peer_route_out_offset = ctx->slab.route_out;
-  return run_forward(f, config, nullptr, ctx->expert_ws, ctx->expert_ws_bytes, stream);
+  const int status = run_forward(f, config, nullptr, ctx->expert_ws, ctx->expert_ws_bytes, stream);
+  if (status != FMOE_OK) return status;
+  // After this barrier every result row of this rank's routes has arrived, and every rank is done reading its slab.
+  const cudaError_t error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, nullptr, ctx->world, ctx->rank, ctx->epoch,
+                                                      reinterpret_cast<int*>(ctx->expert_ws), ctx->wait_limit_ns,
+                                                      static_cast<cudaStream_t>(stream));
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer barrier");
 }
 
 int fmoe_ep_peer_combine(fmoe_ep_peer_context* ctx, const float* topk_weights, int64_t tokens, int32_t tree_merge, void* out,

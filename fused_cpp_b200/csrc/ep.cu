@@ -42,20 +42,41 @@ __global__ void scatter_rows_f32_kernel(const float* __restrict__ rows, const in
 
 // ---- peer-memory path: rows go straight into the expert rank's receive slab, results straight back ----
 
-// From the gathered count matrix C[source][destination] (world x world): where this rank's rows start in every
-// destination's slab (the rows of lower source ranks come first) and how many rows this rank receives.
-__global__ void peer_offsets_kernel(const int* __restrict__ count_matrix, int world, int rank, int* __restrict__ base_at_dest,
-                                    int* __restrict__ received) {
-  const int d = threadIdx.x;
-  if (d < world) {
-    int base = 0;
-    for (int s = 0; s < rank; ++s) base += count_matrix[s * world + d];
-    base_at_dest[d] = base;
-  }
+// Barrier between the ranks of the box, through flags in the slabs.  Every rank bumps its own epoch, (optionally)
+// tells every destination how many rows it has just stored there, then stores the epoch into its flag in every
+// rank's slab and waits until all flags in its own slab have reached that epoch.  The stores of the kernels that
+// ran before it on this stream are complete when it starts (stream order), and the fence orders its own stores,
+// so a rank that sees the flag also sees the rows.  The wait is bounded: after limit_ns it records
+// FMOE_ERR_DEVICE_WAIT (detail = the rank it waited for) and returns.
+__global__ void __launch_bounds__(64)
+peer_barrier_kernel(const uint64_t* __restrict__ peer_slabs, PeerSlabLayout slab, const int* __restrict__ dest_counts, int world, int rank,
+                    unsigned* __restrict__ epoch_counter, int* status, unsigned long long limit_ns) {
+  __shared__ unsigned epoch_shared;
   if (threadIdx.x == 0) {
-    int total = 0;
-    for (int s = 0; s < world; ++s) total += count_matrix[s * world + rank];
-    *received = total;
+    epoch_shared = *epoch_counter + 1u;
+    *epoch_counter = epoch_shared;
+  }
+  __syncthreads();
+  const unsigned epoch = epoch_shared;
+  const int peer = threadIdx.x;
+  if (peer >= world) return;
+  const uint64_t theirs = peer_slabs[peer];
+  if (dest_counts != nullptr) *reinterpret_cast<volatile int*>(theirs + slab.counts + sizeof(int) * rank) = dest_counts[peer];
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs + slab.flags + sizeof(unsigned) * rank), "r"(epoch) : "memory");
+  const uint64_t mine = peer_slabs[rank] + slab.flags + sizeof(unsigned) * peer;
+  unsigned long long start = 0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+  while (true) {
+    unsigned seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (static_cast<int>(seen - epoch) >= 0) break;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - start > limit_ns) {
+      raise_error(status, FMOE_ERR_DEVICE_WAIT, peer);
+      break;
+    }
   }
 }
 
@@ -68,7 +89,8 @@ __device__ __forceinline__ void unpack8_bf16(const uint4& v, float* out) {
   }
 }
 
-// One CTA per token.  The token row is quantised once (int8) or taken as it is (bf16) and stored, with plain
+// One CTA per token.  A destination's slab is divided into one region of `region` rows per source rank, so a
+// source needs to know nothing about the others before it stores.  The token row is quantised once (int8) or taken as it is (bf16) and stored, with plain
 // 16-byte stores, into the receive slab of the rank that owns each of its routes' experts, together with the
 // route's scale, local expert id and return address (source rank, flat route).  Same bits as
 // quantize_tokens_scatter / gather_rows on one GPU.
@@ -76,7 +98,7 @@ template <bool kInt8>
 __global__ void __launch_bounds__(256)
 peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__ topk_ids, int cols, int top_k,
                      const int64_t* __restrict__ dest, const int* __restrict__ route_pos, const int* __restrict__ dest_offsets,
-                     const int* __restrict__ base_at_dest, PeerSlabLayout slab, const uint64_t* __restrict__ peer_slabs, int rank,
+                     int region, PeerSlabLayout slab, const uint64_t* __restrict__ peer_slabs, int rank,
                      int experts_global, int experts_per_rank, int numerics) {
   __shared__ float reduce[32];
   __shared__ int64_t slot_row[32];    // row index in the destination slab, -1 = dropped
@@ -89,7 +111,7 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
     int64_t row = -1;
     uint64_t base = 0;
     if (d >= 0 && position >= 0) {
-      row = base_at_dest[d] + (position - dest_offsets[d]);
+      row = static_cast<int64_t>(rank) * region + (position - dest_offsets[d]);  // this rank's region of the destination's slab
       base = peer_slabs[d];
     }
     slot_row[threadIdx.x] = row;
@@ -173,23 +195,24 @@ __global__ void peer_row_ptrs_kernel(const int* __restrict__ sorted_routes, cons
 
 }  // namespace
 
-cudaError_t launch_peer_offsets(const int* count_matrix, int world, int rank, int* base_at_dest, int* received, cudaStream_t stream) {
-  peer_offsets_kernel<<<1, world < 32 ? 32 : ((world + 31) / 32) * 32, 0, stream>>>(count_matrix, world, rank, base_at_dest, received);
+cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* dest_counts, int world, int rank,
+                                unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream) {
+  peer_barrier_kernel<<<1, 64, 0, stream>>>(peer_slabs, slab, dest_counts, world, rank, epoch_counter, status, limit_ns);
   return cudaGetLastError();
 }
 
 cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
-                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, const int* base_at_dest,
+                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, int region,
                                  const PeerSlabLayout& slab, const uint64_t* peer_slabs, int rank, int experts_global,
                                  int experts_per_rank, int numerics, cudaStream_t stream) {
   if (tokens <= 0) return cudaSuccess;
   if (int8) {
     peer_dispatch_kernel<true><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, dest, route_pos, dest_offsets,
-                                                                                  base_at_dest, slab, peer_slabs, rank, experts_global,
+                                                                                  region, slab, peer_slabs, rank, experts_global,
                                                                                   experts_per_rank, numerics);
   } else {
     peer_dispatch_kernel<false><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, dest, route_pos, dest_offsets,
-                                                                                   base_at_dest, slab, peer_slabs, rank, experts_global,
+                                                                                   region, slab, peer_slabs, rank, experts_global,
                                                                                    experts_per_rank, numerics);
   }
   return cudaGetLastError();

@@ -15,11 +15,12 @@ int report_error(int code, const char* text);
 
 // ---- route.cu
 size_t route_scratch_bytes(int64_t routes, int experts);
-// valid_count (nullable, device): entries at or beyond *valid_count are padding and skipped silently.
+// valid_count (nullable, device): with region == 0, entries at or beyond *valid_count are padding and skipped
+// silently; with region > 0 the list consists of regions of `region` entries and valid_count[r] of region r are filled.
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
                                int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream,
-                               int* route_pos = nullptr, const int* valid_count = nullptr);
+                               int* route_pos = nullptr, const int* valid_count = nullptr, int region = 0);
 
 // Work items of a dense [rows, K] x [N, K]^T product: one "expert", consecutive row tiles.
 cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream);
@@ -67,11 +68,15 @@ struct PeerSlabLayout {
   size_t scale;      // [capacity] fp32: activation scale of each received row (int8)
   size_t source;     // [capacity] int2: (source rank, flat route id at the source)
   size_t route_out;  // [local routes, H] fp32: result rows of this rank's own routes, written by the expert ranks
+  size_t counts;     // [world] int: rows stored by every source rank in its region of `rows`
+  size_t flags;      // [world] uint32: barrier epochs, one per source rank
   size_t total;
 };
-cudaError_t launch_peer_offsets(const int* count_matrix, int world, int rank, int* base_at_dest, int* received, cudaStream_t stream);
+// The received rows form `world` regions of tokens_max * top_k rows, region s filled by source rank s.
+cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* dest_counts, int world, int rank,
+                                unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream);
 cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
-                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, const int* base_at_dest,
+                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, int region,
                                  const PeerSlabLayout& slab, const uint64_t* peer_slabs, int rank, int experts_global,
                                  int experts_per_rank, int numerics, cudaStream_t stream);
 cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows, int64_t capacity, const void* source,

@@ -23,8 +23,8 @@ namespace {
 constexpr int kWarpsPerBlock = 4;
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int experts, int units,
-                  int* unit_hist, int* status) {
+route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int region, int experts,
+                  int units, int* unit_hist, int* status) {
   extern __shared__ int smem_hist[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -33,12 +33,14 @@ route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const in
   for (int e = lane; e < experts; e += 32) hist[e] = 0;
   __syncwarp();
   if (unit >= units) return;
-  // With a device-side count, entries at or beyond it are padding of a fixed-capacity list: skipped, not an error.
-  if (valid_count != nullptr) routes = min(routes, static_cast<int64_t>(*valid_count));
+  // With device-side counts the list has a fixed capacity and its unused entries are padding: skipped, not an
+  // error.  region == 0: one count, the list is filled from the front; region > 0: the list is a sequence of
+  // regions of that many entries and valid_count[r] is how many of region r are filled.
+  if (valid_count != nullptr && region == 0) routes = min(routes, static_cast<int64_t>(*valid_count));
   const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
   for (int round = 0; round < kUnitRoutes / 32; ++round) {
     const int64_t route = begin + round * 32 + lane;
-    if (route < routes) {
+    if (route < routes && (region == 0 || route % region < valid_count[route / region])) {
       const int64_t id = topk_ids[route];
       if (id < 0 || id >= experts) {
         raise_error(status, FMOE_ERR_EXPERT_ID_RANGE, static_cast<int>(route));
@@ -134,7 +136,7 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int experts, int units,
+route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int region, int experts, int units,
                      const int* __restrict__ unit_hist, const int* __restrict__ offsets, int* sorted_routes,
                      int* row_expert, int* route_pos) {
   extern __shared__ int smem_cursor[];
@@ -146,13 +148,13 @@ route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const
   for (int e = lane; e < experts; e += 32) cursor[e] = offsets[e] + unit_hist[static_cast<int64_t>(unit) * experts + e];
   __syncwarp();
   const int64_t listed = routes;
-  if (valid_count != nullptr) routes = min(routes, static_cast<int64_t>(*valid_count));
+  if (valid_count != nullptr && region == 0) routes = min(routes, static_cast<int64_t>(*valid_count));
   const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
   const unsigned lanes_below = (1u << lane) - 1u;
   for (int round = 0; round < kUnitRoutes / 32; ++round) {
     const int64_t route = begin + round * 32 + lane;
     int id = -1;
-    if (route < routes) {
+    if (route < routes && (region == 0 || route % region < valid_count[route / region])) {
       const int64_t value = topk_ids[route];
       if (value >= 0 && value < experts) id = static_cast<int>(value);
     }
@@ -181,19 +183,19 @@ size_t route_scratch_bytes(int64_t routes, int experts) {
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
                                int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos,
-                               const int* valid_count) {
+                               const int* valid_count, int region) {
   const int units = static_cast<int>((routes + kUnitRoutes - 1) / kUnitRoutes);
   int* unit_hist = scratch;
   int* scan_tmp = scratch + static_cast<int64_t>(units > 0 ? units : 1) * experts;
   const size_t smem = static_cast<size_t>(kWarpsPerBlock) * experts * sizeof(int);
   const int blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (blocks > 0) {
-    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, experts, units, unit_hist, status);
+    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, region, experts, units, unit_hist, status);
   }
   route_scan_kernel<<<1, 1024, 0, stream>>>(experts, units, unit_hist, counts, offsets, tile_a, tile_b, items_a, items_b,
                                             max_items, scan_tmp, status);
   if (blocks > 0) {
-    route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, experts, units, unit_hist,
+    route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, region, experts, units, unit_hist,
                                                                         offsets, sorted_routes, row_expert, route_pos);
   }
   return cudaGetLastError();

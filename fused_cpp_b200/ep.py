@@ -154,10 +154,11 @@ class PeerMemoryExpertParallelMoE:
     """The same sharded layer with the row exchanges done by the kernels over peer memory (fmoe_ep_peer_*).
 
     Each rank owns a slab that every other rank of the box maps: the dispatch kernel stores quantised rows straight
-    into the expert ranks' slabs and the down GEMM's epilogue stores the fp32 result rows straight back, so no
-    payload goes through a collective; three small collectives (an all-gather of W counts and two barriers) order
-    the stages, all on the stream, with no host synchronisation.  Bit-identical to ExpertParallelMoE and to the
-    single-GPU forward.  tokens_max bounds the tokens any rank passes to forward().
+    into the expert ranks' slabs and the down GEMM's epilogue stores the fp32 result rows straight back; two flag
+    barriers through the same slabs order the stages.  After set-up (one exchange of IPC handles through
+    torch.distributed) a forward involves no collective library and no host synchronisation.  Bit-identical to
+    ExpertParallelMoE and to the single-GPU forward.  tokens_max bounds the tokens any rank passes to forward();
+    every rank must call forward() the same number of times.
     """
 
     def __init__(self, weights: dict, experts_global: int, *, tokens_max: int, top_k: int, has_shared: bool = False, group=None,
@@ -177,18 +178,12 @@ class PeerMemoryExpertParallelMoE:
         self.hidden = hidden
         self.numerics = numerics
         self.tiles = (gate_up_tile, down_tile)
-        device = weights["w13"].device
         self.context = _lib.PeerContext(self.world, self.rank, int(tokens_max), self.top_k, hidden, two_inter // 2, local_experts, self.int8)
         handles = [None] * self.world
         dist.all_gather_object(handles, self.context.ipc_handle(), group=group)
         self.context.connect(handles)
-        self.dest_counts = torch.zeros(self.world, dtype=torch.int32, device=device)
-        self.count_matrix = torch.zeros(self.world * self.world, dtype=torch.int32, device=device)
-        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.stage_timer = None  # optional _lib.StageTimer: per-kernel CUDA events of the expert stage
         dist.barrier(group=group)  # every rank has mapped every slab before anyone writes
-
-    def _barrier(self) -> None:
-        dist.all_reduce(self.flag, group=self.group)
 
     def forward(self, x, topk_weights, topk_ids, *, routed_scaling_factor: float = 1.0, swiglu_limit: float | None = None, out=None):
         from . import _lib
@@ -212,13 +207,11 @@ class PeerMemoryExpertParallelMoE:
         config.numerics = self.numerics
         config.gate_up_tile, config.down_tile = self.tiles
         config.swiglu_limit = (10.0 if self.int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
+        if self.stage_timer is not None:
+            config.stage_timer = self.stage_timer.handle
         context = self.context
-        context.route(topk_ids, self.experts_global, self.rank if self.has_shared else -1, self.dest_counts)
-        dist.all_gather_into_tensor(self.count_matrix, self.dest_counts, group=self.group)
-        context.dispatch(x, topk_ids, self.experts_global, self.numerics, self.count_matrix)
-        self._barrier()
+        context.dispatch(x, topk_ids, self.experts_global, self.rank if self.has_shared else -1, self.numerics)
         context.experts(self.weights["w13"], self.weights.get("s13"), self.weights["w2"], self.weights.get("s2"), config)
-        self._barrier()
         context.combine(topk_weights, tokens, not self.int8, out)
         return out
 
@@ -295,7 +288,7 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
     local_max = (tokens + world - 1) // world
     if getattr(args, "ep_impl", "peer") == "peer":
         layer = PeerMemoryExpertParallelMoE(weights, experts, tokens_max=local_max, top_k=top_k, has_shared=has_shared)
-        exchange = "rows stored by the dispatch kernel and the down-GEMM epilogue into peer memory over NVLink; NCCL only for W counts and two barriers"
+        exchange = "rows stored by the dispatch kernel and the down-GEMM epilogue into peer memory over NVLink, flag barriers in the same slabs"
     else:
         layer = ExpertParallelMoE(weights, experts, has_shared=has_shared)
         exchange = "NCCL all-to-all dispatch/combine"
@@ -304,24 +297,94 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
     def step():
         return layer(xd, wd, idd, **kwargs)
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, sampler=None):
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler is not None:
+            sampler.start()
         start.record()
         for _ in range(steps):
             fn()
         stop.record()
         torch.cuda.synchronize()
+        clocks = sampler.stop() if sampler is not None else None
         dist.barrier()
         elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-        return float(elapsed.item())
+        return float(elapsed.item()), clocks
 
-    ms = timed(step, args.steps, args.warmup)
+    # The forward makes no host read, so one step (kernels and the three small collectives) is captured into a
+    # CUDA graph and the timed region replays it; every rank replays the same sequence.  Eager launches are
+    # timed as well (eager_ms_per_step).
+    launch_mode = "eager"
+    replay = step
+    if isinstance(layer, PeerMemoryExpertParallelMoE) and os.environ.get("FUSED_CPP_MOE_EP_GRAPH", "1") != "0":
+        try:
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            replay = graph.replay
+            launch_mode = "cuda_graph_replay"
+        except Exception as error:  # noqa: BLE001
+            launch_mode = f"eager (graph capture failed: {type(error).__name__})"
+            replay = step
+    captured = torch.tensor([1 if launch_mode == "cuda_graph_replay" else 0], device=device)
+    dist.all_reduce(captured, op=dist.ReduceOp.MIN)
+    if int(captured.item()) == 0:
+        replay = step
+        if launch_mode == "cuda_graph_replay":
+            launch_mode = "eager (graph capture failed on another rank)"
+    sampler_class = getattr(args, "clock_sampler", None)
+    ms, clocks = timed(replay, args.steps, args.warmup, sampler_class(device.index) if (sampler_class and rank == 0) else None)
+    eager_ms = ms
+    if replay is not step:
+        # Both ways of launching are timed under the same rules; the line reports the faster one as `value`
+        # (with few ranks the eager launches already keep the GPU busy and the captured collectives cost more).
+        graph_ms = ms
+        eager_ms, eager_clocks = timed(step, args.steps, args.warmup, sampler_class(device.index) if (sampler_class and rank == 0) else None)
+        if eager_ms < graph_ms:
+            ms, clocks, launch_mode = eager_ms, eager_clocks, f"eager (cuda_graph_replay: {graph_ms:.4f} ms)"
+
+    # Per-kernel durations of this rank's expert stage (CUDA events around every stage, a second timed pass).
+    roofline = None
+    stage_ms = None
+    if isinstance(layer, PeerMemoryExpertParallelMoE) and getattr(args, "roofline", None) is not None:
+        from . import _lib
+
+        timer = _lib.StageTimer(args.steps)
+        layer.stage_timer = timer
+        for _ in range(args.steps):
+            step()
+        torch.cuda.synchronize()
+        layer.stage_timer = None
+        stage_ms = {stage: 0.0 for stage in _lib.STAGES}
+        for call in range(timer.calls):
+            for stage, value in timer.read(call).items():
+                stage_ms[stage] += value / timer.calls
+        timer.close()
+        # Algorithmic work of this rank's gate_up launch: the weights of its experts that the batch hits, once,
+        # plus the rows it receives in and their SwiGLU rows out.
+        owner = topk_ids // per_rank
+        local_ids = topk_ids[owner == rank]
+        rows = int(local_ids.numel()) + (x_host.shape[0] if has_shared else 0)
+        active = int(local_ids.unique().numel()) + (1 if has_shared else 0)
+        b = 1 if kind == "int8" else 2
+        nbytes = active * 2 * inter * hidden * b + rows * hidden * b + rows * inter * 2 + (active * 2 * inter * 4 + rows * 4 if kind == "int8" else 0)
+        roofline = args.roofline(kind, float(nbytes), 2.0 * rows * 2 * inter * hidden, stage_ms["gate_up"], peaks, None)
+        roofline["scope"] = f"rank 0 of {world}: {active} active local experts, {rows} received rows"
+        dist.barrier()
 
     x_pin, w_pin, ids_pin = x_host.pin_memory(), w_host.pin_memory(), ids_host.pin_memory()
     out_pin = torch.empty((x_host.shape[0], hidden), dtype=torch.bfloat16).pin_memory()
@@ -330,7 +393,7 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
         out = layer(x_pin.to(device, non_blocking=True), w_pin.to(device, non_blocking=True), ids_pin.to(device, non_blocking=True), **kwargs)
         out_pin.copy_(out, non_blocking=True)
 
-    e2e_ms = timed(e2e_step, args.steps, args.warmup)
+    e2e_ms, _ = timed(e2e_step, args.steps, args.warmup)
     local_tokens = x_host.shape[0]
     work = synthetic.algorithmic_work(synthetic.MoEShape(tokens, hidden, inter, experts, top_k), topk_ids, 1 if kind == "int8" else 2,
                                       shared=has_shared)
@@ -343,7 +406,9 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
                    "l2": "inputs larger than L2: every rank streams its experts' weights each step"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": local_tokens * hidden * 2 + local_tokens * top_k * 12,
                 "d2h_bytes_per_step": local_tokens * hidden * 2},
-        "gpu_launches": (14 if kind == "int8" else 13) * args.steps,
+        "gpu_launches": (14 if kind == "int8" else 13) * args.steps, "clocks": clocks, "roofline": roofline, "cpu_baseline": None,
+        "launch_mode": launch_mode, "eager_ms_per_step": eager_ms,
+        "stage_ms_rank0": {k: round(v, 5) for k, v in stage_ms.items()} if stage_ms else None,
         "layer": {"algorithmic_bytes": work["bytes"], "ops": work["ops"],
                   "hbm_gbs_aggregate": work["bytes"] / (ms * 1e-3) / 1e9, "tops_aggregate": work["ops"] / (ms * 1e-3) / 1e12},
     }

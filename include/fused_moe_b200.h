@@ -256,19 +256,21 @@ FMOE_API int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows
 
 /* ---- expert parallelism over peer memory --------------------------------------------------------- */
 
-/* The same sharding as fmoe_ep_dispatch_prepare / fmoe_*_expert_rows_forward / fmoe_ep_combine_finish, with the two
- * row exchanges done by the kernels themselves instead of by a collective library: every rank owns one "slab"
- * (receive rows, their scale / local expert / return address, and the fp32 result rows of its own routes),
- * exported by IPC handle and mapped by every other rank of the box.  The dispatch kernel quantises each token
- * once and stores its rows straight into the owning ranks' slabs; the down GEMM's epilogue stores every result
- * row straight into the slab of the rank the route came from, tile by tile while the GEMM runs.  Only plain
- * stores cross NVLink; all loads (TMA included) read local memory.  The caller provides the ordering between
- * ranks with three small collectives per forward, all on the stream (no host synchronisation):
- *     fmoe_ep_peer_route      -> all-gather of dest_counts into count_matrix[world][world]
- *     fmoe_ep_peer_dispatch   -> barrier
- *     fmoe_ep_peer_experts    -> barrier
- *     fmoe_ep_peer_combine
- * (the all-gather also orders this forward's dispatch after every rank's previous expert stage and combine).
+/* The same sharding as fmoe_ep_dispatch_prepare / fmoe_*_expert_rows_forward / fmoe_ep_combine_finish, with the row
+ * exchanges and the synchronisation done by the kernels themselves instead of by a collective library: every
+ * rank owns one "slab" (receive rows, their scale / local expert / return address, the fp32 result rows of its
+ * own routes, row counts and barrier flags), exported by IPC handle and mapped by every other rank of the box.
+ *     fmoe_ep_peer_dispatch   sorts the routes by destination, quantises each token once and stores its rows
+ *                             straight into the owning ranks' slabs (one region per source rank, so no counts
+ *                             are needed beforehand), then runs a flag barrier that also delivers the counts;
+ *     fmoe_ep_peer_experts    grouped GEMMs over the received rows; the down GEMM's epilogue stores every
+ *                             result row straight into the slab of the rank the route came from, tile by tile
+ *                             while the GEMM runs; then a second barrier;
+ *     fmoe_ep_peer_combine    merges this rank's result rows.
+ * Only plain stores cross NVLink; all loads (TMA included) read local memory.  Nothing synchronises with the host
+ * and no collective library is involved after set-up.  The barrier waits are bounded (5 s, or
+ * FUSED_CPP_MOE_EP_WAIT_MS): a rank that never arrives ends the wait with FMOE_ERR_DEVICE_WAIT in the status
+ * block (fmoe_ep_peer_read_status), not with a hung GPU.  Every rank must make the same sequence of calls.
  * Results are bit-identical to the single-GPU forward.  No counterpart in the reference, which rejects expert
  * parallelism (csrc/moe/arm/i8mm_w8a8/kernels.cpp:488). */
 typedef struct fmoe_ep_peer_context fmoe_ep_peer_context;
@@ -283,14 +285,11 @@ FMOE_API int fmoe_ep_peer_handle(fmoe_ep_peer_context* context, void* handle64);
 FMOE_API int fmoe_ep_peer_connect(fmoe_ep_peer_context* context, const void* handles);
 FMOE_API void fmoe_ep_peer_destroy(fmoe_ep_peer_context* context);
 FMOE_API int64_t fmoe_ep_peer_slab_bytes(const fmoe_ep_peer_context* context);
-/* Sorts this rank's routes by destination rank; dest_counts[world] (device) = rows for every rank.
- * shared_rank >= 0: expert id experts_global is the replicated shared expert, served by that rank. */
-FMOE_API int fmoe_ep_peer_route(fmoe_ep_peer_context* context, const int64_t* topk_ids, int64_t tokens, int32_t experts_global,
-                                int32_t shared_rank, int32_t* dest_counts, void* stream);
-/* count_matrix[s][d] (device) = dest_counts[d] of rank s.  Stores rows and metadata into the peers' slabs. */
+/* shared_rank >= 0: expert id experts_global is the replicated shared expert, served by that rank (the caller
+ * passes its own rank).  Ends with the first barrier. */
 FMOE_API int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* context, const void* x_bf16, const int64_t* topk_ids, int64_t tokens,
-                                   int32_t experts_global, int32_t numerics, const int32_t* count_matrix, void* stream);
-/* Grouped GEMMs over the received rows; result rows go to the source ranks' slabs. */
+                                   int32_t experts_global, int32_t shared_rank, int32_t numerics, void* stream);
+/* Grouped GEMMs over the received rows; result rows go to the source ranks' slabs.  Ends with the second barrier. */
 FMOE_API int fmoe_ep_peer_experts(fmoe_ep_peer_context* context, const void* w13, const float* s13, const void* w2, const float* s2,
                                   const fmoe_config* config, void* stream);
 /* Merge of this rank's result rows in the reference's slot order (tree_merge: the BF16 path's pairwise tree). */
