@@ -21,6 +21,7 @@ cpu_baseline / --impl reference: the CPU port of the reference arithmetic (oracl
 from __future__ import annotations
 
 import argparse
+import atexit
 import json
 import os
 import statistics
@@ -78,59 +79,114 @@ def ncu_traffic_bytes(workload: str) -> float | None:
     return None
 
 
+_SAMPLER_CHILD = r"""
+import sys, time
+import pynvml as nvml
+nvml.nvmlInit()
+uuid, index, period = sys.argv[1], int(sys.argv[2]), float(sys.argv[3])
+try:
+    handle = nvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+except Exception:
+    handle = nvml.nvmlDeviceGetHandleByIndex(index)
+print("max", nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM), flush=True)
+while True:
+    clock = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+    reasons = nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+    print("s", repr(time.time()), clock, reasons, flush=True)
+    time.sleep(period)
+"""
+
+
 class ClockSampler:
-    """Samples SM clock and clock-event reasons through NVML from a thread while the timed region runs
-    (the region lasts tens of milliseconds, too short for a polling nvidia-smi process)."""
+    """SM clock and clock-event reasons of one GPU during a timed region, sampled through NVML by a child process
+    (a thread of the timing process would compete with the launches for the interpreter lock).  The child is
+    started once per GPU and keeps sampling; a region keeps the samples whose time stamps fall inside it."""
 
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+    _children: dict = {}
 
-    def __init__(self, device_index: int, period_s: float = 0.005):
+    def __init__(self, device_index: int, period_s: float = 0.01):
         self.device_index = device_index
         self.period_s = period_s
-        self.thread = None
-        self.stop_flag = False
-        self.clocks: list[int] = []
-        self.reason_bits = 0
-        self.max_clock = None
+        self.begin = None
         self.error = None
 
-    def _run(self, handle, nvml) -> None:
-        while not self.stop_flag:
-            try:
-                self.clocks.append(int(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)))
-                self.reason_bits |= int(nvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
-            except Exception as error:  # noqa: BLE001
-                self.error = repr(error)
-                return
-            time.sleep(self.period_s)
-
-    def start(self) -> None:
+    def _child(self):
+        import queue
+        import subprocess
         import threading
 
-        try:
-            import pynvml as nvml
+        entry = ClockSampler._children.get(self.device_index)
+        if entry is not None:
+            return entry
+        uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
+        if not uuid.startswith("GPU-"):
+            uuid = "GPU-" + uuid
+        process = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, uuid, str(self.device_index), str(self.period_s)],
+                                   stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        lines: "queue.Queue[str]" = queue.Queue()
 
-            nvml.nvmlInit()
-            uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
-            try:
-                handle = nvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode() if not uuid.startswith("GPU-") else uuid.encode())
-            except Exception:  # noqa: BLE001
-                handle = nvml.nvmlDeviceGetHandleByIndex(self.device_index)
-            self.max_clock = int(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
-            self.stop_flag = False
-            self.thread = threading.Thread(target=self._run, args=(handle, nvml), daemon=True)
-            self.thread.start()
+        def pump():
+            for line in process.stdout:
+                lines.put(line)
+
+        threading.Thread(target=pump, daemon=True).start()
+        entry = {"process": process, "lines": lines, "max": None, "samples": []}
+        ClockSampler._children[self.device_index] = entry
+        atexit.register(process.kill)
+        try:  # wait until the child is sampling, so that a short region is not over before its first sample
+            deadline = time.time() + 20.0
+            while time.time() < deadline and not entry["samples"]:
+                self._drain(entry, block=True)
         except Exception as error:  # noqa: BLE001
             self.error = repr(error)
-            self.thread = None
+        return entry
+
+    @staticmethod
+    def _drain(entry, block: bool = False) -> None:
+        import queue
+
+        while True:
+            try:
+                line = entry["lines"].get(timeout=0.2) if block else entry["lines"].get_nowait()
+            except queue.Empty:
+                return
+            block = False
+            parts = line.split()
+            if parts and parts[0] == "max":
+                entry["max"] = int(parts[1])
+            elif parts and parts[0] == "s":
+                entry["samples"].append((float(parts[1]), int(parts[2]), int(parts[3])))
+
+    def prepare(self) -> None:
+        """Starts the child if it is not running yet (takes a second or two: call it before the ranks line up)."""
+        try:
+            self._child()
+        except Exception as error:  # noqa: BLE001
+            self.error = repr(error)
+
+    def start(self) -> None:
+        self.prepare()
+        self.begin = time.time()
 
     def stop(self) -> dict:
-        self.stop_flag = True
-        if self.thread is not None:
-            self.thread.join(timeout=2)
-        reasons = sorted(name for bit, name in self.REASONS.items() if self.reason_bits & bit)
-        result = {"sm_mhz": statistics.median(self.clocks) if self.clocks else None, "sm_max_mhz": self.max_clock,
-                  "reasons": reasons, "samples": len(self.clocks), "source": "nvml"}
+        end = time.time()
+        entry = ClockSampler._children.get(self.device_index)
+        clocks, bits, maximum = [], 0, None
+        if entry is not None:
+            time.sleep(2.5 * self.period_s)  # let the sample that follows the region arrive
+            self._drain(entry)
+            maximum = entry["max"]
+            inside = [s for s in entry["samples"] if self.begin <= s[0] <= end]
+            if not inside:  # a region shorter than the period: the samples next to it
+                inside = sorted(entry["samples"], key=lambda s: min(abs(s[0] - self.begin), abs(s[0] - end)))[:2]
+            clocks = [s[1] for s in inside]
+            for s in inside:
+                bits |= s[2]
+            entry["samples"] = entry["samples"][-8:]
+        reasons = sorted(name for bit, name in self.REASONS.items() if bits & bit)
+        result = {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": maximum, "reasons": reasons,
+                  "samples": len(clocks), "source": "nvml (child process)"}
         if self.error:
             result["error"] = self.error
         return result

@@ -75,25 +75,29 @@ __global__ void __launch_bounds__(1024)
 route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offsets, int tile_a, int tile_b,
                   int* items_a, int* items_b, int max_items, int* scan_tmp, int* status) {
   // Pass 1: per expert, exclusive scan over units (unit_hist becomes the unit's cursor relative to the
-  // expert's first row) and the expert total.  One warp per expert, 32 units per step.
+  // expert's first row) and the expert total.  One thread per expert (adjacent threads read adjacent words);
+  // the units are taken sixteen at a time, all loads of a batch issued before the first store, so the
+  // sweep costs one memory round trip per batch and not one per unit.
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  for (int e = warp; e < experts; e += blockDim.x >> 5) {
-    int carry = 0;
-    for (int base = 0; base < units; base += 32) {
-      const int u = base + lane;
-      const int64_t index = static_cast<int64_t>(u) * experts + e;
-      const int value = u < units ? unit_hist[index] : 0;
-      int inclusive = value;
+  constexpr int kBatch = 16;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int running = 0;
+    for (int base = 0; base < units; base += kBatch) {
+      int values[kBatch];
 #pragma unroll
-      for (int offset = 1; offset < 32; offset <<= 1) {
-        const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
-        if (lane >= offset) inclusive += other;
+      for (int i = 0; i < kBatch; ++i) {
+        const int u = base + i;
+        values[i] = u < units ? unit_hist[static_cast<int64_t>(u) * experts + e] : 0;
       }
-      if (u < units) unit_hist[index] = carry + inclusive - value;
-      carry += __shfl_sync(0xffffffffu, inclusive, 31);
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const int u = base + i;
+        if (u < units) unit_hist[static_cast<int64_t>(u) * experts + e] = running;
+        running += values[i];
+      }
     }
-    if (lane == 0) counts[e] = carry;
+    counts[e] = running;
   }
   __syncthreads();
   if (warp == 0) {
@@ -128,10 +132,11 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
     }
     __syncthreads();
   }
-  if (threadIdx.x == 0) {
+  if (warp == 0) {
     int active = 0;
-    for (int e = 0; e < experts; ++e) active += counts[e] > 0;
-    status[kStatusActive] = active;
+    for (int e = lane; e < experts; e += 32) active += counts[e] > 0;
+    active = warp_sum(active);
+    if (lane == 0) status[kStatusActive] = active;
   }
 }
 

@@ -298,6 +298,8 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
         return layer(xd, wd, idd, **kwargs)
 
     def timed(fn, steps, warmup, sampler=None):
+        if sampler is not None:
+            sampler.prepare()
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
