@@ -36,6 +36,7 @@ EXPORTS = (
     "fmoe_stage_timer_read", "fmoe_route_build_noalloc", "fmoe_ep_dispatch_workspace_bytes", "fmoe_ep_dispatch_prepare",
     "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
     "fmoe_i8gemm_dynamic_scaled_mm_pair", "fmoe_probe_mma_rate",
+    "fmoe_router_topk",
     "fmoe_ep_peer_create", "fmoe_ep_peer_handle", "fmoe_ep_peer_connect", "fmoe_ep_peer_destroy", "fmoe_ep_peer_slab_bytes",
     "fmoe_ep_peer_dispatch", "fmoe_ep_peer_experts", "fmoe_ep_peer_combine", "fmoe_ep_peer_read_status",
 )
@@ -104,6 +105,7 @@ def load() -> ctypes.CDLL:
     lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm_pair.argtypes = [p, i64, i32, p, p, i32, p, p, p, i32, p, p, ctypes.c_size_t, p]
+    lib.fmoe_router_topk.argtypes = [p, p, i64, i32, i32, i32, i32, ctypes.c_float, p, p, p]
     lib.fmoe_ep_peer_create.argtypes = [i32, i32, i64, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_void_p)]
     lib.fmoe_ep_peer_handle.argtypes = [p, p]
     lib.fmoe_ep_peer_connect.argtypes = [p, p]
@@ -410,6 +412,27 @@ def ep_combine_finish(returned_rows, send_order, topk_weights, tokens: int, top_
     check(load().fmoe_ep_combine_finish(_ptr(returned_rows), _ptr(send_order), _ptr(topk_weights), tokens, top_k,
                                         hidden, 1 if tree_merge else 0, _ptr(route_out), _ptr(out), _stream()))
     return out
+
+
+def router_topk(logits: torch.Tensor, top_k: int, *, scoring: str = "softmax", selection_bias: torch.Tensor | None = None,
+                renormalize: bool = True, routed_scaling_factor: float = 1.0):
+    """Expert scores -> (topk_weights fp32 [T, K], topk_ids int64 [T, K]) on the GPU (fmoe_router_topk)."""
+    logits = _require_cuda("logits", logits, torch.float32)
+    if logits.dim() != 2:
+        raise ValueError("logits must be [tokens, experts]")
+    if scoring not in ("softmax", "sigmoid"):
+        raise ValueError("scoring must be 'softmax' or 'sigmoid'")
+    tokens, experts = logits.shape
+    bias = None
+    if selection_bias is not None:
+        bias = _require_cuda("selection_bias", selection_bias, torch.float32)
+        if bias.shape != (experts,):
+            raise ValueError("selection_bias must be [experts]")
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((tokens, top_k), dtype=torch.int64, device=logits.device)
+    check(load().fmoe_router_topk(_ptr(logits), _ptr(bias), tokens, experts, top_k, 1 if scoring == "sigmoid" else 0,
+                                  1 if renormalize else 0, float(routed_scaling_factor), _ptr(weights), _ptr(ids), _stream()))
+    return weights, ids
 
 
 class PeerContext:

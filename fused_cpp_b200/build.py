@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(OUT_DIR, "libfused_moe_b200.so")
-SOURCES = ["api.cu", "route.cu", "quant.cu", "merge.cu", "simt_gemm.cu", "umma_gemm.cu", "umma2_gemm.cu", "ep.cu", "probe.cu"]
+SOURCES = ["api.cu", "route.cu", "quant.cu", "merge.cu", "simt_gemm.cu", "umma_gemm.cu", "umma2_gemm.cu", "ep.cu", "probe.cu", "router.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -101,8 +101,8 @@ int pick_row_tile(int requested, int64_t routes, int experts, bool umma) {
   if (average <= 8) return 16;
   if (average <= 24) return 32;
   if (average <= 48) return 64;
-  if (average <= 160) return 128;
-  return fmoe::kPairRowTile;  // hundreds of rows per expert: the two-SM kernel (256-row work items)
+  if (average <= 96) return 128;
+  return fmoe::kPairRowTile;  // a hundred rows per expert and more: the two-SM kernel (256-row work items)
 }
 
 struct StageTimer {
@@ -709,6 +709,24 @@ int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mod
 }
 
 }  // extern "C"
+
+extern "C" int fmoe_router_topk(const float* logits, const float* selection_bias, int64_t tokens, int32_t experts, int32_t top_k,
+                                int32_t scoring, int32_t renormalize, float routed_scaling_factor, float* topk_weights,
+                                int64_t* topk_ids, void* stream) {
+  int status = check_device();
+  if (status != FMOE_OK) return status;
+  if (tokens < 0 || experts <= 0 || experts > fmoe::kMaxExperts || top_k <= 0 || top_k > 32 || top_k > experts) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "router: experts in 1..%d and top_k in 1..min(32, experts) (got %d, %d)", fmoe::kMaxExperts,
+                experts, top_k);
+  }
+  if (scoring != FMOE_SCORING_SOFTMAX && scoring != FMOE_SCORING_SIGMOID) return fail(FMOE_ERR_INVALID_ARGUMENT, "router: unknown scoring %d", scoring);
+  if (tokens == 0) return FMOE_OK;
+  if (logits == nullptr || topk_weights == nullptr || topk_ids == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "router: null pointer");
+  const cudaError_t error = fmoe::launch_router_topk(logits, selection_bias, tokens, experts, top_k, scoring == FMOE_SCORING_SIGMOID,
+                                                     renormalize != 0, routed_scaling_factor, topk_weights, topk_ids,
+                                                     static_cast<cudaStream_t>(stream));
+  return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "router top-k");
+}
 
 /* ---- expert parallelism over peer memory ---------------------------------------------------------- */
 

@@ -83,6 +83,10 @@ cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows
                                  const uint64_t* peer_slabs, size_t route_out_offset, int hidden, uint64_t* row_out_ptrs,
                                  cudaStream_t stream);
 
+// ---- router.cu: scores -> top-k ids and routing weights, one warp per token (experts <= 2048, top_k <= 32)
+cudaError_t launch_router_topk(const float* logits, const float* selection_bias, int64_t tokens, int experts, int top_k, int sigmoid,
+                               int renormalize, float scaling, float* topk_weights, int64_t* topk_ids, cudaStream_t stream);
+
 // ---- merge.cu
 // W8A8: out[t] = bf16( fma chain over slots of route_out[t*K+slot] * w[t,slot] ).
 // BF16: pairwise tree for K in {2,4,6,8}, chain otherwise.

@@ -71,6 +71,111 @@ __device__ int warp_exclusive_scan(const int* values, int* out, int n, int lane)
   return carry;
 }
 
+// Work items: (expert, first sorted row, rows, group key) for every row tile of every active expert, two lists
+// with independent tile heights (gate_up and down GEMM), plus the number of active experts.  Called by a whole
+// block; scan_tmp has room for 2 * experts + 1 ints (global or shared).
+__device__ void build_items(int experts, const int* counts, const int* offsets, int tile_a, int tile_b, int* items_a, int* items_b,
+                            int max_items, int* scan_tmp, int* status) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int list = 0; list < 2; ++list) {
+    const int tile = list == 0 ? tile_a : tile_b;
+    int* items = list == 0 ? items_a : items_b;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) scan_tmp[e] = (counts[e] + tile - 1) / tile;
+    __syncthreads();
+    if (warp == 0) {
+      const int total = warp_exclusive_scan(scan_tmp, scan_tmp + experts, experts, lane);
+      if (lane == 0) status[list == 0 ? kStatusItems : kStatusItemsB] = total < max_items ? total : max_items;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+      const int tiles = scan_tmp[e];
+      const int first = scan_tmp[experts + e];
+      // The expert's rows are spread evenly over its tiles (in steps of 32 rows, the granularity of the MMA's N):
+      // 290 rows become 160 + 130, not 256 + 34.  Work units of one expert then last about equally long, so
+      // the CTAs that stream the same weight block for different row tiles stay side by side and the second
+      // read comes out of L2.
+      int rows_per = tile;
+      if (tiles > 1) {
+        const int step = tile < 32 ? tile : 32;
+        const int even = ((counts[e] + tiles - 1) / tiles + step - 1) / step * step;
+        if (even <= tile && (tiles - 1) * even < counts[e]) rows_per = even;
+      }
+      for (int t = 0; t < tiles && first + t < max_items; ++t) {
+        int* item = items + 4 * static_cast<int64_t>(first + t);
+        item[0] = e;
+        item[1] = offsets[e] + t * rows_per;
+        item[2] = min(rows_per, counts[e] - t * rows_per);
+        // Group key for the unit order of the grouped GEMM: first item of this expert and its tile count, so
+        // that the row tiles of one (expert, channel block) are consecutive work units (see decode_unit).
+        item[3] = tiles < 2048 ? (first | (tiles << 20)) : ((first + t) | (1 << 20));
+      }
+    }
+    __syncthreads();
+  }
+  if (warp == 0) {
+    int active = 0;
+    for (int e = lane; e < experts; e += 32) active += counts[e] > 0;
+    active = warp_sum(active);
+    if (lane == 0) status[kStatusActive] = active;
+  }
+}
+
+// The whole route build in one block for lists of at most kSmallRoutes entries (decode batches, and the
+// expert-parallel lists at decode): ids and histogram in shared memory, the stable position of a route is its
+// expert's offset plus the number of earlier routes with the same id (a scan of the shared ids, at most
+// kSmallRoutes steps).  Same outputs as the three-kernel form.
+constexpr int kSmallRoutes = 1024;
+
+__global__ void __launch_bounds__(kSmallRoutes)
+route_small_kernel(const int64_t* __restrict__ topk_ids, int routes, const int* __restrict__ valid_count, int region, int experts,
+                   int tile_a, int tile_b, int max_items, int* status, int* counts, int* offsets, int* sorted_routes, int* row_expert,
+                   int* items_a, int* items_b, int* route_pos) {
+  extern __shared__ int small_smem[];
+  int* s_id = small_smem;
+  int* s_counts = s_id + kSmallRoutes;
+  int* s_offsets = s_counts + experts;
+  int* s_tmp = s_offsets + experts + 1;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) s_counts[e] = 0;
+  __syncthreads();
+  const int r = threadIdx.x;
+  int id = -1;
+  bool listed = r < routes;
+  if (listed && valid_count != nullptr) listed = region == 0 ? r < *valid_count : r % region < valid_count[r / region];
+  if (listed) {
+    const int64_t value = topk_ids[r];
+    if (value >= 0 && value < experts) {
+      id = static_cast<int>(value);
+      atomicAdd(s_counts + id, 1);
+    } else {
+      raise_error(status, FMOE_ERR_EXPERT_ID_RANGE, r);
+    }
+  }
+  s_id[r] = id;
+  __syncthreads();
+  if (warp == 0) {
+    const int total = warp_exclusive_scan(s_counts, s_offsets, experts, lane);
+    if (lane == 0) s_offsets[experts] = total;
+  }
+  __syncthreads();
+  int position = -1;
+  if (id >= 0) {
+    int rank = 0;
+    for (int j = 0; j < r; ++j) rank += s_id[j] == id;
+    position = s_offsets[id] + rank;
+    sorted_routes[position] = r;
+    row_expert[position] = id;
+  }
+  if (route_pos != nullptr && r < routes) route_pos[r] = position;
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) {
+    if (e < experts) counts[e] = s_counts[e];
+    offsets[e] = s_offsets[e];
+  }
+  build_items(experts, s_counts, s_offsets, tile_a, tile_b, items_a, items_b, max_items, s_tmp, status);
+}
+
 __global__ void __launch_bounds__(1024)
 route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offsets, int tile_a, int tile_b,
                   int* items_a, int* items_b, int max_items, int* scan_tmp, int* status) {
@@ -105,39 +210,7 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
     if (lane == 0) offsets[experts] = total;
   }
   __syncthreads();
-  // Work items: (expert, first sorted row, rows, 0) for every row tile of every active expert.
-  // Two lists with independent tile heights (gate_up and down GEMM).  scan_tmp holds tiles per expert.
-  for (int list = 0; list < 2; ++list) {
-    const int tile = list == 0 ? tile_a : tile_b;
-    int* items = list == 0 ? items_a : items_b;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) scan_tmp[e] = (counts[e] + tile - 1) / tile;
-    __syncthreads();
-    if (warp == 0) {
-      const int total = warp_exclusive_scan(scan_tmp, scan_tmp + experts, experts, lane);
-      if (lane == 0) status[list == 0 ? kStatusItems : kStatusItemsB] = total < max_items ? total : max_items;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-      const int tiles = scan_tmp[e];
-      const int first = scan_tmp[experts + e];
-      for (int t = 0; t < tiles && first + t < max_items; ++t) {
-        int* item = items + 4 * static_cast<int64_t>(first + t);
-        item[0] = e;
-        item[1] = offsets[e] + t * tile;
-        item[2] = min(tile, counts[e] - t * tile);
-        // Group key for the unit order of the grouped GEMM: first item of this expert and its tile count, so
-        // that the row tiles of one (expert, channel block) are consecutive work units (see decode_unit).
-        item[3] = tiles < 2048 ? (first | (tiles << 20)) : ((first + t) | (1 << 20));
-      }
-    }
-    __syncthreads();
-  }
-  if (warp == 0) {
-    int active = 0;
-    for (int e = lane; e < experts; e += 32) active += counts[e] > 0;
-    active = warp_sum(active);
-    if (lane == 0) status[kStatusActive] = active;
-  }
+  build_items(experts, counts, offsets, tile_a, tile_b, items_a, items_b, max_items, scan_tmp, status);
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -189,6 +262,13 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
                                int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos,
                                const int* valid_count, int region) {
+  if (routes <= kSmallRoutes) {
+    const size_t small_bytes = (static_cast<size_t>(kSmallRoutes) + 4 * static_cast<size_t>(experts) + 4) * sizeof(int);
+    route_small_kernel<<<1, kSmallRoutes, small_bytes, stream>>>(topk_ids, static_cast<int>(routes), valid_count, region, experts, tile_a,
+                                                                 tile_b, max_items, status, counts, offsets, sorted_routes, row_expert,
+                                                                 items_a, items_b, route_pos);
+    return cudaGetLastError();
+  }
   const int units = static_cast<int>((routes + kUnitRoutes - 1) / kUnitRoutes);
   int* unit_hist = scratch;
   int* scan_tmp = scratch + static_cast<int64_t>(units > 0 ? units : 1) * experts;
