@@ -66,7 +66,10 @@ def _worker(rank, world, port, scenario, queue):
             dist.destroy_process_group()
 
 
-def _run(scenario, world=2):
+_RENDEZVOUS_TROUBLE = ("Address already in use", "Connection refused", "Connection reset", "timed out", "Timed out")
+
+
+def _run_once(scenario, world):
     context = mp.get_context("spawn")
     queue = context.Queue()
     port = _free_port()
@@ -77,6 +80,16 @@ def _run(scenario, world=2):
     for p in procs:
         p.join(timeout=60)
     return {rank: (status, payload) for rank, status, payload in results}
+
+
+def _run(scenario, world=2):
+    # The port is picked before the ranks start, so another process can take it in between; a rendezvous that
+    # fails for that reason (and only for that reason) is tried once more on a fresh port.
+    results = _run_once(scenario, world)
+    trouble = [payload for status, payload in results.values() if status == "error" and any(t in str(payload) for t in _RENDEZVOUS_TROUBLE)]
+    if trouble:
+        results = _run_once(scenario, world)
+    return results
 
 
 def _shard(case, rank, world, shared=None):
