@@ -502,7 +502,8 @@ def run_multi_gpu(args) -> None:
     from fused_cpp_b200 import ep
 
     args.hidden, args.inter, args.top_k = H, I, K
-    args.ep_points = ["w8a8_ep_shared_v3_T16384"]
+    # "workload:bf16_return" would add the same workload with the opt-in compact return (not bit-identical).
+    args.ep_points = os.environ.get("FUSED_CPP_MOE_EP_POINTS", "w8a8_ep_shared_v3_T16384").split(",")
     args.clock_sampler = ClockSampler
     args.roofline = gate_up_roofline
     ep.bench_main(args, WORKLOADS, SEED, measured_peaks())

@@ -106,7 +106,7 @@ def load() -> ctypes.CDLL:
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm_pair.argtypes = [p, i64, i32, p, p, i32, p, p, p, i32, p, p, ctypes.c_size_t, p]
     lib.fmoe_router_topk.argtypes = [p, p, i64, i32, i32, i32, i32, ctypes.c_float, p, p, p]
-    lib.fmoe_ep_peer_create.argtypes = [i32, i32, i64, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_void_p)]
+    lib.fmoe_ep_peer_create.argtypes = [i32, i32, i64, i32, i32, i32, i32, i32, i32, ctypes.POINTER(ctypes.c_void_p)]
     lib.fmoe_ep_peer_handle.argtypes = [p, p]
     lib.fmoe_ep_peer_connect.argtypes = [p, p]
     lib.fmoe_ep_peer_destroy.argtypes = [p]
@@ -439,12 +439,13 @@ class PeerContext:
     """One rank's side of the peer-memory expert-parallel exchange (fmoe_ep_peer_*): owns the slab that the other
     ranks write into.  The caller exchanges the 64-byte handles and provides the collectives between the stages."""
 
-    def __init__(self, world: int, rank: int, tokens_max: int, top_k: int, hidden: int, inter: int, local_experts: int, int8: bool):
+    def __init__(self, world: int, rank: int, tokens_max: int, top_k: int, hidden: int, inter: int, local_experts: int, int8: bool,
+                 return_bf16: bool = False):
         self.world, self.rank, self.top_k, self.hidden, self.int8 = world, rank, top_k, hidden, int8
         self.tokens_max = tokens_max
         handle = ctypes.c_void_p()
         check(load().fmoe_ep_peer_create(world, rank, tokens_max, top_k, hidden, inter, local_experts, 1 if int8 else 0,
-                                         ctypes.byref(handle)))
+                                         1 if return_bf16 else 0, ctypes.byref(handle)))
         self.handle = handle
 
     def ipc_handle(self) -> bytes:

@@ -136,6 +136,7 @@ struct Forward {
   const void* rows_source = nullptr;
   const uint64_t* peer_slabs = nullptr;
   size_t peer_route_out_offset = 0;
+  bool peer_rows_bf16 = false;  // result rows travel as bf16 (opt-in, not bit-identical to the fp32 merge input)
 };
 
 int run_forward(const Forward& f, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes, void* stream_ptr) {
@@ -232,7 +233,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (peer) {
     row_out_ptrs = reinterpret_cast<uint64_t*>(base + layout.route_out);
     error = fmoe::launch_peer_row_ptrs(sorted_routes, offsets + f.experts, routes, f.rows_source, f.peer_slabs, f.peer_route_out_offset,
-                                       f.hidden, row_out_ptrs, stream);
+                                       f.hidden * (f.peer_rows_bf16 ? 2 : 4), row_out_ptrs, stream);
     if (error != cudaSuccess) return cuda_fail(error, "peer output addresses");
   }
   mark(FMOE_STAGE_ROUTE + 1);
@@ -301,6 +302,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   dn.y = nullptr;
   dn.route_out = route_out;
   dn.row_out_ptrs = row_out_ptrs;
+  dn.route_out_bf16 = peer && f.peer_rows_bf16 ? 1 : 0;
   dn.dump_acc = cfg.dump_acc2;
   dn.row_tile = tile_dn;
   error = umma ? fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
@@ -731,7 +733,7 @@ extern "C" int fmoe_router_topk(const float* logits, const float* selection_bias
 /* ---- expert parallelism over peer memory ---------------------------------------------------------- */
 
 struct fmoe_ep_peer_context {
-  int world = 0, rank = 0, top_k = 0, hidden = 0, inter = 0, local_experts = 0, int8 = 0;
+  int world = 0, rank = 0, top_k = 0, hidden = 0, inter = 0, local_experts = 0, int8 = 0, rows_bf16 = 0;
   int64_t tokens_max = 0, capacity = 0;
   fmoe::PeerSlabLayout slab{};
   char* slab_base = nullptr;          // this rank's slab (cudaMalloc, exported by IPC handle)
@@ -790,7 +792,7 @@ DispatchScratch carve_dispatch(char* base, int64_t routes, int world) {
 extern "C" {
 
 int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t top_k, int32_t hidden, int32_t inter,
-                        int32_t local_experts, int32_t int8, fmoe_ep_peer_context** out) {
+                        int32_t local_experts, int32_t int8, int32_t return_bf16, fmoe_ep_peer_context** out) {
   int status = check_device();
   if (status != FMOE_OK) return status;
   if (out == nullptr || world <= 0 || world > 64 || rank < 0 || rank >= world || tokens_max <= 0 || top_k <= 0 || top_k > 32 ||
@@ -807,6 +809,7 @@ int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t
   ctx->inter = inter;
   ctx->local_experts = local_experts;
   ctx->int8 = int8 ? 1 : 0;
+  ctx->rows_bf16 = return_bf16 ? 1 : 0;
   ctx->tokens_max = tokens_max;
   // Worst case: every route of every rank lands here.
   ctx->capacity = static_cast<int64_t>(world) * tokens_max * top_k;
@@ -951,6 +954,7 @@ int fmoe_ep_peer_experts(fmoe_ep_peer_context* ctx, const void* w13, const float
   f.rows_source = ctx->slab_base + ctx->slab.source;
   f.peer_slabs = ctx->peer_slabs_dev;
   f.peer_route_out_offset = ctx->slab.route_out;
+  f.peer_rows_bf16 = ctx->rows_bf16 != 0;
   const int status = run_forward(f, config, nullptr, ctx->expert_ws, ctx->expert_ws_bytes, stream);
   if (status != FMOE_OK) return status;
   // After this barrier every result row of this rank's routes has arrived, and every rank is done reading its slab.
@@ -968,9 +972,12 @@ int fmoe_ep_peer_combine(fmoe_ep_peer_context* ctx, const float* topk_weights, i
   if (tokens < 0 || tokens > ctx->tokens_max) return fail(FMOE_ERR_INVALID_ARGUMENT, "tokens exceed the context's maximum");
   if (tokens == 0) return FMOE_OK;
   if (topk_weights == nullptr || out == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
-  const cudaError_t error = fmoe::launch_merge(reinterpret_cast<const float*>(ctx->slab_base + ctx->slab.route_out), topk_weights, tokens,
-                                               ctx->top_k, ctx->hidden, tree_merge, static_cast<uint16_t*>(out),
-                                               static_cast<cudaStream_t>(stream_ptr));
+  const char* rows = ctx->slab_base + ctx->slab.route_out;
+  const cudaError_t error =
+      ctx->rows_bf16 ? fmoe::launch_merge_bf16_rows(reinterpret_cast<const uint16_t*>(rows), topk_weights, tokens, ctx->top_k, ctx->hidden,
+                                                    tree_merge, static_cast<uint16_t*>(out), static_cast<cudaStream_t>(stream_ptr))
+                     : fmoe::launch_merge(reinterpret_cast<const float*>(rows), topk_weights, tokens, ctx->top_k, ctx->hidden, tree_merge,
+                                          static_cast<uint16_t*>(out), static_cast<cudaStream_t>(stream_ptr));
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer combine");
 }
 

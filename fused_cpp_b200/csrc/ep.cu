@@ -186,11 +186,11 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
 // memory of the rank the route came from.
 __global__ void peer_row_ptrs_kernel(const int* __restrict__ sorted_routes, const int* __restrict__ valid_rows, int64_t capacity,
                                      const int2* __restrict__ source, const uint64_t* __restrict__ peer_slabs, size_t route_out_offset,
-                                     int hidden, uint64_t* __restrict__ row_out_ptrs) {
+                                     int row_bytes, uint64_t* __restrict__ row_out_ptrs) {
   const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (p >= capacity || p >= *valid_rows) return;
   const int2 from = source[sorted_routes[p]];
-  row_out_ptrs[p] = peer_slabs[from.x] + route_out_offset + static_cast<uint64_t>(from.y) * hidden * sizeof(float);
+  row_out_ptrs[p] = peer_slabs[from.x] + route_out_offset + static_cast<uint64_t>(from.y) * row_bytes;
 }
 
 }  // namespace
@@ -219,11 +219,11 @@ cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* to
 }
 
 cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows, int64_t capacity, const void* source,
-                                 const uint64_t* peer_slabs, size_t route_out_offset, int hidden, uint64_t* row_out_ptrs,
+                                 const uint64_t* peer_slabs, size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs,
                                  cudaStream_t stream) {
   if (capacity <= 0) return cudaSuccess;
   peer_row_ptrs_kernel<<<static_cast<unsigned>((capacity + 255) / 256), 256, 0, stream>>>(
-      sorted_routes, valid_rows, capacity, static_cast<const int2*>(source), peer_slabs, route_out_offset, hidden, row_out_ptrs);
+      sorted_routes, valid_rows, capacity, static_cast<const int2*>(source), peer_slabs, route_out_offset, row_bytes, row_out_ptrs);
   return cudaGetLastError();
 }
 

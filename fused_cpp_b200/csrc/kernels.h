@@ -80,7 +80,7 @@ cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* to
                                  const PeerSlabLayout& slab, const uint64_t* peer_slabs, int rank, int experts_global,
                                  int experts_per_rank, int numerics, cudaStream_t stream);
 cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows, int64_t capacity, const void* source,
-                                 const uint64_t* peer_slabs, size_t route_out_offset, int hidden, uint64_t* row_out_ptrs,
+                                 const uint64_t* peer_slabs, size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs,
                                  cudaStream_t stream);
 
 // ---- router.cu: scores -> top-k ids and routing weights, one warp per token (experts <= 2048, top_k <= 32)
@@ -92,6 +92,9 @@ cudaError_t launch_router_topk(const float* logits, const float* selection_bias,
 // BF16: pairwise tree for K in {2,4,6,8}, chain otherwise.
 cudaError_t launch_merge(const float* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
                          int tree, uint16_t* out, cudaStream_t stream);
+// Same with the route rows stored as bf16 (opt-in compact return of the expert-parallel path).
+cudaError_t launch_merge_bf16_rows(const uint16_t* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
+                                   int tree, uint16_t* out, cudaStream_t stream);
 
 // ---- grouped GEMM, shared argument block
 struct GroupedGemmArgs {
@@ -122,6 +125,7 @@ struct GroupedGemmArgs {
   // Down GEMM, optional: byte address of the fp32 output row of every sorted row.  Overrides route_out +
   // sorted_routes; the rows may lie in another GPU's memory (expert-parallel return path, plain stores).
   const uint64_t* row_out_ptrs;
+  int route_out_bf16;        // with row_out_ptrs: the result rows are stored as bf16 (2 bytes per channel) instead of fp32
   // Performance diagnosis only (environment FUSED_CPP_MOE_GEMM_DIAG, 0 in production; results are meaningless otherwise):
   // bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.
   int diag;

@@ -34,8 +34,22 @@ __device__ __forceinline__ float merge_fixed(const float* values, const float* w
   return tree_sum<0, TopK>(products);
 }
 
+// Four consecutive values of a route row as fp32.  kBf16Rows: the rows were stored as bf16 (the opt-in compact
+// return of the expert-parallel path); widening is exact, the rounding happened at the store.
+template <bool kBf16Rows>
+__device__ __forceinline__ float4 load_row4(const void* route_out, int64_t element) {
+  if constexpr (kBf16Rows) {
+    const uint2 packed = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(route_out) + element);
+    return make_float4(__uint_as_float(packed.x << 16), __uint_as_float(packed.x & 0xffff0000u), __uint_as_float(packed.y << 16),
+                       __uint_as_float(packed.y & 0xffff0000u));
+  } else {
+    return *reinterpret_cast<const float4*>(static_cast<const float*>(route_out) + element);
+  }
+}
+
+template <bool kBf16Rows>
 __global__ void __launch_bounds__(kMergeThreads)
-merge_kernel(const float* __restrict__ route_out, const float* __restrict__ topk_weights, int top_k, int hidden, int tree,
+merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_weights, int top_k, int hidden, int tree,
              uint16_t* __restrict__ out) {
   __shared__ float weights[kMaxTopK];
   const int64_t token = blockIdx.y;
@@ -43,12 +57,12 @@ merge_kernel(const float* __restrict__ route_out, const float* __restrict__ topk
   __syncthreads();
   const int h = (blockIdx.x * kMergeThreads + threadIdx.x) * 4;
   if (h >= hidden) return;
-  const float* base = route_out + token * top_k * static_cast<int64_t>(hidden) + h;
+  const int64_t base = token * top_k * static_cast<int64_t>(hidden) + h;
   float result[4];
   const bool fixed = tree && (top_k == 2 || top_k == 4 || top_k == 6 || top_k == 8);
   if (fixed) {
     float4 rows[8];
-    for (int slot = 0; slot < top_k; ++slot) rows[slot] = *reinterpret_cast<const float4*>(base + static_cast<int64_t>(slot) * hidden);
+    for (int slot = 0; slot < top_k; ++slot) rows[slot] = load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden);
 #pragma unroll
     for (int lane = 0; lane < 4; ++lane) {
       float values[8];
@@ -64,7 +78,7 @@ merge_kernel(const float* __restrict__ route_out, const float* __restrict__ topk
   } else {
     result[0] = result[1] = result[2] = result[3] = 0.0f;
     for (int slot = 0; slot < top_k; ++slot) {
-      const float4 row = *reinterpret_cast<const float4*>(base + static_cast<int64_t>(slot) * hidden);
+      const float4 row = load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden);
       const float w = weights[slot];
       result[0] = __fmaf_rn(row.x, w, result[0]);
       result[1] = __fmaf_rn(row.y, w, result[1]);
@@ -85,7 +99,16 @@ cudaError_t launch_merge(const float* route_out, const float* topk_weights, int6
   if (tokens <= 0) return cudaSuccess;
   if (top_k > kMaxTopK) return cudaErrorInvalidValue;
   const dim3 grid((hidden / 4 + kMergeThreads - 1) / kMergeThreads, static_cast<unsigned>(tokens));
-  merge_kernel<<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
+  merge_kernel<false><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_merge_bf16_rows(const uint16_t* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
+                                   int tree, uint16_t* out, cudaStream_t stream) {
+  if (tokens <= 0) return cudaSuccess;
+  if (top_k > kMaxTopK) return cudaErrorInvalidValue;
+  const dim3 grid((hidden / 4 + kMergeThreads - 1) / kMergeThreads, static_cast<unsigned>(tokens));
+  merge_kernel<true><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
   return cudaGetLastError();
 }
 

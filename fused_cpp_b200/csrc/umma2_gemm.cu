@@ -520,7 +520,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         } else {
           const float4* scale4 = reinterpret_cast<const float4*>(meta->scale + col0);
           const ulonglong2* rowptr2 = reinterpret_cast<const ulonglong2*>(meta->rowptr + col0);
-          const bool bf16_out = kDense && args.dense_out_bf16;
+          const bool bf16_out = kDense ? args.dense_out_bf16 != 0 : args.route_out_bf16 != 0;
           const uint64_t n_bytes = static_cast<uint64_t>(n) * (bf16_out ? 2 : 4);
           auto body = [&](auto fast_tag, auto native_tag) {
             constexpr bool kFast = decltype(fast_tag)::value;
@@ -547,6 +547,8 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
                   } else {
                     *reinterpret_cast<float*>(rowptrs[h] + n_bytes) = value;
                   }
+                } else if (bf16_out) {
+                  *reinterpret_cast<uint16_t*>(rowptrs[h] + n_bytes) = f32_to_bf16_bits(value);
                 } else {
                   *reinterpret_cast<float*>(rowptrs[h] + n_bytes) = value;
                 }

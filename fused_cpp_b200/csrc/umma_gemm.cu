@@ -304,6 +304,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                   } else {
                     reinterpret_cast<float*>(rowptr)[n] = value;
                   }
+                } else if (args.route_out_bf16) {
+                  reinterpret_cast<uint16_t*>(rowptr)[n] = f32_to_bf16_bits(value);
                 } else {
                   reinterpret_cast<float*>(rowptr)[n] = value;
                 }

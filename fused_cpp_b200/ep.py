@@ -157,12 +157,13 @@ class PeerMemoryExpertParallelMoE:
     into the expert ranks' slabs and the down GEMM's epilogue stores the fp32 result rows straight back; two flag
     barriers through the same slabs order the stages.  After set-up (one exchange of IPC handles through
     torch.distributed) a forward involves no collective library and no host synchronisation.  Bit-identical to
-    ExpertParallelMoE and to the single-GPU forward.  tokens_max bounds the tokens any rank passes to forward();
+    ExpertParallelMoE and to the single-GPU forward; with return_dtype=torch.bfloat16 (opt-in) the result rows travel
+    back rounded to bf16: half the traffic, outputs within a bf16 step of the exact ones, no longer bit-identical.  tokens_max bounds the tokens any rank passes to forward();
     every rank must call forward() the same number of times.
     """
 
     def __init__(self, weights: dict, experts_global: int, *, tokens_max: int, top_k: int, has_shared: bool = False, group=None,
-                 numerics: int = 0, gate_up_tile: int = 0, down_tile: int = 0):
+                 numerics: int = 0, gate_up_tile: int = 0, down_tile: int = 0, return_dtype: torch.dtype = torch.float32):
         from . import _lib
 
         self.group = group
@@ -178,7 +179,11 @@ class PeerMemoryExpertParallelMoE:
         self.hidden = hidden
         self.numerics = numerics
         self.tiles = (gate_up_tile, down_tile)
-        self.context = _lib.PeerContext(self.world, self.rank, int(tokens_max), self.top_k, hidden, two_inter // 2, local_experts, self.int8)
+        if return_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("return_dtype must be torch.float32 (bit-identical to one GPU) or torch.bfloat16 (half the return traffic)")
+        self.return_dtype = return_dtype
+        self.context = _lib.PeerContext(self.world, self.rank, int(tokens_max), self.top_k, hidden, two_inter // 2, local_experts, self.int8,
+                                        return_bf16=return_dtype == torch.bfloat16)
         handles = [None] * self.world
         dist.all_gather_object(handles, self.context.ipc_handle(), group=group)
         self.context.connect(handles)
@@ -253,10 +258,11 @@ def bench_main(args, workloads: dict, seed: int, peaks: dict) -> None:
             raise SystemExit("bench.py needs compute-capability-10.x GPUs")
         hidden, inter, experts, top_k = args.hidden, args.inter, args.experts, args.top_k
         lines = []
-        for name in [args.workload] + ([] if args.no_points else list(args.ep_points)):
+        for entry in [args.workload] + ([] if args.no_points else list(args.ep_points)):
+            name, _, option = entry.partition(":")  # "workload:bf16_return" = the same workload with the compact return
             spec = workloads[name]
             lines.append(_bench_one(name, spec, args, rank, world, device, hidden, inter, experts, top_k, seed, peaks,
-                                    has_shared=spec.get("shared", False)))
+                                    has_shared=spec.get("shared", False), bf16_return=option == "bf16_return"))
         if rank == 0:
             head = lines[0]
             head["points"] = lines[1:]
@@ -265,7 +271,7 @@ def bench_main(args, workloads: dict, seed: int, peaks: dict) -> None:
         dist.destroy_process_group()
 
 
-def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, top_k, seed, peaks, has_shared):
+def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, top_k, seed, peaks, has_shared, bf16_return=False):
     from . import synthetic
 
     kind, tokens = spec["kind"], spec["tokens"]
@@ -287,8 +293,11 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
     xd, wd, idd = x_host.to(device), w_host.to(device), ids_host.to(device)
     local_max = (tokens + world - 1) // world
     if getattr(args, "ep_impl", "peer") == "peer":
-        layer = PeerMemoryExpertParallelMoE(weights, experts, tokens_max=local_max, top_k=top_k, has_shared=has_shared)
+        layer = PeerMemoryExpertParallelMoE(weights, experts, tokens_max=local_max, top_k=top_k, has_shared=has_shared,
+                                            return_dtype=torch.bfloat16 if bf16_return else torch.float32)
         exchange = "rows stored by the dispatch kernel and the down-GEMM epilogue into peer memory over NVLink, flag barriers in the same slabs"
+        if bf16_return:
+            exchange += "; result rows returned as bf16 (opt-in: half the return traffic, outputs within a bf16 step, not bit-identical)"
     else:
         layer = ExpertParallelMoE(weights, experts, has_shared=has_shared)
         exchange = "NCCL all-to-all dispatch/combine"
@@ -324,6 +333,7 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
     # timed as well (eager_ms_per_step).
     launch_mode = "eager"
     replay = step
+    graph = None
     if isinstance(layer, PeerMemoryExpertParallelMoE) and os.environ.get("FUSED_CPP_MOE_EP_GRAPH", "1") != "0":
         try:
             side = torch.cuda.Stream(device=device)
@@ -396,6 +406,13 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
         out_pin.copy_(out, non_blocking=True)
 
     e2e_ms, _ = timed(e2e_step, args.steps, args.warmup)
+    # Every rank is done with every slab before any of them is unmapped and freed.
+    torch.cuda.synchronize()
+    dist.barrier()
+    replay = None
+    graph = None
+    if hasattr(layer, "close"):
+        layer.close()
     local_tokens = x_host.shape[0]
     work = synthetic.algorithmic_work(synthetic.MoEShape(tokens, hidden, inter, experts, top_k), topk_ids, 1 if kind == "int8" else 2,
                                       shared=has_shared)
