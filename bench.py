@@ -339,7 +339,8 @@ def run_point(name: str, layer: dict, device: torch.device, steps: int, warmup: 
         "layer": {"algorithmic_bytes": work["bytes"], "ops": work["ops"], "hbm_gbs": work["bytes"] / (ms_per_step * 1e-3) / 1e9,
                   "hbm_frac": work["bytes"] / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
                   "tops": work["ops"] / (ms_per_step * 1e-3) / 1e12},
-        "gpu_launches_per_step": 8 if kind == "int8" else 7,
+        # route build (1 kernel up to 1024 routes, else 3) + quantise/gather + gate_up (+ requantise) + down + merge
+        "gpu_launches_per_step": (1 if tokens * K <= 1024 else 3) + (5 if kind == "int8" else 4),
     }
     if clocks is not None:
         point["clocks"] = clocks

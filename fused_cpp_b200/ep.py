@@ -414,6 +414,12 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
     if hasattr(layer, "close"):
         layer.close()
     local_tokens = x_host.shape[0]
+    # Kernels of this library per forward on one rank.  Peer form: destination ranks, route build (1 kernel up to
+    # 1024 list entries, else 3), dispatch, barrier | route build, output addresses, row gather (+ scale gather),
+    # gate_up (+ requantise), down, barrier | merge.  (The NCCL form differs by its two barriers and one scatter.)
+    routes_local = local_tokens * (top_k + (1 if has_shared else 0))
+    capacity = world * local_max * (top_k + (1 if has_shared else 0))
+    launches_per_step = (1 + (1 if routes_local <= 1024 else 3) + 2) + ((1 if capacity <= 1024 else 3) + 2 + (3 if kind == "int8" else 1) + 2) + 1
     work = synthetic.algorithmic_work(synthetic.MoEShape(tokens, hidden, inter, experts, top_k), topk_ids, 1 if kind == "int8" else 2,
                                       shared=has_shared)
     return {
@@ -425,7 +431,7 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
                    "l2": "inputs larger than L2: every rank streams its experts' weights each step"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": local_tokens * hidden * 2 + local_tokens * top_k * 12,
                 "d2h_bytes_per_step": local_tokens * hidden * 2},
-        "gpu_launches": (14 if kind == "int8" else 13) * args.steps, "clocks": clocks, "roofline": roofline, "cpu_baseline": None,
+        "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "roofline": roofline, "cpu_baseline": None,
         "launch_mode": launch_mode, "eager_ms_per_step": eager_ms,
         "stage_ms_rank0": {k: round(v, 5) for k, v in stage_ms.items()} if stage_ms else None,
         "layer": {"algorithmic_bytes": work["bytes"], "ops": work["ops"],
