@@ -58,7 +58,7 @@ int check_shape(int64_t tokens, int top_k, int experts, int hidden, int inter) {
 }
 
 // with_route_out = false (peer-memory expert stage): the fp32 route rows live elsewhere and the region only
-// holds one 8-byte output address per row.
+// holds one 8-byte output address per row; the sorted copy of the activation rows is not needed either.
 int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, int inter, fmoe_workspace_layout* layout,
                 bool with_route_out = true) {
   const int status = check_shape(tokens, top_k, experts, hidden, inter);
@@ -81,7 +81,7 @@ int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, i
   layout->row_expert = take(sizeof(int) * rows);
   layout->items = take(sizeof(int) * 4 * max_items * 2);
   layout->scratch = take(fmoe::route_scratch_bytes(routes, experts));
-  layout->a_rows = take(rows * hidden * (int8 ? 1 : 2));
+  layout->a_rows = take(with_route_out ? rows * hidden * (int8 ? 1 : 2) : 256);
   layout->a_scale = take(sizeof(float) * rows);
   layout->y = take(rows * inter * 2);
   layout->yq = take(int8 ? rows * inter : 0);
@@ -128,11 +128,12 @@ struct Forward {
   const float* rows_scale = nullptr;
   float* route_out_override = nullptr;
   bool rows_mode = false;
-  // Peer-memory expert stage: `tokens` is the capacity of the row list, made of regions of rows_region rows of
-  // which rows_valid_count[r] (device) are filled; rows_source[row] = (source rank, flat route) and every result
-  // row is stored into the source rank's slab at peer_slabs[rank] + peer_route_out_offset.
-  const int* rows_valid_count = nullptr;
-  int rows_region = 0;
+  // Peer-memory expert stage: the rows already lie in expert order (sorted_counts[e] rows of local expert e from
+  // sorted_offsets[e]; sorted_offsets[experts] = rows in all; both on the device) in a list of capacity `tokens`;
+  // rows_source[row] = (source rank, flat route) and every result row is stored into the source rank's slab at
+  // peer_slabs[rank] + peer_route_out_offset.  No route build and no gather happen here.
+  const int* sorted_counts = nullptr;
+  const int* sorted_offsets = nullptr;
   const void* rows_source = nullptr;
   const uint64_t* peer_slabs = nullptr;
   size_t peer_route_out_offset = 0;
@@ -147,12 +148,12 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   status = make_layout(f.int8, f.tokens, f.top_k, f.experts, f.hidden, f.inter, &layout, !peer);
   if (status != FMOE_OK) return status;
   if (f.tokens == 0) return FMOE_OK;
-  if (f.x == nullptr || f.w13 == nullptr || f.w2 == nullptr || f.topk_ids == nullptr) {
+  if (f.x == nullptr || f.w13 == nullptr || f.w2 == nullptr || (f.topk_ids == nullptr && !peer)) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
   }
   if (!f.rows_mode && (f.topk_weights == nullptr || out == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
-  if (peer && (!f.rows_mode || f.rows_valid_count == nullptr || f.rows_source == nullptr)) {
-    return fail(FMOE_ERR_INVALID_ARGUMENT, "peer-memory mode needs expert rows with a device-side count and their sources");
+  if (peer && (!f.rows_mode || f.sorted_counts == nullptr || f.sorted_offsets == nullptr || f.rows_source == nullptr)) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "peer-memory mode needs expert-sorted rows with device-side counts and their sources");
   }
   if (peer && config != nullptr && config->gemm_impl == FMOE_GEMM_SIMT) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "peer-memory mode runs on the tensor-core GEMMs only");
@@ -225,21 +226,31 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   mark(0);
   cudaError_t error = cudaMemsetAsync(status_block, 0, sizeof(int) * fmoe::kStatusWords, stream);
   if (error != cudaSuccess) return cuda_fail(error, "cudaMemsetAsync(status)");
-  error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, item_rows_gu, item_rows_dn, max_items, status_block, counts, offsets,
-                                   sorted_routes, row_expert, items_gu, items_dn, scratch, stream,
-                                   reinterpret_cast<int*>(base + layout.route_pos), f.rows_valid_count, f.rows_region);
-  if (error != cudaSuccess) return cuda_fail(error, "route build");
   uint64_t* row_out_ptrs = nullptr;
   if (peer) {
+    // The rows arrived in expert order: only the work items and the output addresses remain to be made.
+    error = fmoe::launch_items_from_counts(f.experts, f.sorted_counts, f.sorted_offsets, item_rows_gu, item_rows_dn, max_items, items_gu,
+                                           items_dn, scratch, status_block, stream);
+    if (error != cudaSuccess) return cuda_fail(error, "work items");
     row_out_ptrs = reinterpret_cast<uint64_t*>(base + layout.route_out);
-    error = fmoe::launch_peer_row_ptrs(sorted_routes, offsets + f.experts, routes, f.rows_source, f.peer_slabs, f.peer_route_out_offset,
+    error = fmoe::launch_peer_row_ptrs(f.sorted_offsets + f.experts, routes, f.rows_source, f.peer_slabs, f.peer_route_out_offset,
                                        f.hidden * (f.peer_rows_bf16 ? 2 : 4), row_out_ptrs, stream);
     if (error != cudaSuccess) return cuda_fail(error, "peer output addresses");
+  } else {
+    error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, item_rows_gu, item_rows_dn, max_items, status_block, counts, offsets,
+                                     sorted_routes, row_expert, items_gu, items_dn, scratch, stream,
+                                     reinterpret_cast<int*>(base + layout.route_pos));
+    if (error != cudaSuccess) return cuda_fail(error, "route build");
   }
   mark(FMOE_STAGE_ROUTE + 1);
-  const int* valid_rows = offsets + f.experts;
+  const int* valid_rows = peer ? f.sorted_offsets + f.experts : offsets + f.experts;
+  const void* gemm_rows = base + layout.a_rows;
+  const float* gemm_row_scale = a_scale;
 
-  if (f.rows_mode && f.int8) {
+  if (peer) {
+    gemm_rows = f.x;  // already sorted, already quantised
+    gemm_row_scale = f.rows_scale;
+  } else if (f.rows_mode && f.int8) {
     // int8 rows travel as H bytes: gather them as H/2 16-bit words, then their scales.
     error = fmoe::launch_gather_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden / 2, sorted_routes, 1, valid_rows,
                                      reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
@@ -257,9 +268,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
 
   fmoe::GroupedGemmArgs gu;
   memset(&gu, 0, sizeof(gu));
-  gu.a_rows = base + layout.a_rows;
+  gu.a_rows = gemm_rows;
   gu.weights = f.w13;
-  gu.a_scale = a_scale;
+  gu.a_scale = gemm_row_scale;
   gu.w_scale = f.s13;
   gu.items = items_gu;
   gu.status = status_block;
@@ -745,7 +756,11 @@ struct fmoe_ep_peer_context {
   size_t dispatch_ws_bytes = 0;
   char* expert_ws = nullptr;
   size_t expert_ws_bytes = 0;
-  int* dest_counts = nullptr;         // [world] rows this rank sends to every rank (last dispatch)
+  int experts_total_max = 0;          // routed experts of all ranks + 1: row length of the count table in the slab
+  int* small = nullptr;               // device: send_base[experts_total_max] | local_counts[local] | local_offsets[local+1] | epoch
+  int* send_base = nullptr;
+  int* local_counts = nullptr;
+  int* local_offsets = nullptr;
   unsigned* epoch = nullptr;          // [1] barrier epoch of this rank
   unsigned long long wait_limit_ns = 5000000000ull;  // bound of the barrier wait (FUSED_CPP_MOE_EP_WAIT_MS)
 };
@@ -754,21 +769,22 @@ namespace {
 
 struct DispatchScratch {
   int* status;
-  int64_t* dest;
-  int* offsets;
-  int* row_rank;
-  int* send_order;
-  int* route_pos;
+  int* counts;      // [experts_total] routes of this rank per global expert
+  int* offsets;     // [experts_total + 1]
+  int* send_order;  // [routes] flat route ids in expert order
+  int* row_expert;  // [routes]
+  int* route_pos;   // [routes] position of every flat route in that order, -1 = dropped
   int* scratch;
 };
 
-size_t dispatch_scratch_bytes(int64_t routes, int world) {
+size_t dispatch_scratch_bytes(int64_t routes, int experts_total) {
   const size_t r = static_cast<size_t>(routes > 0 ? routes : 1);
-  return align_up(sizeof(int) * fmoe::kStatusWords, 256) + align_up(sizeof(int64_t) * r, 256) + align_up(sizeof(int) * (world + 1), 256) +
-         3 * align_up(sizeof(int) * r, 256) + align_up(fmoe::route_scratch_bytes(routes, world), 256);
+  return align_up(sizeof(int) * fmoe::kStatusWords, 256) + align_up(sizeof(int) * experts_total, 256) +
+         align_up(sizeof(int) * (experts_total + 1), 256) + 3 * align_up(sizeof(int) * r, 256) +
+         align_up(fmoe::route_scratch_bytes(routes, experts_total), 256);
 }
 
-DispatchScratch carve_dispatch(char* base, int64_t routes, int world) {
+DispatchScratch carve_dispatch(char* base, int64_t routes, int experts_total) {
   const size_t r = static_cast<size_t>(routes > 0 ? routes : 1);
   char* cursor = base;
   auto take = [&cursor](size_t bytes) {
@@ -778,12 +794,12 @@ DispatchScratch carve_dispatch(char* base, int64_t routes, int world) {
   };
   DispatchScratch d;
   d.status = reinterpret_cast<int*>(take(sizeof(int) * fmoe::kStatusWords));
-  d.dest = reinterpret_cast<int64_t*>(take(sizeof(int64_t) * r));
-  d.offsets = reinterpret_cast<int*>(take(sizeof(int) * (world + 1)));
-  d.row_rank = reinterpret_cast<int*>(take(sizeof(int) * r));
+  d.counts = reinterpret_cast<int*>(take(sizeof(int) * experts_total));
+  d.offsets = reinterpret_cast<int*>(take(sizeof(int) * (experts_total + 1)));
   d.send_order = reinterpret_cast<int*>(take(sizeof(int) * r));
+  d.row_expert = reinterpret_cast<int*>(take(sizeof(int) * r));
   d.route_pos = reinterpret_cast<int*>(take(sizeof(int) * r));
-  d.scratch = reinterpret_cast<int*>(take(fmoe::route_scratch_bytes(routes, world)));
+  d.scratch = reinterpret_cast<int*>(take(fmoe::route_scratch_bytes(routes, experts_total)));
   return d;
 }
 
@@ -820,12 +836,16 @@ int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t
     offset = align_up(offset + bytes, 256);
     return begin;
   };
+  ctx->experts_total_max = world * local_experts + 1;
+  if (ctx->experts_total_max > fmoe::kMaxExperts) {
+    delete ctx;
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "too many experts for the peer context (%d)", world * local_experts);
+  }
   ctx->slab.rows = take(capacity * hidden * (int8 ? 1 : 2));
-  ctx->slab.expert = take(capacity * sizeof(int64_t));
   ctx->slab.scale = take(capacity * sizeof(float));
   ctx->slab.source = take(capacity * 2 * sizeof(int));
   ctx->slab.route_out = take(static_cast<size_t>(tokens_max) * top_k * hidden * sizeof(float));
-  ctx->slab.counts = take(sizeof(int) * world);
+  ctx->slab.counts = take(sizeof(int) * static_cast<size_t>(world) * ctx->experts_total_max);
   ctx->slab.flags = take(sizeof(unsigned) * world);
   ctx->slab.total = offset;
   if (const char* limit = getenv("FUSED_CPP_MOE_EP_WAIT_MS")) {
@@ -839,19 +859,23 @@ int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t
     return status;
   }
   ctx->expert_ws_bytes = layout.total_bytes;
-  ctx->dispatch_ws_bytes = dispatch_scratch_bytes(tokens_max * top_k, world);
+  ctx->dispatch_ws_bytes = dispatch_scratch_bytes(tokens_max * top_k, ctx->experts_total_max);
   cudaError_t error = cudaMalloc(&ctx->slab_base, ctx->slab.total);
   if (error == cudaSuccess) error = cudaMalloc(&ctx->expert_ws, ctx->expert_ws_bytes);
   if (error == cudaSuccess) error = cudaMalloc(&ctx->dispatch_ws, ctx->dispatch_ws_bytes);
   if (error == cudaSuccess) error = cudaMalloc(&ctx->peer_slabs_dev, sizeof(uint64_t) * world);
-  if (error == cudaSuccess) error = cudaMalloc(&ctx->dest_counts, sizeof(int) * (world + 1));
-  if (error == cudaSuccess) error = cudaMemset(ctx->dest_counts, 0, sizeof(int) * (world + 1));
+  const size_t small_ints = static_cast<size_t>(ctx->experts_total_max) + local_experts + (local_experts + 1) + 1;
+  if (error == cudaSuccess) error = cudaMalloc(&ctx->small, sizeof(int) * small_ints);
+  if (error == cudaSuccess) error = cudaMemset(ctx->small, 0, sizeof(int) * small_ints);
   if (error == cudaSuccess) error = cudaMemset(ctx->slab_base + ctx->slab.counts, 0, ctx->slab.total - ctx->slab.counts);
   if (error != cudaSuccess) {
     fmoe_ep_peer_destroy(ctx);
     return cuda_fail(error, "peer context allocation");
   }
-  ctx->epoch = reinterpret_cast<unsigned*>(ctx->dest_counts + world);
+  ctx->send_base = ctx->small;
+  ctx->local_counts = ctx->send_base + ctx->experts_total_max;
+  ctx->local_offsets = ctx->local_counts + local_experts;
+  ctx->epoch = reinterpret_cast<unsigned*>(ctx->local_offsets + local_experts + 1);
   ctx->opened.assign(world, nullptr);
   *out = ctx;
   return FMOE_OK;
@@ -899,7 +923,7 @@ void fmoe_ep_peer_destroy(fmoe_ep_peer_context* ctx) {
   if (ctx->expert_ws) cudaFree(ctx->expert_ws);
   if (ctx->dispatch_ws) cudaFree(ctx->dispatch_ws);
   if (ctx->peer_slabs_dev) cudaFree(ctx->peer_slabs_dev);
-  if (ctx->dest_counts) cudaFree(ctx->dest_counts);
+  if (ctx->small) cudaFree(ctx->small);
   delete ctx;
 }
 
@@ -910,33 +934,47 @@ int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* ctx, const void* x, const int64_
   int status = check_device();
   if (status != FMOE_OK) return status;
   if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
-  if (tokens < 0 || tokens > ctx->tokens_max || experts_global <= 0 || experts_global % ctx->world != 0 || shared_rank >= ctx->world ||
+  const int has_shared = shared_rank >= 0 ? 1 : 0;
+  if (tokens < 0 || tokens > ctx->tokens_max || experts_global <= 0 || experts_global % ctx->world != 0 ||
+      experts_global / ctx->world + has_shared != ctx->local_experts || (has_shared && shared_rank != ctx->rank) ||
       (tokens > 0 && (x == nullptr || topk_ids == nullptr))) {
-    return fail(FMOE_ERR_INVALID_ARGUMENT, "invalid peer dispatch arguments (tokens within the context's maximum, experts divisible by the ranks)");
+    return fail(FMOE_ERR_INVALID_ARGUMENT,
+                "invalid peer dispatch arguments (tokens within the context's maximum, experts split evenly and matching the context's "
+                "local experts, shared_rank = this rank or -1)");
   }
   if (numerics != FMOE_NUMERICS_TORCHREF && numerics != FMOE_NUMERICS_NATIVE) return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown numerics");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const int64_t routes = tokens * ctx->top_k;
-  const int region = static_cast<int>(ctx->tokens_max * ctx->top_k);
-  const DispatchScratch d = carve_dispatch(ctx->dispatch_ws, ctx->tokens_max * ctx->top_k, ctx->world);
+  const int experts_total = experts_global + has_shared;
+  const int per_rank = experts_global / ctx->world;
+  const DispatchScratch d = carve_dispatch(ctx->dispatch_ws, ctx->tokens_max * ctx->top_k, ctx->experts_total_max);
   cudaError_t error = cudaMemsetAsync(d.status, 0, sizeof(int) * fmoe::kStatusWords, stream);
-  if (error == cudaSuccess && routes == 0) error = cudaMemsetAsync(ctx->dest_counts, 0, sizeof(int) * ctx->world, stream);
+  if (error == cudaSuccess && routes == 0) error = cudaMemsetAsync(d.counts, 0, sizeof(int) * experts_total, stream);
   if (error == cudaSuccess && routes > 0) {
-    error = fmoe::launch_dest_ranks(topk_ids, routes, experts_global, experts_global / ctx->world, shared_rank, d.dest, stream);
-  }
-  if (error == cudaSuccess && routes > 0) {
-    // A stable counting sort of the routes by destination rank: the same kernels as the per-expert route build.
-    error = fmoe::launch_route_build(d.dest, routes, ctx->world, 16, 16, 0, d.status, ctx->dest_counts, d.offsets, d.send_order, d.row_rank,
+    // Stable counting sort of this rank's routes by global expert id (the shared expert is id experts_global):
+    // expert order is destination-rank order, and inside a destination its local expert order.
+    error = fmoe::launch_route_build(topk_ids, routes, experts_total, 16, 16, 0, d.status, d.counts, d.offsets, d.send_order, d.row_expert,
                                      nullptr, nullptr, d.scratch, stream, d.route_pos);
   }
   if (error == cudaSuccess) {
-    error = fmoe::launch_peer_dispatch(ctx->int8 != 0, static_cast<const uint16_t*>(x), topk_ids, tokens, ctx->hidden, ctx->top_k, d.dest,
-                                       d.route_pos, d.offsets, region, ctx->slab, ctx->peer_slabs_dev, ctx->rank, experts_global,
-                                       experts_global / ctx->world, numerics, stream);
+    // Every rank learns every rank's counts per expert (row `rank` of the table in each slab) ...
+    error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, d.counts, ctx->experts_total_max, ctx->world, ctx->rank, ctx->epoch,
+                                      d.status, ctx->wait_limit_ns, stream);
   }
   if (error == cudaSuccess) {
-    // Row counts to the destinations, then the barrier: after it every rank's region of this slab is complete.
-    error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, ctx->dest_counts, ctx->world, ctx->rank, ctx->epoch, d.status,
+    // ... and derives from them where its rows go and what it will receive.
+    error = fmoe::launch_peer_layout(reinterpret_cast<const int*>(ctx->slab_base + ctx->slab.counts), ctx->world, ctx->rank, experts_global,
+                                     per_rank, has_shared, ctx->experts_total_max, ctx->send_base, ctx->local_counts, ctx->local_offsets,
+                                     stream);
+  }
+  if (error == cudaSuccess) {
+    error = fmoe::launch_peer_dispatch(ctx->int8 != 0, static_cast<const uint16_t*>(x), topk_ids, tokens, ctx->hidden, ctx->top_k,
+                                       d.route_pos, d.offsets, ctx->send_base, ctx->slab, ctx->peer_slabs_dev, ctx->rank, experts_global,
+                                       per_rank, has_shared, numerics, stream);
+  }
+  if (error == cudaSuccess) {
+    // After this barrier every row of this rank's experts has arrived.
+    error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, nullptr, 0, ctx->world, ctx->rank, ctx->epoch, d.status,
                                       ctx->wait_limit_ns, stream);
   }
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer dispatch");
@@ -945,12 +983,12 @@ int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* ctx, const void* x, const int64_
 int fmoe_ep_peer_experts(fmoe_ep_peer_context* ctx, const void* w13, const float* s13, const void* w2, const float* s2,
                          const fmoe_config* config, void* stream) {
   if (ctx == nullptr || !ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context missing or not connected");
-  Forward f{ctx->int8 != 0, ctx->slab_base + ctx->slab.rows, w13, s13, w2, s2, nullptr,
-            reinterpret_cast<const int64_t*>(ctx->slab_base + ctx->slab.expert), ctx->capacity, 1, ctx->local_experts, ctx->hidden, ctx->inter};
+  Forward f{ctx->int8 != 0, ctx->slab_base + ctx->slab.rows, w13, s13, w2, s2, nullptr, nullptr, ctx->capacity, 1, ctx->local_experts,
+            ctx->hidden, ctx->inter};
   f.rows_scale = reinterpret_cast<const float*>(ctx->slab_base + ctx->slab.scale);
   f.rows_mode = true;
-  f.rows_valid_count = reinterpret_cast<const int*>(ctx->slab_base + ctx->slab.counts);
-  f.rows_region = static_cast<int>(ctx->tokens_max * ctx->top_k);
+  f.sorted_counts = ctx->local_counts;
+  f.sorted_offsets = ctx->local_offsets;
   f.rows_source = ctx->slab_base + ctx->slab.source;
   f.peer_slabs = ctx->peer_slabs_dev;
   f.peer_route_out_offset = ctx->slab.route_out;
@@ -958,7 +996,7 @@ int fmoe_ep_peer_experts(fmoe_ep_peer_context* ctx, const void* w13, const float
   const int status = run_forward(f, config, nullptr, ctx->expert_ws, ctx->expert_ws_bytes, stream);
   if (status != FMOE_OK) return status;
   // After this barrier every result row of this rank's routes has arrived, and every rank is done reading its slab.
-  const cudaError_t error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, nullptr, ctx->world, ctx->rank, ctx->epoch,
+  const cudaError_t error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, nullptr, 0, ctx->world, ctx->rank, ctx->epoch,
                                                       reinterpret_cast<int*>(ctx->expert_ws), ctx->wait_limit_ns,
                                                       static_cast<cudaStream_t>(stream));
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer barrier");

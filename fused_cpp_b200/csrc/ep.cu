@@ -43,25 +43,34 @@ __global__ void scatter_rows_f32_kernel(const float* __restrict__ rows, const in
 // ---- peer-memory path: rows go straight into the expert rank's receive slab, results straight back ----
 
 // Barrier between the ranks of the box, through flags in the slabs.  Every rank bumps its own epoch, (optionally)
-// tells every destination how many rows it has just stored there, then stores the epoch into its flag in every
-// rank's slab and waits until all flags in its own slab have reached that epoch.  The stores of the kernels that
-// ran before it on this stream are complete when it starts (stream order), and the fence orders its own stores,
-// so a rank that sees the flag also sees the rows.  The wait is bounded: after limit_ns it records
-// FMOE_ERR_DEVICE_WAIT (detail = the rank it waited for) and returns.
-__global__ void __launch_bounds__(64)
-peer_barrier_kernel(const uint64_t* __restrict__ peer_slabs, PeerSlabLayout slab, const int* __restrict__ dest_counts, int world, int rank,
-                    unsigned* __restrict__ epoch_counter, int* status, unsigned long long limit_ns) {
+// first stores a vector of ints into row `rank` of a table in every slab (the per-expert route counts), then
+// stores the epoch into its flag in every rank's slab and waits until all flags in its own slab have reached
+// that epoch.  The stores of the kernels that ran before it on this stream are complete when it starts (stream
+// order), and the fence orders its own stores, so a rank that sees the flag also sees the rows and the table
+// row.  The wait is bounded: after limit_ns it records FMOE_ERR_DEVICE_WAIT (detail = the rank it waited for)
+// and returns.
+__global__ void __launch_bounds__(256)
+peer_barrier_kernel(const uint64_t* __restrict__ peer_slabs, PeerSlabLayout slab, const int* __restrict__ payload, int payload_ints,
+                    int world, int rank, unsigned* __restrict__ epoch_counter, int* status, unsigned long long limit_ns) {
   __shared__ unsigned epoch_shared;
   if (threadIdx.x == 0) {
     epoch_shared = *epoch_counter + 1u;
     *epoch_counter = epoch_shared;
   }
+  if (payload != nullptr) {
+    const size_t row = slab.counts + sizeof(int) * static_cast<size_t>(rank) * payload_ints;
+    for (int i = threadIdx.x; i < world * payload_ints; i += blockDim.x) {
+      const int peer = i / payload_ints;
+      const int k = i - peer * payload_ints;
+      reinterpret_cast<volatile int*>(peer_slabs[peer] + row)[k] = payload[k];
+    }
+  }
+  __threadfence_system();
   __syncthreads();
   const unsigned epoch = epoch_shared;
   const int peer = threadIdx.x;
   if (peer >= world) return;
   const uint64_t theirs = peer_slabs[peer];
-  if (dest_counts != nullptr) *reinterpret_cast<volatile int*>(theirs + slab.counts + sizeof(int) * rank) = dest_counts[peer];
   __threadfence_system();
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs + slab.flags + sizeof(unsigned) * rank), "r"(epoch) : "memory");
   const uint64_t mine = peer_slabs[rank] + slab.flags + sizeof(unsigned) * peer;
@@ -80,6 +89,76 @@ peer_barrier_kernel(const uint64_t* __restrict__ peer_slabs, PeerSlabLayout slab
   }
 }
 
+// After the count exchange every rank holds C[source][expert] for all experts (experts_total = routed experts
+// + 1 if there is a shared expert, whose routes stay on their own rank).  The rows of one expert lie together at
+// its owner, sources in rank order, experts in local order (the shared expert last); from C every rank computes
+//   send_base[e]    where this rank's rows for expert e start in the owner's slab, and, as an owner,
+//   local_counts / local_offsets of its own experts (offsets[local_experts] = rows received in all).
+// One block.
+__global__ void __launch_bounds__(1024)
+peer_layout_kernel(const int* __restrict__ count_matrix, int row_stride, int world, int rank, int experts_global, int per_rank,
+                   int has_shared, int* __restrict__ send_base, int* __restrict__ local_counts, int* __restrict__ local_offsets) {
+  extern __shared__ int layout_smem[];
+  const int experts_total = experts_global + (has_shared ? 1 : 0);
+  int* total = layout_smem;                  // rows of expert e at its owner
+  int* before_me = total + experts_total;    // rows of expert e from lower source ranks
+  int* scan = before_me + experts_total;     // exclusive scan of total[] over the routed experts (+ end)
+  for (int e = threadIdx.x; e < experts_total; e += blockDim.x) {
+    int sum = 0, lower = 0;
+    if (e < experts_global) {
+      for (int s = 0; s < world; ++s) {
+        const int c = count_matrix[s * row_stride + e];
+        if (s < rank) lower += c;
+        sum += c;
+      }
+    } else {
+      sum = count_matrix[rank * row_stride + e];  // the shared expert: only this rank's own routes, kept here
+    }
+    total[e] = sum;
+    before_me[e] = lower;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // exclusive scan over the routed experts, 32 per step
+    int carry = 0;
+    for (int base = 0; base < experts_global; base += 32) {
+      const int e = base + threadIdx.x;
+      const int value = e < experts_global ? total[e] : 0;
+      int inclusive = value;
+#pragma unroll
+      for (int offset = 1; offset < 32; offset <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+        if (threadIdx.x >= offset) inclusive += other;
+      }
+      if (e < experts_global) scan[e] = carry + inclusive - value;
+      carry += __shfl_sync(0xffffffffu, inclusive, 31);
+    }
+    if (threadIdx.x == 0) scan[experts_global] = carry;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts_total; e += blockDim.x) {
+    if (e < experts_global) {
+      const int owner = e / per_rank;
+      send_base[e] = scan[e] - scan[owner * per_rank] + before_me[e];
+    } else {
+      send_base[e] = scan[(rank + 1) * per_rank] - scan[rank * per_rank];  // after this rank's routed experts
+    }
+  }
+  const int local_experts = per_rank + (has_shared ? 1 : 0);
+  for (int le = threadIdx.x; le <= local_experts; le += blockDim.x) {
+    const int first = rank * per_rank;
+    const int routed_end = scan[first + per_rank] - scan[first];
+    if (le < per_rank) {
+      local_counts[le] = total[first + le];
+      local_offsets[le] = scan[first + le] - scan[first];
+    } else if (le == per_rank && has_shared) {
+      local_counts[le] = total[experts_global];
+      local_offsets[le] = routed_end;
+    }
+    if (le == local_experts) local_offsets[le] = routed_end + (has_shared ? total[experts_global] : 0);
+  }
+}
+
 __device__ __forceinline__ void unpack8_bf16(const uint4& v, float* out) {
   const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -89,30 +168,32 @@ __device__ __forceinline__ void unpack8_bf16(const uint4& v, float* out) {
   }
 }
 
-// One CTA per token.  A destination's slab is divided into one region of `region` rows per source rank, so a
-// source needs to know nothing about the others before it stores.  The token row is quantised once (int8) or taken as it is (bf16) and stored, with plain
+// One CTA per token.  send_base[e] is where this rank's rows for expert e start in the owner's slab (see
+// peer_layout_kernel), so every row lands at its final, expert-sorted position.  The token row is quantised once (int8) or taken as it is (bf16) and stored, with plain
 // 16-byte stores, into the receive slab of the rank that owns each of its routes' experts, together with the
 // route's scale, local expert id and return address (source rank, flat route).  Same bits as
 // quantize_tokens_scatter / gather_rows on one GPU.
 template <bool kInt8>
 __global__ void __launch_bounds__(256)
 peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__ topk_ids, int cols, int top_k,
-                     const int64_t* __restrict__ dest, const int* __restrict__ route_pos, const int* __restrict__ dest_offsets,
-                     int region, PeerSlabLayout slab, const uint64_t* __restrict__ peer_slabs, int rank,
-                     int experts_global, int experts_per_rank, int numerics) {
+                     const int* __restrict__ route_pos, const int* __restrict__ expert_offsets, const int* __restrict__ send_base,
+                     PeerSlabLayout slab, const uint64_t* __restrict__ peer_slabs, int rank, int experts_global, int experts_per_rank,
+                     int has_shared, int numerics) {
   __shared__ float reduce[32];
   __shared__ int64_t slot_row[32];    // row index in the destination slab, -1 = dropped
   __shared__ uint64_t slot_slab[32];  // base address of the destination slab
   const int64_t token = blockIdx.x;
   if (threadIdx.x < top_k) {
     const int64_t route = token * top_k + threadIdx.x;
-    const int64_t d = dest[route];
-    const int position = route_pos[route];
+    const int64_t id = topk_ids[route];
+    const int position = route_pos[route];  // position in this rank's expert-sorted route list, -1 = dropped
     int64_t row = -1;
     uint64_t base = 0;
-    if (d >= 0 && position >= 0) {
-      row = static_cast<int64_t>(rank) * region + (position - dest_offsets[d]);  // this rank's region of the destination's slab
-      base = peer_slabs[d];
+    if (position >= 0) {
+      const int e = static_cast<int>(id);
+      const int owner = (has_shared && e == experts_global) ? rank : e / experts_per_rank;
+      row = send_base[e] + (position - expert_offsets[e]);
+      base = peer_slabs[owner];
     }
     slot_row[threadIdx.x] = row;
     slot_slab[threadIdx.x] = base;
@@ -144,8 +225,6 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
     const int64_t route = token * top_k + threadIdx.x;
     const int64_t row = slot_row[threadIdx.x];
     const uint64_t base = slot_slab[threadIdx.x];
-    const int64_t id = topk_ids[route];
-    reinterpret_cast<int64_t*>(base + slab.expert)[row] = id >= experts_global ? experts_per_rank : id % experts_per_rank;
     if (kInt8) reinterpret_cast<float*>(base + slab.scale)[row] = scale;
     reinterpret_cast<int2*>(base + slab.source)[row] = make_int2(rank, static_cast<int>(route));
   }
@@ -182,48 +261,54 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
   }
 }
 
-// After the expert rank's route build: the byte address of the fp32 result row of every sorted row, in the
-// memory of the rank the route came from.
-__global__ void peer_row_ptrs_kernel(const int* __restrict__ sorted_routes, const int* __restrict__ valid_rows, int64_t capacity,
+// The byte address of the result row of every received row, in the memory of the rank the route came from.
+__global__ void peer_row_ptrs_kernel(const int* __restrict__ valid_rows, int64_t capacity,
                                      const int2* __restrict__ source, const uint64_t* __restrict__ peer_slabs, size_t route_out_offset,
                                      int row_bytes, uint64_t* __restrict__ row_out_ptrs) {
   const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (p >= capacity || p >= *valid_rows) return;
-  const int2 from = source[sorted_routes[p]];
+  const int2 from = source[p];
   row_out_ptrs[p] = peer_slabs[from.x] + route_out_offset + static_cast<uint64_t>(from.y) * row_bytes;
 }
 
 }  // namespace
 
-cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* dest_counts, int world, int rank,
-                                unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream) {
-  peer_barrier_kernel<<<1, 64, 0, stream>>>(peer_slabs, slab, dest_counts, world, rank, epoch_counter, status, limit_ns);
+cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* payload, int payload_ints, int world,
+                                int rank, unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream) {
+  peer_barrier_kernel<<<1, 256, 0, stream>>>(peer_slabs, slab, payload, payload_ints, world, rank, epoch_counter, status, limit_ns);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_layout(const int* count_matrix, int world, int rank, int experts_global, int per_rank, int has_shared,
+                               int row_stride, int* send_base, int* local_counts, int* local_offsets, cudaStream_t stream) {
+  const size_t smem = (3 * static_cast<size_t>(experts_global + 1) + 1) * sizeof(int);
+  peer_layout_kernel<<<1, 1024, smem, stream>>>(count_matrix, row_stride, world, rank, experts_global, per_rank, has_shared, send_base,
+                                                local_counts, local_offsets);
   return cudaGetLastError();
 }
 
 cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
-                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, int region,
-                                 const PeerSlabLayout& slab, const uint64_t* peer_slabs, int rank, int experts_global,
-                                 int experts_per_rank, int numerics, cudaStream_t stream) {
+                                 const int* route_pos, const int* expert_offsets, const int* send_base, const PeerSlabLayout& slab,
+                                 const uint64_t* peer_slabs, int rank, int experts_global, int experts_per_rank, int has_shared,
+                                 int numerics, cudaStream_t stream) {
   if (tokens <= 0) return cudaSuccess;
   if (int8) {
-    peer_dispatch_kernel<true><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, dest, route_pos, dest_offsets,
-                                                                                  region, slab, peer_slabs, rank, experts_global,
-                                                                                  experts_per_rank, numerics);
+    peer_dispatch_kernel<true><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, route_pos, expert_offsets, send_base,
+                                                                                  slab, peer_slabs, rank, experts_global, experts_per_rank,
+                                                                                  has_shared, numerics);
   } else {
-    peer_dispatch_kernel<false><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, dest, route_pos, dest_offsets,
-                                                                                   region, slab, peer_slabs, rank, experts_global,
-                                                                                   experts_per_rank, numerics);
+    peer_dispatch_kernel<false><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, route_pos, expert_offsets, send_base,
+                                                                                   slab, peer_slabs, rank, experts_global, experts_per_rank,
+                                                                                   has_shared, numerics);
   }
   return cudaGetLastError();
 }
 
-cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows, int64_t capacity, const void* source,
-                                 const uint64_t* peer_slabs, size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs,
-                                 cudaStream_t stream) {
+cudaError_t launch_peer_row_ptrs(const int* valid_rows, int64_t capacity, const void* source, const uint64_t* peer_slabs,
+                                 size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs, cudaStream_t stream) {
   if (capacity <= 0) return cudaSuccess;
   peer_row_ptrs_kernel<<<static_cast<unsigned>((capacity + 255) / 256), 256, 0, stream>>>(
-      sorted_routes, valid_rows, capacity, static_cast<const int2*>(source), peer_slabs, route_out_offset, row_bytes, row_out_ptrs);
+      valid_rows, capacity, static_cast<const int2*>(source), peer_slabs, route_out_offset, row_bytes, row_out_ptrs);
   return cudaGetLastError();
 }
 

@@ -22,6 +22,9 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
                                int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream,
                                int* route_pos = nullptr, const int* valid_count = nullptr, int region = 0);
 
+// Work items from per-expert counts / offsets of rows that are already in expert order (scratch: 2 * experts + 1 ints).
+cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, int tile_a, int tile_b, int max_items,
+                                     int* items_a, int* items_b, int* scratch, int* status, cudaStream_t stream);
 // Work items of a dense [rows, K] x [N, K]^T product: one "expert", consecutive row tiles.
 cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream);
 
@@ -63,25 +66,24 @@ cudaError_t launch_scatter_rows_f32(const float* rows, const int* order, int64_t
 // Peer-memory path.  Every rank owns one slab with the same layout (byte offsets below); peer_slabs[r] is the
 // address of rank r's slab as mapped into this process.
 struct PeerSlabLayout {
-  size_t rows;       // [capacity, H] int8 or bf16: received rows, grouped by source rank
-  size_t expert;     // [capacity] int64: local expert id of each received row
+  size_t rows;       // [capacity, H] int8 or bf16: received rows in expert order (sources in rank order inside an expert)
   size_t scale;      // [capacity] fp32: activation scale of each received row (int8)
   size_t source;     // [capacity] int2: (source rank, flat route id at the source)
-  size_t route_out;  // [local routes, H] fp32: result rows of this rank's own routes, written by the expert ranks
-  size_t counts;     // [world] int: rows stored by every source rank in its region of `rows`
+  size_t route_out;  // [local routes, H] fp32 (or bf16): result rows of this rank's own routes, written by the expert ranks
+  size_t counts;     // [world, row stride] int: route counts per global expert of every source rank
   size_t flags;      // [world] uint32: barrier epochs, one per source rank
   size_t total;
 };
-// The received rows form `world` regions of tokens_max * top_k rows, region s filled by source rank s.
-cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* dest_counts, int world, int rank,
-                                unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream);
+cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* payload, int payload_ints, int world,
+                                int rank, unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream);
+cudaError_t launch_peer_layout(const int* count_matrix, int world, int rank, int experts_global, int per_rank, int has_shared,
+                               int row_stride, int* send_base, int* local_counts, int* local_offsets, cudaStream_t stream);
 cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
-                                 const int64_t* dest, const int* route_pos, const int* dest_offsets, int region,
-                                 const PeerSlabLayout& slab, const uint64_t* peer_slabs, int rank, int experts_global,
-                                 int experts_per_rank, int numerics, cudaStream_t stream);
-cudaError_t launch_peer_row_ptrs(const int* sorted_routes, const int* valid_rows, int64_t capacity, const void* source,
-                                 const uint64_t* peer_slabs, size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs,
-                                 cudaStream_t stream);
+                                 const int* route_pos, const int* expert_offsets, const int* send_base, const PeerSlabLayout& slab,
+                                 const uint64_t* peer_slabs, int rank, int experts_global, int experts_per_rank, int has_shared,
+                                 int numerics, cudaStream_t stream);
+cudaError_t launch_peer_row_ptrs(const int* valid_rows, int64_t capacity, const void* source, const uint64_t* peer_slabs,
+                                 size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs, cudaStream_t stream);
 
 // ---- router.cu: scores -> top-k ids and routing weights, one warp per token (experts <= 2048, top_k <= 32)
 cudaError_t launch_router_topk(const float* logits, const float* selection_bias, int64_t tokens, int experts, int top_k, int sigmoid,

@@ -287,6 +287,14 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
 }
 
 namespace {
+// Work items and the status words of the grouped GEMMs from given per-expert counts and offsets (rows that
+// already lie in expert order: nothing to sort).
+__global__ void __launch_bounds__(1024)
+items_from_counts_kernel(int experts, const int* __restrict__ counts, const int* __restrict__ offsets, int tile_a, int tile_b,
+                         int* items_a, int* items_b, int max_items, int* scan_tmp, int* status) {
+  build_items(experts, counts, offsets, tile_a, tile_b, items_a, items_b, max_items, scan_tmp, status);
+}
+
 __global__ void dense_items_kernel(int64_t rows, int row_tile, int max_items, int* items, int* status) {
   const int tiles = static_cast<int>((rows + row_tile - 1) / row_tile);
   const int count = tiles < max_items ? tiles : max_items;
@@ -303,6 +311,12 @@ __global__ void dense_items_kernel(int64_t rows, int row_tile, int max_items, in
   }
 }
 }  // namespace
+
+cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, int tile_a, int tile_b, int max_items,
+                                     int* items_a, int* items_b, int* scratch, int* status, cudaStream_t stream) {
+  items_from_counts_kernel<<<1, 1024, 0, stream>>>(experts, counts, offsets, tile_a, tile_b, items_a, items_b, max_items, scratch, status);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream) {
   dense_items_kernel<<<8, 256, 0, stream>>>(rows, row_tile, max_items, items, status);

@@ -414,12 +414,11 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
     if hasattr(layer, "close"):
         layer.close()
     local_tokens = x_host.shape[0]
-    # Kernels of this library per forward on one rank.  Peer form: destination ranks, route build (1 kernel up to
-    # 1024 list entries, else 3), dispatch, barrier | route build, output addresses, row gather (+ scale gather),
-    # gate_up (+ requantise), down, barrier | merge.  (The NCCL form differs by its two barriers and one scatter.)
+    # Kernels of this library per forward on one rank, peer form: route build by global expert (1 kernel up to 1024
+    # routes, else 3), count barrier, layout, dispatch, barrier | work items, output addresses, gate_up (+ requantise),
+    # down, barrier | merge.  (The NCCL form has no barriers but a route build, gathers and a scatter on the expert side.)
     routes_local = local_tokens * (top_k + (1 if has_shared else 0))
-    capacity = world * local_max * (top_k + (1 if has_shared else 0))
-    launches_per_step = (1 + (1 if routes_local <= 1024 else 3) + 2) + ((1 if capacity <= 1024 else 3) + 2 + (3 if kind == "int8" else 1) + 2) + 1
+    launches_per_step = ((1 if routes_local <= 1024 else 3) + 4) + (5 + (1 if kind == "int8" else 0)) + 1
     work = synthetic.algorithmic_work(synthetic.MoEShape(tokens, hidden, inter, experts, top_k), topk_ids, 1 if kind == "int8" else 2,
                                       shared=has_shared)
     return {

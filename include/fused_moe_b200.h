@@ -279,12 +279,13 @@ FMOE_API int fmoe_router_topk(const float* logits, const float* selection_bias, 
  * exchanges and the synchronisation done by the kernels themselves instead of by a collective library: every
  * rank owns one "slab" (receive rows, their scale / local expert / return address, the fp32 result rows of its
  * own routes, row counts and barrier flags), exported by IPC handle and mapped by every other rank of the box.
- *     fmoe_ep_peer_dispatch   sorts the routes by destination, quantises each token once and stores its rows
- *                             straight into the owning ranks' slabs (one region per source rank, so no counts
- *                             are needed beforehand), then runs a flag barrier that also delivers the counts;
- *     fmoe_ep_peer_experts    grouped GEMMs over the received rows; the down GEMM's epilogue stores every
- *                             result row straight into the slab of the rank the route came from, tile by tile
- *                             while the GEMM runs; then a second barrier;
+ *     fmoe_ep_peer_dispatch   sorts this rank's routes by global expert id, tells every rank its counts per expert
+ *                             (flag barrier with a payload), derives from the full count table where each of its
+ *                             rows belongs in the owner's slab, then quantises each token once and stores its
+ *                             rows straight to those final, expert-sorted positions; second flag barrier;
+ *     fmoe_ep_peer_experts    the grouped GEMMs directly over the received rows (no route build, no gather); the
+ *                             down GEMM's epilogue stores every result row straight into the slab of the rank
+ *                             the route came from, tile by tile while the GEMM runs; third flag barrier;
  *     fmoe_ep_peer_combine    merges this rank's result rows.
  * Only plain stores cross NVLink; all loads (TMA included) read local memory.  Nothing synchronises with the host
  * and no collective library is involved after set-up.  The barrier waits are bounded (5 s, or
@@ -307,11 +308,11 @@ FMOE_API int fmoe_ep_peer_handle(fmoe_ep_peer_context* context, void* handle64);
 FMOE_API int fmoe_ep_peer_connect(fmoe_ep_peer_context* context, const void* handles);
 FMOE_API void fmoe_ep_peer_destroy(fmoe_ep_peer_context* context);
 FMOE_API int64_t fmoe_ep_peer_slab_bytes(const fmoe_ep_peer_context* context);
-/* shared_rank >= 0: expert id experts_global is the replicated shared expert, served by that rank (the caller
- * passes its own rank).  Ends with the first barrier. */
+/* shared_rank >= 0: expert id experts_global is the replicated shared expert, served by the calling rank itself
+ * (pass the own rank; -1 = no shared expert).  Contains the first two barriers. */
 FMOE_API int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* context, const void* x_bf16, const int64_t* topk_ids, int64_t tokens,
                                    int32_t experts_global, int32_t shared_rank, int32_t numerics, void* stream);
-/* Grouped GEMMs over the received rows; result rows go to the source ranks' slabs.  Ends with the second barrier. */
+/* Grouped GEMMs over the received rows; result rows go to the source ranks' slabs.  Ends with the third barrier. */
 FMOE_API int fmoe_ep_peer_experts(fmoe_ep_peer_context* context, const void* w13, const float* s13, const void* w2, const float* s2,
                                   const fmoe_config* config, void* stream);
 /* Merge of this rank's result rows in the reference's slot order (tree_merge: the BF16 path's pairwise tree). */
