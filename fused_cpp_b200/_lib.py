@@ -417,11 +417,11 @@ def ep_combine_finish(returned_rows, send_order, topk_weights, tokens: int, top_
 def router_topk(logits: torch.Tensor, top_k: int, *, scoring: str = "softmax", selection_bias: torch.Tensor | None = None,
                 renormalize: bool = True, routed_scaling_factor: float = 1.0):
     """Expert scores -> (topk_weights fp32 [T, K], topk_ids int64 [T, K]) on the GPU (fmoe_router_topk)."""
+    if scoring not in ("softmax", "sigmoid"):
+        raise ValueError("scoring must be 'softmax' or 'sigmoid'")
     logits = _require_cuda("logits", logits, torch.float32)
     if logits.dim() != 2:
         raise ValueError("logits must be [tokens, experts]")
-    if scoring not in ("softmax", "sigmoid"):
-        raise ValueError("scoring must be 'softmax' or 'sigmoid'")
     tokens, experts = logits.shape
     bias = None
     if selection_bias is not None:

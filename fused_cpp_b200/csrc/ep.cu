@@ -202,6 +202,7 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
   const int vec16 = cols >> 4;
   float scale = 1.0f;
   float operand = 1.0f;
+  float inverse = 1.0f;
   if constexpr (kInt8) {
     float local = 0.0f;
     for (int v = threadIdx.x; v < vec16; v += blockDim.x) {
@@ -218,6 +219,7 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
     amax = warp_max(amax);
     scale = row_scale_from_amax(amax, numerics);
     operand = quantize_operand(scale, numerics);
+    inverse = __fdiv_rn(1.0f, scale);
   } else {
     __syncthreads();
   }
@@ -242,7 +244,11 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
       for (int w = 0; w < 4; ++w) {
         uint32_t word = 0;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) word |= (static_cast<uint32_t>(quantize_value(values[4 * w + i], operand, numerics)) & 0xffu) << (8 * i);
+        for (int i = 0; i < 4; ++i) {
+          const int q = numerics == FMOE_NUMERICS_TORCHREF ? quantize_value_torchref_fast(values[4 * w + i], operand, inverse)
+                                                           : quantize_value(values[4 * w + i], operand, numerics);
+          word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+        }
         words[w] = word;
       }
       packed = make_uint4(words[0], words[1], words[2], words[3]);

@@ -127,6 +127,7 @@ struct GroupedGemmArgs {
   // Down GEMM, optional: byte address of the fp32 output row of every sorted row.  Overrides route_out +
   // sorted_routes; the rows may lie in another GPU's memory (expert-parallel return path, plain stores).
   const uint64_t* row_out_ptrs;
+  int gate_up_one_box;       // two-SM gate_up: the weight rows of a stage arrive as one 16 KB TMA box (set by the launcher)
   int route_out_bf16;        // with row_out_ptrs: the result rows are stored as bf16 (2 bytes per channel) instead of fp32
   // Performance diagnosis only (environment FUSED_CPP_MOE_GEMM_DIAG, 0 in production; results are meaningless otherwise):
   // bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.

@@ -45,11 +45,13 @@ __device__ __forceinline__ float amax8(const uint4& v) {
   return m;
 }
 
-__device__ __forceinline__ uint32_t pack4(const float* values, float operand, int numerics) {
+// operand: 1/scale (NATIVE) or scale (TORCHREF); inverse: 1/scale, used by the TORCHREF fast path.
+__device__ __forceinline__ uint32_t pack4(const float* values, float operand, float inverse, int numerics) {
   uint32_t packed = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int q = quantize_value(values[i], operand, numerics);
+    const int q = numerics == FMOE_NUMERICS_TORCHREF ? quantize_value_torchref_fast(values[i], operand, inverse)
+                                                     : quantize_value(values[i], operand, numerics);
     packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
   }
   return packed;
@@ -82,16 +84,17 @@ quantize_rows_kernel(const uint16_t* __restrict__ x, int cols, const int* __rest
   }
   if (threadIdx.x == 0) scale_out[row] = scale;
   const float operand = quantize_operand(scale, mode);
+  const float inverse = __fdiv_rn(1.0f, scale);
   uint4* dst = reinterpret_cast<uint4*>(q + row * cols);
   for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
     float values[16];
     unpack8(src[2 * v], values);
     unpack8(src[2 * v + 1], values + 8);
     uint4 out;
-    out.x = pack4(values, operand, mode);
-    out.y = pack4(values + 4, operand, mode);
-    out.z = pack4(values + 8, operand, mode);
-    out.w = pack4(values + 12, operand, mode);
+    out.x = pack4(values, operand, inverse, mode);
+    out.y = pack4(values + 4, operand, inverse, mode);
+    out.z = pack4(values + 8, operand, inverse, mode);
+    out.w = pack4(values + 12, operand, inverse, mode);
     dst[v] = out;
   }
 }
@@ -133,6 +136,7 @@ quantize_rows_warp_kernel(const uint16_t* __restrict__ x, int64_t out_rows, int 
   }
   if (lane == 0) scale_out[row] = scale;
   const float operand = quantize_operand(scale, mode);
+  const float inverse = __fdiv_rn(1.0f, scale);
   uint4* dst = reinterpret_cast<uint4*>(q + row * cols);
 #pragma unroll
   for (int i = 0; i < kVectors; ++i) {
@@ -142,10 +146,10 @@ quantize_rows_warp_kernel(const uint16_t* __restrict__ x, int64_t out_rows, int 
       unpack8(held[i][0], values);
       unpack8(held[i][1], values + 8);
       uint4 out;
-      out.x = pack4(values, operand, mode);
-      out.y = pack4(values + 4, operand, mode);
-      out.z = pack4(values + 8, operand, mode);
-      out.w = pack4(values + 12, operand, mode);
+      out.x = pack4(values, operand, inverse, mode);
+      out.y = pack4(values + 4, operand, inverse, mode);
+      out.z = pack4(values + 8, operand, inverse, mode);
+      out.w = pack4(values + 12, operand, inverse, mode);
       dst[v] = out;
     }
   }
@@ -171,15 +175,16 @@ quantize_tokens_scatter_kernel(const uint16_t* __restrict__ x, int cols, int top
   const float scale = row_scale_from_amax(amax, numerics);
   if (threadIdx.x < top_k && positions[threadIdx.x] >= 0) scale_out[positions[threadIdx.x]] = scale;
   const float operand = quantize_operand(scale, numerics);
+  const float inverse = __fdiv_rn(1.0f, scale);
   for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
     float values[16];
     unpack8(src[2 * v], values);
     unpack8(src[2 * v + 1], values + 8);
     uint4 out;
-    out.x = pack4(values, operand, numerics);
-    out.y = pack4(values + 4, operand, numerics);
-    out.z = pack4(values + 8, operand, numerics);
-    out.w = pack4(values + 12, operand, numerics);
+    out.x = pack4(values, operand, inverse, numerics);
+    out.y = pack4(values + 4, operand, inverse, numerics);
+    out.z = pack4(values + 8, operand, inverse, numerics);
+    out.w = pack4(values + 12, operand, inverse, numerics);
     for (int slot = 0; slot < top_k; ++slot) {
       const int position = positions[slot];
       if (position >= 0) reinterpret_cast<uint4*>(q + static_cast<int64_t>(position) * cols)[v] = out;

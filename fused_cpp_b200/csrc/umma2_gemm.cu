@@ -24,6 +24,7 @@
 // both CTAs, and the follower's epilogue warps arrive on the leader's "accumulator empty" barrier
 // through its cluster address.  No load is a multicast load.  Every wait is bounded (see ptx.cuh).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -280,9 +281,15 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
             if (leader) ptx::mbar_arrive_expect_tx(&ctl->full[stage], 2 * kStageBytes);
             const int x = kb * kBlockKElems;
             if constexpr (kGateUp) {
-              // Four boxes of [16 gate rows | 16 up rows]: tensor dimensions {K, row in group, group, gate/up, expert}.
+              if (args.gate_up_one_box) {
+                // One 16 KB box of four groups of [16 gate rows | 16 up rows]: tensor dimensions
+                // {K, row in group, gate/up, group, expert}.
+                tma_load_5d_pair(dst, &weight_map, bar, x, 0, 0, group, cur.expert);
+              } else {
+                // The same rows as four 4 KB boxes: tensor dimensions {K, row in group, group, gate/up, expert}.
 #pragma unroll
-              for (int g = 0; g < 4; ++g) tma_load_5d_pair(dst + g * 32 * kBlockKBytes, &weight_map, bar, x, 0, group + g, 0, cur.expert);
+                for (int g = 0; g < 4; ++g) tma_load_5d_pair(dst + g * 32 * kBlockKBytes, &weight_map, bar, x, 0, group + g, 0, cur.expert);
+              }
             } else {
               tma_load_2d_pair(dst, &weight_map, bar, x, weight_row);
             }
@@ -617,20 +624,31 @@ bool make_tensor_map(CUtensorMap* map, const void* base, bool int8, uint64_t row
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// gate_up weights [E, 2I, K] seen as {K, 16 rows, I/16 groups, gate|up, E}: one box is the 16 gate rows of a
-// channel group followed by its 16 up rows.
-bool make_gate_up_map(CUtensorMap* map, const void* base, bool int8, uint64_t experts, uint64_t inter, uint64_t k) {
+// gate_up weights [E, 2I, K] as a 5-D tensor whose boxes put the 16 gate rows of a channel group next to its 16
+// up rows.  one_box: dimensions {K, 16 rows, gate|up, I/16 groups, E} and a box of four groups (16 KB, one TMA
+// operation per stage; the gate|up stride is larger than the group stride that follows it).  Otherwise
+// {K, 16 rows, I/16 groups, gate|up, E} with strides in ascending order and a box of one group (4 KB, four
+// operations per stage): the fallback if the driver refuses the first encoding.
+bool make_gate_up_map(CUtensorMap* map, const void* base, bool int8, uint64_t experts, uint64_t inter, uint64_t k, bool one_box) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
   const uint64_t elem_bytes = int8 ? 1 : 2;
   const uint64_t row_bytes = k * elem_bytes;
+  const cuuint32_t inner = static_cast<cuuint32_t>(kBlockKBytes / elem_bytes);
+  const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType type = int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (one_box) {
+    const cuuint64_t dims[5] = {k, 16, 2, inter / 16, experts};
+    const cuuint64_t strides[4] = {row_bytes, inter * row_bytes, 16 * row_bytes, 2 * inter * row_bytes};
+    const cuuint32_t box[5] = {inner, 16, 2, 4, 1};
+    return encode(map, type, 5, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
   const cuuint64_t dims[5] = {k, 16, inter / 16, 2, experts};
   const cuuint64_t strides[4] = {row_bytes, 16 * row_bytes, inter * row_bytes, 2 * inter * row_bytes};
-  const cuuint32_t box[5] = {static_cast<cuuint32_t>(kBlockKBytes / elem_bytes), 16, 1, 2, 1};
-  const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
-  return encode(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides,
-                box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const cuuint32_t box[5] = {inner, 16, 1, 2, 1};
+  return encode(map, type, 5, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <bool kInt8, bool kGateUp, bool kDense>
@@ -644,9 +662,16 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
   }
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   CUtensorMap weight_map, token_map;
-  const bool weights_ok = kGateUp ? make_gate_up_map(&weight_map, args.weights, kInt8, args.experts, args.n_out, args.k)
-                                  : make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total,
-                                                    args.k, kRowsPerCta);
+  GroupedGemmArgs launch_args = args;
+  bool weights_ok;
+  if (kGateUp) {
+    const char* forced = getenv("FUSED_CPP_MOE_GATE_UP_BOXES");  // "4": use the four-box encoding (experiments)
+    const bool try_one = !(forced != nullptr && forced[0] == '4') && args.n_out % 64 == 0;
+    launch_args.gate_up_one_box = try_one && make_gate_up_map(&weight_map, args.weights, kInt8, args.experts, args.n_out, args.k, true);
+    weights_ok = launch_args.gate_up_one_box || make_gate_up_map(&weight_map, args.weights, kInt8, args.experts, args.n_out, args.k, false);
+  } else {
+    weights_ok = make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total, args.k, kRowsPerCta);
+  }
   if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowsPerCta)) {
     return cudaErrorInvalidValue;
   }
@@ -658,7 +683,7 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
   int64_t pairs = static_cast<int64_t>(args.max_items) * n_blocks;
   if (pairs > sms / 2) pairs = sms / 2;
   if (pairs <= 0) return cudaSuccess;
-  kernel<<<static_cast<unsigned>(2 * pairs), kThreads, kSmemBytes, stream>>>(weight_map, token_map, args);
+  kernel<<<static_cast<unsigned>(2 * pairs), kThreads, kSmemBytes, stream>>>(weight_map, token_map, launch_args);
   return cudaGetLastError();
 }
 

@@ -253,3 +253,19 @@ def test_naive_matches_explicit_loop():
             mid = torch.nn.functional.silu(gate_up[:4]) * gate_up[4:]
             expected[t] += w[t, s] * (w2[e] @ mid)
     torch.testing.assert_close(moe.fused_moe_naive(x, w13, w2, w, ids), expected, rtol=1e-5, atol=1e-5)
+
+
+def test_router_and_projection_helpers_have_no_cpu_path():
+    """The router front-end and the dense projection helpers import without a GPU and refuse CPU tensors loudly."""
+    from fused_cpp_b200 import deepseek_v4_w8a8, router
+
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        router.router_topk(torch.zeros((2, 8)), 2)
+    with pytest.raises(ValueError, match="scoring"):
+        router.router_topk(torch.zeros((2, 8)), 2, scoring="tanh")
+    weight = deepseek_v4_w8a8.PreparedDeepSeekV4W8A8LinearWeight.__new__(deepseek_v4_w8a8.PreparedDeepSeekV4W8A8LinearWeight)
+    with pytest.raises(TypeError, match="CUDA torch.bfloat16"):
+        deepseek_v4_w8a8.deepseek_v4_w8a8_linear(torch.zeros((2, 8), dtype=torch.bfloat16), weight)
+    assert set(deepseek_v4_w8a8.__all__) == {
+        "PreparedDeepSeekV4W8A8LinearWeight", "_HAS_DEEPSEEK_V4_W8A8", "deepseek_v4_w8a8_linear", "deepseek_v4_w8a8_linear_pair",
+        "deepseek_v4_wo_b_w8a8", "prepare_deepseek_v4_w8a8_linear_quantized_weight", "prepare_deepseek_v4_w8a8_linear_weight"}
