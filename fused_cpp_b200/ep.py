@@ -406,6 +406,24 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
         out_pin.copy_(out, non_blocking=True)
 
     e2e_ms, _ = timed(e2e_step, args.steps, args.warmup)
+    # Cross-check at benchmark scale: the peer-memory forward against the NCCL all-to-all form on the same batch
+    # (each is bit-identical to the single-GPU forward in the tests; here they must agree with each other).
+    parity = None
+    if isinstance(layer, PeerMemoryExpertParallelMoE):
+        other = ExpertParallelMoE(weights, experts, has_shared=has_shared)
+        expected = other(xd, wd, idd, **kwargs)
+        got = layer(xd, wd, idd, **kwargs)
+        if bf16_return:
+            error = float((got.float() - expected.float()).norm() / expected.float().norm().clamp_min(1e-30))
+            agree = torch.tensor([1 if error <= 5e-3 else 0], device=device)
+            parity = "relative L2 to the NCCL all-to-all form on this batch <= 5e-3"
+        else:
+            agree = torch.tensor([1 if torch.equal(got.view(torch.int16), expected.view(torch.int16)) else 0], device=device)
+            parity = "bit-identical to the NCCL all-to-all form on this batch, every rank"
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) != 1:
+            raise RuntimeError(f"{name}: the peer-memory forward disagrees with the NCCL form on at least one rank")
+        del other, expected, got
     # Every rank is done with every slab before any of them is unmapped and freed.
     torch.cuda.synchronize()
     dist.barrier()
@@ -431,7 +449,7 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": local_tokens * hidden * 2 + local_tokens * top_k * 12,
                 "d2h_bytes_per_step": local_tokens * hidden * 2},
         "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "roofline": roofline, "cpu_baseline": None,
-        "launch_mode": launch_mode, "eager_ms_per_step": eager_ms,
+        "launch_mode": launch_mode, "eager_ms_per_step": eager_ms, "parity": parity,
         "stage_ms_rank0": {k: round(v, 5) for k, v in stage_ms.items()} if stage_ms else None,
         "layer": {"algorithmic_bytes": work["bytes"], "ops": work["ops"],
                   "hbm_gbs_aggregate": work["bytes"] / (ms * 1e-3) / 1e9, "tops_aggregate": work["ops"] / (ms * 1e-3) / 1e12},
