@@ -15,12 +15,10 @@ int report_error(int code, const char* text);
 
 // ---- route.cu
 size_t route_scratch_bytes(int64_t routes, int experts);
-// valid_count (nullable, device): with region == 0, entries at or beyond *valid_count are padding and skipped
-// silently; with region > 0 the list consists of regions of `region` entries and valid_count[r] of region r are filled.
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
                                int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream,
-                               int* route_pos = nullptr, const int* valid_count = nullptr, int region = 0);
+                               int* route_pos = nullptr);
 
 // Work items from per-expert counts / offsets of rows that are already in expert order (scratch: 2 * experts + 1 ints).
 cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, int tile_a, int tile_b, int max_items,

@@ -23,8 +23,7 @@ namespace {
 constexpr int kWarpsPerBlock = 4;
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int region, int experts,
-                  int units, int* unit_hist, int* status) {
+route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int experts, int units, int* unit_hist, int* status) {
   extern __shared__ int smem_hist[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -33,14 +32,10 @@ route_hist_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const in
   for (int e = lane; e < experts; e += 32) hist[e] = 0;
   __syncwarp();
   if (unit >= units) return;
-  // With device-side counts the list has a fixed capacity and its unused entries are padding: skipped, not an
-  // error.  region == 0: one count, the list is filled from the front; region > 0: the list is a sequence of
-  // regions of that many entries and valid_count[r] is how many of region r are filled.
-  if (valid_count != nullptr && region == 0) routes = min(routes, static_cast<int64_t>(*valid_count));
   const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
   for (int round = 0; round < kUnitRoutes / 32; ++round) {
     const int64_t route = begin + round * 32 + lane;
-    if (route < routes && (region == 0 || route % region < valid_count[route / region])) {
+    if (route < routes) {
       const int64_t id = topk_ids[route];
       if (id < 0 || id >= experts) {
         raise_error(status, FMOE_ERR_EXPERT_ID_RANGE, static_cast<int>(route));
@@ -128,8 +123,7 @@ __device__ void build_items(int experts, const int* counts, const int* offsets, 
 constexpr int kSmallRoutes = 1024;
 
 __global__ void __launch_bounds__(kSmallRoutes)
-route_small_kernel(const int64_t* __restrict__ topk_ids, int routes, const int* __restrict__ valid_count, int region, int experts,
-                   int tile_a, int tile_b, int max_items, int* status, int* counts, int* offsets, int* sorted_routes, int* row_expert,
+route_small_kernel(const int64_t* __restrict__ topk_ids, int routes, int experts, int tile_a, int tile_b, int max_items, int* status, int* counts, int* offsets, int* sorted_routes, int* row_expert,
                    int* items_a, int* items_b, int* route_pos) {
   extern __shared__ int small_smem[];
   int* s_id = small_smem;
@@ -142,9 +136,7 @@ route_small_kernel(const int64_t* __restrict__ topk_ids, int routes, const int* 
   __syncthreads();
   const int r = threadIdx.x;
   int id = -1;
-  bool listed = r < routes;
-  if (listed && valid_count != nullptr) listed = region == 0 ? r < *valid_count : r % region < valid_count[r / region];
-  if (listed) {
+  if (r < routes) {
     const int64_t value = topk_ids[r];
     if (value >= 0 && value < experts) {
       id = static_cast<int>(value);
@@ -214,7 +206,7 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const int* __restrict__ valid_count, int region, int experts, int units,
+route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, int experts, int units,
                      const int* __restrict__ unit_hist, const int* __restrict__ offsets, int* sorted_routes,
                      int* row_expert, int* route_pos) {
   extern __shared__ int smem_cursor[];
@@ -225,14 +217,12 @@ route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const
   int* cursor = smem_cursor + warp * experts;
   for (int e = lane; e < experts; e += 32) cursor[e] = offsets[e] + unit_hist[static_cast<int64_t>(unit) * experts + e];
   __syncwarp();
-  const int64_t listed = routes;
-  if (valid_count != nullptr && region == 0) routes = min(routes, static_cast<int64_t>(*valid_count));
   const int64_t begin = static_cast<int64_t>(unit) * kUnitRoutes;
   const unsigned lanes_below = (1u << lane) - 1u;
   for (int round = 0; round < kUnitRoutes / 32; ++round) {
     const int64_t route = begin + round * 32 + lane;
     int id = -1;
-    if (route < routes && (region == 0 || route % region < valid_count[route / region])) {
+    if (route < routes) {
       const int64_t value = topk_ids[route];
       if (value >= 0 && value < experts) id = static_cast<int>(value);
     }
@@ -247,7 +237,7 @@ route_scatter_kernel(const int64_t* __restrict__ topk_ids, int64_t routes, const
       row_expert[position] = id;
     }
     // Inverse permutation: sorted position of every flat route (-1 for a dropped route).
-    if (route_pos != nullptr && route < listed) route_pos[route] = position;
+    if (route_pos != nullptr && route < routes) route_pos[route] = position;
   }
 }
 
@@ -260,11 +250,10 @@ size_t route_scratch_bytes(int64_t routes, int experts) {
 
 cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
                                int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
-                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos,
-                               const int* valid_count, int region) {
+                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos) {
   if (routes <= kSmallRoutes) {
     const size_t small_bytes = (static_cast<size_t>(kSmallRoutes) + 4 * static_cast<size_t>(experts) + 4) * sizeof(int);
-    route_small_kernel<<<1, kSmallRoutes, small_bytes, stream>>>(topk_ids, static_cast<int>(routes), valid_count, region, experts, tile_a,
+    route_small_kernel<<<1, kSmallRoutes, small_bytes, stream>>>(topk_ids, static_cast<int>(routes), experts, tile_a,
                                                                  tile_b, max_items, status, counts, offsets, sorted_routes, row_expert,
                                                                  items_a, items_b, route_pos);
     return cudaGetLastError();
@@ -275,12 +264,12 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
   const size_t smem = static_cast<size_t>(kWarpsPerBlock) * experts * sizeof(int);
   const int blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (blocks > 0) {
-    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, region, experts, units, unit_hist, status);
+    route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist, status);
   }
   route_scan_kernel<<<1, 1024, 0, stream>>>(experts, units, unit_hist, counts, offsets, tile_a, tile_b, items_a, items_b,
                                             max_items, scan_tmp, status);
   if (blocks > 0) {
-    route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, valid_count, region, experts, units, unit_hist,
+    route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist,
                                                                         offsets, sorted_routes, row_expert, route_pos);
   }
   return cudaGetLastError();
