@@ -193,6 +193,12 @@ class ForwardResult:
         check(load().fmoe_read_status(_ptr(self.workspace), _stream(), ctypes.byref(error), ctypes.byref(detail)))
         return error.value, detail.value
 
+    def status_word(self, index: int) -> int:
+        """One int32 word of the status block (2, 5: work items of the two GEMMs; 6, 7: those of the experts routed to
+        the two-SM kernel when the tiles are automatic; 3: active experts).  Synchronises."""
+        torch.cuda.current_stream().synchronize()
+        return int(self.workspace[: 64].view(torch.int32)[index].item())
+
     def raise_for_status(self) -> None:
         error, detail = self.status()
         if error == ERR_EXPERT_ID_RANGE:

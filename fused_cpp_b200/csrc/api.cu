@@ -40,6 +40,8 @@ int check_device() {
   return FMOE_OK;
 }
 
+constexpr int kSplitRows = 64;  // experts with more rows than this go to the two-SM kernel when the tiles are automatic
+
 int64_t max_items_for(int64_t routes, int experts) {
   // Upper bound on (expert, row tile) items for any tile height >= 8.
   return experts + routes / 8 + 1;
@@ -79,7 +81,7 @@ int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, i
   layout->offsets = take(sizeof(int) * (experts + 1));
   layout->sorted_routes = take(sizeof(int) * rows);
   layout->row_expert = take(sizeof(int) * rows);
-  layout->items = take(sizeof(int) * 4 * max_items * 2);
+  layout->items = take(sizeof(int) * 4 * max_items * 4);  // four work-item lists (see fmoe::ItemLists)
   layout->scratch = take(fmoe::route_scratch_bytes(routes, experts));
   layout->a_rows = take(with_route_out ? rows * hidden * (int8 ? 1 : 2) : 256);
   layout->a_scale = take(sizeof(float) * rows);
@@ -189,8 +191,14 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   }
   const bool umma = cfg.gemm_impl != FMOE_GEMM_SIMT;
   const int64_t routes = f.tokens * f.top_k;
-  const int tile_gu = pick_row_tile(cfg.gate_up_tile, routes, f.experts, umma);
-  const int tile_dn = pick_row_tile(cfg.down_tile, routes, f.experts, umma);
+  // Above 64 tokens an expert can hold anything from one row to all of them, and the host does not know the routing.
+  // Unless the caller fixed the tiles, the experts are then split on the device: those with at most 64 rows
+  // go through the one-SM kernel (64-row tile, every weight byte streamed once), the others through the
+  // two-SM kernel (256-row work items).  Up to 64 tokens no expert can exceed 64 rows and the tile follows
+  // the average.
+  const bool split = umma && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
+  const int tile_gu = split ? kSplitRows : pick_row_tile(cfg.gate_up_tile, routes, f.experts, umma);
+  const int tile_dn = split ? kSplitRows : pick_row_tile(cfg.down_tile, routes, f.experts, umma);
   if (umma && (!fmoe::umma_row_tile_supported(tile_gu) || !fmoe::umma_row_tile_supported(tile_dn))) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128, 256 or 512 = two-SM pairs (got %d, %d)", tile_gu, tile_dn);
   }
@@ -208,6 +216,10 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   const int max_items = static_cast<int>(max_items_for(routes, f.experts));
   int* items_gu = reinterpret_cast<int*>(base + layout.items);
   int* items_dn = items_gu + 4 * static_cast<size_t>(max_items);
+  int* items_gu_big = items_dn + 4 * static_cast<size_t>(max_items);
+  int* items_dn_big = items_gu_big + 4 * static_cast<size_t>(max_items);
+  const fmoe::ItemLists lists{item_rows_gu, item_rows_dn, items_gu, items_dn, max_items, split ? kSplitRows : 0, split ? 256 : 0,
+                              items_gu_big, items_dn_big};
   int* scratch = reinterpret_cast<int*>(base + layout.scratch);
   float* a_scale = reinterpret_cast<float*>(base + layout.a_scale);
   uint16_t* y = reinterpret_cast<uint16_t*>(base + layout.y);
@@ -229,17 +241,15 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   uint64_t* row_out_ptrs = nullptr;
   if (peer) {
     // The rows arrived in expert order: only the work items and the output addresses remain to be made.
-    error = fmoe::launch_items_from_counts(f.experts, f.sorted_counts, f.sorted_offsets, item_rows_gu, item_rows_dn, max_items, items_gu,
-                                           items_dn, scratch, status_block, stream);
+    error = fmoe::launch_items_from_counts(f.experts, f.sorted_counts, f.sorted_offsets, lists, scratch, status_block, stream);
     if (error != cudaSuccess) return cuda_fail(error, "work items");
     row_out_ptrs = reinterpret_cast<uint64_t*>(base + layout.route_out);
     error = fmoe::launch_peer_row_ptrs(f.sorted_offsets + f.experts, routes, f.rows_source, f.peer_slabs, f.peer_route_out_offset,
                                        f.hidden * (f.peer_rows_bf16 ? 2 : 4), row_out_ptrs, stream);
     if (error != cudaSuccess) return cuda_fail(error, "peer output addresses");
   } else {
-    error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, item_rows_gu, item_rows_dn, max_items, status_block, counts, offsets,
-                                     sorted_routes, row_expert, items_gu, items_dn, scratch, stream,
-                                     reinterpret_cast<int*>(base + layout.route_pos));
+    error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, lists, status_block, counts, offsets, sorted_routes, row_expert, scratch,
+                                     stream, reinterpret_cast<int*>(base + layout.route_pos));
     if (error != cudaSuccess) return cuda_fail(error, "route build");
   }
   mark(FMOE_STAGE_ROUTE + 1);
@@ -289,6 +299,13 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.total_rows = routes;
   gu.row_tile = tile_gu;
   error = umma ? fmoe::launch_umma_grouped_gemm(gu, f.int8, true, stream) : fmoe::launch_simt_grouped_gemm(gu, f.int8, true, stream);
+  if (error == cudaSuccess && split) {
+    fmoe::GroupedGemmArgs big = gu;
+    big.items = items_gu_big;
+    big.item_count_word = fmoe::kStatusItemsC;
+    big.row_tile = fmoe::kPairRowTile;
+    error = fmoe::launch_umma_grouped_gemm(big, f.int8, true, stream);
+  }
   if (error != cudaSuccess) return cuda_fail(error, "gate_up grouped GEMM");
   mark(FMOE_STAGE_GATE_UP + 1);
 
@@ -317,6 +334,13 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   dn.dump_acc = cfg.dump_acc2;
   dn.row_tile = tile_dn;
   error = umma ? fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
+  if (error == cudaSuccess && split) {
+    fmoe::GroupedGemmArgs big = dn;
+    big.items = items_dn_big;
+    big.item_count_word = fmoe::kStatusItemsD;
+    big.row_tile = fmoe::kPairRowTile;
+    error = fmoe::launch_umma_grouped_gemm(big, f.int8, false, stream);
+  }
   if (error != cudaSuccess) return cuda_fail(error, "down grouped GEMM");
   mark(FMOE_STAGE_DOWN + 1);
 
@@ -504,8 +528,8 @@ int fmoe_ep_dispatch_prepare(const void* x, const int64_t* topk_ids, int64_t tok
   error = fmoe::launch_dest_ranks(topk_ids, routes, experts_global, experts_global / world, shared_rank, dest, stream);
   if (error == cudaSuccess) {
     // A stable counting sort of the routes by destination rank: the same kernels as the per-expert route build.
-    error = fmoe::launch_route_build(dest, routes, world, 16, 16, 0, status_block, dest_counts, offsets, send_order, row_rank,
-                                     nullptr, nullptr, scratch, stream);
+    error = fmoe::launch_route_build(dest, routes, world, fmoe::no_item_lists(), status_block, dest_counts, offsets, send_order, row_rank,
+                                     scratch, stream);
   }
   const int* valid_rows = offsets + world;
   if (error == cudaSuccess) {
@@ -953,8 +977,8 @@ int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* ctx, const void* x, const int64_
   if (error == cudaSuccess && routes > 0) {
     // Stable counting sort of this rank's routes by global expert id (the shared expert is id experts_global):
     // expert order is destination-rank order, and inside a destination its local expert order.
-    error = fmoe::launch_route_build(topk_ids, routes, experts_total, 16, 16, 0, d.status, d.counts, d.offsets, d.send_order, d.row_expert,
-                                     nullptr, nullptr, d.scratch, stream, d.route_pos);
+    error = fmoe::launch_route_build(topk_ids, routes, experts_total, fmoe::no_item_lists(), d.status, d.counts, d.offsets, d.send_order,
+                                     d.row_expert, d.scratch, stream, d.route_pos);
   }
   if (error == cudaSuccess) {
     // Every rank learns every rank's counts per expert (row `rank` of the table in each slab) ...

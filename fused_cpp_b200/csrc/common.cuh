@@ -23,6 +23,8 @@ enum StatusWord : int {
   kStatusActive = 3,     // number of experts with at least one route
   kStatusWaitSite = 4,   // which bounded wait gave up (0 = none)
   kStatusItemsB = 5,     // work items of the second list (down GEMM)
+  kStatusItemsC = 6,     // split mode: gate_up work items of the experts with many rows (two-SM kernel)
+  kStatusItemsD = 7,     // split mode: down work items of those experts
   kStatusWords = 16,
 };
 

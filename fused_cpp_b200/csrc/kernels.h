@@ -15,14 +15,27 @@ int report_error(int code, const char* text);
 
 // ---- route.cu
 size_t route_scratch_bytes(int64_t routes, int experts);
-cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
-                               int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
-                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream,
+// The work-item lists a route build fills: a and b for the gate_up and the down GEMM (tile heights tile_a,
+// tile_b).  With split_rows > 0, a and b hold only the experts with at most split_rows rows and c and d
+// (tile big_tile) the experts with more; every list has room for max_items items of four ints.
+struct ItemLists {
+  int tile_a, tile_b;
+  int* items_a;
+  int* items_b;
+  int max_items;
+  int split_rows;
+  int big_tile;
+  int* items_c;
+  int* items_d;
+};
+inline ItemLists no_item_lists() { return ItemLists{16, 16, nullptr, nullptr, 0, 0, 0, nullptr, nullptr}; }
+cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, const ItemLists& lists, int* status, int* counts,
+                               int* offsets, int* sorted_routes, int* row_expert, int* scratch, cudaStream_t stream,
                                int* route_pos = nullptr);
 
 // Work items from per-expert counts / offsets of rows that are already in expert order (scratch: 2 * experts + 1 ints).
-cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, int tile_a, int tile_b, int max_items,
-                                     int* items_a, int* items_b, int* scratch, int* status, cudaStream_t stream);
+cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, const ItemLists& lists, int* scratch, int* status,
+                                     cudaStream_t stream);
 // Work items of a dense [rows, K] x [N, K]^T product: one "expert", consecutive row tiles.
 cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream);
 

@@ -66,30 +66,41 @@ __device__ int warp_exclusive_scan(const int* values, int* out, int n, int lane)
   return carry;
 }
 
-// Work items: (expert, first sorted row, rows, group key) for every row tile of every active expert, two lists
-// with independent tile heights (gate_up and down GEMM), plus the number of active experts.  Called by a whole
-// block; scan_tmp has room for 2 * experts + 1 ints (global or shared).
-__device__ void build_items(int experts, const int* counts, const int* offsets, int tile_a, int tile_b, int* items_a, int* items_b,
-                            int max_items, int* scan_tmp, int* status) {
+// Work items: (expert, first sorted row, rows, group key) for every row tile of every active expert, and the
+// number of active experts.  Lists a and b (gate_up and down GEMM) have independent tile heights.  With
+// split_rows > 0 they hold only the experts with at most split_rows rows, and lists c and d (tile big_tile) the
+// experts with more: the batch's routing decides on the device, expert by expert, whether an expert's rows go to
+// the weight-streaming kernel or to the two-SM kernel, with no host-side guess about the distribution.
+// Called by a whole block; scan_tmp has room for 2 * experts + 1 ints (global or shared).
+__device__ void build_items(int experts, const int* counts, const int* offsets, const ItemLists& lists, int* scan_tmp, int* status) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  for (int list = 0; list < 2; ++list) {
-    const int tile = list == 0 ? tile_a : tile_b;
-    int* items = list == 0 ? items_a : items_b;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) scan_tmp[e] = (counts[e] + tile - 1) / tile;
+  const int split_rows = lists.split_rows;
+  const int max_items = lists.max_items;
+  for (int list = 0; list < 4; ++list) {
+    const bool big = list >= 2;
+    const int word = list == 0 ? kStatusItems : list == 1 ? kStatusItemsB : list == 2 ? kStatusItemsC : kStatusItemsD;
+    if (big && split_rows <= 0) {
+      if (threadIdx.x == 0) status[word] = 0;
+      continue;
+    }
+    const int tile = list == 0 ? lists.tile_a : list == 1 ? lists.tile_b : lists.big_tile;
+    int* items = list == 0 ? lists.items_a : list == 1 ? lists.items_b : list == 2 ? lists.items_c : lists.items_d;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+      const bool mine = split_rows <= 0 || (big ? counts[e] > split_rows : counts[e] <= split_rows);
+      scan_tmp[e] = mine ? (counts[e] + tile - 1) / tile : 0;
+    }
     __syncthreads();
     if (warp == 0) {
       const int total = warp_exclusive_scan(scan_tmp, scan_tmp + experts, experts, lane);
-      if (lane == 0) status[list == 0 ? kStatusItems : kStatusItemsB] = total < max_items ? total : max_items;
+      if (lane == 0) status[word] = total < max_items ? total : max_items;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
       const int tiles = scan_tmp[e];
       const int first = scan_tmp[experts + e];
       // The expert's rows are spread evenly over its tiles (in steps of 32 rows, the granularity of the MMA's N):
-      // 290 rows become 160 + 130, not 256 + 34.  Work units of one expert then last about equally long, so
-      // the CTAs that stream the same weight block for different row tiles stay side by side and the second
-      // read comes out of L2.
+      // 290 rows become 160 + 130, not 256 + 34.
       int rows_per = tile;
       if (tiles > 1) {
         const int step = tile < 32 ? tile : 32;
@@ -123,8 +134,8 @@ __device__ void build_items(int experts, const int* counts, const int* offsets, 
 constexpr int kSmallRoutes = 1024;
 
 __global__ void __launch_bounds__(kSmallRoutes)
-route_small_kernel(const int64_t* __restrict__ topk_ids, int routes, int experts, int tile_a, int tile_b, int max_items, int* status, int* counts, int* offsets, int* sorted_routes, int* row_expert,
-                   int* items_a, int* items_b, int* route_pos) {
+route_small_kernel(const int64_t* __restrict__ topk_ids, int routes, int experts, ItemLists lists, int* status, int* counts, int* offsets,
+                   int* sorted_routes, int* row_expert, int* route_pos) {
   extern __shared__ int small_smem[];
   int* s_id = small_smem;
   int* s_counts = s_id + kSmallRoutes;
@@ -165,12 +176,11 @@ route_small_kernel(const int64_t* __restrict__ topk_ids, int routes, int experts
     if (e < experts) counts[e] = s_counts[e];
     offsets[e] = s_offsets[e];
   }
-  build_items(experts, s_counts, s_offsets, tile_a, tile_b, items_a, items_b, max_items, s_tmp, status);
+  build_items(experts, s_counts, s_offsets, lists, s_tmp, status);
 }
 
 __global__ void __launch_bounds__(1024)
-route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offsets, int tile_a, int tile_b,
-                  int* items_a, int* items_b, int max_items, int* scan_tmp, int* status) {
+route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offsets, ItemLists lists, int* scan_tmp, int* status) {
   // Pass 1: per expert, exclusive scan over units (unit_hist becomes the unit's cursor relative to the
   // expert's first row) and the expert total.  One thread per expert (adjacent threads read adjacent words);
   // the units are taken sixteen at a time, all loads of a batch issued before the first store, so the
@@ -202,7 +212,7 @@ route_scan_kernel(int experts, int units, int* unit_hist, int* counts, int* offs
     if (lane == 0) offsets[experts] = total;
   }
   __syncthreads();
-  build_items(experts, counts, offsets, tile_a, tile_b, items_a, items_b, max_items, scan_tmp, status);
+  build_items(experts, counts, offsets, lists, scan_tmp, status);
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -248,14 +258,12 @@ size_t route_scratch_bytes(int64_t routes, int experts) {
   return static_cast<size_t>((units > 0 ? units : 1) * experts + 2 * (experts + 1)) * sizeof(int);
 }
 
-cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, int tile_a, int tile_b,
-                               int max_items, int* status, int* counts, int* offsets, int* sorted_routes,
-                               int* row_expert, int* items_a, int* items_b, int* scratch, cudaStream_t stream, int* route_pos) {
+cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int experts, const ItemLists& lists, int* status, int* counts,
+                               int* offsets, int* sorted_routes, int* row_expert, int* scratch, cudaStream_t stream, int* route_pos) {
   if (routes <= kSmallRoutes) {
     const size_t small_bytes = (static_cast<size_t>(kSmallRoutes) + 4 * static_cast<size_t>(experts) + 4) * sizeof(int);
-    route_small_kernel<<<1, kSmallRoutes, small_bytes, stream>>>(topk_ids, static_cast<int>(routes), experts, tile_a,
-                                                                 tile_b, max_items, status, counts, offsets, sorted_routes, row_expert,
-                                                                 items_a, items_b, route_pos);
+    route_small_kernel<<<1, kSmallRoutes, small_bytes, stream>>>(topk_ids, static_cast<int>(routes), experts, lists, status, counts, offsets,
+                                                                 sorted_routes, row_expert, route_pos);
     return cudaGetLastError();
   }
   const int units = static_cast<int>((routes + kUnitRoutes - 1) / kUnitRoutes);
@@ -266,8 +274,7 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
   if (blocks > 0) {
     route_hist_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist, status);
   }
-  route_scan_kernel<<<1, 1024, 0, stream>>>(experts, units, unit_hist, counts, offsets, tile_a, tile_b, items_a, items_b,
-                                            max_items, scan_tmp, status);
+  route_scan_kernel<<<1, 1024, 0, stream>>>(experts, units, unit_hist, counts, offsets, lists, scan_tmp, status);
   if (blocks > 0) {
     route_scatter_kernel<<<blocks, kWarpsPerBlock * 32, smem, stream>>>(topk_ids, routes, experts, units, unit_hist,
                                                                         offsets, sorted_routes, row_expert, route_pos);
@@ -279,9 +286,9 @@ namespace {
 // Work items and the status words of the grouped GEMMs from given per-expert counts and offsets (rows that
 // already lie in expert order: nothing to sort).
 __global__ void __launch_bounds__(1024)
-items_from_counts_kernel(int experts, const int* __restrict__ counts, const int* __restrict__ offsets, int tile_a, int tile_b,
-                         int* items_a, int* items_b, int max_items, int* scan_tmp, int* status) {
-  build_items(experts, counts, offsets, tile_a, tile_b, items_a, items_b, max_items, scan_tmp, status);
+items_from_counts_kernel(int experts, const int* __restrict__ counts, const int* __restrict__ offsets, ItemLists lists, int* scan_tmp,
+                         int* status) {
+  build_items(experts, counts, offsets, lists, scan_tmp, status);
 }
 
 __global__ void dense_items_kernel(int64_t rows, int row_tile, int max_items, int* items, int* status) {
@@ -301,9 +308,9 @@ __global__ void dense_items_kernel(int64_t rows, int row_tile, int max_items, in
 }
 }  // namespace
 
-cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, int tile_a, int tile_b, int max_items,
-                                     int* items_a, int* items_b, int* scratch, int* status, cudaStream_t stream) {
-  items_from_counts_kernel<<<1, 1024, 0, stream>>>(experts, counts, offsets, tile_a, tile_b, items_a, items_b, max_items, scratch, status);
+cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, const ItemLists& lists, int* scratch, int* status,
+                                     cudaStream_t stream) {
+  items_from_counts_kernel<<<1, 1024, 0, stream>>>(experts, counts, offsets, lists, scratch, status);
   return cudaGetLastError();
 }
 
@@ -391,8 +398,8 @@ extern "C" int fmoe_route_build_noalloc(const int64_t* topk_ids, int64_t tokens,
   int* work = scratch + fmoe::kStatusWords;    // histograms + scan temporaries: fully rewritten by every call
   error = cudaMemsetAsync(status, 0, sizeof(int) * fmoe::kStatusWords, stream);
   if (error == cudaSuccess) {
-    error = fmoe::launch_route_build(topk_ids, routes, experts, 16, 16, 0, status, counts, offsets, sorted_routes, row_expert, nullptr,
-                                     nullptr, work, stream);
+    error = fmoe::launch_route_build(topk_ids, routes, experts, fmoe::no_item_lists(), status, counts, offsets, sorted_routes, row_expert, work,
+                                     stream);
   }
   if (error == cudaSuccess) error = cudaMemcpyAsync(status_out, status, 2 * sizeof(int), cudaMemcpyDeviceToDevice, stream);
   if (error != cudaSuccess) {

@@ -41,7 +41,7 @@ constexpr int kBlockKBytes = 128;   // bytes of K per pipeline stage = one 128-b
 constexpr int kUmmaKBytes = 32;     // bytes of K per tcgen05.mma
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarp0 = 2;
-constexpr int kSmemBudget = 196 * 1024;
+constexpr int kSmemBudget = 216 * 1024;  // operand stages; with the control block and alignment slack 224 KB of the 227 KB a CTA may have
 
 template <bool kGateUp, int kRowTile>
 struct TileConfig {

@@ -10,7 +10,7 @@ import os
 import pytest
 import torch
 
-from fused_cpp_b200 import _lib
+from fused_cpp_b200 import _lib, synthetic
 from oracle import oracle
 from tests import cases
 
@@ -88,6 +88,31 @@ def test_w8a8_matches_reference_golden(cuda_device, name, impl):
     assert torch.equal(result.region("a_scale", torch.float32, (routes,)).cpu(), golden["a"].float()[token_of_row])
     # The reference's own native-vs-Python tolerance is atol=3e-6 (tests/test_moe_w8a8.py:225); this path is bit-exact.
     assert torch.equal(result.out.cpu().view(torch.int16), golden["out"].view(torch.int16))
+
+
+def _skewed_case(tokens=300, experts=14, top_k=3, hidden=128, inter=96):
+    """One expert takes a route of every token (hundreds of rows), one takes 70, the rest a handful, one none:
+    with automatic tiles the experts above 64 rows go to the two-SM kernel and the others to the one-SM kernel
+    in the same forward."""
+    shape = synthetic.MoEShape(tokens=tokens, hidden=hidden, inter=inter, experts=experts, top_k=top_k)
+    case = synthetic.make_w8a8_case(shape, seed=424242)
+    generator = torch.Generator().manual_seed(99)
+    ids = torch.empty((tokens, top_k), dtype=torch.int64)
+    ids[:, 0] = 0
+    ids[:, 1] = torch.where(torch.arange(tokens) < 70, torch.full((tokens,), 1), 2 + torch.randint(0, 5, (tokens,), generator=generator))
+    ids[:, 2] = 7 + torch.randint(0, 6, (tokens,), generator=generator)  # experts 7..12; expert 13 stays empty
+    case["topk_ids"] = ids
+    return case
+
+
+@pytest.mark.parametrize("numerics", [0, 1], ids=["torchref", "native"])
+def test_w8a8_experts_split_between_the_two_kernels(cuda_device, numerics):
+    case = _skewed_case()
+    counts = torch.bincount(case["topk_ids"].reshape(-1), minlength=14)
+    assert counts.max() > 256 and (counts > 64).sum() >= 2 and ((counts > 0) & (counts <= 64)).sum() >= 5 and counts[13] == 0
+    result = _run(case, cuda_device, numerics=numerics, gemm_impl=_lib.GEMM_UMMA, dump=True)
+    _check_all_stages(case, result, numerics)
+    assert result.status_word(6) > 0 and result.status_word(2) > 0  # both kernels had work items
 
 
 @pytest.mark.parametrize("name", ["wide", "cfg1", "ragged"])
