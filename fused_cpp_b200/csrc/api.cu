@@ -94,17 +94,16 @@ int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, i
   return FMOE_OK;
 }
 
-int pick_row_tile(int requested, int64_t routes, int experts, bool umma) {
+// Row tile when the caller leaves it to the library and the batch has at most 64 tokens: an expert can then hold at
+// most `tokens` rows, so the smallest tile that holds them all puts every expert in one work item whatever the
+// routing looks like (the MMA's N follows the rows an item really has, a taller tile only costs shared memory:
+// +0.4 % on uniformly routed decode, -26 % on Zipf-routed decode at T = 64).
+int pick_row_tile(int requested, int64_t tokens, bool umma) {
   if (!umma) return fmoe::kSimtRowTile;
   if (requested != 0) return requested;
-  // Expected rows per expert decide the tile: the smallest MMA N that holds a typical expert in one
-  // work item, so each weight byte is streamed once.
-  const int64_t average = (routes + experts - 1) / experts;
-  if (average <= 8) return 16;
-  if (average <= 24) return 32;
-  if (average <= 48) return 64;
-  if (average <= 96) return 128;
-  return fmoe::kPairRowTile;  // a hundred rows per expert and more: the two-SM kernel (256-row work items)
+  if (tokens <= 16) return 16;
+  if (tokens <= 32) return 32;
+  return 64;
 }
 
 struct StageTimer {
@@ -195,10 +194,10 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   // Unless the caller fixed the tiles, the experts are then split on the device: those with at most 64 rows
   // go through the one-SM kernel (64-row tile, every weight byte streamed once), the others through the
   // two-SM kernel (256-row work items).  Up to 64 tokens no expert can exceed 64 rows and the tile follows
-  // the average.
+  // the batch size (pick_row_tile).
   const bool split = umma && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
-  const int tile_gu = split ? kSplitRows : pick_row_tile(cfg.gate_up_tile, routes, f.experts, umma);
-  const int tile_dn = split ? kSplitRows : pick_row_tile(cfg.down_tile, routes, f.experts, umma);
+  const int tile_gu = split ? kSplitRows : pick_row_tile(cfg.gate_up_tile, f.tokens, umma);
+  const int tile_dn = split ? kSplitRows : pick_row_tile(cfg.down_tile, f.tokens, umma);
   if (umma && (!fmoe::umma_row_tile_supported(tile_gu) || !fmoe::umma_row_tile_supported(tile_dn))) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128, 256 or 512 = two-SM pairs (got %d, %d)", tile_gu, tile_dn);
   }

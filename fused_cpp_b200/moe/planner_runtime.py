@@ -31,19 +31,10 @@ from .plan import AsyncMoEPlanV2, gpu_placeholder_plan
 
 DEFAULT_MOE_COST_CACHE_DIR = Path(os.environ.get("FUSED_CPP_MOE_COST_CACHE_DIR", Path.home() / ".cache" / "fused_cpp_b200" / "moe"))
 ROUTE_BUCKETS = (1, 2, 4, 8, 12, 24, 48, 96, 192, 384, 768, 1536, 2040, 4096, 8192)
-CANDIDATE_TILES = (16, 32, 64, 128, 256, 512)  # 512 = the two-SM (cta_group::2) kernel with 256-row items
+# 0 = the library's automatic choice (by batch size, and above 64 tokens a per-expert split made on the device);
+# 512 = the two-SM (cta_group::2) kernel with 256-row items for every expert.
+CANDIDATE_TILES = (0, 16, 32, 64, 128, 256, 512)
 PROFILE_SCHEMA = 1
-
-
-def default_tile(rows_per_expert: int) -> int:
-    """Built-in choice when no profile covers the bucket: the smallest MMA N that holds the expert."""
-    if rows_per_expert <= 8:
-        return 16
-    if rows_per_expert <= 24:
-        return 32
-    if rows_per_expert <= 48:
-        return 64
-    return 128
 
 
 @dataclass(frozen=True)
@@ -64,8 +55,9 @@ class GpuTileCalibration:
             if rows_per_expert <= bucket:
                 break
         if best is None:
-            tile = default_tile(rows_per_expert)
-            return tile, tile
+            # No measurement for this kind: 0 = the library's own choice (by batch size up to 64 tokens, above that a
+            # per-expert split between the one-SM and the two-SM kernel made on the device from the actual routing).
+            return 0, 0
         pair = table.get(best, table.get(str(best)))
         return int(pair[0]), int(pair[1])
 
@@ -142,7 +134,7 @@ def calibrate_moe_planner_quick(cpu_ids: Sequence[int] | None = None, *, output:
 
     Signature of the reference's quick calibration (quick_calibration.py:359-368).  `cpu_ids` is kept
     for compatibility and recorded only; `supported_widths` names the candidate row tiles
-    (default 16..256).  `_probe` lets tests substitute synthetic timings.
+    (default: automatic and 16..512).  `_probe` lets tests substitute synthetic timings.
     """
     begin = time.perf_counter()
     path = Path(output) if output is not None else None
@@ -170,6 +162,10 @@ def calibrate_moe_planner_quick(cpu_ids: Sequence[int] | None = None, *, output:
         for bucket in buckets:
             measured = probe(kind, bucket, tiles, seed, 2048, 1024, 32)
             best = min(measured, key=lambda t: (measured[t], t))
+            # The probe routes uniformly; a fixed tile that is not clearly faster there is not worth giving up the
+            # automatic choice, which adapts to the routing of every batch.
+            if 0 in measured and measured[0] <= 1.03 * measured[best]:
+                best = 0
             table[kind][int(bucket)] = (int(best), int(best))
             timings[kind][int(bucket)] = {int(t): float(v) for t, v in measured.items()}
             if report is not None:
