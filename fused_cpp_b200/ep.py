@@ -328,9 +328,9 @@ def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, to
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
         return float(elapsed.item()), clocks
 
-    # The forward makes no host read, so one step (kernels and the three small collectives) is captured into a
-    # CUDA graph and the timed region replays it; every rank replays the same sequence.  Eager launches are
-    # timed as well (eager_ms_per_step).
+    # The forward makes no host read and calls no collective library, so one step (kernels, flag barriers included)
+    # is captured into a CUDA graph and the timed region replays it; every rank replays the same sequence.  Eager
+    # launches are timed as well (eager_ms_per_step).
     launch_mode = "eager"
     replay = step
     graph = None
