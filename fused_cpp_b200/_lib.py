@@ -23,10 +23,11 @@ ERR_UNSUPPORTED_DEVICE = 6
 NUMERICS_TORCHREF = 0
 NUMERICS_NATIVE = 1
 GEMM_AUTO = 0
-GEMM_SIMT = 1
+GEMM_SIMT = 1  # the CUDA-core cross-check GEMM: exists only in the diagnostic library (load_diag)
 GEMM_UMMA = 2
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfused_moe_b200.so")
+DIAG_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfused_moe_b200_diag.so")
 
 EXPORTS = (
     "fmoe_abi_version", "fmoe_last_error", "fmoe_device_supported", "fmoe_read_status",
@@ -35,10 +36,11 @@ EXPORTS = (
     "fmoe_stage_timer_create", "fmoe_stage_timer_destroy", "fmoe_stage_timer_reset", "fmoe_stage_timer_calls",
     "fmoe_stage_timer_read", "fmoe_route_build_noalloc", "fmoe_ep_dispatch_workspace_bytes", "fmoe_ep_dispatch_prepare",
     "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
-    "fmoe_i8gemm_dynamic_scaled_mm_pair", "fmoe_probe_mma_rate",
+    "fmoe_i8gemm_dynamic_scaled_mm_pair",
     "fmoe_router_topk",
     "fmoe_ep_peer_create", "fmoe_ep_peer_handle", "fmoe_ep_peer_connect", "fmoe_ep_peer_destroy", "fmoe_ep_peer_slab_bytes",
     "fmoe_ep_peer_dispatch", "fmoe_ep_peer_experts", "fmoe_ep_peer_combine", "fmoe_ep_peer_read_status",
+    "fmoe_ep_peer_slab_address", "fmoe_ep_peer_connect_addresses",
 )
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
@@ -64,17 +66,33 @@ class FusedMoEError(RuntimeError):
 
 
 _LIB = None
+_DIAG_LIB = None
 
 
 def load() -> ctypes.CDLL:
     """Load the shared library; raise (never fall back) if it is absent."""
     global _LIB
-    if _LIB is not None:
-        return _LIB
-    if not os.path.exists(LIB_PATH):
-        raise FusedMoEError(ERR_CUDA, f"{LIB_PATH} is missing: build it with `python -m fused_cpp_b200.build` "
+    if _LIB is None:
+        _LIB = _open(LIB_PATH)
+    return _LIB
+
+
+def load_diag() -> ctypes.CDLL:
+    """The diagnostic twin of the library (same ABI plus the CUDA-core GEMM, the MMA-rate probe and the stage
+    switches of FUSED_CPP_MOE_GEMM_DIAG).  For tests and measurements; the package's forward path never loads it."""
+    global _DIAG_LIB
+    if _DIAG_LIB is None:
+        _DIAG_LIB = _open(DIAG_LIB_PATH)
+        _DIAG_LIB.fmoe_probe_mma_rate.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                                  ctypes.POINTER(ctypes.c_float)]
+    return _DIAG_LIB
+
+
+def _open(path: str) -> ctypes.CDLL:
+    if not os.path.exists(path):
+        raise FusedMoEError(ERR_CUDA, f"{path} is missing: build it with `python -m fused_cpp_b200.build` "
                                       "(there is no CPU or PyTorch fallback for this path)")
-    lib = ctypes.CDLL(LIB_PATH)
+    lib = ctypes.CDLL(path)
     lib.fmoe_last_error.restype = ctypes.c_char_p
     lib.fmoe_i8gemm_workspace_bytes.restype = ctypes.c_size_t
     lib.fmoe_i8gemm_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
@@ -101,7 +119,6 @@ def load() -> ctypes.CDLL:
                                                   ctypes.c_size_t, p]
     lib.fmoe_bf16_expert_rows_forward.argtypes = [p, p, i64, p, p, i32, i32, i32, ctypes.POINTER(Config), p, p, ctypes.c_size_t, p]
     lib.fmoe_ep_combine_finish.argtypes = [p, p, p, i64, i32, i32, i32, p, p, p]
-    lib.fmoe_probe_mma_rate.argtypes = [i32, i32, i32, i32, ctypes.POINTER(ctypes.c_float)]
     lib.fmoe_route_build_noalloc.argtypes = [p, i64, i32, i32, p, p, p, p, p, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm.argtypes = [p, i32, i64, i32, p, p, p, i32, p, i32, p, ctypes.c_size_t, p]
     lib.fmoe_i8gemm_dynamic_scaled_mm_pair.argtypes = [p, i64, i32, p, p, i32, p, p, p, i32, p, p, ctypes.c_size_t, p]
@@ -111,19 +128,21 @@ def load() -> ctypes.CDLL:
     lib.fmoe_ep_peer_connect.argtypes = [p, p]
     lib.fmoe_ep_peer_destroy.argtypes = [p]
     lib.fmoe_ep_peer_destroy.restype = None
+    lib.fmoe_ep_peer_slab_address.argtypes = [p]
+    lib.fmoe_ep_peer_slab_address.restype = ctypes.c_void_p
+    lib.fmoe_ep_peer_connect_addresses.argtypes = [p, ctypes.POINTER(ctypes.c_void_p)]
     lib.fmoe_ep_peer_slab_bytes.argtypes = [p]
     lib.fmoe_ep_peer_slab_bytes.restype = ctypes.c_int64
     lib.fmoe_ep_peer_dispatch.argtypes = [p, p, p, i64, i32, i32, i32, p]
     lib.fmoe_ep_peer_experts.argtypes = [p, p, p, p, p, ctypes.POINTER(Config), p]
     lib.fmoe_ep_peer_combine.argtypes = [p, p, i64, i32, p, p]
     lib.fmoe_ep_peer_read_status.argtypes = [p, p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
-    _LIB = lib
     return lib
 
 
-def check(code: int) -> None:
+def check(code: int, lib: ctypes.CDLL | None = None) -> None:
     if code != OK:
-        message = load().fmoe_last_error().decode("utf-8", "replace")
+        message = (lib or load()).fmoe_last_error().decode("utf-8", "replace")
         error_type = ValueError if code == ERR_INVALID_ARGUMENT else FusedMoEError
         if error_type is ValueError:
             raise ValueError(message)
@@ -252,8 +271,9 @@ def _require_cuda(name: str, tensor: torch.Tensor, dtype: torch.dtype) -> torch.
 def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numerics: int = NUMERICS_TORCHREF,
                 gemm_impl: int = GEMM_AUTO, gate_up_tile: int = 0, down_tile: int = 0, swiglu_limit: float | None = None,
                 out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None,
-                stage_timer: "StageTimer | None" = None) -> ForwardResult:
-    """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8."""
+                stage_timer: "StageTimer | None" = None, diagnostic: bool = False) -> ForwardResult:
+    """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8.
+    diagnostic=True (or gemm_impl=GEMM_SIMT) runs the call in the diagnostic library instead of the product one."""
     int8 = w13.dtype == torch.int8
     x = _require_cuda("input", x, torch.bfloat16)
     w13 = _require_cuda("w13", w13, torch.int8 if int8 else torch.bfloat16)
@@ -290,7 +310,8 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
         acc2 = torch.zeros((max(tokens * top_k, 1), hidden), dtype=acc_dtype, device=x.device)
         config.dump_acc1 = acc1.data_ptr()
         config.dump_acc2 = acc2.data_ptr()
-    lib = load()
+    # The CUDA-core cross-check and the stage switches exist only in the diagnostic library.
+    lib = load_diag() if (gemm_impl == GEMM_SIMT or diagnostic) else load()
     if int8:
         code = lib.fmoe_w8a8_forward(_ptr(x), _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2), _ptr(topk_weights), _ptr(topk_ids),
                                      tokens, top_k, experts, hidden, inter, ctypes.byref(config), _ptr(out),
@@ -299,7 +320,7 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
         code = lib.fmoe_bf16_forward(_ptr(x), _ptr(w13), _ptr(w2), _ptr(topk_weights), _ptr(topk_ids), tokens, top_k,
                                      experts, hidden, inter, ctypes.byref(config), _ptr(out), _ptr(workspace),
                                      workspace.numel(), _stream())
-    check(code)
+    check(code, lib)
     return ForwardResult(out=out, workspace=workspace, layout=layout, acc1=acc1, acc2=acc2)
 
 
@@ -466,6 +487,17 @@ class PeerContext:
         check(load().fmoe_ep_peer_connect(self.handle, ctypes.create_string_buffer(blob, len(blob))))
 
     @property
+    def slab_address(self) -> int:
+        return int(load().fmoe_ep_peer_slab_address(self.handle) or 0)
+
+    def connect_addresses(self, addresses: list) -> None:
+        """Connect ranks that can already address one another's slabs (contexts of one process)."""
+        if len(addresses) != self.world:
+            raise ValueError("expected one slab address per rank")
+        table = (ctypes.c_void_p * self.world)(*[ctypes.c_void_p(int(a)) for a in addresses])
+        check(load().fmoe_ep_peer_connect_addresses(self.handle, table))
+
+    @property
     def slab_bytes(self) -> int:
         return int(load().fmoe_ep_peer_slab_bytes(self.handle))
 
@@ -501,5 +533,5 @@ def probe_mma_rate(int8: bool, n: int = 256, iterations: int = 20000, *, nonzero
 
     nonzero: operands hold a non-zero pattern instead of zeros; commit_every: a tcgen05.commit after every c MMAs."""
     value = ctypes.c_float(0.0)
-    check(load().fmoe_probe_mma_rate(1 if int8 else 0, n, iterations, (1 if nonzero else 0) | (commit_every << 8), ctypes.byref(value)))
+    check(load_diag().fmoe_probe_mma_rate(1 if int8 else 0, n, iterations, (1 if nonzero else 0) | (commit_every << 8), ctypes.byref(value)))
     return float(value.value)

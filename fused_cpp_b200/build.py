@@ -1,8 +1,14 @@
-"""Build libfused_moe_b200.so in-tree with nvcc for sm_100a.
+"""Build libfused_moe_b200.so (and its diagnostic twin) in-tree with nvcc for sm_100a.
 
 Usage: python -m fused_cpp_b200.build [--force] [--verbose]
 The library links only the CUDA runtime (statically); it has no torch dependency, so it builds
 in seconds and the same file serves Python (ctypes) and any other C-ABI caller.
+
+Two files come out:
+  lib/libfused_moe_b200.so       the product: the tcgen05 kernels and the C ABI of include/fused_moe_b200.h;
+  lib/libfused_moe_b200_diag.so  the same sources compiled with -DFMOE_DIAG plus a CUDA-core cross-check GEMM and
+                                 a tensor-core issue-rate probe (csrc/diag.h).  Only tests and measurement
+                                 scripts load it; nothing in the package's forward path does.
 """
 from __future__ import annotations
 
@@ -15,7 +21,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(OUT_DIR, "libfused_moe_b200.so")
-SOURCES = ["api.cu", "route.cu", "quant.cu", "merge.cu", "simt_gemm.cu", "umma_gemm.cu", "umma2_gemm.cu", "ep.cu", "probe.cu", "router.cu"]
+DIAG_LIB = os.path.join(OUT_DIR, "libfused_moe_b200_diag.so")
+SOURCES = ["api.cu", "route.cu", "quant.cu", "merge.cu", "umma_gemm.cu", "umma2_gemm.cu", "ep.cu", "router.cu"]
+DIAG_ONLY_SOURCES = ["simt_gemm.cu", "probe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
@@ -37,14 +45,16 @@ def _newest_input() -> float:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OUT_DIR, exist_ok=True)
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_input():
+    newest = _newest_input()
+    if not force and all(os.path.exists(p) and os.path.getmtime(p) >= newest for p in (LIB, DIAG_LIB)):
         return LIB
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
 
-    def compile_one(name: str) -> str:
-        obj = os.path.join(OUT_DIR, name.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, name), "-o", obj]
+    def compile_one(job) -> str:
+        name, diag = job
+        obj = os.path.join(OUT_DIR, ("diag_" if diag else "") + name.replace(".cu", ".o"))
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DFMOE_DIAG"] if diag else []), *extra, "-c", os.path.join(CSRC, name), "-o", obj]
         result = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or result.returncode != 0:
             sys.stderr.write(result.stdout + result.stderr)
@@ -52,10 +62,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {name}")
         return obj
 
-    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
-        objects = list(pool.map(compile_one, SOURCES))
-    link = [nvcc, "-shared", "-o", LIB, *objects, "-gencode", "arch=compute_100a,code=sm_100a"]
-    subprocess.run(link, check=True)
+    jobs = [(name, False) for name in SOURCES] + [(name, True) for name in SOURCES + DIAG_ONLY_SOURCES]
+    with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
+        objects = list(pool.map(compile_one, jobs))
+    product = objects[: len(SOURCES)]
+    diagnostic = objects[len(SOURCES):]
+    for target, parts in ((LIB, product), (DIAG_LIB, diagnostic)):
+        subprocess.run([nvcc, "-shared", "-o", target, *parts, "-gencode", "arch=compute_100a,code=sm_100a"], check=True)
     return LIB
 
 

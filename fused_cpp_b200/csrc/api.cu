@@ -8,6 +8,9 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#ifdef FMOE_DIAG
+#include "diag.h"
+#endif
 
 namespace {
 
@@ -139,6 +142,11 @@ struct Forward {
   const uint64_t* peer_slabs = nullptr;
   size_t peer_route_out_offset = 0;
   bool peer_rows_bf16 = false;  // result rows travel as bf16 (opt-in, not bit-identical to the fp32 merge input)
+  // Bounds of a valid return address (source rank < peer_world, flat route < peer_routes_max) and the local row
+  // that takes the stores of a row whose return address is not valid.
+  int peer_world = 0;
+  int64_t peer_routes_max = 0;
+  void* peer_scrap_row = nullptr;
 };
 
 int run_forward(const Forward& f, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes, void* stream_ptr) {
@@ -153,12 +161,15 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
   }
   if (!f.rows_mode && (f.topk_weights == nullptr || out == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null tensor pointer");
-  if (peer && (!f.rows_mode || f.sorted_counts == nullptr || f.sorted_offsets == nullptr || f.rows_source == nullptr)) {
+  if (peer && (!f.rows_mode || f.sorted_counts == nullptr || f.sorted_offsets == nullptr || f.rows_source == nullptr ||
+               f.peer_scrap_row == nullptr || f.peer_world <= 0)) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "peer-memory mode needs expert-sorted rows with device-side counts and their sources");
   }
+#ifdef FMOE_DIAG
   if (peer && config != nullptr && config->gemm_impl == FMOE_GEMM_SIMT) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "peer-memory mode runs on the tensor-core GEMMs only");
   }
+#endif
   if (f.rows_mode && ((f.route_out_override == nullptr && !peer) || (f.int8 && f.rows_scale == nullptr) || f.top_k != 1)) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "expert-rows mode needs route_out, row scales (int8) and one route per row");
   }
@@ -185,10 +196,17 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (cfg.numerics != FMOE_NUMERICS_TORCHREF && cfg.numerics != FMOE_NUMERICS_NATIVE) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown numerics %d", cfg.numerics);
   }
+#ifdef FMOE_DIAG
   if (cfg.gemm_impl < FMOE_GEMM_AUTO || cfg.gemm_impl > FMOE_GEMM_UMMA) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown gemm_impl %d", cfg.gemm_impl);
   }
   const bool umma = cfg.gemm_impl != FMOE_GEMM_SIMT;
+#else
+  if (cfg.gemm_impl != FMOE_GEMM_AUTO && cfg.gemm_impl != FMOE_GEMM_UMMA) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown gemm_impl %d (this library has one grouped-GEMM implementation, tcgen05)", cfg.gemm_impl);
+  }
+  const bool umma = true;
+#endif
   const int64_t routes = f.tokens * f.top_k;
   // Above 64 tokens an expert can hold anything from one row to all of them, and the host does not know the routing.
   // Unless the caller fixed the tiles, the experts are then split on the device: those with at most 64 rows
@@ -244,7 +262,8 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     if (error != cudaSuccess) return cuda_fail(error, "work items");
     row_out_ptrs = reinterpret_cast<uint64_t*>(base + layout.route_out);
     error = fmoe::launch_peer_row_ptrs(f.sorted_offsets + f.experts, routes, f.rows_source, f.peer_slabs, f.peer_route_out_offset,
-                                       f.hidden * (f.peer_rows_bf16 ? 2 : 4), row_out_ptrs, stream);
+                                       f.hidden * (f.peer_rows_bf16 ? 2 : 4), row_out_ptrs, f.peer_world, f.peer_routes_max,
+                                       f.peer_scrap_row, status_block, stream);
     if (error != cudaSuccess) return cuda_fail(error, "peer output addresses");
   } else {
     error = fmoe::launch_route_build(f.topk_ids, routes, f.experts, lists, status_block, counts, offsets, sorted_routes, row_expert, scratch,
@@ -297,7 +316,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.dump_acc = cfg.dump_acc1;
   gu.total_rows = routes;
   gu.row_tile = tile_gu;
+#ifdef FMOE_DIAG
   error = umma ? fmoe::launch_umma_grouped_gemm(gu, f.int8, true, stream) : fmoe::launch_simt_grouped_gemm(gu, f.int8, true, stream);
+#else
+  error = fmoe::launch_umma_grouped_gemm(gu, f.int8, true, stream);
+#endif
   if (error == cudaSuccess && split) {
     fmoe::GroupedGemmArgs big = gu;
     big.items = items_gu_big;
@@ -332,7 +355,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   dn.route_out_bf16 = peer && f.peer_rows_bf16 ? 1 : 0;
   dn.dump_acc = cfg.dump_acc2;
   dn.row_tile = tile_dn;
+#ifdef FMOE_DIAG
   error = umma ? fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
+#else
+  error = fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream);
+#endif
   if (error == cudaSuccess && split) {
     fmoe::GroupedGemmArgs big = dn;
     big.items = items_dn_big;
@@ -384,8 +411,15 @@ int fmoe_read_status(const void* workspace, void* stream, int32_t* error, int32_
   if (words[fmoe::kStatusError] == FMOE_ERR_EXPERT_ID_RANGE) {
     fail(FMOE_ERR_EXPERT_ID_RANGE, "topk expert id is out of range at flat route %d", words[fmoe::kStatusDetail]);
   } else if (words[fmoe::kStatusError] == FMOE_ERR_DEVICE_WAIT) {
-    fail(FMOE_ERR_DEVICE_WAIT, "a bounded device wait gave up (CTA %d, site %d)", words[fmoe::kStatusDetail],
-         words[fmoe::kStatusWaitSite]);
+    if (words[fmoe::kStatusWaitSite] != 0) {
+      fail(FMOE_ERR_DEVICE_WAIT, "a bounded device wait gave up (CTA %d, site %d)", words[fmoe::kStatusDetail],
+           words[fmoe::kStatusWaitSite]);
+    } else if (words[fmoe::kStatusDetail] >= 0) {
+      fail(FMOE_ERR_DEVICE_WAIT, "a peer barrier gave up waiting for rank %d", words[fmoe::kStatusDetail]);
+    } else {
+      fail(FMOE_ERR_DEVICE_WAIT, "an expert-parallel row carried an invalid destination or return address (check %d)",
+           -words[fmoe::kStatusDetail]);
+    }
   }
   return FMOE_OK;
 }
@@ -709,11 +743,13 @@ int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows, int32_t
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm pair GEMM");
 }
 
+#ifdef FMOE_DIAG
 int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mode, float* tera_ops_per_s) {
   int status = check_device();
   if (status != FMOE_OK) return status;
-  if (tera_ops_per_s == nullptr || iterations <= 0 || n < 16 || n > 256 || n % 16 != 0) {
-    return fail(FMOE_ERR_INVALID_ARGUMENT, "probe: n must be a multiple of 16 in [16, 256] and iterations positive");
+  // The iteration cap keeps one launch (about 0.1 us per MMA at n = 256) far below the kernels' one-second wait limit.
+  if (tera_ops_per_s == nullptr || iterations <= 0 || iterations > 1000000 || n < 16 || n > 256 || n % 16 != 0) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "probe: n must be a multiple of 16 in [16, 256] and iterations in 1..1000000");
   }
   int device = 0, sms = 0;
   cudaGetDevice(&device);
@@ -743,6 +779,7 @@ int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mod
   *tera_ops_per_s = static_cast<float>(ops / (best_ms * 1e-3) / 1e12);
   return FMOE_OK;
 }
+#endif  // FMOE_DIAG
 
 }  // extern "C"
 
@@ -780,6 +817,7 @@ struct fmoe_ep_peer_context {
   char* expert_ws = nullptr;
   size_t expert_ws_bytes = 0;
   int experts_total_max = 0;          // routed experts of all ranks + 1: row length of the count table in the slab
+  char* scrap_row = nullptr;          // device: one result row that absorbs stores of rows without a valid return address
   int* small = nullptr;               // device: send_base[experts_total_max] | local_counts[local] | local_offsets[local+1] | epoch
   int* send_base = nullptr;
   int* local_counts = nullptr;
@@ -890,7 +928,11 @@ int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max, int32_t
   const size_t small_ints = static_cast<size_t>(ctx->experts_total_max) + local_experts + (local_experts + 1) + 1;
   if (error == cudaSuccess) error = cudaMalloc(&ctx->small, sizeof(int) * small_ints);
   if (error == cudaSuccess) error = cudaMemset(ctx->small, 0, sizeof(int) * small_ints);
-  if (error == cudaSuccess) error = cudaMemset(ctx->slab_base + ctx->slab.counts, 0, ctx->slab.total - ctx->slab.counts);
+  if (error == cudaSuccess) error = cudaMalloc(&ctx->scrap_row, static_cast<size_t>(hidden) * sizeof(float));
+  // The whole slab starts at zero: counts and flags must, and a row that is read before it ever arrived (after a
+  // barrier that gave up) then carries the return address (rank 0, route 0) and zero data instead of whatever the
+  // allocation held.
+  if (error == cudaSuccess) error = cudaMemset(ctx->slab_base, 0, ctx->slab.total);
   if (error != cudaSuccess) {
     fmoe_ep_peer_destroy(ctx);
     return cuda_fail(error, "peer context allocation");
@@ -937,6 +979,22 @@ int fmoe_ep_peer_connect(fmoe_ep_peer_context* ctx, const void* handles) {
   return FMOE_OK;
 }
 
+void* fmoe_ep_peer_slab_address(fmoe_ep_peer_context* ctx) { return ctx ? ctx->slab_base : nullptr; }
+
+int fmoe_ep_peer_connect_addresses(fmoe_ep_peer_context* ctx, const void* const* slabs) {
+  if (ctx == nullptr || slabs == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  if (ctx->connected) return fail(FMOE_ERR_INVALID_ARGUMENT, "peer context is already connected");
+  std::vector<uint64_t> table(ctx->world, 0);
+  for (int r = 0; r < ctx->world; ++r) {
+    table[r] = r == ctx->rank ? reinterpret_cast<uint64_t>(ctx->slab_base) : reinterpret_cast<uint64_t>(slabs[r]);
+    if (table[r] == 0 || table[r] % 256 != 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "slab address of rank %d is null or misaligned", r);
+  }
+  const cudaError_t error = cudaMemcpy(ctx->peer_slabs_dev, table.data(), sizeof(uint64_t) * ctx->world, cudaMemcpyHostToDevice);
+  if (error != cudaSuccess) return cuda_fail(error, "peer table upload");
+  ctx->connected = true;
+  return FMOE_OK;
+}
+
 void fmoe_ep_peer_destroy(fmoe_ep_peer_context* ctx) {
   if (ctx == nullptr) return;
   for (void* mapped : ctx->opened) {
@@ -947,6 +1005,7 @@ void fmoe_ep_peer_destroy(fmoe_ep_peer_context* ctx) {
   if (ctx->dispatch_ws) cudaFree(ctx->dispatch_ws);
   if (ctx->peer_slabs_dev) cudaFree(ctx->peer_slabs_dev);
   if (ctx->small) cudaFree(ctx->small);
+  if (ctx->scrap_row) cudaFree(ctx->scrap_row);
   delete ctx;
 }
 
@@ -988,17 +1047,22 @@ int fmoe_ep_peer_dispatch(fmoe_ep_peer_context* ctx, const void* x, const int64_
     // ... and derives from them where its rows go and what it will receive.
     error = fmoe::launch_peer_layout(reinterpret_cast<const int*>(ctx->slab_base + ctx->slab.counts), ctx->world, ctx->rank, experts_global,
                                      per_rank, has_shared, ctx->experts_total_max, ctx->send_base, ctx->local_counts, ctx->local_offsets,
-                                     stream);
+                                     d.status, stream);
   }
   if (error == cudaSuccess) {
     error = fmoe::launch_peer_dispatch(ctx->int8 != 0, static_cast<const uint16_t*>(x), topk_ids, tokens, ctx->hidden, ctx->top_k,
                                        d.route_pos, d.offsets, ctx->send_base, ctx->slab, ctx->peer_slabs_dev, ctx->rank, experts_global,
-                                       per_rank, has_shared, numerics, stream);
+                                       per_rank, has_shared, numerics, ctx->capacity, d.status, stream);
   }
   if (error == cudaSuccess) {
-    // After this barrier every row of this rank's experts has arrived.
+    // After this barrier every row of this rank's experts has arrived.  If it (or the first one) gave up, the
+    // counts of this rank's experts are cleared: the expert stage then finds no rows, makes no work items and
+    // stores nothing, instead of multiplying rows that are not there.  Every index the later stages derive from
+    // the counts stays below `capacity` either way: send_base and the local offsets are sums of at most
+    // world x tokens_max x top_k counts when the table is whole, are all zero when the exchange failed, and the
+    // dispatch kernel drops (and reports) any row at or beyond `capacity`.
     error = fmoe::launch_peer_barrier(ctx->peer_slabs_dev, ctx->slab, nullptr, 0, ctx->world, ctx->rank, ctx->epoch, d.status,
-                                      ctx->wait_limit_ns, stream);
+                                      ctx->wait_limit_ns, stream, ctx->local_counts, 2 * ctx->local_experts + 1);
   }
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "peer dispatch");
 }
@@ -1016,6 +1080,9 @@ int fmoe_ep_peer_experts(fmoe_ep_peer_context* ctx, const void* w13, const float
   f.peer_slabs = ctx->peer_slabs_dev;
   f.peer_route_out_offset = ctx->slab.route_out;
   f.peer_rows_bf16 = ctx->rows_bf16 != 0;
+  f.peer_world = ctx->world;
+  f.peer_routes_max = ctx->tokens_max * ctx->top_k;
+  f.peer_scrap_row = ctx->scrap_row;
   const int status = run_forward(f, config, nullptr, ctx->expert_ws, ctx->expert_ws_bytes, stream);
   if (status != FMOE_OK) return status;
   // After this barrier every result row of this rank's routes has arrived, and every rank is done reading its slab.
@@ -1044,10 +1111,16 @@ int fmoe_ep_peer_combine(fmoe_ep_peer_context* ctx, const float* topk_weights, i
 
 int fmoe_ep_peer_read_status(fmoe_ep_peer_context* ctx, void* stream, int32_t* dispatch_error, int32_t* expert_error) {
   if (ctx == nullptr || dispatch_error == nullptr || expert_error == nullptr) return fail(FMOE_ERR_INVALID_ARGUMENT, "null pointer");
+  // The text of fmoe_last_error() describes the first stage that reported something.
   int32_t detail = 0;
-  int status = fmoe_read_status(ctx->dispatch_ws, stream, dispatch_error, &detail);
+  int status = fmoe_read_status(ctx->expert_ws, stream, expert_error, &detail);
   if (status != FMOE_OK) return status;
-  return fmoe_read_status(ctx->expert_ws, stream, expert_error, &detail);
+  char expert_text[sizeof(g_error)];
+  memcpy(expert_text, g_error, sizeof(expert_text));
+  status = fmoe_read_status(ctx->dispatch_ws, stream, dispatch_error, &detail);
+  if (status != FMOE_OK) return status;
+  if (*dispatch_error == FMOE_OK && *expert_error != FMOE_OK) memcpy(g_error, expert_text, sizeof(g_error));
+  return FMOE_OK;
 }
 
 }  // extern "C"

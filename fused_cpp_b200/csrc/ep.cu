@@ -48,11 +48,16 @@ __global__ void scatter_rows_f32_kernel(const float* __restrict__ rows, const in
 // that epoch.  The stores of the kernels that ran before it on this stream are complete when it starts (stream
 // order), and the fence orders its own stores, so a rank that sees the flag also sees the rows and the table
 // row.  The wait is bounded: after limit_ns it records FMOE_ERR_DEVICE_WAIT (detail = the rank it waited for)
-// and returns.
+// and returns.  What the barrier was meant to guarantee then does not hold, so the caller names the row counts that
+// the following stages trust (zero_on_fail, zero_ints of them): they are cleared on expiry and those stages find
+// no rows to work on instead of rows that never arrived.
 __global__ void __launch_bounds__(256)
 peer_barrier_kernel(const uint64_t* __restrict__ peer_slabs, PeerSlabLayout slab, const int* __restrict__ payload, int payload_ints,
-                    int world, int rank, unsigned* __restrict__ epoch_counter, int* status, unsigned long long limit_ns) {
+                    int world, int rank, unsigned* __restrict__ epoch_counter, int* status, unsigned long long limit_ns,
+                    int* __restrict__ zero_on_fail, int zero_ints) {
   __shared__ unsigned epoch_shared;
+  __shared__ int expired;
+  if (threadIdx.x == 0) expired = 0;
   if (threadIdx.x == 0) {
     epoch_shared = *epoch_counter + 1u;
     *epoch_counter = epoch_shared;
@@ -69,23 +74,30 @@ peer_barrier_kernel(const uint64_t* __restrict__ peer_slabs, PeerSlabLayout slab
   __syncthreads();
   const unsigned epoch = epoch_shared;
   const int peer = threadIdx.x;
-  if (peer >= world) return;
-  const uint64_t theirs = peer_slabs[peer];
-  __threadfence_system();
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs + slab.flags + sizeof(unsigned) * rank), "r"(epoch) : "memory");
-  const uint64_t mine = peer_slabs[rank] + slab.flags + sizeof(unsigned) * peer;
-  unsigned long long start = 0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
-  while (true) {
-    unsigned seen;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-    if (static_cast<int>(seen - epoch) >= 0) break;
-    unsigned long long now;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    if (now - start > limit_ns) {
-      raise_error(status, FMOE_ERR_DEVICE_WAIT, peer);
-      break;
+  if (peer < world) {
+    const uint64_t theirs = peer_slabs[peer];
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs + slab.flags + sizeof(unsigned) * rank), "r"(epoch) : "memory");
+    const uint64_t mine = peer_slabs[rank] + slab.flags + sizeof(unsigned) * peer;
+    unsigned long long start = 0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    while (true) {
+      unsigned seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int>(seen - epoch) >= 0) break;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - start > limit_ns) {
+        raise_error(status, FMOE_ERR_DEVICE_WAIT, peer);
+        expired = 1;
+        break;
+      }
     }
+  }
+  __syncthreads();
+  // An error raised earlier on this status block (an earlier barrier of the same call) counts as well.
+  if (zero_on_fail != nullptr && (expired || *reinterpret_cast<volatile int*>(status + kStatusError) == FMOE_ERR_DEVICE_WAIT)) {
+    for (int i = threadIdx.x; i < zero_ints; i += blockDim.x) zero_on_fail[i] = 0;
   }
 }
 
@@ -97,9 +109,21 @@ peer_barrier_kernel(const uint64_t* __restrict__ peer_slabs, PeerSlabLayout slab
 // One block.
 __global__ void __launch_bounds__(1024)
 peer_layout_kernel(const int* __restrict__ count_matrix, int row_stride, int world, int rank, int experts_global, int per_rank,
-                   int has_shared, int* __restrict__ send_base, int* __restrict__ local_counts, int* __restrict__ local_offsets) {
+                   int has_shared, int* __restrict__ send_base, int* __restrict__ local_counts, int* __restrict__ local_offsets,
+                   const int* __restrict__ status) {
   extern __shared__ int layout_smem[];
   const int experts_total = experts_global + (has_shared ? 1 : 0);
+  if (status[kStatusError] == FMOE_ERR_DEVICE_WAIT) {
+    // The count exchange gave up: a row of the table may be missing or half written.  Nothing is sent and nothing
+    // is expected (the dispatch kernel checks the same word).
+    const int local_experts = per_rank + (has_shared ? 1 : 0);
+    for (int e = threadIdx.x; e < experts_total; e += blockDim.x) send_base[e] = 0;
+    for (int le = threadIdx.x; le <= local_experts; le += blockDim.x) {
+      if (le < local_experts) local_counts[le] = 0;
+      local_offsets[le] = 0;
+    }
+    return;
+  }
   int* total = layout_smem;                  // rows of expert e at its owner
   int* before_me = total + experts_total;    // rows of expert e from lower source ranks
   int* scan = before_me + experts_total;     // exclusive scan of total[] over the routed experts (+ end)
@@ -178,11 +202,12 @@ __global__ void __launch_bounds__(256)
 peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__ topk_ids, int cols, int top_k,
                      const int* __restrict__ route_pos, const int* __restrict__ expert_offsets, const int* __restrict__ send_base,
                      PeerSlabLayout slab, const uint64_t* __restrict__ peer_slabs, int rank, int experts_global, int experts_per_rank,
-                     int has_shared, int numerics) {
+                     int has_shared, int numerics, int64_t capacity, int* __restrict__ status) {
   __shared__ float reduce[32];
   __shared__ int64_t slot_row[32];    // row index in the destination slab, -1 = dropped
   __shared__ uint64_t slot_slab[32];  // base address of the destination slab
   const int64_t token = blockIdx.x;
+  if (status[kStatusError] == FMOE_ERR_DEVICE_WAIT) return;  // the count exchange gave up: no destination is known
   if (threadIdx.x < top_k) {
     const int64_t route = token * top_k + threadIdx.x;
     const int64_t id = topk_ids[route];
@@ -194,6 +219,12 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
       const int owner = (has_shared && e == experts_global) ? rank : e / experts_per_rank;
       row = send_base[e] + (position - expert_offsets[e]);
       base = peer_slabs[owner];
+      if (row < 0 || row >= capacity) {
+        // Cannot happen with a consistent count table (capacity is every route of every rank); a torn table must
+        // not turn into a store outside the slab.
+        raise_error(status, FMOE_ERR_DEVICE_WAIT, -1);
+        row = -1;
+      }
     }
     slot_row[threadIdx.x] = row;
     slot_slab[threadIdx.x] = base;
@@ -268,53 +299,67 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
 }
 
 // The byte address of the result row of every received row, in the memory of the rank the route came from.
+// A return address that does not name a rank of the box and one of its routes (a row that never arrived: the slab
+// starts zeroed, and a failed barrier leaves old rows behind) is reported and replaced by the local scrap row, so
+// that the down GEMM's epilogue never stores through it.
 __global__ void peer_row_ptrs_kernel(const int* __restrict__ valid_rows, int64_t capacity,
                                      const int2* __restrict__ source, const uint64_t* __restrict__ peer_slabs, size_t route_out_offset,
-                                     int row_bytes, uint64_t* __restrict__ row_out_ptrs) {
+                                     int row_bytes, uint64_t* __restrict__ row_out_ptrs, int world, int64_t routes_max, uint64_t scrap_row,
+                                     int* __restrict__ status) {
   const int64_t p = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   if (p >= capacity || p >= *valid_rows) return;
   const int2 from = source[p];
+  if (from.x < 0 || from.x >= world || from.y < 0 || from.y >= routes_max) {
+    raise_error(status, FMOE_ERR_DEVICE_WAIT, -2);
+    row_out_ptrs[p] = scrap_row;
+    return;
+  }
   row_out_ptrs[p] = peer_slabs[from.x] + route_out_offset + static_cast<uint64_t>(from.y) * row_bytes;
 }
 
 }  // namespace
 
 cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* payload, int payload_ints, int world,
-                                int rank, unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream) {
-  peer_barrier_kernel<<<1, 256, 0, stream>>>(peer_slabs, slab, payload, payload_ints, world, rank, epoch_counter, status, limit_ns);
+                                int rank, unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream,
+                                int* zero_on_fail, int zero_ints) {
+  peer_barrier_kernel<<<1, 256, 0, stream>>>(peer_slabs, slab, payload, payload_ints, world, rank, epoch_counter, status, limit_ns,
+                                             zero_on_fail, zero_ints);
   return cudaGetLastError();
 }
 
 cudaError_t launch_peer_layout(const int* count_matrix, int world, int rank, int experts_global, int per_rank, int has_shared,
-                               int row_stride, int* send_base, int* local_counts, int* local_offsets, cudaStream_t stream) {
+                               int row_stride, int* send_base, int* local_counts, int* local_offsets, const int* status,
+                               cudaStream_t stream) {
   const size_t smem = (3 * static_cast<size_t>(experts_global + 1) + 1) * sizeof(int);
   peer_layout_kernel<<<1, 1024, smem, stream>>>(count_matrix, row_stride, world, rank, experts_global, per_rank, has_shared, send_base,
-                                                local_counts, local_offsets);
+                                                local_counts, local_offsets, status);
   return cudaGetLastError();
 }
 
 cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
                                  const int* route_pos, const int* expert_offsets, const int* send_base, const PeerSlabLayout& slab,
                                  const uint64_t* peer_slabs, int rank, int experts_global, int experts_per_rank, int has_shared,
-                                 int numerics, cudaStream_t stream) {
+                                 int numerics, int64_t capacity, int* status, cudaStream_t stream) {
   if (tokens <= 0) return cudaSuccess;
   if (int8) {
     peer_dispatch_kernel<true><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, route_pos, expert_offsets, send_base,
                                                                                   slab, peer_slabs, rank, experts_global, experts_per_rank,
-                                                                                  has_shared, numerics);
+                                                                                  has_shared, numerics, capacity, status);
   } else {
     peer_dispatch_kernel<false><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(x, topk_ids, cols, top_k, route_pos, expert_offsets, send_base,
                                                                                    slab, peer_slabs, rank, experts_global, experts_per_rank,
-                                                                                   has_shared, numerics);
+                                                                                   has_shared, numerics, capacity, status);
   }
   return cudaGetLastError();
 }
 
 cudaError_t launch_peer_row_ptrs(const int* valid_rows, int64_t capacity, const void* source, const uint64_t* peer_slabs,
-                                 size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs, cudaStream_t stream) {
+                                 size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs, int world, int64_t routes_max,
+                                 void* scrap_row, int* status, cudaStream_t stream) {
   if (capacity <= 0) return cudaSuccess;
   peer_row_ptrs_kernel<<<static_cast<unsigned>((capacity + 255) / 256), 256, 0, stream>>>(
-      valid_rows, capacity, static_cast<const int2*>(source), peer_slabs, route_out_offset, row_bytes, row_out_ptrs);
+      valid_rows, capacity, static_cast<const int2*>(source), peer_slabs, route_out_offset, row_bytes, row_out_ptrs, world, routes_max,
+      reinterpret_cast<uint64_t>(scrap_row), status);
   return cudaGetLastError();
 }
 

@@ -85,16 +85,22 @@ struct PeerSlabLayout {
   size_t flags;      // [world] uint32: barrier epochs, one per source rank
   size_t total;
 };
+// zero_on_fail (nullable): zero_ints ints that are cleared when the wait gives up (row counts the next stages trust).
 cudaError_t launch_peer_barrier(const uint64_t* peer_slabs, const PeerSlabLayout& slab, const int* payload, int payload_ints, int world,
-                                int rank, unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream);
+                                int rank, unsigned* epoch_counter, int* status, unsigned long long limit_ns, cudaStream_t stream,
+                                int* zero_on_fail = nullptr, int zero_ints = 0);
+// status: the dispatch status block; after a failed count exchange the layout publishes empty lists.
 cudaError_t launch_peer_layout(const int* count_matrix, int world, int rank, int experts_global, int per_rank, int has_shared,
-                               int row_stride, int* send_base, int* local_counts, int* local_offsets, cudaStream_t stream);
+                               int row_stride, int* send_base, int* local_counts, int* local_offsets, const int* status,
+                               cudaStream_t stream);
 cudaError_t launch_peer_dispatch(bool int8, const uint16_t* x, const int64_t* topk_ids, int64_t tokens, int cols, int top_k,
                                  const int* route_pos, const int* expert_offsets, const int* send_base, const PeerSlabLayout& slab,
                                  const uint64_t* peer_slabs, int rank, int experts_global, int experts_per_rank, int has_shared,
-                                 int numerics, cudaStream_t stream);
+                                 int numerics, int64_t capacity, int* status, cudaStream_t stream);
+// Return addresses outside [0, world) x [0, routes_max) are reported in `status` and replaced by scrap_row (local).
 cudaError_t launch_peer_row_ptrs(const int* valid_rows, int64_t capacity, const void* source, const uint64_t* peer_slabs,
-                                 size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs, cudaStream_t stream);
+                                 size_t route_out_offset, int row_bytes, uint64_t* row_out_ptrs, int world, int64_t routes_max,
+                                 void* scrap_row, int* status, cudaStream_t stream);
 
 // ---- router.cu: scores -> top-k ids and routing weights, one warp per token (experts <= 2048, top_k <= 32)
 cudaError_t launch_router_topk(const float* logits, const float* selection_bias, int64_t tokens, int experts, int top_k, int sigmoid,
@@ -140,12 +146,46 @@ struct GroupedGemmArgs {
   const uint64_t* row_out_ptrs;
   int gate_up_one_box;       // two-SM gate_up: the weight rows of a stage arrive as one 16 KB TMA box (set by the launcher)
   int route_out_bf16;        // with row_out_ptrs: the result rows are stored as bf16 (2 bytes per channel) instead of fp32
-  // Performance diagnosis only (environment FUSED_CPP_MOE_GEMM_DIAG, 0 in production; results are meaningless otherwise):
-  // bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.
+  // Diagnostic build only (compiled with -DFMOE_DIAG, the separate libfused_moe_b200_diag.so; the product library
+  // ignores the field): bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.
   int diag;
 };
 
-// ---- simt_gemm.cu: diagnostic CUDA-core grouped GEMM (work items of at most 8 rows)
+// The stage switches above exist only in the diagnostic build; in the product build the tests fold to `false`.
+#ifdef FMOE_DIAG
+#define FMOE_DIAG_BIT(args, bit) (((args).diag & (bit)) != 0)
+#else
+#define FMOE_DIAG_BIT(args, bit) false
+#endif
+
+// Launch set-up that belongs to a device, not to the process: the opt-in to more than 48 KB of dynamic shared
+// memory (a function attribute) and the SM count are remembered per device ordinal.
+constexpr int kMaxDevices = 64;
+inline int current_device_ordinal() {
+  int device = 0;
+  cudaGetDevice(&device);
+  return device;
+}
+struct PerDeviceOnce {
+  bool done[kMaxDevices] = {};
+  // True when `device` still needs its set-up (ordinals beyond the table are set up on every call).
+  bool needed(int device) const { return device < 0 || device >= kMaxDevices || !done[device]; }
+  void mark(int device) {
+    if (device >= 0 && device < kMaxDevices) done[device] = true;
+  }
+};
+inline int sm_count_of_current_device() {
+  static int counts[kMaxDevices] = {};
+  const int device = current_device_ordinal();
+  if (device >= 0 && device < kMaxDevices && counts[device] > 0) return counts[device];
+  int count = 0;
+  cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+  if (count <= 0) count = 148;
+  if (device >= 0 && device < kMaxDevices) counts[device] = count;
+  return count;
+}
+
+// ---- simt_gemm.cu: CUDA-core grouped GEMM of the diagnostic library only (work items of at most 8 rows)
 constexpr int kSimtRowTile = 8;
 cudaError_t launch_simt_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
 
@@ -158,7 +198,7 @@ constexpr int kPairRowTile = 512;
 bool umma_pair_supported(bool gate_up, int n_out, int64_t output_rows);  // else callers use the one-SM kernel on the same items
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream);
 
-// ---- probe.cu: tcgen05.mma issue-rate probe (128 x n x 32-byte MMAs back to back on every CTA)
+// ---- probe.cu (diagnostic library only): tcgen05.mma issue-rate probe (128 x n x 32-byte MMAs back to back on every CTA)
 cudaError_t launch_mma_rate_probe(bool int8, int n, int iterations, int mode, int blocks, int* status, cudaStream_t stream);
 
 }  // namespace fmoe

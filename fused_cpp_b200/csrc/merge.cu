@@ -52,10 +52,11 @@ __global__ void __launch_bounds__(kMergeThreads)
 merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_weights, int top_k, int hidden, int tree,
              uint16_t* __restrict__ out) {
   __shared__ float weights[kMaxTopK];
-  const int64_t token = blockIdx.y;
+  // Tokens ride on grid.x (up to 2^31 - 1 blocks), the few chunks of a row on grid.y (at most 65535).
+  const int64_t token = blockIdx.x;
   if (threadIdx.x < top_k) weights[threadIdx.x] = topk_weights[token * top_k + threadIdx.x];
   __syncthreads();
-  const int h = (blockIdx.x * kMergeThreads + threadIdx.x) * 4;
+  const int h = (blockIdx.y * kMergeThreads + threadIdx.x) * 4;
   if (h >= hidden) return;
   const int64_t base = token * top_k * static_cast<int64_t>(hidden) + h;
   float result[4];
@@ -98,7 +99,7 @@ cudaError_t launch_merge(const float* route_out, const float* topk_weights, int6
                          int tree, uint16_t* out, cudaStream_t stream) {
   if (tokens <= 0) return cudaSuccess;
   if (top_k > kMaxTopK) return cudaErrorInvalidValue;
-  const dim3 grid((hidden / 4 + kMergeThreads - 1) / kMergeThreads, static_cast<unsigned>(tokens));
+  const dim3 grid(static_cast<unsigned>(tokens), (hidden / 4 + kMergeThreads - 1) / kMergeThreads);
   merge_kernel<false><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
   return cudaGetLastError();
 }
@@ -107,7 +108,7 @@ cudaError_t launch_merge_bf16_rows(const uint16_t* route_out, const float* topk_
                                    int tree, uint16_t* out, cudaStream_t stream) {
   if (tokens <= 0) return cudaSuccess;
   if (top_k > kMaxTopK) return cudaErrorInvalidValue;
-  const dim3 grid((hidden / 4 + kMergeThreads - 1) / kMergeThreads, static_cast<unsigned>(tokens));
+  const dim3 grid(static_cast<unsigned>(tokens), (hidden / 4 + kMergeThreads - 1) / kMergeThreads);
   merge_kernel<true><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
   return cudaGetLastError();
 }

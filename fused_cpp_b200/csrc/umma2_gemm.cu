@@ -273,7 +273,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         const int group = channel0 >> 4;                         // gate_up: 16-channel group
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 11);
-          if (args.diag & 2) {
+          if (FMOE_DIAG_BIT(args, 2)) {
             if (leader) ptx::mbar_arrive(&ctl->full[stage]);
           } else {
             const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes;
@@ -352,7 +352,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->full[stage], phase, abort_flag, status, 13);
           ptx::tcgen05_fence_after();
-          if (!(args.diag & 4)) {
+          if (!FMOE_DIAG_BIT(args, 4)) {
 #pragma unroll
             for (uint32_t ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
               umma_pair<kInt8>(acc, a_lo + 2u * ks, a_lo + kTokenStep + 2u * ks, desc_hi, idesc, accumulate);
@@ -478,7 +478,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       const bool channel_ok = n < n_out;
       const bool block_full = (cur.block + 1) * kChannelsPerUnit <= n_out;  // every thread's channel exists
       const ColumnMeta* meta = &ctl->meta[local & 1];
-      const int chunks = (args.diag & 1) ? 0 : (rows + 31) >> 5;
+      const int chunks = FMOE_DIAG_BIT(args, 1) ? 0 : (rows + 31) >> 5;
 
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 14);
       ptx::tcgen05_fence_after();
@@ -654,19 +654,23 @@ bool make_gate_up_map(CUtensorMap* map, const void* base, bool int8, uint64_t ex
 template <bool kInt8, bool kGateUp, bool kDense>
 cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
   auto kernel = umma_pair_grouped_gemm_kernel<kInt8, kGateUp, kDense>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  const int device = current_device_ordinal();
+  if (configured.needed(device)) {
     const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
     if (err != cudaSuccess) return err;
-    configured = true;
+    configured.mark(device);
   }
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   CUtensorMap weight_map, token_map;
   GroupedGemmArgs launch_args = args;
   bool weights_ok;
   if (kGateUp) {
-    const char* forced = getenv("FUSED_CPP_MOE_GATE_UP_BOXES");  // "4": use the four-box encoding (experiments)
-    const bool try_one = !(forced != nullptr && forced[0] == '4') && args.n_out % 64 == 0;
+    bool try_one = args.n_out % 64 == 0;
+#ifdef FMOE_DIAG
+    const char* forced = getenv("FUSED_CPP_MOE_GATE_UP_BOXES");  // diagnostic library only: "4" forces the four-box encoding
+    if (forced != nullptr && forced[0] == '4') try_one = false;
+#endif
     launch_args.gate_up_one_box = try_one && make_gate_up_map(&weight_map, args.weights, kInt8, args.experts, args.n_out, args.k, true);
     weights_ok = launch_args.gate_up_one_box || make_gate_up_map(&weight_map, args.weights, kInt8, args.experts, args.n_out, args.k, false);
   } else {
@@ -675,9 +679,7 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
   if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowsPerCta)) {
     return cudaErrorInvalidValue;
   }
-  int device = 0, sms = 148;
-  cudaGetDevice(&device);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const int sms = sm_count_of_current_device();
   const int channels_per_unit = kGateUp ? 128 : 256;
   const int n_blocks = (args.n_out + channels_per_unit - 1) / channels_per_unit;
   int64_t pairs = static_cast<int64_t>(args.max_items) * n_blocks;

@@ -144,7 +144,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
           uint8_t* stage_base = smem + static_cast<size_t>(stage) * Cfg::kStageBytes;
-          if (args.diag & 2) {
+          if (FMOE_DIAG_BIT(args, 2)) {
             ptx::mbar_arrive(&ctl->full[stage]);
           } else {
             ptx::mbar_arrive_expect_tx(&ctl->full[stage], Cfg::kStageBytes);
@@ -201,7 +201,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
           const uint32_t stage_addr = ptx::smem_u32(smem + static_cast<size_t>(stage) * Cfg::kStageBytes);
 #pragma unroll
           for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
-            if (args.diag & 4) break;
+            if (FMOE_DIAG_BIT(args, 4)) break;
             const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
             const uint64_t desc_tok = ptx::make_smem_desc_sw128(stage_addr + Cfg::kWeightBytes + ks * kUmmaKBytes);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
@@ -263,7 +263,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 4);
       ptx::tcgen05_fence_after();
       const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
-      for (int c0 = 0; c0 < ((args.diag & 1) ? 0 : rows); c0 += 8) {
+      for (int c0 = 0; c0 < (FMOE_DIAG_BIT(args, 1) ? 0 : rows); c0 += 8) {
         uint32_t gate_bits[8];
         uint32_t up_bits[8];
         ptx::tmem_ld_x8(acc + c0, gate_bits);
@@ -363,26 +363,16 @@ bool make_tensor_map(CUtensorMap* map, const void* base, bool int8, uint64_t row
   return result == CUDA_SUCCESS;
 }
 
-int sm_count() {
-  static int count = 0;
-  if (count == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
-    if (count <= 0) count = 148;
-  }
-  return count;
-}
-
 template <bool kInt8, bool kGateUp, int kRowTile, bool kDense>
 cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   using Cfg = TileConfig<kGateUp, kRowTile>;
   auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile, kDense>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  const int device = current_device_ordinal();
+  if (configured.needed(device)) {
     const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmemBytes));
     if (err != cudaSuccess) return err;
-    configured = true;
+    configured.mark(device);
   }
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   CUtensorMap weight_map, token_map;
@@ -392,7 +382,8 @@ cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   }
   const int n_blocks = (args.n_out + kBlockM - 1) / kBlockM;
   int64_t grid = static_cast<int64_t>(args.max_items) * n_blocks;
-  if (grid > sm_count()) grid = sm_count();
+  const int sms = sm_count_of_current_device();
+  if (grid > sms) grid = sms;
   if (grid <= 0) return cudaSuccess;
   kernel<<<static_cast<unsigned>(grid), kThreads, Cfg::kSmemBytes, stream>>>(weight_map, token_map, args);
   return cudaGetLastError();
@@ -418,8 +409,12 @@ bool umma_row_tile_supported(int row_tile) {
 
 cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& caller_args, bool int8, bool gate_up, cudaStream_t stream) {
   GroupedGemmArgs args = caller_args;
-  const char* diag = getenv("FUSED_CPP_MOE_GEMM_DIAG");
+#ifdef FMOE_DIAG
+  const char* diag = getenv("FUSED_CPP_MOE_GEMM_DIAG");  // diagnostic library only: stage switches of GroupedGemmArgs::diag
   args.diag = diag ? atoi(diag) : 0;
+#else
+  args.diag = 0;
+#endif
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
   if (args.row_tile == kPairRowTile) {
     if (umma_pair_supported(gate_up, args.n_out, args.total_rows)) return launch_umma_pair_grouped_gemm(args, int8, gate_up, stream);

@@ -18,8 +18,6 @@ ranks (gloo) and a stand-in backend; the product backend is CudaBackend and noth
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import dataclass
 
 import torch
@@ -229,7 +227,8 @@ class PeerMemoryExpertParallelMoE:
         dispatch_error, expert_error = self.context.read_status()
         for where, code in (("dispatch", dispatch_error), ("expert stage", expert_error)):
             if code != 0:
-                raise _lib.FusedMoEError(code, f"expert-parallel {where} reported device-side error {code} on rank {self.rank}")
+                text = _lib.load().fmoe_last_error().decode("utf-8", "replace")
+                raise _lib.FusedMoEError(code, f"expert-parallel {where} reported device-side error {code} on rank {self.rank}: {text}")
 
     def close(self) -> None:
         self.context.close()
@@ -240,217 +239,3 @@ def shard_rows(total: int, world: int, rank: int) -> slice:
     base, extra = divmod(total, world)
     begin = rank * base + min(rank, extra)
     return slice(begin, begin + base + (1 if rank < extra else 0))
-
-
-# ---- multi-GPU benchmark leg (called by bench.py under torchrun) -----------------------------------
-
-def bench_main(args, workloads: dict, seed: int, peaks: dict) -> None:
-    from . import _lib, synthetic
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    dist.init_process_group("nccl", device_id=device)
-    try:
-        if not _lib.device_supported():
-            raise SystemExit("bench.py needs compute-capability-10.x GPUs")
-        hidden, inter, experts, top_k = args.hidden, args.inter, args.experts, args.top_k
-        lines = []
-        for entry in [args.workload] + ([] if args.no_points else list(args.ep_points)):
-            name, _, option = entry.partition(":")  # "workload:bf16_return" = the same workload with the compact return
-            spec = workloads[name]
-            lines.append(_bench_one(name, spec, args, rank, world, device, hidden, inter, experts, top_k, seed, peaks,
-                                    has_shared=spec.get("shared", False), bf16_return=option == "bf16_return"))
-        if rank == 0:
-            head = lines[0]
-            head["points"] = lines[1:]
-            print(json.dumps(head), flush=True)
-    finally:
-        dist.destroy_process_group()
-
-
-def _bench_one(name, spec, args, rank, world, device, hidden, inter, experts, top_k, seed, peaks, has_shared, bf16_return=False):
-    from . import synthetic
-
-    kind, tokens = spec["kind"], spec["tokens"]
-    per_rank = experts // world
-    generator = torch.Generator(device=device).manual_seed(seed + 2 + rank)
-    local = per_rank + (1 if has_shared else 0)
-    if kind == "int8":
-        weights = {"w13": torch.randint(-127, 128, (local, 2 * inter, hidden), generator=generator, dtype=torch.int8, device=device),
-                   "w2": torch.randint(-127, 128, (local, hidden, inter), generator=generator, dtype=torch.int8, device=device),
-                   "s13": (torch.rand((local, 2 * inter), generator=generator, device=device) * 1.5 + 0.5) / (127.0 * hidden ** 0.5),
-                   "s2": (torch.rand((local, hidden), generator=generator, device=device) * 1.5 + 0.5) / (127.0 * inter ** 0.5)}
-    else:
-        weights = {"w13": torch.empty((local, 2 * inter, hidden), dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=generator),
-                   "w2": torch.empty((local, hidden, inter), dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=generator)}
-    topk_w, topk_ids = synthetic.make_routing(tokens, experts, top_k, seed, spec.get("skew", False))
-    x = synthetic.make_activations(tokens, hidden, seed + 1)
-    mine = shard_rows(tokens, world, rank)
-    x_host, w_host, ids_host = x[mine].contiguous(), topk_w[mine].contiguous(), topk_ids[mine].contiguous()
-    xd, wd, idd = x_host.to(device), w_host.to(device), ids_host.to(device)
-    local_max = (tokens + world - 1) // world
-    if getattr(args, "ep_impl", "peer") == "peer":
-        layer = PeerMemoryExpertParallelMoE(weights, experts, tokens_max=local_max, top_k=top_k, has_shared=has_shared,
-                                            return_dtype=torch.bfloat16 if bf16_return else torch.float32)
-        exchange = "rows stored by the dispatch kernel and the down-GEMM epilogue into peer memory over NVLink, flag barriers in the same slabs"
-        if bf16_return:
-            exchange += "; result rows returned as bf16 (opt-in: half the return traffic, outputs within a bf16 step, not bit-identical)"
-    else:
-        layer = ExpertParallelMoE(weights, experts, has_shared=has_shared)
-        exchange = "NCCL all-to-all dispatch/combine"
-    kwargs = {"swiglu_limit": 10.0} if kind == "int8" else {}
-
-    def step():
-        return layer(xd, wd, idd, **kwargs)
-
-    def timed(fn, steps, warmup, sampler=None):
-        if sampler is not None:
-            sampler.prepare()
-        for _ in range(warmup):
-            fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if sampler is not None:
-            sampler.start()
-        start.record()
-        for _ in range(steps):
-            fn()
-        stop.record()
-        torch.cuda.synchronize()
-        clocks = sampler.stop() if sampler is not None else None
-        dist.barrier()
-        elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-        return float(elapsed.item()), clocks
-
-    # The forward makes no host read and calls no collective library, so one step (kernels, flag barriers included)
-    # is captured into a CUDA graph and the timed region replays it; every rank replays the same sequence.  Eager
-    # launches are timed as well (eager_ms_per_step).
-    launch_mode = "eager"
-    replay = step
-    graph = None
-    if isinstance(layer, PeerMemoryExpertParallelMoE) and os.environ.get("FUSED_CPP_MOE_EP_GRAPH", "1") != "0":
-        try:
-            side = torch.cuda.Stream(device=device)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                for _ in range(3):
-                    step()
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            dist.barrier()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                step()
-            replay = graph.replay
-            launch_mode = "cuda_graph_replay"
-        except Exception as error:  # noqa: BLE001
-            launch_mode = f"eager (graph capture failed: {type(error).__name__})"
-            replay = step
-    captured = torch.tensor([1 if launch_mode == "cuda_graph_replay" else 0], device=device)
-    dist.all_reduce(captured, op=dist.ReduceOp.MIN)
-    if int(captured.item()) == 0:
-        replay = step
-        if launch_mode == "cuda_graph_replay":
-            launch_mode = "eager (graph capture failed on another rank)"
-    sampler_class = getattr(args, "clock_sampler", None)
-    ms, clocks = timed(replay, args.steps, args.warmup, sampler_class(device.index) if (sampler_class and rank == 0) else None)
-    eager_ms = ms
-    if replay is not step:
-        # Both ways of launching are timed under the same rules; the line reports the faster one as `value`
-        # (with few ranks the eager launches already keep the GPU busy and the captured collectives cost more).
-        graph_ms = ms
-        eager_ms, eager_clocks = timed(step, args.steps, args.warmup, sampler_class(device.index) if (sampler_class and rank == 0) else None)
-        if eager_ms < graph_ms:
-            ms, clocks, launch_mode = eager_ms, eager_clocks, f"eager (cuda_graph_replay: {graph_ms:.4f} ms)"
-
-    # Per-kernel durations of this rank's expert stage (CUDA events around every stage, a second timed pass).
-    roofline = None
-    stage_ms = None
-    if isinstance(layer, PeerMemoryExpertParallelMoE) and getattr(args, "roofline", None) is not None:
-        from . import _lib
-
-        timer = _lib.StageTimer(args.steps)
-        layer.stage_timer = timer
-        for _ in range(args.steps):
-            step()
-        torch.cuda.synchronize()
-        layer.stage_timer = None
-        stage_ms = {stage: 0.0 for stage in _lib.STAGES}
-        for call in range(timer.calls):
-            for stage, value in timer.read(call).items():
-                stage_ms[stage] += value / timer.calls
-        timer.close()
-        # Algorithmic work of this rank's gate_up launch: the weights of its experts that the batch hits, once,
-        # plus the rows it receives in and their SwiGLU rows out.
-        owner = topk_ids // per_rank
-        local_ids = topk_ids[owner == rank]
-        rows = int(local_ids.numel()) + (x_host.shape[0] if has_shared else 0)
-        active = int(local_ids.unique().numel()) + (1 if has_shared else 0)
-        b = 1 if kind == "int8" else 2
-        nbytes = active * 2 * inter * hidden * b + rows * hidden * b + rows * inter * 2 + (active * 2 * inter * 4 + rows * 4 if kind == "int8" else 0)
-        roofline = args.roofline(kind, float(nbytes), 2.0 * rows * 2 * inter * hidden, stage_ms["gate_up"], peaks, None)
-        roofline["scope"] = f"rank 0 of {world}: {active} active local experts, {rows} received rows"
-        dist.barrier()
-
-    x_pin, w_pin, ids_pin = x_host.pin_memory(), w_host.pin_memory(), ids_host.pin_memory()
-    out_pin = torch.empty((x_host.shape[0], hidden), dtype=torch.bfloat16).pin_memory()
-
-    def e2e_step():
-        out = layer(x_pin.to(device, non_blocking=True), w_pin.to(device, non_blocking=True), ids_pin.to(device, non_blocking=True), **kwargs)
-        out_pin.copy_(out, non_blocking=True)
-
-    e2e_ms, _ = timed(e2e_step, args.steps, args.warmup)
-    # Cross-check at benchmark scale: the peer-memory forward against the NCCL all-to-all form on the same batch
-    # (each is bit-identical to the single-GPU forward in the tests; here they must agree with each other).
-    parity = None
-    if isinstance(layer, PeerMemoryExpertParallelMoE):
-        other = ExpertParallelMoE(weights, experts, has_shared=has_shared)
-        expected = other(xd, wd, idd, **kwargs)
-        got = layer(xd, wd, idd, **kwargs)
-        if bf16_return:
-            error = float((got.float() - expected.float()).norm() / expected.float().norm().clamp_min(1e-30))
-            agree = torch.tensor([1 if error <= 5e-3 else 0], device=device)
-            parity = "relative L2 to the NCCL all-to-all form on this batch <= 5e-3"
-        else:
-            agree = torch.tensor([1 if torch.equal(got.view(torch.int16), expected.view(torch.int16)) else 0], device=device)
-            parity = "bit-identical to the NCCL all-to-all form on this batch, every rank"
-        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
-        if int(agree.item()) != 1:
-            raise RuntimeError(f"{name}: the peer-memory forward disagrees with the NCCL form on at least one rank")
-        del other, expected, got
-    # Every rank is done with every slab before any of them is unmapped and freed.
-    torch.cuda.synchronize()
-    dist.barrier()
-    replay = None
-    graph = None
-    if hasattr(layer, "close"):
-        layer.close()
-    local_tokens = x_host.shape[0]
-    # Kernels of this library per forward on one rank, peer form: route build by global expert (1 kernel up to 1024
-    # routes, else 3), count barrier, layout, dispatch, barrier | work items, output addresses, gate_up (+ requantise),
-    # down, barrier | merge.  (The NCCL form has no barriers but a route build, gathers and a scatter on the expert side.)
-    routes_local = local_tokens * (top_k + (1 if has_shared else 0))
-    launches_per_step = ((1 if routes_local <= 1024 else 3) + 4) + (5 + (1 if kind == "int8" else 0)) + 1
-    work = synthetic.algorithmic_work(synthetic.MoEShape(tokens, hidden, inter, experts, top_k), topk_ids, 1 if kind == "int8" else 2,
-                                      shared=has_shared)
-    return {
-        "metric": "moe_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16" if kind == "bf16" else "int8(w8a8)", "data": "synthetic",
-        "config": {"workload": name, "tokens": tokens, "hidden": hidden, "inter": inter, "experts": experts, "top_k": top_k,
-                   "shared_expert": has_shared, "parallelism": f"ep{world}: experts and tokens split evenly, {exchange}",
-                   "l2": "inputs larger than L2: every rank streams its experts' weights each step"},
-        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": local_tokens * hidden * 2 + local_tokens * top_k * 12,
-                "d2h_bytes_per_step": local_tokens * hidden * 2},
-        "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "roofline": roofline, "cpu_baseline": None,
-        "launch_mode": launch_mode, "eager_ms_per_step": eager_ms, "parity": parity,
-        "stage_ms_rank0": {k: round(v, 5) for k, v in stage_ms.items()} if stage_ms else None,
-        "layer": {"algorithmic_bytes": work["bytes"], "ops": work["ops"],
-                  "hbm_gbs_aggregate": work["bytes"] / (ms * 1e-3) / 1e9, "tops_aggregate": work["ops"] / (ms * 1e-3) / 1e12},
-    }

@@ -53,11 +53,9 @@ extern "C" {
 #define FMOE_NUMERICS_TORCHREF 0 /* tests/test_moe_w8a8.py:40-69: x/scale, ties-to-even, (acc*a)*s */
 #define FMOE_NUMERICS_NATIVE 1   /* csrc/moe/arm/i8mm_w8a8/kernels.cpp:211-257: x*(1/scale), ties away, acc*(a*s) */
 
-/* Grouped-GEMM implementation.  AUTO is the product path (tcgen05); SIMT is a diagnostic CUDA-core
- * kernel kept as a stage-level cross-check, in the spirit of the reference's fused_moe_test_* hooks
- * (csrc/moe/module.cpp:41-115). */
+/* Grouped-GEMM implementation: there is one, on tcgen05 tensor cores.  0 and 2 both select it (2 is kept so that
+ * callers written against earlier headers keep working); any other value is refused. */
 #define FMOE_GEMM_AUTO 0
-#define FMOE_GEMM_SIMT 1
 #define FMOE_GEMM_UMMA 2
 
 typedef struct fmoe_config {
@@ -290,7 +288,10 @@ FMOE_API int fmoe_router_topk(const float* logits, const float* selection_bias, 
  * Only plain stores cross NVLink; all loads (TMA included) read local memory.  Nothing synchronises with the host
  * and no collective library is involved after set-up.  The barrier waits are bounded (5 s, or
  * FUSED_CPP_MOE_EP_WAIT_MS): a rank that never arrives ends the wait with FMOE_ERR_DEVICE_WAIT in the status
- * block (fmoe_ep_peer_read_status), not with a hung GPU.  Every rank must make the same sequence of calls.
+ * block (fmoe_ep_peer_read_status), not with a hung GPU.  After a wait that gave up the rest of the forward sends
+ * nothing and multiplies nothing (the row counts the later stages trust are cleared; return addresses are checked
+ * before anything is stored through them); the output of that forward is undefined, the status says so.
+ * Every rank must make the same sequence of calls.
  * Results are bit-identical to the single-GPU forward.  No counterpart in the reference, which rejects expert
  * parallelism (csrc/moe/arm/i8mm_w8a8/kernels.cpp:488). */
 typedef struct fmoe_ep_peer_context fmoe_ep_peer_context;
@@ -306,6 +307,11 @@ FMOE_API int fmoe_ep_peer_create(int32_t world, int32_t rank, int64_t tokens_max
 FMOE_API int fmoe_ep_peer_handle(fmoe_ep_peer_context* context, void* handle64);
 /* handles: world x 64 bytes, entry r = rank r's handle (this rank's own entry is ignored). */
 FMOE_API int fmoe_ep_peer_connect(fmoe_ep_peer_context* context, const void* handles);
+/* The same connection for ranks that can already address one another's slabs: several contexts inside one process
+ * (one per GPU with peer access enabled, or, for tests, several on one GPU).  slabs[r] = fmoe_ep_peer_slab_address
+ * of rank r's context as valid in this process (this rank's own entry is ignored).  No IPC handle is opened. */
+FMOE_API void* fmoe_ep_peer_slab_address(fmoe_ep_peer_context* context);
+FMOE_API int fmoe_ep_peer_connect_addresses(fmoe_ep_peer_context* context, const void* const* slabs);
 FMOE_API void fmoe_ep_peer_destroy(fmoe_ep_peer_context* context);
 FMOE_API int64_t fmoe_ep_peer_slab_bytes(const fmoe_ep_peer_context* context);
 /* shared_rank >= 0: expert id experts_global is the replicated shared expert, served by the calling rank itself
@@ -320,17 +326,6 @@ FMOE_API int fmoe_ep_peer_combine(fmoe_ep_peer_context* context, const float* to
                                   void* out_bf16, void* stream);
 /* First device-side error of the last dispatch and expert stage (synchronises the stream). */
 FMOE_API int fmoe_ep_peer_read_status(fmoe_ep_peer_context* context, void* stream, int32_t* dispatch_error, int32_t* expert_error);
-
-/* ---- measurement helper ---------------------------------------------------------------------- */
-
-/* Dense tensor-core peak of the current GPU for one MMA shape: every SM issues `iterations` back-to-back
- * tcgen05.mma of 128 x n x 32 bytes (kind::i8 when int8 != 0, else kind::f16 with bf16 operands) on shared
- * memory that is zeroed (mode bit 0 clear) or filled with a non-zero pattern (bit 0 set: zero operands draw
- * less power than real data and give the rate at full clock); mode >> 8 = c > 0 adds a tcgen05.commit after
- * every c MMAs.  Returns tera-operations per second (2 per multiply-add), best of three timed launches.
- * No counterpart in the reference (its ceilings are per-core SMMLA/BFMMLA rates,
- * docs/agent_performance_references.md:85-91).  Allocates a few bytes and synchronises: not for hot paths. */
-FMOE_API int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mode, float* tera_ops_per_s);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,20 @@ def lib() -> ctypes.CDLL:
     return _LIB
 
 
+def set_threads(count: int) -> None:
+    """OpenMP thread count of the oracle's parallel loops (omp_set_num_threads of the runtime the library links).
+
+    A launcher may export OMP_NUM_THREADS=1 to its children (torch.distributed.run does); a timing that is meant
+    to use every host core sets the count here instead of trusting the environment."""
+    lib().omp_set_num_threads(ctypes.c_int(max(1, int(count))))
+
+
+def get_max_threads() -> int:
+    fn = lib().omp_get_max_threads
+    fn.restype = ctypes.c_int
+    return int(fn())
+
+
 def _ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
     if tensor is None:
         return ctypes.c_void_p(0)

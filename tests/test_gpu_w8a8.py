@@ -132,6 +132,14 @@ def test_w8a8_row_tile_does_not_change_results(cuda_device, tile):
     _check_all_stages(case, result, 0)
 
 
+def test_w8a8_more_than_65535_tokens(cuda_device):
+    """The reference accepts any token count; the merge must not put tokens on a 65535-limited grid axis."""
+    shape = synthetic.MoEShape(tokens=70000, hidden=64, inter=64, experts=2, top_k=2)
+    case = synthetic.make_w8a8_case(shape, seed=31337)
+    result = _run(case, cuda_device, dump=True)
+    _check_all_stages(case, result, 0)
+
+
 def test_w8a8_repeated_call_is_bit_identical(cuda_device):
     case = cases.w8a8_case("ragged")
     first = _run(case, cuda_device).out.clone()
