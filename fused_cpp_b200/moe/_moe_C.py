@@ -288,6 +288,169 @@ def fused_moe_bf16_tiled_async(input, w13_packed, w13_K, w13_N, w2_packed, w2_K,
                          activation, global_num_experts, skip_weighted, out)
 
 
+def shared_mlp_bf16_tiled(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, thread_cpu_ids=None, num_threads=1,
+                          fuse_silu=True, silu_poly_degree=5, gemm_backend=1, backend_n_tile=8, out=None, clamp_swiglu=False):
+    """One packed BF16 expert as a standalone MLP over every row (csrc/moe/module.cpp:244-250, api.h:158-162):
+    no routing, every row goes to expert 0 with weight 1."""
+    if w13_packed.dim() != 3 or int(w13_packed.shape[0]) != 1:
+        raise RuntimeError("shared_mlp_bf16_tiled expects a single-expert packed weight")
+    if input.dim() != 2:
+        raise RuntimeError("input must be a [tokens, H] tensor")
+    tokens = int(input.shape[0])
+    ids = torch.zeros((tokens, 1), dtype=torch.int64, device=input.device)
+    ones = torch.ones((tokens, 1), dtype=torch.float32, device=input.device)
+    return _bf16_forward(input, w13_packed, w13_K, w13_N, w2_packed, w2_K, w2_N, ones, ids, None, None,
+                         "silu_clamp10" if clamp_swiglu else "silu", -1, False, out)
+
+
+class NativeQuickPlanner:
+    """Greedy longest-first lane assignment over homogeneous team shapes: the class the reference's Python planner
+    looks up in `fused_cpp._moe_C` (csrc/moe_planner/quick_bindings.cpp:120-132; behaviour of
+    csrc/moe_planner/interval_planner.cpp:1616-1870).  Costs come from the caller's model as plain floats.
+
+    A shape is a list of equal team widths that sum to num_cores; a lane is one team.  Experts are taken in
+    descending route count (stable), each goes to the lane whose load after adding the expert's cost is smallest,
+    ties to the lower lane index.  `plan` scores every configured shape and keeps the smallest makespan (ties:
+    working-set bytes, then lanes); `plan_shared` pins the synthetic shared expert to lane 0 first and accepts
+    shapes of mixed widths with one cost row per width.  On the GPU build nothing consumes the CPU placement that
+    comes out; the class exists so that the planner tool chain keeps working against this package.
+    """
+
+    def __init__(self, num_cores, shapes, max_stage_bytes, window_bytes_by_width, relative_error, profile_runs=1,
+                 planner_threads=1):
+        self._cores = int(num_cores)
+        self._shapes = [[int(w) for w in shape] for shape in shapes]
+        self._stage_bytes = int(max_stage_bytes)
+        self._window = {int(width): int(nbytes) for width, nbytes in window_bytes_by_width}
+        self._relative_error = float(relative_error)
+        self._profile_runs = int(profile_runs)
+        if self._cores <= 0 or self._stage_bytes <= 0 or self._profile_runs <= 0:
+            raise ValueError("native quick planner dimensions and profile_runs must be positive")
+        if int(planner_threads) < 0:
+            raise ValueError("native quick planner threads must be non-negative")
+        workers = int(planner_threads) if int(planner_threads) > 0 else min(8, self._cores, os.cpu_count() or self._cores)
+        self._workers = max(1, min(workers, self._cores))
+        if not (self._relative_error >= 0.0) or self._relative_error == float("inf"):
+            raise ValueError("native quick planner relative_error must be finite and non-negative")
+        if not self._shapes:
+            raise ValueError("native quick planner requires homogeneous shapes")
+        for shape in self._shapes:
+            if not self._homogeneous(shape):
+                raise ValueError("native quick planner shapes must be homogeneous and cover num_cores")
+            if self._window.get(shape[0], 0) <= 0:
+                raise ValueError("native quick planner is missing positive window bytes for a shape width")
+
+    @property
+    def configured_workers(self) -> int:
+        return self._workers
+
+    def _homogeneous(self, shape) -> bool:
+        return bool(shape) and sum(shape) == self._cores and all(width == shape[0] for width in shape)
+
+    def _candidate(self, shape, lanes, loads, expert_ids, routes, windows) -> dict:
+        makespan = max(loads)
+        waves = max(1, -(-len(routes) // len(shape)))
+        uncertainty = makespan * self._relative_error / float(waves * self._profile_runs) ** 0.5
+        tasks = []
+        core_begin = 0
+        for lane, members in enumerate(lanes):
+            previous = -1
+            for index in members:
+                tasks.append((int(expert_ids[index]), int(routes[index]), core_begin, int(shape[lane]), [previous] if previous >= 0 else []))
+                previous = len(tasks) - 1
+            core_begin += int(shape[lane])
+        return {"shape": list(shape), "assignment_order": "lpt", "execution_mode": "strict", "tail_pool_threads": None,
+                "tail_pool_max_routes": None, "tail_pool_tasks": 0, "tail_repartition_width": None, "tail_repartition_tasks": 0,
+                "tail_repartition_route_slices": 1, "makespan_ns": makespan, "uncertainty_ns": uncertainty,
+                "pessimistic_ns": makespan + uncertainty, "tasks": tasks,
+                "active_working_set_bytes": len(shape) * self._stage_bytes, "window_bytes_per_worker": list(windows),
+                "resource_groups": len(shape)}
+
+    @staticmethod
+    def _descending_by_routes(routes, skip=None):
+        return sorted((i for i in range(len(routes)) if i != skip), key=lambda i: -routes[i])  # sorted() is stable
+
+    def assign(self, expert_ids, routes, shape, costs) -> dict:
+        expert_ids, routes, shape = list(expert_ids), [int(r) for r in routes], [int(w) for w in shape]
+        costs = [float(c) for c in costs]
+        if not expert_ids or len(expert_ids) != len(routes) or len(routes) != len(costs):
+            raise ValueError("native quick planner expert_ids, routes, and costs must have equal positive size")
+        if not self._homogeneous(shape):
+            raise ValueError("native quick assignment requires a homogeneous shape covering num_cores")
+        if any(r <= 0 for r in routes) or any(not (0.0 < c < float("inf")) for c in costs):
+            raise ValueError("native quick planner routes and costs must be positive and finite")
+        if shape[0] not in self._window:
+            raise ValueError("native quick planner is missing window bytes for assignment width")
+        loads = [0.0] * len(shape)
+        lanes = [[] for _ in shape]
+        for index in self._descending_by_routes(routes):
+            # Smallest resulting load; among equal sums (after rounding) the lowest lane.
+            best = min(range(len(shape)), key=lambda lane: (loads[lane] + costs[index], lane))
+            lanes[best].append(index)
+            loads[best] += costs[index]
+        return self._candidate(shape, lanes, loads, expert_ids, routes, [self._window[shape[0]]] * len(shape))
+
+    def _assign_shared(self, expert_ids, routes, shared_expert_id, shape, cost_rows) -> dict:
+        if not shape or sum(shape) != self._cores:
+            raise ValueError("native shared quick shape must cover num_cores")
+        for width in shape:
+            if width <= 0 or width not in cost_rows:
+                raise ValueError("native shared quick shape width is missing a cost row")
+            if width not in self._window:
+                raise ValueError("native shared quick shape width is missing window bytes")
+        if expert_ids.count(shared_expert_id) != 1:
+            raise ValueError("native shared quick planner requires exactly one synthetic shared expert")
+        shared = expert_ids.index(shared_expert_id)
+        loads = [0.0] * len(shape)
+        lanes = [[] for _ in shape]
+        lanes[0].append(shared)
+        loads[0] = cost_rows[shape[0]][shared]
+        for index in self._descending_by_routes(routes, skip=shared):
+            best = min(range(len(shape)), key=lambda lane: (loads[lane] + cost_rows[shape[lane]][index], lane))
+            loads[best] += cost_rows[shape[best]][index]
+            lanes[best].append(index)
+        return self._candidate(shape, lanes, loads, expert_ids, routes, [self._window[w] for w in shape])
+
+    @staticmethod
+    def _select_with_uncertainty(candidates) -> dict:
+        """Among the candidates whose uncertainty band overlaps the fastest one's, the smallest working set, then
+        the fewest lanes, then the smaller pessimistic time (interval_planner.cpp:150-172)."""
+        ordered = sorted(candidates, key=lambda c: c["makespan_ns"])
+        fastest = ordered[0]
+        low, high = fastest["makespan_ns"] - fastest["uncertainty_ns"], fastest["pessimistic_ns"]
+        overlapping = [c for c in ordered if c["makespan_ns"] - c["uncertainty_ns"] <= high and c["pessimistic_ns"] >= low]
+        return min(overlapping, key=lambda c: (c["active_working_set_bytes"], c["resource_groups"], 0, c["pessimistic_ns"], c["makespan_ns"]))
+
+    def _result(self, candidates, selected) -> dict:
+        return {"selected": selected, "candidates": [{k: v for k, v in c.items() if k != "tasks"} for c in candidates],
+                "configured_workers": self._workers, "strict_candidates": len(candidates)}
+
+    def plan(self, expert_ids, routes, costs) -> dict:
+        costs = [list(row) for row in costs]
+        if len(costs) != len(self._shapes):
+            raise ValueError("native quick planner requires one cost row per shape")
+        candidates = [self.assign(expert_ids, routes, shape, row) for shape, row in zip(self._shapes, costs)]
+        selected = min(candidates, key=lambda c: (c["makespan_ns"], c["active_working_set_bytes"], c["resource_groups"]))
+        return self._result(candidates, selected)
+
+    def plan_shared(self, expert_ids, routes, shared_expert_id, shapes, cost_widths, costs_by_width) -> dict:
+        expert_ids, routes = list(expert_ids), [int(r) for r in routes]
+        shapes = [[int(w) for w in shape] for shape in shapes]
+        if not shapes:
+            raise ValueError("native shared quick planner requires candidate shapes")
+        if not expert_ids or len(expert_ids) != len(routes) or len(cost_widths) != len(costs_by_width):
+            raise ValueError("native shared quick planner inputs must have matching positive sizes")
+        cost_rows: dict = {}
+        for width, row in zip(cost_widths, costs_by_width):
+            if int(width) <= 0 or len(row) != len(routes) or int(width) in cost_rows:
+                raise ValueError("native shared quick cost rows must have unique positive widths and expert costs")
+            cost_rows[int(width)] = [float(c) for c in row]
+        candidates = [self._assign_shared(expert_ids, routes, int(shared_expert_id), shape, cost_rows) for shape in shapes]
+        # The selection sorts by makespan first; the candidate list is returned in that order, as the reference's is.
+        candidates.sort(key=lambda c: c["makespan_ns"])
+        return self._result(candidates, self._select_with_uncertainty(candidates))
+
+
 def _not_built(name: str, why: str):
     def raiser(*_args, **_kwargs):
         raise RuntimeError(f"{name} is not implemented on this backend: {why}")
