@@ -77,9 +77,18 @@ class PreparedW8A8TiledRoutedSharedMoEWeights:
 _HAS_BF16_TILED_FUSED_MOE = bool(_native.fused_moe_bf16_tiled_available_backends())
 _HAS_W8A8_TILED_FUSED_MOE = bool(_native.fused_moe_w8a8_tiled_available())
 
+# The native ops the wrappers call, under the module-level names the reference binds them to
+# (src/fused_cpp/moe/bf16_tiled.py:87-96), so that callers and tests that substitute an op find the same hook.
+# The wrappers below validate types and shapes only; the rule that tensors live on a CUDA device belongs to the
+# native ops.
+_fused_moe_bf16_tiled_impl = _native.fused_moe_bf16_tiled
+_fused_moe_bf16_tiled_async_plan_v2_impl = _native.fused_moe_bf16_tiled_async_plan_v2
+_fused_moe_w8a8_async_plan_v2_impl = _native.fused_moe_w8a8_tiled_async_plan_v2
+_shared_mlp_bf16_tiled_impl = _native.shared_mlp_bf16_tiled
+
 
 def _require_backend() -> None:
-    if not _native.fused_moe_bf16_tiled_available_backends():
+    if not _HAS_BF16_TILED_FUSED_MOE:
         raise RuntimeError("the B200 fused MoE backend is unavailable: no compute-capability-10.x CUDA device "
                            "(there is no CPU fallback)")
 
@@ -93,11 +102,13 @@ def _activation_name(activation: Any) -> str:
     return value if isinstance(value, str) else str(value)
 
 
-def _native_activation_name(activation: Any, swiglu_limit: float | None) -> str:
+def _native_activation_name(activation: Any, weights: Any, swiglu_limit: float | None) -> str:
+    """Activation string of the native op (bf16_tiled.py:245-260).  Every prepared weight of this backend supports
+    the clamp-10 variant, so `weights` takes no part in the decision."""
     name = _activation_name(activation)
     if swiglu_limit is None or float(swiglu_limit) == 0.0:
         return name
-    if float(swiglu_limit) != 10.0:
+    if not math.isfinite(float(swiglu_limit)) or float(swiglu_limit) != 10.0:
         raise ValueError("clamped SwiGLU currently requires swiglu_limit=10.0")
     if name != "silu":
         raise ValueError("swiglu_limit is only valid with activation='silu'")
@@ -118,8 +129,6 @@ def _validate_output_buffer(input: torch.Tensor, out: torch.Tensor | None) -> No
 def _check_forward_inputs(input, topk_weights, topk_ids, num_threads) -> None:
     if input.dtype != torch.bfloat16:
         raise TypeError(f"input must be torch.bfloat16, got {input.dtype}")
-    if input.device.type != "cuda":
-        raise ValueError("input must be a CUDA tensor")
     if topk_ids.dtype not in _INTEGER_DTYPES:
         raise TypeError(f"topk_ids must use an integer dtype, got {topk_ids.dtype}")
     if not topk_weights.dtype.is_floating_point:
@@ -228,15 +237,17 @@ def fused_moe_bf16_tiled_async_plan(input, weights, topk_weights, topk_ids, plan
                                     activation: Any = "silu", global_num_experts: int = -1, skip_weighted: bool = False,
                                     silu_poly_degree: int = 5, swiglu_limit: float | None = None, out=None):
     """BF16 forward under an explicit Plan V2 (bf16_tiled.py:1224)."""
-    if not isinstance(weights, PreparedBF16TiledFusedMoEWeights):
+    if _fused_moe_bf16_tiled_async_plan_v2_impl is None:
+        raise RuntimeError("BF16 tiled fused MoE Plan V2 requires native fused_moe_bf16_tiled_async_plan_v2 support")
+    if not all(hasattr(weights, name) for name in ("w13", "w2", "fused_silu", "gemm_backend", "backend_n_tile")):
         raise TypeError("weights must be PreparedBF16TiledFusedMoEWeights")
     _check_forward_inputs(input, topk_weights, topk_ids, 1)
     _validate_output_buffer(input, out)
     materialized = plan if isinstance(plan, AsyncMoEPlanV2) else AsyncMoEPlanV2.from_dict(plan)
-    result = _native.fused_moe_bf16_tiled_async_plan_v2(
+    result = _fused_moe_bf16_tiled_async_plan_v2_impl(
         input.contiguous(), weights.w13[0], weights.w13[1], weights.w13[2], weights.w2[0], weights.w2[1], weights.w2[2],
         topk_weights.to(torch.float32).contiguous(), topk_ids.to(torch.int64).contiguous(), *_plan_args(materialized),
-        w13_bias, w2_bias, materialized.num_threads, _native_activation_name(activation, swiglu_limit), int(global_num_experts),
+        w13_bias, w2_bias, materialized.num_threads, _native_activation_name(activation, weights, swiglu_limit), int(global_num_experts),
         bool(skip_weighted), bool(weights.fused_silu), int(silu_poly_degree), int(weights.gemm_backend),
         int(weights.backend_n_tile), out, materialized.native_early_merge)
     return out if out is not None else result
@@ -263,10 +274,10 @@ def fused_moe_bf16_tiled(input, weights, topk_weights, topk_ids, *, w13_bias=Non
                                                    activation=activation, global_num_experts=global_num_experts,
                                                    skip_weighted=skip_weighted, silu_poly_degree=silu_poly_degree,
                                                    swiglu_limit=swiglu_limit, out=out)
-    result = _native.fused_moe_bf16_tiled(
+    result = _fused_moe_bf16_tiled_impl(
         input.contiguous(), weights.w13[0], weights.w13[1], weights.w13[2], weights.w2[0], weights.w2[1], weights.w2[2],
         topk_weights.to(torch.float32).contiguous(), topk_ids.to(torch.int64).contiguous(), w13_bias, w2_bias, int(num_threads),
-        _native_activation_name(activation, swiglu_limit), int(global_num_experts), bool(skip_weighted), bool(weights.fused_silu),
+        _native_activation_name(activation, weights, swiglu_limit), int(global_num_experts), bool(skip_weighted), bool(weights.fused_silu),
         int(silu_poly_degree), int(weights.gemm_backend), int(weights.backend_n_tile), out)
     return out if out is not None else result
 
@@ -312,8 +323,10 @@ def fused_moe_w8a8_tiled_async_plan(input, weights, topk_weights, topk_ids, plan
     """W8A8 forward under an explicit Plan V2 (bf16_tiled.py:1450)."""
     if not isinstance(weights, PreparedW8A8TiledFusedMoEWeights):
         raise TypeError("weights must be PreparedW8A8TiledFusedMoEWeights")
-    if input.dtype != torch.bfloat16 or input.device.type != "cuda":
-        raise TypeError("W8A8 input must be a CUDA torch.bfloat16 tensor")
+    if _fused_moe_w8a8_async_plan_v2_impl is None:
+        raise RuntimeError("W8A8 fused MoE Plan V2 requires native fused_moe_w8a8_tiled_async_plan_v2 support")
+    if input.dtype != torch.bfloat16:
+        raise TypeError("W8A8 input must be a torch.bfloat16 tensor")
     if _activation_name(activation) != "silu" or float(swiglu_limit) != 10.0:
         raise ValueError("W8A8 supports only activation='silu' with swiglu_limit=10.0")
     if topk_ids.dtype not in _INTEGER_DTYPES:
@@ -322,7 +335,7 @@ def fused_moe_w8a8_tiled_async_plan(input, weights, topk_weights, topk_ids, plan
         raise TypeError(f"topk_weights must use a floating dtype, got {topk_weights.dtype}")
     _validate_output_buffer(input, out)
     materialized = plan if isinstance(plan, AsyncMoEPlanV2) else AsyncMoEPlanV2.from_dict(plan)
-    result = _native.fused_moe_w8a8_tiled_async_plan_v2(
+    result = _fused_moe_w8a8_async_plan_v2_impl(
         input.contiguous(), weights.w13[0], weights.w13[1], weights.w13[2], weights.w13[3], weights.w2[0], weights.w2[1],
         weights.w2[2], weights.w2[3], topk_weights.to(torch.float32).contiguous(), topk_ids.to(torch.int64).contiguous(),
         *_plan_args(materialized), materialized.num_threads, "silu", int(global_num_experts), bool(skip_weighted),
@@ -389,8 +402,8 @@ def _combine_with_shared(topk_weights, topk_ids, shared_expert_id: int, scaling:
 
 
 def _check_shared_call(input, topk_weights, topk_ids, num_threads, routed_scaling_factor) -> float:
-    if input.dtype != torch.bfloat16 or input.device.type != "cuda":
-        raise TypeError("input must be a CUDA torch.bfloat16 tensor")
+    if input.dtype != torch.bfloat16:
+        raise TypeError("input must be a torch.bfloat16 tensor")
     if topk_ids.dtype not in _INTEGER_DTYPES:
         raise TypeError("topk_ids must be an integer tensor")
     if not topk_weights.dtype.is_floating_point:
