@@ -539,7 +539,7 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
         point["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": tokens * hidden * 2 + tokens * top_k * 4 + tokens * top_k * 8,
                         "d2h_bytes_per_step": tokens * hidden * 2,
-                        "planner": {k: last_plan.get(k) for k in ("planner", "dispatch", "kind", "rows_per_expert", "gate_up_tile", "down_tile", "machine_id") if k in last_plan}}
+                        "planner": {k: last_plan.get(k) for k in ("planner", "dispatch", "kind", "rows_per_expert", "gate_up_tile", "down_tile", "machine_id", "calibrated") if k in last_plan}}
     return point
 
 
@@ -656,6 +656,31 @@ class LayerCache:
         torch.cuda.empty_cache()
 
 
+class Runtimes:
+    """One planner runtime per (dims, shared expert) for the end-to-end legs.  With calibrate=True the row-tile
+    table comes from the library's own quick calibration on this GPU (calibrate_moe_planner_quick on a probe layer
+    of the workload's H and I, once per dims); otherwise the runtime carries no table and every call uses the
+    library's automatic tiles."""
+
+    def __init__(self, calibrate: bool):
+        self.calibrate = calibrate
+        self.calibrations: dict = {}
+        self.seconds: dict = {}
+
+    def get(self, spec: dict):
+        from fused_cpp_b200 import moe
+        from fused_cpp_b200.moe import planner_runtime
+
+        d = dims_of(spec)
+        key = (d["hidden"], d["inter"], d["experts"])
+        if self.calibrate and key not in self.calibrations:
+            result = planner_runtime.calibrate_moe_planner_quick(None, _shape=key)
+            self.calibrations[key] = result.calibration
+            self.seconds[key] = result.elapsed_seconds
+        return moe.MoePlannerRuntime(self.calibrations.get(key), hidden_size=d["hidden"], intermediate_size=d["inter"],
+                                     global_experts=d["experts"], local_experts=d["experts"], shared_experts=1 if spec.get("shared") else 0)
+
+
 POINT_KEYS = ("workload", "tokens", "dtype", "ms_per_step", "launch_mode", "eager_ms_per_step", "l2", "value", "active_experts",
               "stage_ms", "roofline", "layer", "e2e")
 
@@ -671,9 +696,11 @@ def run_single_gpu(args) -> None:
     if args.experts:
         spec = dict(spec, dims=dict(dims_of(spec), experts=args.experts))
     int8_peak = None if args.skip_peak else measure_int8_library_peak(device)
+    runtimes = Runtimes(calibrate=not args.skip_e2e and not args.skip_calibration)
     layers = LayerCache(device)
     sampler = ClockSampler(0)
-    head = run_point(args.workload, spec, layers.get(spec), device, args.steps, args.warmup, not args.skip_e2e, sampler, int8_peak)
+    head = run_point(args.workload, spec, layers.get(spec), device, args.steps, args.warmup, not args.skip_e2e, sampler, int8_peak,
+                     runtimes.get(spec))
     points = []
     if args.sweep:
         for kind in ("int8", "bf16"):
@@ -691,7 +718,7 @@ def run_single_gpu(args) -> None:
             other = WORKLOADS[name]
             heavy = other["tokens"] > 1024
             point = run_point(name, other, layers.get(other), device, max(3, args.steps // 4) if heavy else args.steps, args.warmup, True,
-                              None, int8_peak)
+                              None, int8_peak, runtimes.get(other))
             points.append({k: point[k] for k in POINT_KEYS if k in point})
     cpu = None
     if not args.skip_cpu:
@@ -707,7 +734,8 @@ def run_single_gpu(args) -> None:
         "clocks": head.get("clocks"),
         "e2e": {k: head["e2e"][k] for k in ("value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step", "planner")} if "e2e" in head else None,
         "gpu_launches": head["gpu_launches_per_step"] * args.steps, "roofline": head["roofline"], "cpu_baseline": cpu,
-        "int8_library_peak": int8_peak, "stage_ms": head["stage_ms"], "layer": head["layer"], "launch_mode": head["launch_mode"],
+        "int8_library_peak": int8_peak, "planner_calibration_seconds": {"x".join(str(v) for v in k): round(v2, 2) for k, v2 in runtimes.seconds.items()},
+        "stage_ms": head["stage_ms"], "layer": head["layer"], "launch_mode": head["launch_mode"],
         "eager_ms_per_step": head["eager_ms_per_step"], "points": points,
     }
     print(json.dumps(line), flush=True)
@@ -955,6 +983,8 @@ def main() -> None:
     parser.add_argument("--skip-e2e", action="store_true", help="profiling captures only")
     parser.add_argument("--skip-cpu", action="store_true", help="profiling captures only")
     parser.add_argument("--skip-peak", action="store_true", help="profiling captures only: do not time the int8 library GEMM")
+    parser.add_argument("--skip-calibration", action="store_true",
+                        help="end-to-end legs run under a planner runtime without a calibrated tile table (automatic tiles)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -25,6 +25,9 @@ NUMERICS_NATIVE = 1
 GEMM_AUTO = 0
 GEMM_SIMT = 1  # the CUDA-core cross-check GEMM: exists only in the diagnostic library (load_diag)
 GEMM_UMMA = 2
+ACTIVATION_SILU = 0
+ACTIVATION_GELU = 2
+ACTIVATION_SWIGLUOAI = 3
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfused_moe_b200.so")
 DIAG_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfused_moe_b200_diag.so")
@@ -48,8 +51,9 @@ STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 class Config(ctypes.Structure):
     _fields_ = [
         ("numerics", ctypes.c_int32), ("gemm_impl", ctypes.c_int32), ("gate_up_tile", ctypes.c_int32),
-        ("down_tile", ctypes.c_int32), ("swiglu_limit", ctypes.c_float), ("reserved0", ctypes.c_int32),
+        ("down_tile", ctypes.c_int32), ("swiglu_limit", ctypes.c_float), ("activation", ctypes.c_int32),
         ("stage_timer", ctypes.c_void_p), ("dump_acc1", ctypes.c_void_p), ("dump_acc2", ctypes.c_void_p),
+        ("w13_bias", ctypes.c_void_p), ("w2_bias", ctypes.c_void_p),
     ]
 
 
@@ -271,7 +275,8 @@ def _require_cuda(name: str, tensor: torch.Tensor, dtype: torch.dtype) -> torch.
 def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numerics: int = NUMERICS_TORCHREF,
                 gemm_impl: int = GEMM_AUTO, gate_up_tile: int = 0, down_tile: int = 0, swiglu_limit: float | None = None,
                 out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None,
-                stage_timer: "StageTimer | None" = None, diagnostic: bool = False) -> ForwardResult:
+                stage_timer: "StageTimer | None" = None, diagnostic: bool = False, activation: int = ACTIVATION_SILU,
+                w13_bias: torch.Tensor | None = None, w2_bias: torch.Tensor | None = None) -> ForwardResult:
     """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8.
     diagnostic=True (or gemm_impl=GEMM_SIMT) runs the call in the diagnostic library instead of the product one."""
     int8 = w13.dtype == torch.int8
@@ -301,6 +306,17 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
     config.gate_up_tile = gate_up_tile
     config.down_tile = down_tile
     config.swiglu_limit = (10.0 if int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
+    config.activation = int(activation)
+    if w13_bias is not None:
+        w13_bias = _require_cuda("w13_bias", w13_bias, torch.float32)
+        if tuple(w13_bias.shape) != (experts, two_i):
+            raise ValueError("w13_bias must be [E, 2I]")
+        config.w13_bias = w13_bias.data_ptr()
+    if w2_bias is not None:
+        w2_bias = _require_cuda("w2_bias", w2_bias, torch.float32)
+        if tuple(w2_bias.shape) != (experts, hidden):
+            raise ValueError("w2_bias must be [E, H]")
+        config.w2_bias = w2_bias.data_ptr()
     if stage_timer is not None:
         config.stage_timer = stage_timer.handle
     acc1 = acc2 = None

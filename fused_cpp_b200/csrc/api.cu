@@ -193,6 +193,15 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (!f.int8 && cfg.swiglu_limit != 0.0f && cfg.swiglu_limit != 10.0f) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "BF16 supports swiglu_limit 0 (plain SiLU) or 10.0");
   }
+  if (cfg.activation != FMOE_ACTIVATION_SILU && cfg.activation != FMOE_ACTIVATION_GELU && cfg.activation != FMOE_ACTIVATION_SWIGLUOAI) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown activation %d", cfg.activation);
+  }
+  if (f.int8 && (cfg.activation != FMOE_ACTIVATION_SILU || cfg.w13_bias != nullptr || cfg.w2_bias != nullptr)) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "W8A8 supports only the clamped SiLU activation and no w13_bias / w2_bias");
+  }
+  if (cfg.activation != FMOE_ACTIVATION_SILU && cfg.swiglu_limit != 0.0f) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "swiglu_limit is only valid with the SiLU activation");
+  }
   if (cfg.numerics != FMOE_NUMERICS_TORCHREF && cfg.numerics != FMOE_NUMERICS_NATIVE) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown numerics %d", cfg.numerics);
   }
@@ -311,6 +320,8 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.n_out = f.inter;
   gu.numerics = cfg.numerics;
   gu.swiglu_limit = cfg.swiglu_limit;
+  gu.activation = cfg.activation;
+  gu.expert_bias = cfg.w13_bias;
   gu.y = y;
   gu.route_out = nullptr;
   gu.dump_acc = cfg.dump_acc1;
@@ -345,6 +356,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   dn.weights = f.w2;
   dn.a_scale = y_scale;
   dn.w_scale = f.s2;
+  dn.expert_bias = cfg.w2_bias;
   dn.items = items_dn;
   dn.item_count_word = fmoe::kStatusItemsB;
   dn.k = f.inter;
@@ -371,7 +383,8 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   mark(FMOE_STAGE_DOWN + 1);
 
   if (!f.rows_mode) {
-    error = fmoe::launch_merge(route_out, f.topk_weights, f.tokens, f.top_k, f.hidden, f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream);
+    error = fmoe::launch_merge(route_out, f.topk_weights, f.tokens, f.top_k, f.hidden, f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream,
+                               reinterpret_cast<const int*>(base + layout.route_pos));
     if (error != cudaSuccess) return cuda_fail(error, "top-k merge");
   }
   mark(FMOE_STAGE_MERGE + 1);

@@ -98,6 +98,27 @@ __device__ __forceinline__ uint16_t swiglu_to_bf16_with(float gate, float up, fl
   return f32_to_bf16_bits(value);
 }
 
+// The other gated activations of the reference's BF16 op (csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1911-1936,
+// arithmetic as in src/fused_cpp/moe/naive.py:28-54).  Rare paths: kept out of line so that the SiLU loops do not
+// carry their registers.
+//   gelu:      0.5 * gate * (1 + erf(gate / sqrt(2))) * up
+//   swigluoai: gate = min(gate, 7), up = clamp(up, +-7), (up + 1) * gate * sigmoid(1.702 * gate)
+#define FMOE_ACT_SILU 0
+#define FMOE_ACT_GELU 2
+#define FMOE_ACT_SWIGLUOAI 3
+static __device__ __noinline__ uint16_t other_activation_to_bf16(int activation, float gate, float up) {
+  float value;
+  if (activation == FMOE_ACT_GELU) {
+    value = 0.5f * gate * (1.0f + erff(gate * 0.70710678118654752440f)) * up;
+  } else {
+    gate = fminf(gate, 7.0f);
+    up = fmaxf(fminf(up, 7.0f), -7.0f);
+    const float glu = gate / (1.0f + expf(-1.702f * gate));
+    value = (up + 1.0f) * glu;
+  }
+  return f32_to_bf16_bits(value);
+}
+
 __device__ __forceinline__ uint16_t swiglu_to_bf16(float gate, float up, float limit) {
   return swiglu_to_bf16_with(gate, up, limit, kExp2Table);
 }

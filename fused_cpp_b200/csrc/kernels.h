@@ -109,8 +109,9 @@ cudaError_t launch_router_topk(const float* logits, const float* selection_bias,
 // ---- merge.cu
 // W8A8: out[t] = bf16( fma chain over slots of route_out[t*K+slot] * w[t,slot] ).
 // BF16: pairwise tree for K in {2,4,6,8}, chain otherwise.
+// route_pos (nullable): sorted position of every flat route, -1 = dropped by the route build; such rows count as zeros.
 cudaError_t launch_merge(const float* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
-                         int tree, uint16_t* out, cudaStream_t stream);
+                         int tree, uint16_t* out, cudaStream_t stream, const int* route_pos = nullptr);
 // Same with the route rows stored as bf16 (opt-in compact return of the expert-parallel path).
 cudaError_t launch_merge_bf16_rows(const uint16_t* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
                                    int tree, uint16_t* out, cudaStream_t stream);
@@ -144,6 +145,11 @@ struct GroupedGemmArgs {
   // Down GEMM, optional: byte address of the fp32 output row of every sorted row.  Overrides route_out +
   // sorted_routes; the rows may lie in another GPU's memory (expert-parallel return path, plain stores).
   const uint64_t* row_out_ptrs;
+  // BF16 path only: per-expert bias added to the fp32 accumulators before the activation (gate_up: [E, 2I], gate
+  // channels then up channels) or before the store (down: [E, H]); null = none.  `activation` selects the gated
+  // activation of the gate_up epilogue: FMOE_ACT_SILU (with swiglu_limit), FMOE_ACT_GELU, FMOE_ACT_SWIGLUOAI.
+  const float* expert_bias;
+  int activation;
   int gate_up_one_box;       // two-SM gate_up: the weight rows of a stage arrive as one 16 KB TMA box (set by the launcher)
   int route_out_bf16;        // with row_out_ptrs: the result rows are stored as bf16 (2 bytes per channel) instead of fp32
   // Diagnostic build only (compiled with -DFMOE_DIAG, the separate libfused_moe_b200_diag.so; the product library

@@ -49,12 +49,18 @@ __device__ __forceinline__ float4 load_row4(const void* route_out, int64_t eleme
 
 template <bool kBf16Rows>
 __global__ void __launch_bounds__(kMergeThreads)
-merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_weights, int top_k, int hidden, int tree,
-             uint16_t* __restrict__ out) {
+merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_weights, const int* __restrict__ route_pos, int top_k,
+             int hidden, int tree, uint16_t* __restrict__ out) {
   __shared__ float weights[kMaxTopK];
+  __shared__ bool present[kMaxTopK];
   // Tokens ride on grid.x (up to 2^31 - 1 blocks), the few chunks of a row on grid.y (at most 65535).
   const int64_t token = blockIdx.x;
-  if (threadIdx.x < top_k) weights[threadIdx.x] = topk_weights[token * top_k + threadIdx.x];
+  if (threadIdx.x < top_k) {
+    weights[threadIdx.x] = topk_weights[token * top_k + threadIdx.x];
+    // A route dropped by the route build (expert id out of range; reported in the status block) has no row: the
+    // down GEMM never wrote it, so it counts as a row of zeros instead of whatever the workspace held.
+    present[threadIdx.x] = route_pos == nullptr || route_pos[token * top_k + threadIdx.x] >= 0;
+  }
   __syncthreads();
   const int h = (blockIdx.y * kMergeThreads + threadIdx.x) * 4;
   if (h >= hidden) return;
@@ -63,7 +69,9 @@ merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_
   const bool fixed = tree && (top_k == 2 || top_k == 4 || top_k == 6 || top_k == 8);
   if (fixed) {
     float4 rows[8];
-    for (int slot = 0; slot < top_k; ++slot) rows[slot] = load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden);
+    for (int slot = 0; slot < top_k; ++slot) {
+      rows[slot] = present[slot] ? load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
 #pragma unroll
     for (int lane = 0; lane < 4; ++lane) {
       float values[8];
@@ -79,7 +87,8 @@ merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_
   } else {
     result[0] = result[1] = result[2] = result[3] = 0.0f;
     for (int slot = 0; slot < top_k; ++slot) {
-      const float4 row = load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden);
+      const float4 row = present[slot] ? load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden)
+                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       const float w = weights[slot];
       result[0] = __fmaf_rn(row.x, w, result[0]);
       result[1] = __fmaf_rn(row.y, w, result[1]);
@@ -96,11 +105,11 @@ merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_
 }  // namespace
 
 cudaError_t launch_merge(const float* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
-                         int tree, uint16_t* out, cudaStream_t stream) {
+                         int tree, uint16_t* out, cudaStream_t stream, const int* route_pos) {
   if (tokens <= 0) return cudaSuccess;
   if (top_k > kMaxTopK) return cudaErrorInvalidValue;
   const dim3 grid(static_cast<unsigned>(tokens), (hidden / 4 + kMergeThreads - 1) / kMergeThreads);
-  merge_kernel<false><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
+  merge_kernel<false><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, route_pos, top_k, hidden, tree, out);
   return cudaGetLastError();
 }
 
@@ -109,7 +118,7 @@ cudaError_t launch_merge_bf16_rows(const uint16_t* route_out, const float* topk_
   if (tokens <= 0) return cudaSuccess;
   if (top_k > kMaxTopK) return cudaErrorInvalidValue;
   const dim3 grid(static_cast<unsigned>(tokens), (hidden / 4 + kMergeThreads - 1) / kMergeThreads);
-  merge_kernel<true><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, top_k, hidden, tree, out);
+  merge_kernel<true><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, nullptr, top_k, hidden, tree, out);
   return cudaGetLastError();
 }
 

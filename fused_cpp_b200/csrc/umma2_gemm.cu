@@ -383,6 +383,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
     const int n_out = args.n_out;
     const bool native = args.numerics == FMOE_NUMERICS_NATIVE;
     const float limit = args.swiglu_limit;
+    const int activation = args.activation;
     uint32_t* const dump = static_cast<uint32_t*>(args.dump_acc);
     const bool low = lane < 16;  // gate_up: lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same channels
     // Output channel of this thread inside the unit's channel block.
@@ -400,7 +401,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       float scale_gate, scale_up, bias;
     };
     auto fetch = [&](const UnitInfo& info, bool valid) {
-      ThreadUnit t = {0.0f, 0ull, 1.0f, 1.0f, 0.0f};
+      ThreadUnit t = {0.0f, 0ull, kInt8 ? 1.0f : 0.0f, kInt8 ? 1.0f : 0.0f, 0.0f};
       if (!valid) return t;
       if (tid < info.rows) {
         const int row = info.row0 + tid;
@@ -421,6 +422,12 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
           if (kGateUp) t.scale_up = s[n + n_out];
         }
         if (kDense && args.bias != nullptr) t.bias = args.bias[n];
+        if (!kInt8 && !kDense && args.expert_bias != nullptr) {
+          // BF16 path: the per-expert bias rides in the scale slots (unused without int8) and is ADDED.
+          const float* b = args.expert_bias + static_cast<int64_t>(info.expert) * n_total;
+          t.scale_gate = b[n];
+          if (kGateUp) t.scale_up = b[n + n_out];
+        }
       }
       return t;
     };
@@ -435,7 +442,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
           return __fmul_rn(__fmul_rn(value, a), s);
         }
       } else {
-        return __uint_as_float(bits);
+        return __fadd_rn(__uint_as_float(bits), s);  // s = the channel's bias (0 without one)
       }
     };
     // Calls body(fast, native) with both flags turned into types: four instances of the element loop, one branch.
@@ -519,7 +526,9 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
                 }
                 const float gate = to_float(native_tag, gate_bits, a, mine.scale_gate);
                 const float up = to_float(native_tag, up_bits, a, mine.scale_up);
-                out0[static_cast<uint32_t>(p) * pair_stride] = swiglu_to_bf16_with(gate, up, limit, exp_table);
+                out0[static_cast<uint32_t>(p) * pair_stride] =
+                    (kInt8 || activation == FMOE_ACT_SILU) ? swiglu_to_bf16_with(gate, up, limit, exp_table)
+                                                           : other_activation_to_bf16(activation, gate, up);
               }
             }
           };

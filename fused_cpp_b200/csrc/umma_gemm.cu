@@ -228,6 +228,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
     const int n_out = args.n_out;
     const int numerics = args.numerics;
     const float limit = args.swiglu_limit;
+    const int activation = args.activation;
     uint32_t* const dump = static_cast<uint32_t*>(args.dump_acc);
     int local = 0;
     for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
@@ -259,6 +260,12 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       }
       float bias = 0.0f;
       if (kDense && channel_ok && args.bias != nullptr) bias = args.bias[n];
+      float bias_gate = 0.0f, bias_up = 0.0f;  // per-expert bias of the BF16 path (gate_up: gate / up; down: bias_gate)
+      if (!kInt8 && !kDense && channel_ok && args.expert_bias != nullptr) {
+        const float* b = args.expert_bias + static_cast<int64_t>(expert) * n_total;
+        bias_gate = b[n];
+        if (kGateUp) bias_up = b[n + n_out];
+      }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // metadata visible to the four epilogue warps
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 4);
       ptx::tcgen05_fence_after();
@@ -285,16 +292,18 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                   gate = dequantize(static_cast<int>(gate_bits[j]), a, scale_gate, numerics);
                   up = dequantize(static_cast<int>(up_bits[j]), a, scale_up, numerics);
                 } else {
-                  gate = __uint_as_float(gate_bits[j]);
-                  up = __uint_as_float(up_bits[j]);
+                  gate = __fadd_rn(__uint_as_float(gate_bits[j]), bias_gate);
+                  up = __fadd_rn(__uint_as_float(up_bits[j]), bias_up);
                 }
-                args.y[static_cast<int64_t>(row0 + c0 + j) * n_out + n] = swiglu_to_bf16_with(gate, up, limit, ctl->exp_table);
+                args.y[static_cast<int64_t>(row0 + c0 + j) * n_out + n] =
+                    (kInt8 || activation == FMOE_ACT_SILU) ? swiglu_to_bf16_with(gate, up, limit, ctl->exp_table)
+                                                           : other_activation_to_bf16(activation, gate, up);
               } else {
                 float value;
                 if constexpr (kInt8) {
                   value = dequantize(static_cast<int>(gate_bits[j]), meta->scale[c0 + j], scale_gate, numerics);
                 } else {
-                  value = __uint_as_float(gate_bits[j]);
+                  value = __fadd_rn(__uint_as_float(gate_bits[j]), bias_gate);
                 }
                 const uint64_t rowptr = meta->rowptr[c0 + j];
                 if constexpr (kDense) {

@@ -209,18 +209,47 @@ def fused_moe_w8a8_tiled_async_plan_v2(
     return result.out
 
 
-def _native_activation(activation: str) -> float:
-    if activation == "silu":
-        return 0.0
-    if activation == "silu_clamp10":
-        return 10.0
-    raise RuntimeError(f"unsupported activation {activation!r}: the GPU path implements 'silu' and 'silu_clamp10'")
+def _native_activation(activation: str) -> tuple[int, float]:
+    """Activation string of the op -> (activation id of the C ABI, swiglu_limit)."""
+    table = {"silu": (_lib.ACTIVATION_SILU, 0.0), "silu_clamp10": (_lib.ACTIVATION_SILU, 10.0),
+             "gelu": (_lib.ACTIVATION_GELU, 0.0), "swigluoai": (_lib.ACTIVATION_SWIGLUOAI, 0.0)}
+    if activation not in table:
+        raise RuntimeError(f"unsupported MoE activation: {activation}")
+    return table[activation]
+
+
+def _check_bias(bias, experts: int, channels: int, name: str):
+    """check_optional_bias of the reference (fused_moe_bf16_tiled.cpp:6420-6421): [E, N] of a floating dtype."""
+    if bias is None:
+        return None
+    if bias.dim() != 2 or tuple(bias.shape) != (experts, channels) or not bias.dtype.is_floating_point:
+        raise RuntimeError(f"{name} must be a floating [E, N] = [{experts}, {channels}] tensor")
+    return bias.to(device=_device(), dtype=torch.float32).contiguous()
+
+
+# swigluoai checkpoints interleave gate and up channels (row 2j = gate j, row 2j + 1 = up j; naive.py:39-47); the
+# kernels take gate rows then up rows.  The reordered copy is made once per weight tensor and kept while it lives.
+_DEINTERLEAVED: dict = {}
+
+
+def _gate_then_up(tensor: torch.Tensor, dim: int) -> torch.Tensor:
+    key = (tensor.data_ptr(), tuple(tensor.shape), tensor.dtype, dim)
+    cached = _DEINTERLEAVED.get(key)
+    if cached is not None and cached[0]() is tensor:
+        return cached[1]
+    import weakref
+
+    count = tensor.shape[dim]
+    order = torch.cat((torch.arange(0, count, 2), torch.arange(1, count, 2))).to(tensor.device)
+    result = tensor.index_select(dim, order).contiguous()
+    for stale in [k for k, v in _DEINTERLEAVED.items() if v[0]() is None]:
+        del _DEINTERLEAVED[stale]
+    _DEINTERLEAVED[key] = (weakref.ref(tensor), result)
+    return result
 
 
 def _bf16_forward(input, w13_packed, w13_k, w13_n, w2_packed, w2_k, w2_n, topk_weights, topk_ids, w13_bias, w2_bias,
                   activation, global_num_experts, skip_weighted, out, gate_up_tile=0, down_tile=0):
-    if w13_bias is not None or w2_bias is not None:
-        raise RuntimeError("w13_bias / w2_bias are not implemented on the GPU path")
     if input.dim() != 2 or input.dtype != torch.bfloat16 or input.device.type != "cuda":
         raise RuntimeError("input must be a CUDA BF16 [tokens, H] tensor")
     if topk_ids.dim() != 2 or topk_weights.shape != topk_ids.shape or topk_ids.shape[0] != input.shape[0]:
@@ -228,17 +257,36 @@ def _bf16_forward(input, w13_packed, w13_k, w13_n, w2_packed, w2_k, w2_n, topk_w
     if input.shape[1] != w13_k or w13_n != 2 * w2_k or w2_n != w13_k:
         raise RuntimeError("expert dimensions mismatch")
     experts = w13_packed.shape[0]
+    if global_num_experts == 0 or global_num_experts < -1:
+        raise RuntimeError(f"global_num_experts must be positive or -1, got {global_num_experts}")
     if global_num_experts != -1 and global_num_experts > experts:
         raise RuntimeError("global_num_experts cannot exceed the packed expert count")
     if skip_weighted and topk_ids.shape[1] != 1:
         raise RuntimeError("skip_weighted is only valid when top_k == 1")
     _check_out(input, out, (input, w13_packed, w2_packed, topk_weights, topk_ids))
+    activation_id, limit = _native_activation(activation)
+    w13_bias = _check_bias(w13_bias, experts, w13_n, "w13_bias")
+    w2_bias = _check_bias(w2_bias, experts, w2_n, "w2_bias")
+    w13 = w13_packed.reshape(experts, w13_n, w13_k)
+    w2 = w2_packed.reshape(experts, w2_n, w2_k)
+    if activation_id == _lib.ACTIVATION_SWIGLUOAI:
+        w13 = _gate_then_up(w13, 1)
+        if w13_bias is not None:
+            w13_bias = _gate_then_up(w13_bias, 1)
+    # The reference narrows the valid id range to [0, global_num_experts) and raises on ids beyond it
+    # (fused_moe_bf16_tiled.cpp:6439-6458): the route build sees only that many experts, so such ids are reported as
+    # out of range instead of being routed to the trailing prepared experts.
+    if global_num_experts != -1 and global_num_experts < experts:
+        experts = int(global_num_experts)
+        w13, w2 = w13[:experts], w2[:experts]
+        w13_bias = None if w13_bias is None else w13_bias[:experts]
+        w2_bias = None if w2_bias is None else w2_bias[:experts]
     weights = topk_weights.to(torch.float32)
     if skip_weighted:
         weights = torch.ones_like(weights)
-    result = _lib.moe_forward(input, w13_packed.reshape(experts, w13_n, w13_k), w2_packed.reshape(experts, w2_n, w2_k), weights,
-                              topk_ids.to(torch.int64), gemm_impl=_gemm_impl(), gate_up_tile=gate_up_tile, down_tile=down_tile,
-                              swiglu_limit=_native_activation(activation), out=out)
+    result = _lib.moe_forward(input, w13, w2, weights, topk_ids.to(torch.int64), gemm_impl=_gemm_impl(), gate_up_tile=gate_up_tile,
+                              down_tile=down_tile, swiglu_limit=limit, out=out, activation=activation_id, w13_bias=w13_bias,
+                              w2_bias=w2_bias)
     if _sync_check():
         result.raise_for_status()
     return result.out

@@ -89,39 +89,78 @@ class QuickMoeCalibrationResult:
     fit_report: dict
 
 
+# Device memory the probe layer's weights may take (bytes): the layer keeps the caller's H and I and as many of its
+# local experts as fit, so that tile timings are taken at the real operand widths.
+PROBE_WEIGHT_BYTES = 3 << 30
+DEFAULT_PROBE_SHAPE = (2048, 1024, 32)  # (hidden, inter, experts) when no layer shape is given
+CALIBRATION_BUCKETS = (1, 8, 24, 48, 96, 192, 384)
+
+
+def _probe_layer(kind: str, hidden: int, inter: int, experts: int, device: torch.device, seed: int) -> dict:
+    """Random weights of the probe layer, generated on the device (values do not affect timing)."""
+    per_expert = 3 * hidden * inter * (1 if kind == "int8" else 2)
+    experts = max(2, min(int(experts), PROBE_WEIGHT_BYTES // per_expert))
+    generator = torch.Generator(device=device).manual_seed(seed)
+    if kind == "int8":
+        return {"experts": experts,
+                "w13": torch.randint(-127, 128, (experts, 2 * inter, hidden), generator=generator, dtype=torch.int8, device=device),
+                "w2": torch.randint(-127, 128, (experts, hidden, inter), generator=generator, dtype=torch.int8, device=device),
+                "s13": torch.full((experts, 2 * inter), 1e-3, device=device), "s2": torch.full((experts, hidden), 1e-3, device=device)}
+    return {"experts": experts,
+            "w13": torch.empty((experts, 2 * inter, hidden), dtype=torch.bfloat16, device=device).normal_(0.0, 0.02, generator=generator),
+            "w2": torch.empty((experts, hidden, inter), dtype=torch.bfloat16, device=device).normal_(0.0, 0.02, generator=generator),
+            "s13": None, "s2": None}
+
+
+def _probe_routing(rows_per_expert: int, experts: int, skewed: bool, seed: int):
+    """(tokens, top-k ids [T, K]) with `rows_per_expert` routes per expert on average.  Uniform: every expert gets
+    exactly that many.  Skewed: softmax top-k of N(0,1) logits plus the Zipf-like bias 2 ln(1/(rank+1)), the
+    benchmark's skewed router, so a few experts take most routes and some take none."""
+    top_k = min(8, experts)
+    routes = max(top_k, rows_per_expert * experts)
+    tokens = max(1, routes // top_k)
+    if not skewed:
+        ids = (torch.arange(tokens * top_k, dtype=torch.int64) % experts).reshape(tokens, top_k)
+        return tokens, ids
+    generator = torch.Generator(device="cpu").manual_seed(seed)
+    rank = torch.randperm(experts, generator=generator).to(torch.float32)
+    logits = torch.randn((tokens, experts), generator=generator) + 2.0 * torch.log(1.0 / (rank + 1.0))
+    return tokens, torch.topk(logits, top_k, dim=-1).indices.to(torch.int64).contiguous()
+
+
 def _probe_tiles(kind: str, rows_per_expert: int, tiles: Sequence[int], seed: int, hidden: int, inter: int, experts: int,
-                 repeats: int = 5) -> dict[int, float]:
-    """Time one forward per candidate tile on a probe layer where every expert gets `rows_per_expert` rows."""
+                 repeats: int = 5, _cache: dict | None = None) -> dict[int, float]:
+    """Time one forward per candidate tile on a probe layer of the caller's H and I: the sum of a uniformly routed
+    batch and a skewed one with `rows_per_expert` routes per expert on average (ms)."""
     from .. import _lib
 
     device = torch.device("cuda", torch.cuda.current_device())
-    generator = torch.Generator(device="cpu").manual_seed(seed)
-    tokens = rows_per_expert * experts
-    x = torch.randn((tokens, hidden), generator=generator).to(torch.bfloat16).to(device)
-    ids = (torch.arange(tokens, dtype=torch.int64) % experts).reshape(tokens, 1).to(device)
-    weights = torch.ones((tokens, 1), dtype=torch.float32, device=device)
-    if kind == "int8":
-        w13 = torch.randint(-127, 128, (experts, 2 * inter, hidden), generator=generator, dtype=torch.int8).to(device)
-        w2 = torch.randint(-127, 128, (experts, hidden, inter), generator=generator, dtype=torch.int8).to(device)
-        s13 = torch.full((experts, 2 * inter), 1e-3, device=device)
-        s2 = torch.full((experts, hidden), 1e-3, device=device)
-    else:
-        w13 = (torch.randn((experts, 2 * inter, hidden), generator=generator) * 0.02).to(torch.bfloat16).to(device)
-        w2 = (torch.randn((experts, hidden, inter), generator=generator) * 0.02).to(torch.bfloat16).to(device)
-        s13 = s2 = None
-    result: dict[int, float] = {}
-    for tile in tiles:
-        def run():
-            return _lib.moe_forward(x, w13, w2, weights, ids, s13=s13, s2=s2, gate_up_tile=tile, down_tile=tile)
-        run()
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(repeats):
+    cache = _cache if _cache is not None else {}
+    key = (kind, hidden, inter, experts)
+    if key not in cache:
+        cache.clear()  # one probe layer at a time on the device
+        cache[key] = _probe_layer(kind, hidden, inter, experts, device, seed)
+    layer = cache[key]
+    result: dict[int, float] = {int(tile): 0.0 for tile in tiles}
+    for skewed in (False, True):
+        tokens, ids = _probe_routing(rows_per_expert, layer["experts"], skewed, seed + 1)
+        ids = ids.to(device)
+        generator = torch.Generator(device=device).manual_seed(seed + 2)
+        x = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device).normal_(0.0, 1.0, generator=generator)
+        weights = torch.full(ids.shape, 1.0 / ids.shape[1], dtype=torch.float32, device=device)
+        for tile in tiles:
+            def run():
+                return _lib.moe_forward(x, layer["w13"], layer["w2"], weights, ids, s13=layer["s13"], s2=layer["s2"],
+                                        gate_up_tile=tile, down_tile=tile)
             run()
-        stop.record()
-        torch.cuda.synchronize()
-        result[int(tile)] = start.elapsed_time(stop) / repeats
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(repeats):
+                run()
+            stop.record()
+            torch.cuda.synchronize()
+            result[int(tile)] += start.elapsed_time(stop) / repeats
     return result
 
 
@@ -129,12 +168,15 @@ def calibrate_moe_planner_quick(cpu_ids: Sequence[int] | None = None, *, output:
                                 supported_widths: Sequence[int] | None = None, machine_id: str | None = None,
                                 overwrite: bool = False, seed: int = 20260814, report: Callable[[str], None] | None = None,
                                 _probe: Callable[..., dict[int, float]] | None = None,
-                                _buckets: Sequence[int] | None = None) -> QuickMoeCalibrationResult:
+                                _buckets: Sequence[int] | None = None,
+                                _shape: tuple[int, int, int] | None = None) -> QuickMoeCalibrationResult:
     """Time the grouped GEMM's row tiles per rows-per-expert bucket on this GPU and write the profile.
 
     Signature of the reference's quick calibration (quick_calibration.py:359-368).  `cpu_ids` is kept
     for compatibility and recorded only; `supported_widths` names the candidate row tiles
-    (default: automatic and 16..512).  `_probe` lets tests substitute synthetic timings.
+    (default: automatic and 16..512).  `_shape` = (hidden, inter, local experts) of the layer the table is for
+    (enable_moe_planner_quick passes its own; a bare call probes a small default layer); `_probe` lets tests
+    substitute synthetic timings.
     """
     begin = time.perf_counter()
     path = Path(output) if output is not None else None
@@ -143,33 +185,37 @@ def calibrate_moe_planner_quick(cpu_ids: Sequence[int] | None = None, *, output:
     tiles = tuple(int(t) for t in (supported_widths or CANDIDATE_TILES))
     if any(t not in CANDIDATE_TILES for t in tiles):
         raise ValueError(f"supported_widths (row tiles) must be drawn from {CANDIDATE_TILES}")
+    hidden, inter, experts = (int(v) for v in (_shape or DEFAULT_PROBE_SHAPE))
     probe = _probe
+    probe_kwargs: dict = {}
     if probe is None:
         from .. import _lib
 
         if not _lib.device_supported():
             raise RuntimeError("quick calibration requires a compute-capability-10.x CUDA device")
         probe = _probe_tiles
+        probe_kwargs = {"_cache": {}}
         gpu_name = torch.cuda.get_device_name()
         sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     else:
         gpu_name, sm_count = "synthetic", 0
-    buckets = tuple(_buckets) if _buckets is not None else (1, 8, 24, 48, 96, 192, 384)
+    buckets = tuple(_buckets) if _buckets is not None else CALIBRATION_BUCKETS
     table: dict[str, dict[int, tuple[int, int]]] = {}
     timings: dict[str, dict[int, dict[int, float]]] = {}
     for kind in ("int8", "bf16"):
         table[kind], timings[kind] = {}, {}
         for bucket in buckets:
-            measured = probe(kind, bucket, tiles, seed, 2048, 1024, 32)
+            measured = probe(kind, bucket, tiles, seed, hidden, inter, experts, **probe_kwargs)
             best = min(measured, key=lambda t: (measured[t], t))
-            # The probe routes uniformly; a fixed tile that is not clearly faster there is not worth giving up the
-            # automatic choice, which adapts to the routing of every batch.
+            # A fixed tile that is not clearly faster on the probe batches is not worth giving up the automatic
+            # choice, which adapts to the routing of every batch.
             if 0 in measured and measured[0] <= 1.03 * measured[best]:
                 best = 0
             table[kind][int(bucket)] = (int(best), int(best))
             timings[kind][int(bucket)] = {int(t): float(v) for t, v in measured.items()}
             if report is not None:
-                report(f"[quick-calibration] {kind} rows/expert<={bucket}: tile {best} ({measured[best]:.3f} ms)")
+                report(f"[quick-calibration] {kind} H={hidden} I={inter} rows/expert<={bucket}: tile {best} ({measured[best]:.3f} ms)")
+    probe_kwargs.clear()
     calibration = GpuTileCalibration(machine_id=machine_id or gpu_name, gpu_name=gpu_name, sm_count=int(sm_count), tiles=table,
                                      timings_ms=timings)
     if path is not None:
@@ -186,7 +232,8 @@ def calibrate_moe_planner_quick(cpu_ids: Sequence[int] | None = None, *, output:
     resolved_cpus = tuple(int(c) for c in cpu_ids) if cpu_ids is not None else tuple(sorted(os.sched_getaffinity(0)))
     return QuickMoeCalibrationResult(calibration=calibration, output_path=path, cpu_ids=resolved_cpus, service_widths=tiles,
                                      supported_widths=tiles, elapsed_seconds=time.perf_counter() - begin,
-                                     fit_report={"buckets": list(buckets), "kinds": ["int8", "bf16"]})
+                                     fit_report={"buckets": list(buckets), "kinds": ["int8", "bf16"], "probe_shape": [hidden, inter, experts],
+                                                 "routings": ["uniform", "zipf"]})
 
 
 class MoePlannerRuntime:
@@ -237,7 +284,7 @@ class MoePlannerRuntime:
         with self._lock:
             self._last = {"planner": "gpu_tile_table", "dispatch": label, "kind": kind, "routes": routes,
                           "rows_per_expert": rows_per_expert, "gate_up_tile": gate_up_tile, "down_tile": down_tile,
-                          "machine_id": self.calibration.machine_id}
+                          "machine_id": self.calibration.machine_id, "calibrated": bool(self.calibration.tiles.get(kind))}
         return gpu_placeholder_plan(gate_up_tile, down_tile)
 
     def plan_for_dispatch(self, weights: Any, topk_ids: torch.Tensor, *, num_threads: int, activation: Any,
@@ -296,7 +343,8 @@ def enable_moe_planner_quick(*, hidden_size: int, intermediate_size: int, global
                              report: Callable[[str], None] | None = None) -> MoePlannerRuntime:
     """Calibrate, construct and install the default planner runtime (planner_runtime.py:348-391)."""
     result = calibrate_moe_planner_quick(cpu_ids, output=output, supported_widths=supported_widths, machine_id=machine_id,
-                                         overwrite=overwrite, seed=seed, report=report)
+                                         overwrite=overwrite, seed=seed, report=report,
+                                         _shape=(int(hidden_size), int(intermediate_size), int(local_experts) + int(shared_experts)))
     runtime = MoePlannerRuntime(result.calibration, hidden_size=hidden_size, intermediate_size=intermediate_size,
                                 global_experts=global_experts, local_experts=local_experts, mode=mode, degree=degree,
                                 concurrent_ranks=concurrent_ranks, cpu_ids=result.cpu_ids, shared_experts=shared_experts,

@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define FMOE_ABI_VERSION 1
+#define FMOE_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define FMOE_API __attribute__((visibility("default")))
@@ -64,11 +64,25 @@ typedef struct fmoe_config {
   int32_t gate_up_tile;  /* rows of one expert per work item in the gate_up GEMM: 16..256, 512 = two-SM pairs of 256 rows; 0 = auto */
   int32_t down_tile;     /* same for the down GEMM; 0 = auto */
   float swiglu_limit;    /* BF16: 0 = plain SiLU, 10 = clamp-10 SwiGLU.  W8A8 requires 10. */
-  int32_t reserved0;
+  int32_t activation;    /* BF16 only: FMOE_ACTIVATION_* (W8A8 requires SILU) */
   void* stage_timer;     /* optional handle from fmoe_stage_timer_create: per-stage CUDA events are recorded */
   int32_t* dump_acc1;    /* optional [T*K, 2I] int32 (W8A8) / fp32 (BF16): raw gate_up accumulators, sorted-row order */
   int32_t* dump_acc2;    /* optional [T*K, H]: raw down accumulators, sorted-row order */
+  /* BF16 only, optional per-expert biases in fp32 (the reference converts them to fp32 as well,
+   * csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:6420-6427): w13_bias[E, 2I] (gate channels then up channels) is added
+   * to the gate_up accumulators before the activation, w2_bias[E, H] to every route row before the top-k merge. */
+  const float* w13_bias;
+  const float* w2_bias;
 } fmoe_config;
+
+/* Gated activations of the BF16 op (activation_to_bf16, csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1911-1936):
+ * SILU = gate * up / (1 + exp(-gate)) with the optional clamp of swiglu_limit; GELU = gelu_erf(gate) * up;
+ * SWIGLUOAI = (clamp(up, +-7) + 1) * g * sigmoid(1.702 g) with g = min(gate, 7).  The kernels take gate channels
+ * [0, I) and up channels [I, 2I) of w13 for every activation (callers holding the interleaved SWIGLUOAI layout
+ * de-interleave once at preparation). */
+#define FMOE_ACTIVATION_SILU 0
+#define FMOE_ACTIVATION_GELU 2
+#define FMOE_ACTIVATION_SWIGLUOAI 3
 
 /* Byte offsets of the regions of a forward workspace (all 256-byte aligned).  Rows of the
  * per-route regions are in SORTED order: position p holds flat route sorted_routes[p]. */

@@ -354,12 +354,44 @@ static inline float dot_bf16(const uint16_t* a, const uint16_t* b, int n) {
 }
 
 /*
- * BF16 routed-expert forward: bf16 operands, fp32 accumulation, SiLU(gate)*up rounded to bf16,
- * fp32 route rows, tree/chain merge.  swiglu_limit <= 0: plain SiLU; 10: clamp-10 variant.
+ * The other gated activations of the BF16 op (activation_to_bf16, csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1911-1936;
+ * arithmetic as in src/fused_cpp/moe/naive.py:28-54): 2 = gelu(erf)(gate) * up, 3 = swigluoai
+ * ((clamp(up, +-7) + 1) * g * sigmoid(1.702 g), g = min(gate, 7)).  Compared to tolerance, so libm's erff / expf serve.
  */
+static inline uint16_t other_activation_to_bf16(int activation, float gate, float up) {
+  float value;
+  if (activation == 2) {
+    value = 0.5f * gate * (1.0f + erff(gate * 0.70710678118654752440f)) * up;
+  } else {
+    gate = gate < 7.0f ? gate : 7.0f;
+    up = up > 7.0f ? 7.0f : (up < -7.0f ? -7.0f : up);
+    value = (up + 1.0f) * (gate / (1.0f + expf(-1.702f * gate)));
+  }
+  return fmoe_oracle_f32_to_bf16(value);
+}
+
+/*
+ * BF16 routed-expert forward: bf16 operands, fp32 accumulation, gated activation rounded to bf16,
+ * fp32 route rows, tree/chain merge.  activation 0: SiLU(gate)*up with swiglu_limit <= 0 plain, 10 the clamp-10
+ * variant; 2, 3: see above.  w13_bias[E, 2I] / w2_bias[E, H] (fp32, NULL = none) are added to the accumulators
+ * before the activation / before the merge (fused_moe_bf16_tiled.cpp:6420-6427; F.linear(..., bias) in naive.py:229-239).
+ */
+int fmoe_oracle_bf16_forward_ex(const uint16_t* x, const uint16_t* w13, const uint16_t* w2, const float* topk_w,
+                                const int64_t* topk_ids, int64_t tokens, int top_k, int experts, int hidden, int inter,
+                                float swiglu_limit, int activation, const float* w13_bias, const float* w2_bias,
+                                uint16_t* out, uint16_t* dump_y, float* dump_route_out);
+
 int fmoe_oracle_bf16_forward(const uint16_t* x, const uint16_t* w13, const uint16_t* w2, const float* topk_w,
                              const int64_t* topk_ids, int64_t tokens, int top_k, int experts, int hidden, int inter,
                              float swiglu_limit, uint16_t* out, uint16_t* dump_y, float* dump_route_out) {
+  return fmoe_oracle_bf16_forward_ex(x, w13, w2, topk_w, topk_ids, tokens, top_k, experts, hidden, inter, swiglu_limit, 0, NULL,
+                                     NULL, out, dump_y, dump_route_out);
+}
+
+int fmoe_oracle_bf16_forward_ex(const uint16_t* x, const uint16_t* w13, const uint16_t* w2, const float* topk_w,
+                                const int64_t* topk_ids, int64_t tokens, int top_k, int experts, int hidden, int inter,
+                                float swiglu_limit, int activation, const float* w13_bias, const float* w2_bias,
+                                uint16_t* out, uint16_t* dump_y, float* dump_route_out) {
   const int64_t routes = tokens * top_k;
   for (int64_t route = 0; route < routes; ++route) {
     if (topk_ids[route] < 0 || topk_ids[route] >= experts) return -1;
@@ -374,13 +406,22 @@ int fmoe_oracle_bf16_forward(const uint16_t* x, const uint16_t* w13, const uint1
       const int64_t expert = topk_ids[route];
       const uint16_t* xrow = x + token * hidden;
       const uint16_t* w13_e = w13 + expert * 2 * (int64_t)inter * hidden;
+      const float* b13 = w13_bias ? w13_bias + expert * 2 * (int64_t)inter : NULL;
+      const float* b2 = w2_bias ? w2_bias + expert * (int64_t)hidden : NULL;
       for (int j = 0; j < inter; ++j) {
-        const float gate = dot_bf16(xrow, w13_e + (int64_t)j * hidden, hidden);
-        const float up = dot_bf16(xrow, w13_e + (int64_t)(inter + j) * hidden, hidden);
-        y[j] = swiglu_to_bf16(gate, up, swiglu_limit);
+        float gate = dot_bf16(xrow, w13_e + (int64_t)j * hidden, hidden);
+        float up = dot_bf16(xrow, w13_e + (int64_t)(inter + j) * hidden, hidden);
+        if (b13) {
+          gate += b13[j];
+          up += b13[inter + j];
+        }
+        y[j] = activation == 0 ? swiglu_to_bf16(gate, up, swiglu_limit) : other_activation_to_bf16(activation, gate, up);
       }
       const uint16_t* w2_e = w2 + expert * (int64_t)hidden * inter;
-      for (int h = 0; h < hidden; ++h) route_out[route * hidden + h] = dot_bf16(y, w2_e + (int64_t)h * inter, inter);
+      for (int h = 0; h < hidden; ++h) {
+        const float value = dot_bf16(y, w2_e + (int64_t)h * inter, inter);
+        route_out[route * hidden + h] = b2 ? value + b2[h] : value;
+      }
       if (dump_y) memcpy(dump_y + route * inter, y, sizeof(uint16_t) * (size_t)inter);
     }
     free(y);

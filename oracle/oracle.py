@@ -123,8 +123,11 @@ def w8a8_forward(x, w13, s13, w2, s2, topk_w, topk_ids, numerics: int = NUMERICS
     return (out, d) if dumps else out
 
 
-def bf16_forward(x, w13, w2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps: bool = False):
-    """fmoe_oracle_bf16_forward.  Returns out bf16 [T,H] (and {y, route_out} with dumps=True)."""
+def bf16_forward(x, w13, w2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps: bool = False, activation: int = 0,
+                 w13_bias=None, w2_bias=None):
+    """fmoe_oracle_bf16_forward_ex.  Returns out bf16 [T,H] (and {y, route_out} with dumps=True).
+    activation: 0 SiLU (with swiglu_limit), 2 gelu, 3 swigluoai; biases fp32 [E,2I] / [E,H] or None.
+    w13 holds gate rows [0,I) then up rows [I,2I) for every activation."""
     tokens, hidden = x.shape
     experts, two_i, _ = w13.shape
     inter = two_i // 2
@@ -137,10 +140,13 @@ def bf16_forward(x, w13, w2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps:
              "route_out": torch.empty((routes, hidden), dtype=torch.float32)}
     x, w13, w2 = x.contiguous(), w13.contiguous(), w2.contiguous()
     topk_w, topk_ids = topk_w.to(torch.float32).contiguous(), topk_ids.to(torch.int64).contiguous()
-    status = lib().fmoe_oracle_bf16_forward(
+    b13 = None if w13_bias is None else w13_bias.to(torch.float32).reshape(experts, two_i).contiguous()
+    b2 = None if w2_bias is None else w2_bias.to(torch.float32).reshape(experts, hidden).contiguous()
+    status = lib().fmoe_oracle_bf16_forward_ex(
         _ptr(x), _ptr(w13), _ptr(w2), _ptr(topk_w), _ptr(topk_ids),
         ctypes.c_int64(tokens), ctypes.c_int(top_k), ctypes.c_int(experts), ctypes.c_int(hidden), ctypes.c_int(inter),
-        ctypes.c_float(swiglu_limit), _ptr(out), _ptr(d.get("y")), _ptr(d.get("route_out")))
+        ctypes.c_float(swiglu_limit), ctypes.c_int(activation), _ptr(b13), _ptr(b2), _ptr(out), _ptr(d.get("y")),
+        _ptr(d.get("route_out")))
     if status != 0:
         raise ValueError("topk expert id is out of range")
     return (out, d) if dumps else out

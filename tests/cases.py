@@ -64,6 +64,33 @@ def bf16_case(name: str) -> dict:
                                     skew=(name == "ragged"), std=std)
 
 
+# BF16 op variants beyond plain SiLU: (base case, activation of the op, with biases).  For "swigluoai" the case's w13
+# (and w13 bias) is in the checkpoint's interleaved layout (row 2j = gate j, row 2j + 1 = up j), as the reference's
+# naive implementation reads it (src/fused_cpp/moe/naive.py:39-47).
+BF16_VARIANTS = {"bias": ("ragged", "silu", True), "gelu": ("top8", "gelu", False), "gelu_bias": ("tiny", "gelu", True),
+                 "swigluoai": ("tiny", "swigluoai", True)}
+
+
+def bf16_variant_case(name: str) -> dict:
+    base, activation, with_bias = BF16_VARIANTS[name]
+    case = bf16_case(base)
+    case["activation"] = activation
+    experts, two_i, hidden = case["w13"].shape
+    if with_bias:
+        generator = torch.Generator().manual_seed(8800 + sorted(BF16_VARIANTS).index(name))
+        case["w13_bias"] = (torch.randn((experts, two_i), generator=generator) * 0.5).to(torch.bfloat16)
+        case["w2_bias"] = (torch.randn((experts, hidden), generator=generator) * 0.5).to(torch.bfloat16)
+    else:
+        case["w13_bias"] = case["w2_bias"] = None
+    return case
+
+
+def gate_then_up(tensor: torch.Tensor) -> torch.Tensor:
+    """Interleaved gate/up channels along dim 1 -> gate channels then up channels."""
+    count = tensor.shape[1]
+    return tensor.index_select(1, torch.cat((torch.arange(0, count, 2), torch.arange(1, count, 2)))).contiguous()
+
+
 # Dense W8A8 linear cases: (M, K, N, x dtype, out dtype, bias).  The first three are the shapes of the
 # reference's own test (tests/test_i8gemm.py:41-47); the others add tile tails and a larger K.
 I8GEMM_CASES = {

@@ -6,7 +6,7 @@ Run in a container that has the reference checkout:
 
 It imports, unmodified,
   * tests/test_moe_w8a8.py::_quantize_row and ::_reference   (the W8A8 per-token reference), and
-  * src/fused_cpp/moe/naive.py::fused_moe_naive               (the BF16 reference),
+  * src/fused_cpp/moe/naive.py::fused_moe_naive               (the BF16 reference, also with biases, gelu and swigluoai),
   * tests/test_i8gemm.py::_reference_dynamic_scaled_mm        (the dense W8A8 linear reference),
 runs them on seeded inputs from fused_cpp_b200.synthetic (plus the input recipe of the reference's
 own W8A8 test), and stores ONLY their outputs (inputs are regenerated from the seeds by the tests).
@@ -63,6 +63,16 @@ def main() -> None:
         torch.save({"out": out}, os.path.join(HERE, f"bf16_{name}.pt"))
         print("bf16", name, tuple(out.shape))
 
+
+    # BF16 op variants: biases, gelu, swigluoai through the same fused_moe_naive
+    for name in cases.BF16_VARIANTS:
+        case = cases.bf16_variant_case(name)
+        bias13 = None if case["w13_bias"] is None else case["w13_bias"].float()
+        bias2 = None if case["w2_bias"] is None else case["w2_bias"].float()
+        out = fused_moe_naive(case["x"].float(), case["w13"].float(), case["w2"].float(), case["topk_weights"], case["topk_ids"],
+                              w13_bias=bias13, w2_bias=bias2, activation=case["activation"]).to(torch.bfloat16)
+        torch.save({"out": out}, os.path.join(HERE, f"bf16_variant_{name}.pt"))
+        print("bf16 variant", name, tuple(out.shape))
 
     # appended: dense W8A8 linear, tests/test_i8gemm.py::_reference_dynamic_scaled_mm of the reference
     for name in cases.I8GEMM_CASES:

@@ -49,7 +49,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(_lib.LIB_PATH)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.fmoe_abi_version() == 1
+    assert lib.fmoe_abi_version() == 2
 
 
 def test_workspace_layout_needs_no_gpu():

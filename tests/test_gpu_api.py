@@ -2,6 +2,8 @@
 weight quantiser.  Parity is against the CPU oracle (bit-exact for W8A8)."""
 from __future__ import annotations
 
+import os
+
 import pytest
 import torch
 
@@ -119,3 +121,36 @@ def test_forward_rejects_cpu_tensors(cuda_device):
     weights = moe.prepare_fused_moe_bf16_tiled_weights(case["w13"], case["w2"])
     with pytest.raises(ValueError, match="CUDA"):
         moe.fused_moe_bf16_tiled(case["x"], weights, case["topk_weights"], case["topk_ids"])
+
+
+@pytest.mark.parametrize("tile", [0, 512], ids=["auto", "two_sm"])
+@pytest.mark.parametrize("name", sorted(cases.BF16_VARIANTS))
+def test_bf16_op_biases_gelu_and_swigluoai(cuda_device, name, tile):
+    """w13_bias / w2_bias and the gelu / swigluoai activations of the reference's BF16 op
+    (csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:6420-6427, :1911-1936) against the oracle and against the golden
+    output of fused_moe_naive with the same arguments; swigluoai weights arrive interleaved, as in a checkpoint."""
+    from tests.test_oracle_golden import oracle_variant
+
+    case = cases.bf16_variant_case(name)
+    prepared = moe.prepare_fused_moe_bf16_tiled_weights(case["w13"], case["w2"], fuse_silu=True)
+    plan = moe.plan.gpu_placeholder_plan(tile, tile)
+    out = moe.fused_moe_bf16_tiled_async_plan(case["x"].to(cuda_device), prepared, case["topk_weights"].to(cuda_device),
+                                              case["topk_ids"].to(cuda_device), plan, w13_bias=case["w13_bias"], w2_bias=case["w2_bias"],
+                                              activation=case["activation"]).cpu().float()
+    expected = oracle_variant(case).float()
+    assert float((out - expected).norm() / expected.norm()) <= 5e-3
+    golden = torch.load(os.path.join(os.path.dirname(__file__), "golden", f"bf16_variant_{name}.pt"))["out"].float()
+    assert float((out - golden).norm() / golden.norm()) <= 5e-3
+
+
+def test_bf16_op_global_num_experts_narrows_the_valid_ids(cuda_device):
+    """global_num_experts below the prepared expert count makes the ids beyond it invalid, as in the reference
+    (fused_moe_bf16_tiled.cpp:6439-6458), instead of routing them to the trailing experts."""
+    case = cases.bf16_case("top8")  # 16 experts
+    prepared = moe.prepare_fused_moe_bf16_tiled_weights(case["w13"], case["w2"], fuse_silu=True)
+    x, w, ids = (case[k].to(cuda_device) for k in ("x", "topk_weights", "topk_ids"))
+    assert int(ids.max()) >= 12
+    with pytest.raises(Exception, match="out of range"):
+        moe.fused_moe_bf16_tiled(x, prepared, w, ids, global_num_experts=12)
+    full = moe.fused_moe_bf16_tiled(x, prepared, w, ids, global_num_experts=16)
+    assert torch.equal(full, moe.fused_moe_bf16_tiled(x, prepared, w, ids))

@@ -47,6 +47,30 @@ def test_bf16_oracle_against_fused_moe_naive(name):
     assert float((out - golden).norm() / golden.norm()) <= 5e-3
 
 
+ACTIVATION_IDS = {"silu": 0, "gelu": 2, "swigluoai": 3}
+
+
+def oracle_variant(case):
+    """The oracle on a BF16 variant case (biases, gelu, swigluoai); interleaved swigluoai weights are reordered to
+    gate rows then up rows first, which is what the kernels (and the oracle) take."""
+    w13, b13 = case["w13"], case["w13_bias"]
+    if case["activation"] == "swigluoai":
+        w13 = cases.gate_then_up(w13)
+        b13 = None if b13 is None else cases.gate_then_up(b13)
+    return oracle.bf16_forward(case["x"], w13, case["w2"], case["topk_weights"], case["topk_ids"], activation=ACTIVATION_IDS[case["activation"]],
+                               w13_bias=None if b13 is None else b13.float(), w2_bias=None if case["w2_bias"] is None else case["w2_bias"].float())
+
+
+@pytest.mark.parametrize("name", sorted(cases.BF16_VARIANTS))
+def test_bf16_oracle_variants_against_fused_moe_naive(name):
+    """Biases, gelu and swigluoai of the reference's BF16 op: the oracle against fused_moe_naive with the same
+    arguments (fp32 end to end there, bf16 intermediate here): relative L2 <= 5e-3."""
+    case = cases.bf16_variant_case(name)
+    golden = torch.load(os.path.join(GOLDEN, f"bf16_variant_{name}.pt"))["out"].float()
+    out = oracle_variant(case).float()
+    assert float((out - golden).norm() / golden.norm()) <= 5e-3
+
+
 def test_expneg_tracks_exp():
     for gate in (-20.0, -3.3, -1.0, -1e-3, 0.0, 1e-3, 0.5, 2.0, 9.99, 10.0, 40.0):
         assert oracle.expneg(gate) == pytest.approx(math.exp(-gate), rel=3e-7)
