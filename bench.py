@@ -50,6 +50,8 @@ WORKLOADS = {
     "w8a8_prefill_zipf_v3_T2048": {"kind": "int8", "tokens": 2048, "skew": True},
     # Routed experts plus one always-active shared expert (expert id E, route K, weight 1).
     "w8a8_ep_shared_v3_T16384": {"kind": "int8", "tokens": 16384, "shared": True},
+    # int8 weights, unquantised bf16 activations: the W8A8 layer's weights through the W8A16 entry point.
+    "w8a16_decode_v3_T64": {"kind": "w8a16", "tokens": 64},
     "bf16_decode_v3_T64": {"kind": "bf16", "tokens": 64},
     "bf16_decode_v3_T32": {"kind": "bf16", "tokens": 32},
     "bf16_decode_v3_T8": {"kind": "bf16", "tokens": 8},
@@ -62,7 +64,7 @@ WORKLOADS = {
     "w8a8_small_zipf_T8192": {"kind": "int8", "tokens": 8192, "skew": True, "dims": SMALL},
 }
 DEFAULT_WORKLOAD = "w8a8_decode_v3_T64"
-EXTRA_POINTS = ["w8a8_prefill_v3_T8192", "w8a8_prefill_zipf_v3_T8192", "w8a8_ep_shared_v3_T16384", "bf16_decode_v3_T64",
+EXTRA_POINTS = ["w8a8_prefill_v3_T8192", "w8a8_prefill_zipf_v3_T8192", "w8a8_ep_shared_v3_T16384", "w8a16_decode_v3_T64", "bf16_decode_v3_T64",
                 "bf16_decode_v3_T32", "bf16_decode_v3_T8", "bf16_decode_v3_T1", "w8a8_small_T16", "w8a8_small_zipf_T8192"]
 EP_POINTS = ["w8a8_ep_shared_v3_T16384", "w8a8_ep_shared_v3_T16384:bf16_return", "bf16_decode_v3_T64"]
 SWEEP_TOKENS = (1, 8, 64, 512, 4096, 16384)
@@ -74,6 +76,14 @@ NOMINAL = {"hbm_gbs": 7700.0, "int8_tops": 4500.0, "bf16_tflops": 2250.0}
 
 def dims_of(spec: dict) -> dict:
     return dict(spec.get("dims", V3))
+
+
+DTYPE_LABEL = {"int8": "int8(w8a8)", "bf16": "bf16", "w8a16": "bf16 x int8 weights (w8a16)"}
+
+
+def weight_kind(kind: str) -> str:
+    """Storage type of the expert weights of a workload kind."""
+    return "bf16" if kind == "bf16" else "int8"
 
 
 def sweep_spec(kind: str, tokens: int, skew: bool) -> tuple[str, dict]:
@@ -317,7 +327,7 @@ def layer_work(spec: dict, topk_ids: torch.Tensor) -> dict:
 
     d = dims_of(spec)
     shape = synthetic.MoEShape(tokens=spec["tokens"], hidden=d["hidden"], inter=d["inter"], experts=d["experts"], top_k=d["top_k"])
-    return synthetic.algorithmic_work(shape, topk_ids, 1 if spec["kind"] == "int8" else 2, shared=bool(spec.get("shared", False)))
+    return synthetic.algorithmic_work(shape, topk_ids, 2 if spec["kind"] == "bf16" else 1, shared=bool(spec.get("shared", False)))
 
 
 def gate_up_work(spec: dict, active: int) -> tuple[float, float]:
@@ -325,11 +335,12 @@ def gate_up_work(spec: dict, active: int) -> tuple[float, float]:
     sorted activation rows in, the bf16 SwiGLU rows out; 2 * rows * 2I * H operations."""
     d = dims_of(spec)
     h, i = d["hidden"], d["inter"]
-    b = 1 if spec["kind"] == "int8" else 2
+    b = 2 if spec["kind"] == "bf16" else 1           # weight bytes
+    a = 1 if spec["kind"] == "int8" else 2           # bytes of an activation element entering the GEMM
     rows = spec["tokens"] * (d["top_k"] + (1 if spec.get("shared") else 0))
-    total = active * 2 * i * h * b + rows * h * b + rows * i * 2
-    if spec["kind"] == "int8":
-        total += active * 2 * i * 4 + rows * 4
+    total = active * 2 * i * h * b + rows * h * a + rows * i * 2
+    if spec["kind"] != "bf16":
+        total += active * 2 * i * 4 + (rows * 4 if spec["kind"] == "int8" else 0)
     return float(total), 2.0 * rows * 2 * i * h
 
 
@@ -456,7 +467,8 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
     timer = _lib.StageTimer(steps)
 
     def step(stage_timer=None):
-        return _lib.moe_forward(x, weights["w13"], weights["w2"], tw_run, ids_run, s13=weights["s13"], s2=weights["s2"], stage_timer=stage_timer)
+        return _lib.moe_forward(x, weights["w13"], weights["w2"], tw_run, ids_run, s13=weights["s13"], s2=weights["s2"], stage_timer=stage_timer,
+                                w8a16=kind == "w8a16")
 
     for _ in range(warmup):
         step()
@@ -485,7 +497,7 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
     gu_bytes, gu_ops = gate_up_work(spec, work["active_experts"])
     routes = tokens * (top_k + (1 if shared else 0))
     point = {
-        "workload": name, "tokens": tokens, "dtype": "bf16" if kind == "bf16" else "int8(w8a8)", "ms_per_step": ms_per_step,
+        "workload": name, "tokens": tokens, "dtype": DTYPE_LABEL[kind], "ms_per_step": ms_per_step,
         "launch_mode": "cuda_graph_replay" if graph is not None else "eager", "eager_ms_per_step": eager_ms_per_step,
         "l2": "flushed between steps (a buffer of twice the L2 is written)" if flush is not None else "inputs larger than L2",
         "value": tokens / (ms_per_step * 1e-3), "active_experts": work["active_experts"],
@@ -501,7 +513,11 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
 
     if with_e2e:
         # Public API, host buffers: H2D of x / top-k weights / ids, the op (with its status check), D2H of out.
-        if kind == "int8":
+        if kind == "w8a16":
+            holder = moe.PreparedW8A16TiledFusedMoEWeights(w13=(weights["w13"], hidden, 2 * inter, weights["s13"]),
+                                                           w2=(weights["w2"], inter, hidden, weights["s2"]))
+            prepared = moe.PreparedW8A16TiledRoutedSharedMoEWeights(packed=holder, routed_experts=experts, shared_expert_id=experts) if shared else holder
+        elif kind == "int8":
             holder = moe.PreparedW8A8TiledFusedMoEWeights(w13=(weights["w13"], hidden, 2 * inter, weights["s13"]),
                                                           w2=(weights["w2"], inter, hidden, weights["s2"]))
             prepared = moe.PreparedW8A8TiledRoutedSharedMoEWeights(packed=holder, routed_experts=experts, shared_expert_id=experts) if shared else holder
@@ -523,7 +539,8 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
                 idd = ids_pin.to(device, non_blocking=True)
                 kwargs = {"swiglu_limit": 10.0} if kind == "int8" else {}
                 if shared:
-                    op = moe.fused_moe_w8a8_tiled_with_shared if kind == "int8" else moe.fused_moe_bf16_tiled_with_shared
+                    op = {"int8": moe.fused_moe_w8a8_tiled_with_shared, "w8a16": moe.fused_moe_w8a16_tiled_with_shared,
+                          "bf16": moe.fused_moe_bf16_tiled_with_shared}[kind]
                     op(xd, prepared, wd, idd, out=out_dev, **kwargs)
                 else:
                     moe.fused_moe_tiled(xd, prepared, wd, idd, out=out_dev, **kwargs)
@@ -562,7 +579,7 @@ def cpu_inputs(spec: dict, layer: dict | None):
     remap = torch.full((experts + 1,), -1, dtype=torch.int64)
     remap[hit] = torch.arange(hit.numel())
     local_ids = remap[ids]
-    kind = spec["kind"]
+    kind = weight_kind(spec["kind"])
     if layer is not None:
         index = hit.to(layer["w13"].device)
         weights = {k: (None if v is None else v.index_select(0, index).cpu()) for k, v in layer.items()}
@@ -597,6 +614,8 @@ def time_cpu_port(name: str, spec: dict, layer: dict | None, warmup: int, passes
         begin = time.perf_counter()
         if spec["kind"] == "int8":
             oracle.w8a8_forward(x, weights["w13"], weights["s13"], weights["w2"], weights["s2"], tw, ids)
+        elif spec["kind"] == "w8a16":
+            oracle.w8a16_forward(x, weights["w13"], weights["s13"], weights["w2"], weights["s2"], tw, ids)
         else:
             oracle.bf16_forward(x, weights["w13"], weights["w2"], tw, ids)
         return time.perf_counter() - begin
@@ -626,7 +645,7 @@ def run_reference_arm(args) -> None:
     value = baseline["value"]
     line = {"impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if spec["kind"] == "bf16" else "int8(w8a8)",
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_LABEL[spec["kind"]],
             "data": "synthetic", "config": public_config(args.workload, spec, args.gpus),
             "note": "the reference's native kernels are AArch64 SVE/I8MM only; this arm times the CPU port of the same arithmetic "
                     "(oracle/moe_oracle.c) on the host cores, every step the workload's whole batch",
@@ -646,9 +665,9 @@ class LayerCache:
 
     def get(self, spec: dict) -> dict:
         d = dims_of(spec)
-        key = (spec["kind"], d["hidden"], d["inter"], d["experts"])
+        key = (weight_kind(spec["kind"]), d["hidden"], d["inter"], d["experts"])
         if key not in self.layers:
-            self.layers[key] = make_experts(spec["kind"], self.device, SEED + 2, range(d["experts"] + 1), d["hidden"], d["inter"])
+            self.layers[key] = make_experts(key[0], self.device, SEED + 2, range(d["experts"] + 1), d["hidden"], d["inter"])
         return self.layers[key]
 
     def drop(self) -> None:

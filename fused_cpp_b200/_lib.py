@@ -35,7 +35,7 @@ DIAG_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", 
 EXPORTS = (
     "fmoe_abi_version", "fmoe_last_error", "fmoe_device_supported", "fmoe_read_status",
     "fmoe_w8a8_workspace_layout", "fmoe_w8a8_forward", "fmoe_quantize_weight_rows", "fmoe_quantize_rows",
-    "fmoe_bf16_workspace_layout", "fmoe_bf16_forward", "fmoe_i8gemm_workspace_bytes", "fmoe_i8gemm_dynamic_scaled_mm",
+    "fmoe_bf16_workspace_layout", "fmoe_bf16_forward", "fmoe_w8a16_forward", "fmoe_i8gemm_workspace_bytes", "fmoe_i8gemm_dynamic_scaled_mm",
     "fmoe_stage_timer_create", "fmoe_stage_timer_destroy", "fmoe_stage_timer_reset", "fmoe_stage_timer_calls",
     "fmoe_stage_timer_read", "fmoe_route_build_noalloc", "fmoe_ep_dispatch_workspace_bytes", "fmoe_ep_dispatch_prepare",
     "fmoe_w8a8_expert_rows_forward", "fmoe_bf16_expert_rows_forward", "fmoe_ep_combine_finish",
@@ -109,6 +109,7 @@ def _open(path: str) -> ctypes.CDLL:
                                       ctypes.c_size_t, p]
     lib.fmoe_bf16_forward.argtypes = [p, p, p, p, p, i64, i32, i32, i32, i32, ctypes.POINTER(Config), p, p,
                                       ctypes.c_size_t, p]
+    lib.fmoe_w8a16_forward.argtypes = lib.fmoe_w8a8_forward.argtypes
     lib.fmoe_quantize_weight_rows.argtypes = [p, i64, i32, p, p, p]
     lib.fmoe_quantize_rows.argtypes = [p, i64, i32, i32, p, p, p]
     lib.fmoe_stage_timer_create.argtypes = [i32, ctypes.POINTER(ctypes.c_void_p)]
@@ -276,20 +277,24 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
                 gemm_impl: int = GEMM_AUTO, gate_up_tile: int = 0, down_tile: int = 0, swiglu_limit: float | None = None,
                 out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None,
                 stage_timer: "StageTimer | None" = None, diagnostic: bool = False, activation: int = ACTIVATION_SILU,
-                w13_bias: torch.Tensor | None = None, w2_bias: torch.Tensor | None = None) -> ForwardResult:
-    """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8.
+                w13_bias: torch.Tensor | None = None, w2_bias: torch.Tensor | None = None, w8a16: bool = False) -> ForwardResult:
+    """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8, or, with
+    w8a16=True, the W8A16 path (bf16 activations are not quantised).
     diagnostic=True (or gemm_impl=GEMM_SIMT) runs the call in the diagnostic library instead of the product one."""
-    int8 = w13.dtype == torch.int8
+    quantised_weights = w13.dtype == torch.int8
+    if w8a16 and not quantised_weights:
+        raise TypeError("w8a16 needs int8 weights with s13 / s2")
+    int8 = quantised_weights and not w8a16
     x = _require_cuda("input", x, torch.bfloat16)
-    w13 = _require_cuda("w13", w13, torch.int8 if int8 else torch.bfloat16)
-    w2 = _require_cuda("w2", w2, torch.int8 if int8 else torch.bfloat16)
+    w13 = _require_cuda("w13", w13, torch.int8 if quantised_weights else torch.bfloat16)
+    w2 = _require_cuda("w2", w2, torch.int8 if quantised_weights else torch.bfloat16)
     topk_weights = _require_cuda("topk_weights", topk_weights, torch.float32)
     topk_ids = _require_cuda("topk_ids", topk_ids, torch.int64)
     tokens, hidden = x.shape
     experts, two_i, _ = w13.shape
     inter = two_i // 2
     top_k = topk_ids.shape[1]
-    if int8:
+    if quantised_weights:
         s13 = _require_cuda("w13_scale", s13, torch.float32)
         s2 = _require_cuda("w2_scale", s2, torch.float32)
     if out is None:
@@ -328,10 +333,11 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
         config.dump_acc2 = acc2.data_ptr()
     # The CUDA-core cross-check and the stage switches exist only in the diagnostic library.
     lib = load_diag() if (gemm_impl == GEMM_SIMT or diagnostic) else load()
-    if int8:
-        code = lib.fmoe_w8a8_forward(_ptr(x), _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2), _ptr(topk_weights), _ptr(topk_ids),
-                                     tokens, top_k, experts, hidden, inter, ctypes.byref(config), _ptr(out),
-                                     _ptr(workspace), workspace.numel(), _stream())
+    if quantised_weights:
+        entry = lib.fmoe_w8a16_forward if w8a16 else lib.fmoe_w8a8_forward
+        code = entry(_ptr(x), _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2), _ptr(topk_weights), _ptr(topk_ids),
+                     tokens, top_k, experts, hidden, inter, ctypes.byref(config), _ptr(out),
+                     _ptr(workspace), workspace.numel(), _stream())
     else:
         code = lib.fmoe_bf16_forward(_ptr(x), _ptr(w13), _ptr(w2), _ptr(topk_weights), _ptr(topk_ids), tokens, top_k,
                                      experts, hidden, inter, ctypes.byref(config), _ptr(out), _ptr(workspace),

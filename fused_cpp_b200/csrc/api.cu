@@ -141,6 +141,9 @@ struct Forward {
   const void* rows_source = nullptr;
   const uint64_t* peer_slabs = nullptr;
   size_t peer_route_out_offset = 0;
+  // W8A16: int8 weights with per-output-channel scales s13 / s2, bf16 activations (int8 = false: no activation
+  // quantisation, the BF16 workspace and merge).
+  bool w8a16 = false;
   bool peer_rows_bf16 = false;  // result rows travel as bf16 (opt-in, not bit-identical to the fp32 merge input)
   // Bounds of a valid return address (source rank < peer_world, flat route < peer_routes_max) and the local row
   // that takes the stores of a row whose return address is not valid.
@@ -173,7 +176,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (f.rows_mode && ((f.route_out_override == nullptr && !peer) || (f.int8 && f.rows_scale == nullptr) || f.top_k != 1)) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "expert-rows mode needs route_out, row scales (int8) and one route per row");
   }
-  if (f.int8 && (f.s13 == nullptr || f.s2 == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null scale pointer");
+  if ((f.int8 || f.w8a16) && (f.s13 == nullptr || f.s2 == nullptr)) return fail(FMOE_ERR_INVALID_ARGUMENT, "null scale pointer");
   if (workspace == nullptr || workspace_bytes < layout.total_bytes) {
     return fail(FMOE_ERR_WORKSPACE, "workspace too small: %zu bytes given, %zu needed", workspace_bytes, layout.total_bytes);
   }
@@ -199,6 +202,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (f.int8 && (cfg.activation != FMOE_ACTIVATION_SILU || cfg.w13_bias != nullptr || cfg.w2_bias != nullptr)) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "W8A8 supports only the clamped SiLU activation and no w13_bias / w2_bias");
   }
+  if (f.w8a16 && (cfg.w13_bias != nullptr || cfg.w2_bias != nullptr)) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "W8A16 takes no w13_bias / w2_bias");
+  }
   if (cfg.activation != FMOE_ACTIVATION_SILU && cfg.swiglu_limit != 0.0f) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "swiglu_limit is only valid with the SiLU activation");
   }
@@ -222,9 +228,12 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   // go through the one-SM kernel (64-row tile, every weight byte streamed once), the others through the
   // two-SM kernel (256-row work items).  Up to 64 tokens no expert can exceed 64 rows and the tile follows
   // the batch size (pick_row_tile).
-  const bool split = umma && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
-  const int tile_gu = split ? kSplitRows : pick_row_tile(cfg.gate_up_tile, f.tokens, umma);
-  const int tile_dn = split ? kSplitRows : pick_row_tile(cfg.down_tile, f.tokens, umma);
+  // W8A16 runs every expert through the one-SM kernel (the int8 -> bf16 widening lives there): no split, and a
+  // 128-row tile above 64 tokens.
+  const bool split = umma && !f.w8a16 && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
+  const bool w8a16_wide = f.w8a16 && f.tokens > kSplitRows;
+  const int tile_gu = split ? kSplitRows : (w8a16_wide && cfg.gate_up_tile == 0) ? 128 : pick_row_tile(cfg.gate_up_tile, f.tokens, umma);
+  const int tile_dn = split ? kSplitRows : (w8a16_wide && cfg.down_tile == 0) ? 128 : pick_row_tile(cfg.down_tile, f.tokens, umma);
   if (umma && (!fmoe::umma_row_tile_supported(tile_gu) || !fmoe::umma_row_tile_supported(tile_dn))) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128, 256 or 512 = two-SM pairs (got %d, %d)", tile_gu, tile_dn);
   }
@@ -319,6 +328,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.k = f.hidden;
   gu.n_out = f.inter;
   gu.numerics = cfg.numerics;
+  gu.w8a16 = f.w8a16 ? 1 : 0;
   gu.swiglu_limit = cfg.swiglu_limit;
   gu.activation = cfg.activation;
   gu.expert_bias = cfg.w13_bias;
@@ -504,6 +514,17 @@ int fmoe_bf16_forward(const void* x, const void* w13, const void* w2, const floa
                       int32_t inter, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes,
                       void* stream) {
   const Forward f{false, x, w13, nullptr, w2, nullptr, topk_weights, topk_ids, tokens, top_k, experts, hidden, inter};
+  return run_forward(f, config, out, workspace, workspace_bytes, stream);
+}
+
+int fmoe_w8a16_forward(const void* x, const int8_t* w13, const float* s13, const int8_t* w2, const float* s2, const float* topk_weights,
+                       const int64_t* topk_ids, int64_t tokens, int32_t top_k, int32_t experts, int32_t hidden, int32_t inter,
+                       const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes, void* stream) {
+  Forward f{false, x, w13, s13, w2, s2, topk_weights, topk_ids, tokens, top_k, experts, hidden, inter};
+  f.w8a16 = true;
+#ifdef FMOE_DIAG
+  if (config != nullptr && config->gemm_impl == FMOE_GEMM_SIMT) return fail(FMOE_ERR_INVALID_ARGUMENT, "W8A16 runs on the tensor-core GEMM only");
+#endif
   return run_forward(f, config, out, workspace, workspace_bytes, stream);
 }
 

@@ -150,6 +150,7 @@ struct GroupedGemmArgs {
   // activation of the gate_up epilogue: FMOE_ACT_SILU (with swiglu_limit), FMOE_ACT_GELU, FMOE_ACT_SWIGLUOAI.
   const float* expert_bias;
   int activation;
+  int w8a16;                 // weights are int8 with w_scale, activations bf16 (one-SM kernel widens the tile to bf16)
   int gate_up_one_box;       // two-SM gate_up: the weight rows of a stage arrive as one 16 KB TMA box (set by the launcher)
   int route_out_bf16;        // with row_out_ptrs: the result rows are stored as bf16 (2 bytes per channel) instead of fp32
   // Diagnostic build only (compiled with -DFMOE_DIAG, the separate libfused_moe_b200_diag.so; the product library

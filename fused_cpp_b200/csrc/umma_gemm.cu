@@ -22,6 +22,11 @@
 //   warp 1      allocates TMEM, issues tcgen05.mma (one thread), commits to the stage's "empty"
 //               barrier and, per work unit, to the accumulator's "full" barrier;
 //   warps 2..5  epilogue: tcgen05.ld their 32-lane TMEM quarter, apply the epilogue, store.
+// W8A16 (int8 weights, bf16 activations; the reference's fused_moe_w8a16_* ops, csrc/moe/arm/common/
+// fused_moe_bf16_tiled.cpp:4916-5000, 8740-8760): the weight tile arrives as int8 (half the HBM bytes of bf16) in a
+// landing area of the stage, eight more warps (6..13) widen it to bf16 -- exact, |q| <= 128 -- into the 128-byte
+// swizzled operand tile the kind::f16 MMA reads, and the epilogue multiplies by the per-output-channel scale in
+// fp32.  Everything else is the BF16 instance of this kernel.
 // Accumulators are double-buffered in TMEM when two buffers fit in 512 columns, so the epilogue of
 // one unit overlaps the main loop of the next.  No load uses cluster multicast; weight-tile reuse
 // between row tiles of one expert comes from L2 (adjacent work items run concurrently).
@@ -41,23 +46,52 @@ constexpr int kBlockKBytes = 128;   // bytes of K per pipeline stage = one 128-b
 constexpr int kUmmaKBytes = 32;     // bytes of K per tcgen05.mma
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarp0 = 2;
+constexpr int kConvertWarp0 = 6;          // W8A16: warps 6.. widen the int8 weight tile to bf16
+#ifndef FMOE_W8A16_CONVERT_WARPS
+#define FMOE_W8A16_CONVERT_WARPS 8
+#endif
+#ifndef FMOE_W8A16_STAGES
+#define FMOE_W8A16_STAGES 2
+#endif
+constexpr int kConvertWarps = FMOE_W8A16_CONVERT_WARPS;
+constexpr int kThreadsW8A16 = kThreads + kConvertWarps * 32;
+constexpr int kLandingRowBytes = 64;      // W8A16: one K block = 64 weights = 64 int8 bytes per channel row
 constexpr int kSmemBudget = 216 * 1024;  // operand stages; with the control block and alignment slack 224 KB of the 227 KB a CTA may have
 
-template <bool kGateUp, int kRowTile>
+// W8A16: the most operand stages (up to `wanted`) that still leave three landing slots in the budget.
+constexpr int w8a16_stages(int wanted, int stage_bytes, int landing_bytes, int budget) {
+  int stages = wanted;
+  while (stages > 2 && (budget - stages * stage_bytes) / landing_bytes < 3) --stages;
+  return stages;
+}
+
+template <bool kGateUp, int kRowTile, bool kW8A16 = false>
 struct TileConfig {
   static constexpr int kWeightTiles = kGateUp ? 2 : 1;
   static constexpr int kWeightBytes = kWeightTiles * kBlockM * kBlockKBytes;
   static constexpr int kTokenBytes = kRowTile * kBlockKBytes;
-  static constexpr int kStageBytes = kWeightBytes + kTokenBytes;
-  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  // W8A16: what arrives from HBM per K block -- the token tile (MMA-ready) and the int8 weight tiles -- lands in a ring
+  // of its own (kLandingSlots slots: [token tile | int8 weights]) that runs as far ahead of the MMAs as shared memory
+  // allows, since those are the bytes in flight that have to cover the memory latency.  An operand stage then only
+  // holds the widened bf16 weight tile; a few stages suffice (widen one while the MMAs read another).
+  static constexpr int kStageBytes = kW8A16 ? kWeightBytes : kWeightBytes + kTokenBytes;
+  static constexpr int kInt8TileBytes = kWeightTiles * kBlockM * kLandingRowBytes;
+  static constexpr int kLandingBytes = kW8A16 ? kTokenBytes + kInt8TileBytes : 0;
+  static constexpr int kStagesRaw = kW8A16 ? w8a16_stages(FMOE_W8A16_STAGES, kStageBytes, kTokenBytes + kInt8TileBytes, kSmemBudget)
+                                            : kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kLandingSlotsRaw = kW8A16 ? (kSmemBudget - kStages * kStageBytes) / kLandingBytes : 0;
+  static constexpr int kLandingSlots = kLandingSlotsRaw > 8 ? 8 : kLandingSlotsRaw;
+  static constexpr int kLandingOffset = kStages * kStageBytes;  // the landing ring follows the operand stages
   static constexpr int kAccColumns = kWeightTiles * kRowTile;
   static constexpr int kAccBuffers = (2 * kAccColumns <= 512) ? 2 : 1;
   static constexpr int kTmemColumnsRaw = kAccBuffers * kAccColumns;
   static constexpr int kTmemColumns = kTmemColumnsRaw <= 32 ? 32 : kTmemColumnsRaw <= 64 ? 64 : kTmemColumnsRaw <= 128 ? 128
                                       : kTmemColumnsRaw <= 256 ? 256 : 512;
-  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes + 7168 /*control block*/;
+  static constexpr int kOperandBytes = kStages * kStageBytes + kLandingSlots * kLandingBytes;
+  static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kOperandBytes) + 7168 /*control block*/;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
+  static_assert(!kW8A16 || kLandingSlots >= 2, "W8A16 needs at least two landing slots");
   static_assert(kAccColumns <= 512, "accumulator does not fit tensor memory");
 };
 
@@ -71,6 +105,8 @@ struct ColumnMeta {
 struct SmemControl {
   uint64_t full[8];
   uint64_t empty[8];
+  uint64_t landed[8];        // W8A16: the int8 weight tile of a landing slot has arrived
+  uint64_t landing_free[8];  // W8A16: every converter warp has read the slot
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -81,17 +117,32 @@ struct SmemControl {
 
 static_assert(sizeof(SmemControl) <= 7168, "control block exceeds its shared-memory reservation");
 
-template <bool kInt8, bool kGateUp, int kRowTile, bool kDense>
-__global__ void __launch_bounds__(kThreads, 1)
+// Four int8 values (one 32-bit word) -> four bf16 values, exactly.  byte ^ 0x80 is the value + 128 as an unsigned
+// byte; placed in the low mantissa bits of 2^23 it makes the float 2^23 + 128 + value, and subtracting 2^23 + 128
+// leaves the value itself, whose upper 16 bits are its bf16 form (|value| <= 128 has at most 8 significant bits).
+__device__ __forceinline__ void widen_int8x4(uint32_t word, uint32_t* low_pair, uint32_t* high_pair) {
+  const uint32_t biased = word ^ 0x80808080u;
+  const float magic = 8388736.0f;  // 2^23 + 128
+  const float f0 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7540)), magic);
+  const float f1 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7541)), magic);
+  const float f2 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7542)), magic);
+  const float f3 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7543)), magic);
+  *low_pair = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+  *high_pair = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+}
+
+template <bool kInt8, bool kGateUp, int kRowTile, bool kDense, bool kW8A16 = false>
+__global__ void __launch_bounds__(kW8A16 ? kThreadsW8A16 : kThreads, 1)
 umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap token_map,
                          GroupedGemmArgs args) {
-  using Cfg = TileConfig<kGateUp, kRowTile>;
+  static_assert(!kW8A16 || (!kInt8 && !kDense), "W8A16 is an instance of the bf16 grouped kernel");
+  using Cfg = TileConfig<kGateUp, kRowTile, kW8A16>;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  SmemControl* ctl = reinterpret_cast<SmemControl*>(smem + static_cast<size_t>(Cfg::kStages) * Cfg::kStageBytes);
+  SmemControl* ctl = reinterpret_cast<SmemControl*>(smem + static_cast<size_t>(Cfg::kOperandBytes));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -105,8 +156,13 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
-      ptx::mbar_init(&ctl->full[s], 1);
+      // W8A16: an operand stage is full when every converter warp has written its share of the bf16 weight tile.
+      ptx::mbar_init(&ctl->full[s], kW8A16 ? kConvertWarps : 1);
       ptx::mbar_init(&ctl->empty[s], 1);
+    }
+    for (int s = 0; s < 8; ++s) {
+      ptx::mbar_init(&ctl->landed[s], 1);
+      ptx::mbar_init(&ctl->landing_free[s], kConvertWarps + 1);  // the converter warps read the int8 tile, the MMAs the token tile
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&ctl->acc_full[b], 1);
@@ -134,7 +190,50 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
-      for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      if constexpr (kW8A16) {
+        // Landing producer: the token tile and the int8 weight tiles of every K block into the landing ring, as far
+        // ahead as the ring allows.
+        int slot = 0;
+        uint32_t slot_phase = 0;
+        int landed_issued = 0;
+        for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+          int item, block;
+          decode_unit(args.items, unit, n_blocks, &item, &block);
+          const int weight_row = args.items[4 * item + 0] * n_total + block * kBlockM;
+          const int row0 = args.items[4 * item + 1];
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            ptx::mbar_wait(&ctl->landing_free[slot], slot_phase ^ 1u, abort_flag, status, 6);
+            uint8_t* landing = smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes;
+            const int x = kb * kBlockKElems;
+            ptx::mbar_arrive_expect_tx(&ctl->landed[slot], Cfg::kLandingBytes);
+            ptx::tma_load_2d(landing, &token_map, &ctl->landed[slot], x, row0);
+            ptx::tma_load_2d(landing + Cfg::kTokenBytes, &weight_map, &ctl->landed[slot], x, weight_row);
+            if (kGateUp) {
+              ptx::tma_load_2d(landing + Cfg::kTokenBytes + kBlockM * kLandingRowBytes, &weight_map, &ctl->landed[slot], x, weight_row + args.n_out);
+            }
+            ++landed_issued;
+            if (++slot == Cfg::kLandingSlots) {
+              slot = 0;
+              slot_phase ^= 1u;
+            }
+          }
+        }
+        // Drain (matters only after an abort): the loads issued last must have landed before the CTA exits.
+        const int outstanding = landed_issued < Cfg::kLandingSlots ? landed_issued : Cfg::kLandingSlots;
+        for (int back = 0; back < outstanding; ++back) {
+          int sl = slot - 1 - back;
+          uint32_t p = slot_phase;
+          if (sl < 0) {
+            sl += Cfg::kLandingSlots;
+            p ^= 1u;
+          }
+          const unsigned long long start = ptx::global_timer_ns();
+          while (!ptx::mbar_try_wait(&ctl->landed[sl], p)) {
+            if (ptx::global_timer_ns() - start > ptx::kWaitLimitNs) break;
+          }
+        }
+      }
+      for (int64_t unit = blockIdx.x; !kW8A16 && unit < units; unit += gridDim.x) {
         int item, block;
         decode_unit(args.items, unit, n_blocks, &item, &block);
         const int n0 = block * kBlockM;
@@ -176,11 +275,71 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         }
       }
     }
+  } else if (kW8A16 && warp >= kConvertWarp0) {
+    // ---------------- W8A16: widen the landed int8 weight tiles into the MMA's bf16 operand tiles ----------------
+    // Per K block: wait until the operand stage is free (the MMAs that read it have completed) and the int8 tile has
+    // landed; widen.
+    // A row's 16-byte bf16 chunks go to the 128-byte-swizzled position the MMA descriptor expects (chunk index
+    // XOR row mod 8).
+    const int converter = static_cast<int>(threadIdx.x) - kConvertWarp0 * 32;
+    constexpr int kUnits = Cfg::kWeightTiles * kBlockM * 4;  // 16-byte units of the int8 tile
+    int stage = 0, slot = 0;
+    uint32_t phase = 0, slot_phase = 0;
+    for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
+        uint8_t* stage_base = smem + static_cast<size_t>(stage) * Cfg::kStageBytes;
+        ptx::mbar_wait(&ctl->landed[slot], slot_phase, abort_flag, status, 5);
+        const uint8_t* landing = smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes + Cfg::kTokenBytes;
+        if (!FMOE_DIAG_BIT(args, 8)) {
+          // Consecutive threads take consecutive 16-byte units (16 weights) of the landing slot: conflict-free
+          // loads; the two 16-byte bf16 chunks of a unit go to swizzled positions that are conflict-free as well.
+          uint4 packed[(kUnits + kConvertWarps * 32 - 1) / (kConvertWarps * 32)];
+#pragma unroll
+          for (int i = 0; i < static_cast<int>(sizeof(packed) / sizeof(packed[0])); ++i) {
+            const int unit16 = converter + i * kConvertWarps * 32;
+            if (unit16 < kUnits) packed[i] = reinterpret_cast<const uint4*>(landing)[unit16];
+          }
+#pragma unroll
+          for (int i = 0; i < static_cast<int>(sizeof(packed) / sizeof(packed[0])); ++i) {
+            const int unit16 = converter + i * kConvertWarps * 32;
+            if (unit16 < kUnits) {
+              const int row = unit16 >> 2;  // 0..127 gate (or the only) tile, 128..255 up tile: the tiles are contiguous
+              const int chunk = (unit16 & 3) * 2;
+              uint4 first, second;
+              widen_int8x4(packed[i].x, &first.x, &first.y);
+              widen_int8x4(packed[i].y, &first.z, &first.w);
+              widen_int8x4(packed[i].z, &second.x, &second.y);
+              widen_int8x4(packed[i].w, &second.z, &second.w);
+              uint8_t* out_row = stage_base + row * kBlockKBytes;
+              *reinterpret_cast<uint4*>(out_row + ((chunk ^ (row & 7)) << 4)) = first;
+              *reinterpret_cast<uint4*>(out_row + (((chunk + 1) ^ (row & 7)) << 4)) = second;
+            }
+          }
+        }
+        // Generic-proxy writes must be visible to the tensor core's (async proxy) reads before the arrival.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(&ctl->full[stage]);
+          ptx::mbar_arrive(&ctl->landing_free[slot]);
+        }
+        if (++stage == Cfg::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (++slot == Cfg::kLandingSlots) {
+          slot = 0;
+          slot_phase ^= 1u;
+        }
+      }
+    }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int slot = 0;  // W8A16: landing slot of the K block (its token tile is the MMA's B operand)
       int local = 0;
       for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
         const int buffer = local % Cfg::kAccBuffers;
@@ -199,11 +358,14 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
           ptx::mbar_wait(&ctl->full[stage], phase, abort_flag, status, 3);
           ptx::tcgen05_fence_after();
           const uint32_t stage_addr = ptx::smem_u32(smem + static_cast<size_t>(stage) * Cfg::kStageBytes);
+          // Token tile: behind the weight tile(s) of the stage, or (W8A16) at the head of the K block's landing slot.
+          const uint32_t token_addr = kW8A16 ? ptx::smem_u32(smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes)
+                                             : stage_addr + Cfg::kWeightBytes;
 #pragma unroll
           for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
             if (FMOE_DIAG_BIT(args, 4)) break;
             const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
-            const uint64_t desc_tok = ptx::make_smem_desc_sw128(stage_addr + Cfg::kWeightBytes + ks * kUmmaKBytes);
+            const uint64_t desc_tok = ptx::make_smem_desc_sw128(token_addr + ks * kUmmaKBytes);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
             ptx::umma_ss<kInt8>(acc, desc_gate, desc_tok, idesc, accumulate);
             if (kGateUp) {
@@ -212,6 +374,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
             }
           }
           ptx::tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs have read it
+          if constexpr (kW8A16) {
+            ptx::tcgen05_commit(&ctl->landing_free[slot]);  // ... and, with the converter warps' arrivals, the landing slot
+            if (++slot == Cfg::kLandingSlots) slot = 0;
+          }
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -253,7 +419,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         }
       }
       float scale_gate = 1.0f, scale_up = 1.0f;
-      if (kInt8 && channel_ok) {
+      if ((kInt8 || kW8A16) && channel_ok) {
         const float* s = args.w_scale + static_cast<int64_t>(expert) * n_total;
         scale_gate = s[n];
         if (kGateUp) scale_up = s[n + n_out];
@@ -291,6 +457,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                   const float a = meta->scale[c0 + j];
                   gate = dequantize(static_cast<int>(gate_bits[j]), a, scale_gate, numerics);
                   up = dequantize(static_cast<int>(up_bits[j]), a, scale_up, numerics);
+                } else if constexpr (kW8A16) {
+                  gate = __fmul_rn(__uint_as_float(gate_bits[j]), scale_gate);
+                  up = __fmul_rn(__uint_as_float(up_bits[j]), scale_up);
                 } else {
                   gate = __fadd_rn(__uint_as_float(gate_bits[j]), bias_gate);
                   up = __fadd_rn(__uint_as_float(up_bits[j]), bias_up);
@@ -302,6 +471,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                 float value;
                 if constexpr (kInt8) {
                   value = dequantize(static_cast<int>(gate_bits[j]), meta->scale[c0 + j], scale_gate, numerics);
+                } else if constexpr (kW8A16) {
+                  value = __fmul_rn(__uint_as_float(gate_bits[j]), scale_gate);
                 } else {
                   value = __fadd_rn(__uint_as_float(gate_bits[j]), bias_gate);
                 }
@@ -372,10 +543,23 @@ bool make_tensor_map(CUtensorMap* map, const void* base, bool int8, uint64_t row
   return result == CUDA_SUCCESS;
 }
 
-template <bool kInt8, bool kGateUp, int kRowTile, bool kDense>
+// W8A16 landing loads: int8 weight rows [rows, k] as plain (unswizzled) boxes of {64 bytes of K, 128 rows}.
+bool make_landing_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {k, rows};
+  const cuuint64_t strides[1] = {k};
+  const cuuint32_t box[2] = {kLandingRowBytes, kBlockM};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool kInt8, bool kGateUp, int kRowTile, bool kDense, bool kW8A16 = false>
 cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
-  using Cfg = TileConfig<kGateUp, kRowTile>;
-  auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile, kDense>;
+  using Cfg = TileConfig<kGateUp, kRowTile, kW8A16>;
+  auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile, kDense, kW8A16>;
   static PerDeviceOnce configured;
   const int device = current_device_ordinal();
   if (configured.needed(device)) {
@@ -385,8 +569,9 @@ cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   }
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   CUtensorMap weight_map, token_map;
-  if (!make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total, args.k, kBlockM) ||
-      !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowTile)) {
+  const bool weights_ok = kW8A16 ? make_landing_map(&weight_map, args.weights, static_cast<uint64_t>(args.experts) * n_total, args.k)
+                                 : make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total, args.k, kBlockM);
+  if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowTile)) {
     return cudaErrorInvalidValue;
   }
   const int n_blocks = (args.n_out + kBlockM - 1) / kBlockM;
@@ -394,18 +579,18 @@ cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   const int sms = sm_count_of_current_device();
   if (grid > sms) grid = sms;
   if (grid <= 0) return cudaSuccess;
-  kernel<<<static_cast<unsigned>(grid), kThreads, Cfg::kSmemBytes, stream>>>(weight_map, token_map, args);
+  kernel<<<static_cast<unsigned>(grid), kW8A16 ? kThreadsW8A16 : kThreads, Cfg::kSmemBytes, stream>>>(weight_map, token_map, args);
   return cudaGetLastError();
 }
 
-template <bool kInt8, bool kGateUp, bool kDense>
+template <bool kInt8, bool kGateUp, bool kDense, bool kW8A16 = false>
 cudaError_t launch_tile(const GroupedGemmArgs& args, cudaStream_t stream) {
   switch (args.row_tile) {
-    case 16: return launch_config<kInt8, kGateUp, 16, kDense>(args, stream);
-    case 32: return launch_config<kInt8, kGateUp, 32, kDense>(args, stream);
-    case 64: return launch_config<kInt8, kGateUp, 64, kDense>(args, stream);
-    case 128: return launch_config<kInt8, kGateUp, 128, kDense>(args, stream);
-    case 256: return launch_config<kInt8, kGateUp, 256, kDense>(args, stream);
+    case 16: return launch_config<kInt8, kGateUp, 16, kDense, kW8A16>(args, stream);
+    case 32: return launch_config<kInt8, kGateUp, 32, kDense, kW8A16>(args, stream);
+    case 64: return launch_config<kInt8, kGateUp, 64, kDense, kW8A16>(args, stream);
+    case 128: return launch_config<kInt8, kGateUp, 128, kDense, kW8A16>(args, stream);
+    case 256: return launch_config<kInt8, kGateUp, 256, kDense, kW8A16>(args, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -425,6 +610,12 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& caller_args, bool in
   args.diag = 0;
 #endif
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
+  if (args.w8a16) {
+    // int8 weights with bf16 activations: the one-SM kernel with its widening warps, for every row tile.
+    if (int8 || args.dense_out != nullptr || args.w_scale == nullptr) return cudaErrorInvalidValue;
+    if (args.row_tile == kPairRowTile) args.row_tile = 256;
+    return gate_up ? launch_tile<false, true, false, true>(args, stream) : launch_tile<false, false, false, true>(args, stream);
+  }
   if (args.row_tile == kPairRowTile) {
     if (umma_pair_supported(gate_up, args.n_out, args.total_rows)) return launch_umma_pair_grouped_gemm(args, int8, gate_up, stream);
     args.row_tile = 256;  // same 256-row work items, one-SM kernel

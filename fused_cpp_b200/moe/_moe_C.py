@@ -507,11 +507,87 @@ def _not_built(name: str, why: str):
 
 
 _CPU_ONLY = "it is a CPU thread-scheduling experiment; use fused_moe_bf16_tiled or fused_moe_bf16_tiled_async_plan_v2"
-_W8A16 = "the W8A16 path (int8 weights, bf16 activations) is not built yet"
 fused_moe_bf16_tiled_planned_staged = _not_built("fused_moe_bf16_tiled_planned_staged", _CPU_ONLY)
 fused_moe_bf16_tiled_vllm_staged = _not_built("fused_moe_bf16_tiled_vllm_staged", _CPU_ONLY)
-fused_moe_w8a16_tiled_prepare_weights = _not_built("fused_moe_w8a16_tiled_prepare_weights", _W8A16)
-fused_moe_w8a16_tiled_prepare_quantized_weights = _not_built("fused_moe_w8a16_tiled_prepare_quantized_weights", _W8A16)
-fused_moe_w8a16_tiled_prepare_quantized_routed_shared_weights = _not_built(
-    "fused_moe_w8a16_tiled_prepare_quantized_routed_shared_weights", _W8A16)
-fused_moe_w8a16_tiled_async_plan_v2 = _not_built("fused_moe_w8a16_tiled_async_plan_v2", _W8A16)
+
+
+# ---- W8A16: int8 weights + per-output-channel scales, bf16 activations --------------------------------------
+
+W8A16_BACKEND_NAME = "cuda_sm100_w8a16_tcgen05"
+
+
+def fused_moe_w8a16_tiled_prepare_quantized_weights(w13_weight, w13_scale, w2_weight, w2_scale):
+    """Checkpoint int8 weights + scales -> (q13, K13, N13, s13[E,2F], q2, K2, N2, s2[E,H], backend_id, n_tile) on the GPU
+    (api.h:64-66).  The layout and the checks are those of the W8A8 preparation: both paths read the same tensors."""
+    return fused_moe_w8a8_tiled_prepare_quantized_weights(w13_weight, w13_scale, w2_weight, w2_scale)
+
+
+def fused_moe_w8a16_tiled_prepare_weights(w13_weight, w2_weight):
+    """bf16 weights -> symmetric per-output-channel int8 (scale = amax / 127, round to nearest even, clamp +-127:
+    quantize_pack_expert_weight_per_channel, fused_moe_bf16_tiled.cpp:4950-4976), api.h:61-62."""
+    return fused_moe_w8a8_tiled_prepare_weights(w13_weight, w2_weight)
+
+
+def fused_moe_w8a16_tiled_prepare_quantized_routed_shared_weights(routed_w13_weight, routed_w13_scale, routed_w2_weight,
+                                                                  routed_w2_scale, shared_w13_weight, shared_w13_scale,
+                                                                  shared_w2_weight, shared_w2_scale):
+    """Routed experts followed by the shared expert as expert id E (api.h:67-71)."""
+    if shared_w13_weight.dim() != 2 or shared_w2_weight.dim() != 2:
+        raise RuntimeError("shared W8A16 weights must be [2F, H] and [H, F]")
+    experts = routed_w13_weight.shape[0]
+    return fused_moe_w8a16_tiled_prepare_quantized_weights(
+        torch.cat((routed_w13_weight, shared_w13_weight.unsqueeze(0).to(routed_w13_weight.device)), dim=0),
+        torch.cat((routed_w13_scale.reshape(experts, -1), shared_w13_scale.reshape(1, -1).to(routed_w13_scale.device)), dim=0),
+        torch.cat((routed_w2_weight, shared_w2_weight.unsqueeze(0).to(routed_w2_weight.device)), dim=0),
+        torch.cat((routed_w2_scale.reshape(experts, -1), shared_w2_scale.reshape(1, -1).to(routed_w2_scale.device)), dim=0))
+
+
+def fused_moe_w8a16_tiled_async_plan_v2(
+        input, w13_packed, w13_K, w13_N, w13_scales, w2_packed, w2_K, w2_N, w2_scales, topk_weights, topk_ids,
+        task_expert_ids, task_core_begins, task_threads, task_dep_offsets, task_deps, plan_version, execution_mode,
+        task_preferred_threads, task_min_threads, task_max_threads, task_allowed_thread_offsets, task_allowed_threads,
+        task_placement_modes, task_numa_nodes, task_stage_ids, task_resize_points, task_range_granularities,
+        task_w13_window_tiles=None, task_w2_window_tiles=None, thread_cpu_ids=None, num_threads=1, activation="silu",
+        global_num_experts=-1, skip_weighted=False, silu_poly_degree=5, backend_n_tile=8, out=None, early_merge=-1,
+        cache_dequant=False):
+    """The W8A16 forward op (csrc/moe/module.cpp:180-194).  cache_dequant is accepted and has no effect: it selects
+    the reference's cached bf16 copy of a weight window, a CPU cache-blocking device; here the int8 tile is widened
+    in shared memory on every pass and the per-channel scale multiplies the fp32 accumulator."""
+    if plan_version != 2:
+        raise RuntimeError("W8A16 async plan requires plan_version 2")
+    if input.dim() != 2 or input.dtype != torch.bfloat16 or input.device.type != "cuda":
+        raise RuntimeError("W8A16 input must be a CUDA BF16 [tokens, H] tensor")
+    if topk_ids.dim() != 2 or topk_weights.shape != topk_ids.shape or topk_ids.shape[0] != input.shape[0]:
+        raise RuntimeError("W8A16 topk tensors must be matching [tokens, top_k]")
+    if input.shape[1] != w13_K or w13_N != 2 * w2_K or w2_N != w13_K:
+        raise RuntimeError("W8A16 expert dimensions mismatch")
+    if w13_packed.dtype != torch.int8 or w2_packed.dtype != torch.int8:
+        raise RuntimeError("W8A16 packed weights must be int8")
+    experts = int(w13_packed.shape[0])
+    if tuple(w13_scales.shape) != (experts, w13_N) or tuple(w2_scales.shape) != (experts, w2_N):
+        raise RuntimeError("W8A16 scale shapes are invalid")
+    if global_num_experts == 0 or global_num_experts < -1 or global_num_experts > experts:
+        raise RuntimeError("global_num_experts must be -1 or in [1, prepared experts]")
+    if skip_weighted and topk_ids.shape[1] != 1:
+        raise RuntimeError("skip_weighted is only valid when top_k == 1")
+    if silu_poly_degree not in (4, 5, 6):
+        raise RuntimeError("silu_poly_degree must be 4, 5 or 6")
+    _check_out(input, out, (input, w13_packed, w2_packed, topk_weights, topk_ids))
+    activation_id, limit = _native_activation(activation)
+    w13 = w13_packed.reshape(experts, w13_N, w13_K)
+    w2 = w2_packed.reshape(experts, w2_N, w2_K)
+    s13, s2 = w13_scales, w2_scales
+    if activation_id == _lib.ACTIVATION_SWIGLUOAI:
+        w13, s13 = _gate_then_up(w13, 1), _gate_then_up(s13, 1)
+    if global_num_experts != -1 and global_num_experts < experts:
+        experts = int(global_num_experts)
+        w13, w2, s13, s2 = w13[:experts], w2[:experts], s13[:experts], s2[:experts]
+    weights = topk_weights.to(torch.float32)
+    if skip_weighted:
+        weights = torch.ones_like(weights)
+    result = _lib.moe_forward(input, w13, w2, weights, topk_ids.to(torch.int64), s13=s13.contiguous(), s2=s2.contiguous(), w8a16=True,
+                              gate_up_tile=_tile_from(task_w13_window_tiles), down_tile=_tile_from(task_w2_window_tiles),
+                              swiglu_limit=limit, out=out, activation=activation_id)
+    if _sync_check():
+        result.raise_for_status()
+    return result.out

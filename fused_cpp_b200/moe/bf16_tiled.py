@@ -34,12 +34,13 @@ class PreparedBF16TiledFusedMoEWeights:
 
 @dataclass(frozen=True)
 class PreparedW8A16TiledFusedMoEWeights:
+    """Per-output-channel int8 expert weights + fp32 scales, multiplied with unquantised bf16 activations."""
     w13: tuple[torch.Tensor, int, int, torch.Tensor]
     w2: tuple[torch.Tensor, int, int, torch.Tensor]
     fused_silu: bool = True
     gemm_backend: int = _native.BACKEND_ID
     backend_n_tile: int = _native.BACKEND_N_TILE
-    backend_name: str = "cuda_sm100_w8a16"
+    backend_name: str = _native.W8A16_BACKEND_NAME
 
 
 @dataclass(frozen=True)
@@ -85,6 +86,7 @@ _fused_moe_bf16_tiled_impl = _native.fused_moe_bf16_tiled
 _fused_moe_bf16_tiled_async_plan_v2_impl = _native.fused_moe_bf16_tiled_async_plan_v2
 _fused_moe_w8a8_async_plan_v2_impl = _native.fused_moe_w8a8_tiled_async_plan_v2
 _shared_mlp_bf16_tiled_impl = _native.shared_mlp_bf16_tiled
+_fused_moe_w8a16_async_plan_v2_impl = _native.fused_moe_w8a16_tiled_async_plan_v2
 
 
 def _require_backend() -> None:
@@ -208,16 +210,39 @@ def prepare_routed_shared_moe_w8a8_tiled_quantized_weights(routed_w13_weight, ro
     return PreparedW8A8TiledRoutedSharedMoEWeights(packed=packed, routed_experts=int(experts), shared_expert_id=int(experts))
 
 
-def _w8a16_unavailable(*_args, **_kwargs):
-    raise RuntimeError("W8A16 fused MoE is unavailable in this build")
+def _prepared_w8a16(packed) -> PreparedW8A16TiledFusedMoEWeights:
+    return PreparedW8A16TiledFusedMoEWeights(w13=(packed[0], int(packed[1]), int(packed[2]), packed[3]),
+                                             w2=(packed[4], int(packed[5]), int(packed[6]), packed[7]),
+                                             gemm_backend=int(packed[8]), backend_n_tile=int(packed[9]))
 
 
-prepare_fused_moe_w8a16_tiled_weights = _w8a16_unavailable
-prepare_fused_moe_w8a16_tiled_quantized_weights = _w8a16_unavailable
-prepare_routed_shared_moe_w8a16_tiled_quantized_weights = _w8a16_unavailable
-fused_moe_w8a16_tiled = _w8a16_unavailable
-fused_moe_w8a16_tiled_async_plan = _w8a16_unavailable
-fused_moe_w8a16_tiled_with_shared = _w8a16_unavailable
+def prepare_fused_moe_w8a16_tiled_weights(w13_weight, w2_weight):
+    """Quantise bf16 expert weights to symmetric per-output-channel int8 on the GPU (bf16_tiled.py:453)."""
+    _require_backend()
+    if w13_weight.dtype != torch.bfloat16 or w2_weight.dtype != torch.bfloat16:
+        raise TypeError("W8A16 source weights must be torch.bfloat16")
+    return _prepared_w8a16(_native.fused_moe_w8a16_tiled_prepare_weights(w13_weight, w2_weight))
+
+
+def prepare_fused_moe_w8a16_tiled_quantized_weights(w13_weight, w13_scale, w2_weight, w2_scale):
+    """Checkpoint int8 weights + per-output-channel scales (compressed-tensors style) -> prepared W8A16 weights
+    (bf16_tiled.py:483; docs/vllm_bf16_tiled_moe_integration.md:252-259)."""
+    _require_backend()
+    if w13_weight.dtype != torch.int8 or w2_weight.dtype != torch.int8:
+        raise TypeError("W8A16 quantized weights must be torch.int8")
+    return _prepared_w8a16(_native.fused_moe_w8a16_tiled_prepare_quantized_weights(w13_weight, w13_scale.to(torch.float32),
+                                                                                   w2_weight, w2_scale.to(torch.float32)))
+
+
+def prepare_routed_shared_moe_w8a16_tiled_quantized_weights(routed_w13_weight, routed_w13_scale, routed_w2_weight, routed_w2_scale,
+                                                            shared_w13_weight, shared_w13_scale, shared_w2_weight, shared_w2_scale):
+    """Routed experts followed by the shared expert as expert id E (bf16_tiled.py:541)."""
+    _require_backend()
+    packed = _native.fused_moe_w8a16_tiled_prepare_quantized_routed_shared_weights(
+        routed_w13_weight, routed_w13_scale.to(torch.float32), routed_w2_weight, routed_w2_scale.to(torch.float32),
+        shared_w13_weight, shared_w13_scale.to(torch.float32), shared_w2_weight, shared_w2_scale.to(torch.float32))
+    experts = int(routed_w13_weight.shape[0])
+    return PreparedW8A16TiledRoutedSharedMoEWeights(packed=_prepared_w8a16(packed), routed_experts=experts, shared_expert_id=experts)
 
 
 # ---- forward -------------------------------------------------------------------------------------
@@ -316,6 +341,61 @@ def fused_moe_bf16_tiled_vllm_staged(*_args, **_kwargs):
 
 bf16_tiled_fused_moe_planned_staged = fused_moe_bf16_tiled_planned_staged
 bf16_tiled_fused_moe_vllm_staged = fused_moe_bf16_tiled_vllm_staged
+
+
+def fused_moe_w8a16_tiled_async_plan(input, weights, topk_weights, topk_ids, plan, *, activation: Any = "silu",
+                                     global_num_experts: int = -1, skip_weighted: bool = False, silu_poly_degree: int = 5,
+                                     swiglu_limit: float | None = None, cache_dequant: bool = False, out=None):
+    """W8A16 forward under an explicit Plan V2 (bf16_tiled.py:1309)."""
+    if _fused_moe_w8a16_async_plan_v2_impl is None:
+        raise RuntimeError("W8A16 Plan V2 execution is unavailable in this build")
+    materialized = plan if isinstance(plan, AsyncMoEPlanV2) else AsyncMoEPlanV2.from_dict(plan)
+    if input.dtype != torch.bfloat16:
+        raise TypeError("W8A16 input must be a torch.bfloat16 tensor")
+    if topk_ids.dtype not in _INTEGER_DTYPES:
+        raise TypeError(f"topk_ids must use an integer dtype, got {topk_ids.dtype}")
+    if not topk_weights.dtype.is_floating_point:
+        raise TypeError(f"topk_weights must use a floating dtype, got {topk_weights.dtype}")
+    _validate_output_buffer(input, out)
+    result = _fused_moe_w8a16_async_plan_v2_impl(
+        input.contiguous(), weights.w13[0], weights.w13[1], weights.w13[2], weights.w13[3], weights.w2[0], weights.w2[1],
+        weights.w2[2], weights.w2[3], topk_weights.contiguous(), topk_ids.contiguous(), *_plan_args(materialized),
+        materialized.num_threads, _native_activation_name(activation, weights, swiglu_limit), int(global_num_experts),
+        bool(skip_weighted), int(silu_poly_degree), int(weights.backend_n_tile), out, materialized.native_early_merge,
+        bool(cache_dequant))
+    return out if out is not None else result
+
+
+def fused_moe_w8a16_tiled(input, weights, topk_weights, topk_ids, *, num_threads: int = 1, activation: Any = "silu",
+                          global_num_experts: int = -1, skip_weighted: bool = False, silu_poly_degree: int = 5,
+                          swiglu_limit: float | None = None, cache_dequant: bool = False, out=None):
+    """W8A16 forward through the installed planner runtime (bf16_tiled.py:1380): like W8A8 it has no unplanned path."""
+    _require_backend()
+    if not isinstance(weights, PreparedW8A16TiledFusedMoEWeights):
+        raise TypeError("weights must be PreparedW8A16TiledFusedMoEWeights")
+    if input.dtype != torch.bfloat16:
+        raise TypeError("W8A16 input must be a torch.bfloat16 tensor")
+    if topk_ids.dtype not in _INTEGER_DTYPES:
+        raise TypeError(f"topk_ids must use an integer dtype, got {topk_ids.dtype}")
+    if not topk_weights.dtype.is_floating_point:
+        raise TypeError(f"topk_weights must use a floating dtype, got {topk_weights.dtype}")
+    if int(num_threads) <= 0:
+        raise ValueError(f"num_threads must be positive, got {num_threads}")
+    from .planner_runtime import get_default_moe_planner_runtime
+
+    runtime = get_default_moe_planner_runtime()
+    if runtime is None:
+        raise RuntimeError("W8A16 fused MoE requires an installed MoePlannerRuntime; "
+                           "call enable_moe_planner_quick() or set_default_moe_planner_runtime() first")
+    plan = runtime.plan_for_dispatch(weights, topk_ids, num_threads=int(num_threads), activation=activation,
+                                     global_num_experts=int(global_num_experts))
+    if plan is None:
+        raise RuntimeError("the installed MoePlannerRuntime is incompatible with this W8A16 shape, thread count, activation, "
+                           "or expert topology")
+    return fused_moe_w8a16_tiled_async_plan(input, weights, topk_weights, topk_ids, plan, activation=activation,
+                                            global_num_experts=global_num_experts, skip_weighted=skip_weighted,
+                                            silu_poly_degree=silu_poly_degree, swiglu_limit=swiglu_limit,
+                                            cache_dequant=cache_dequant, out=out)
 
 
 def fused_moe_w8a8_tiled_async_plan(input, weights, topk_weights, topk_ids, plan, *, activation: Any = "silu",
@@ -442,6 +522,32 @@ def fused_moe_w8a8_tiled_with_shared(input, weights, topk_weights, topk_ids, *, 
         raise RuntimeError("routed+shared W8A8 fused MoE requires a compatible shared-aware MoePlannerRuntime")
     return fused_moe_w8a8_tiled_async_plan(input, weights.packed, combined_weights, combined_ids, plan, activation="silu",
                                            global_num_experts=-1, swiglu_limit=swiglu_limit, out=out)
+
+
+def fused_moe_w8a16_tiled_with_shared(input, weights, topk_weights, topk_ids, *, num_threads: int = 1,
+                                      routed_scaling_factor: float = 1.0, activation: Any = "silu", silu_poly_degree: int = 5,
+                                      swiglu_limit: float | None = None, cache_dequant: bool = False, out=None):
+    """W8A16 routed experts plus one always-active shared expert (bf16_tiled.py:881)."""
+    _require_backend()
+    if not isinstance(weights, PreparedW8A16TiledRoutedSharedMoEWeights):
+        raise TypeError("weights must be PreparedW8A16TiledRoutedSharedMoEWeights")
+    scaling = _check_shared_call(input, topk_weights, topk_ids, num_threads, routed_scaling_factor)
+    _native_activation_name(activation, weights.packed, swiglu_limit)
+    if _activation_name(activation) != "silu":
+        raise ValueError("routed+shared W8A16 scheduling currently requires activation='silu'")
+    _validate_output_buffer(input, out)
+    combined_weights, combined_ids = _combine_with_shared(topk_weights, topk_ids, weights.shared_expert_id, scaling)
+    from .planner_runtime import get_default_moe_planner_runtime
+
+    runtime = get_default_moe_planner_runtime()
+    plan = None
+    if runtime is not None:
+        plan = runtime.plan_for_shared_dispatch(weights, combined_ids, num_threads=int(num_threads), activation="silu")
+    if plan is None:
+        raise RuntimeError("routed+shared W8A16 fused MoE requires a compatible shared-aware MoePlannerRuntime")
+    return fused_moe_w8a16_tiled_async_plan(input, weights.packed, combined_weights, combined_ids, plan, activation="silu",
+                                            global_num_experts=weights.routed_experts + 1, silu_poly_degree=silu_poly_degree,
+                                            swiglu_limit=swiglu_limit, cache_dequant=cache_dequant, out=out)
 
 
 def fused_moe_bf16_tiled_with_shared(input, weights, topk_weights, topk_ids, *, num_threads: int = 1,

@@ -93,7 +93,7 @@ class QuickMoeCalibrationResult:
 # local experts as fit, so that tile timings are taken at the real operand widths.
 PROBE_WEIGHT_BYTES = 3 << 30
 DEFAULT_PROBE_SHAPE = (2048, 1024, 32)  # (hidden, inter, experts) when no layer shape is given
-CALIBRATION_BUCKETS = (1, 8, 24, 48, 96, 192, 384)
+CALIBRATION_BUCKETS = (1, 2, 4, 8, 24, 48, 96, 192, 384)
 
 
 def _probe_layer(kind: str, hidden: int, inter: int, experts: int, device: torch.device, seed: int) -> dict:
@@ -129,7 +129,7 @@ def _probe_routing(rows_per_expert: int, experts: int, skewed: bool, seed: int):
 
 
 def _probe_tiles(kind: str, rows_per_expert: int, tiles: Sequence[int], seed: int, hidden: int, inter: int, experts: int,
-                 repeats: int = 5, _cache: dict | None = None) -> dict[int, float]:
+                 repeats: int = 8, _cache: dict | None = None) -> dict[int, float]:
     """Time one forward per candidate tile on a probe layer of the caller's H and I: the sum of a uniformly routed
     batch and a skewed one with `rows_per_expert` routes per expert on average (ms)."""
     from .. import _lib
@@ -209,7 +209,7 @@ def calibrate_moe_planner_quick(cpu_ids: Sequence[int] | None = None, *, output:
             best = min(measured, key=lambda t: (measured[t], t))
             # A fixed tile that is not clearly faster on the probe batches is not worth giving up the automatic
             # choice, which adapts to the routing of every batch.
-            if 0 in measured and measured[0] <= 1.03 * measured[best]:
+            if 0 in measured and measured[0] <= 1.05 * measured[best]:
                 best = 0
             table[kind][int(bucket)] = (int(best), int(best))
             timings[kind][int(bucket)] = {int(t): float(v) for t, v in measured.items()}
@@ -277,7 +277,10 @@ class MoePlannerRuntime:
                 and int(packed.w2[2]) == self.hidden_size)
 
     def _plan(self, packed: Any, topk_ids: torch.Tensor, experts: int, label: str) -> AsyncMoEPlanV2:
-        kind = "int8" if packed.w13[0].dtype == torch.int8 else "bf16"
+        if type(packed).__name__.startswith("PreparedW8A16"):
+            kind = "w8a16"  # no tile table of its own: the library's automatic choice
+        else:
+            kind = "int8" if packed.w13[0].dtype == torch.int8 else "bf16"
         routes = int(topk_ids.shape[0]) * int(topk_ids.shape[1])
         rows_per_expert = max(1, -(-routes // max(1, experts)))
         gate_up_tile, down_tile = self.calibration.lookup(kind, rows_per_expert)

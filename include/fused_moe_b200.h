@@ -198,6 +198,20 @@ FMOE_API int fmoe_bf16_forward(const void* x, const void* w13, const void* w2, c
                       int32_t inter, const fmoe_config* config, void* out, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/* ---- W8A16 routed-expert MoE ----------------------------------------------------------------- */
+
+/* int8 weights with per-output-channel fp32 scales (layouts of the W8A8 entry point), bf16 activations that are NOT
+ * quantised: acc = sum_k x[k] * q[n, k] in fp32 on the bf16 tensor-core path (the int8 weights are widened to bf16
+ * exactly, inside the kernel, after they crossed HBM as bytes), value = acc * scale[n], then the BF16 path's
+ * activation, fp32 route rows and tree / chain merge.  Replaces fused_moe_w8a16_tiled_async_plan_v2
+ * (csrc/moe/common/api.h:113-124; csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:8740-8760) in its "scale the
+ * accumulator" form; the reference's cache_dequant variant, which rounds q * scale to bf16 before multiplying, is
+ * not reproduced (results agree to the BF16 tolerance).  Workspace: fmoe_bf16_workspace_layout.  No biases. */
+FMOE_API int fmoe_w8a16_forward(const void* x, const int8_t* w13, const float* s13, const int8_t* w2, const float* s2,
+                                const float* topk_weights, const int64_t* topk_ids, int64_t tokens, int32_t top_k,
+                                int32_t experts, int32_t hidden, int32_t inter, const fmoe_config* config, void* out,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- expert-parallel building blocks ------------------------------------------------------------
  *
  * The reference has no expert parallelism (it rejects expert id remapping,

@@ -431,6 +431,60 @@ int fmoe_oracle_bf16_forward_ex(const uint16_t* x, const uint16_t* w13, const ui
   return 0;
 }
 
+static inline float dot_bf16_i8(const uint16_t* a, const int8_t* b, int n) {
+  /* bf16 x int8 products are exact in fp32 (8 + 7 significant bits); summation order is covered by the tolerance. */
+  float partial[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int i = 0;
+  for (; i + 8 <= n; i += 8) {
+    for (int lane = 0; lane < 8; ++lane) partial[lane] += bf16_to_f32(a[i + lane]) * (float)b[i + lane];
+  }
+  float sum = ((partial[0] + partial[1]) + (partial[2] + partial[3])) + ((partial[4] + partial[5]) + (partial[6] + partial[7]));
+  for (; i < n; ++i) sum += bf16_to_f32(a[i]) * (float)b[i];
+  return sum;
+}
+
+/*
+ * W8A16 routed-expert forward: int8 weights with per-output-channel fp32 scales, bf16 activations that are not
+ * quantised.  acc = sum_k x[k] * q[n,k] in fp32, value = acc * scale[n] (the reference applies the packed
+ * per-channel scales to its accumulators, csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:4916-4948, 8740-8760), then
+ * the BF16 path: activation rounded to bf16, fp32 route rows, tree / chain merge.
+ */
+int fmoe_oracle_w8a16_forward(const uint16_t* x, const int8_t* w13, const float* s13, const int8_t* w2, const float* s2,
+                              const float* topk_w, const int64_t* topk_ids, int64_t tokens, int top_k, int experts,
+                              int hidden, int inter, float swiglu_limit, int activation, uint16_t* out, uint16_t* dump_y,
+                              float* dump_route_out) {
+  const int64_t routes = tokens * top_k;
+  for (int64_t route = 0; route < routes; ++route) {
+    if (topk_ids[route] < 0 || topk_ids[route] >= experts) return -1;
+  }
+  float* route_out = dump_route_out ? dump_route_out : (float*)malloc(sizeof(float) * (size_t)(routes > 0 ? routes : 1) * hidden);
+#pragma omp parallel
+  {
+    uint16_t* y = (uint16_t*)malloc(sizeof(uint16_t) * (size_t)inter);
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t route = 0; route < routes; ++route) {
+      const int64_t token = route / top_k;
+      const int64_t expert = topk_ids[route];
+      const uint16_t* xrow = x + token * hidden;
+      const int8_t* w13_e = w13 + expert * 2 * (int64_t)inter * hidden;
+      const float* s13_e = s13 + expert * 2 * (int64_t)inter;
+      for (int j = 0; j < inter; ++j) {
+        const float gate = dot_bf16_i8(xrow, w13_e + (int64_t)j * hidden, hidden) * s13_e[j];
+        const float up = dot_bf16_i8(xrow, w13_e + (int64_t)(inter + j) * hidden, hidden) * s13_e[inter + j];
+        y[j] = activation == 0 ? swiglu_to_bf16(gate, up, swiglu_limit) : other_activation_to_bf16(activation, gate, up);
+      }
+      const int8_t* w2_e = w2 + expert * (int64_t)hidden * inter;
+      const float* s2_e = s2 + expert * (int64_t)hidden;
+      for (int h = 0; h < hidden; ++h) route_out[route * hidden + h] = dot_bf16_i8(y, w2_e + (int64_t)h * inter, inter) * s2_e[h];
+      if (dump_y) memcpy(dump_y + route * inter, y, sizeof(uint16_t) * (size_t)inter);
+    }
+    free(y);
+  }
+  fmoe_oracle_merge_bf16_path(route_out, topk_w, tokens, top_k, hidden, out);
+  if (!dump_route_out) free(route_out);
+  return 0;
+}
+
 /*
  * Dense dynamic-quant W8A8 linear, scalar fallback of csrc/i8gemm.cpp:366-399: per-row
  * scale = amax/127 (1 when the row is zero), q = clamp(nearbyint(x/scale), -128, 127),

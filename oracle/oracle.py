@@ -152,6 +152,32 @@ def bf16_forward(x, w13, w2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps:
     return (out, d) if dumps else out
 
 
+def w8a16_forward(x, w13, s13, w2, s2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps: bool = False, activation: int = 0):
+    """fmoe_oracle_w8a16_forward: int8 weights + per-channel scales, bf16 activations.  Returns out bf16 [T,H]
+    (and {y, route_out} with dumps=True)."""
+    tokens, hidden = x.shape
+    experts, two_i, _ = w13.shape
+    inter = two_i // 2
+    top_k = topk_ids.shape[1]
+    routes = tokens * top_k
+    out = torch.empty((tokens, hidden), dtype=torch.bfloat16)
+    d = {}
+    if dumps:
+        d = {"y": torch.empty((routes, inter), dtype=torch.bfloat16),
+             "route_out": torch.empty((routes, hidden), dtype=torch.float32)}
+    x, w13, w2 = x.contiguous(), w13.contiguous(), w2.contiguous()
+    s13 = s13.to(torch.float32).reshape(experts, two_i).contiguous()
+    s2 = s2.to(torch.float32).reshape(experts, hidden).contiguous()
+    topk_w, topk_ids = topk_w.to(torch.float32).contiguous(), topk_ids.to(torch.int64).contiguous()
+    status = lib().fmoe_oracle_w8a16_forward(
+        _ptr(x), _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2), _ptr(topk_w), _ptr(topk_ids),
+        ctypes.c_int64(tokens), ctypes.c_int(top_k), ctypes.c_int(experts), ctypes.c_int(hidden), ctypes.c_int(inter),
+        ctypes.c_float(swiglu_limit), ctypes.c_int(activation), _ptr(out), _ptr(d.get("y")), _ptr(d.get("route_out")))
+    if status != 0:
+        raise ValueError("topk expert id is out of range")
+    return (out, d) if dumps else out
+
+
 def merge_bf16_path(route_out: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
     """fmoe_oracle_merge_bf16_path: route_out fp32 [T,K,H] + weights [T,K] -> bf16 [T,H]."""
     tokens, top_k, hidden = route_out.shape

@@ -74,6 +74,15 @@ def main() -> None:
         torch.save({"out": out}, os.path.join(HERE, f"bf16_variant_{name}.pt"))
         print("bf16 variant", name, tuple(out.shape))
 
+    # W8A16: fused_moe_naive on the dequantised weights (q * scale in fp32) of the W8A8 cases
+    for name in cases.W8A16_CASES:
+        case = cases.w8a8_case(name)
+        w13 = case["w13"].float() * case["s13"].reshape(case["w13"].shape[0], -1, 1)
+        w2 = case["w2"].float() * case["s2"].reshape(case["w2"].shape[0], -1, 1)
+        out = fused_moe_naive(case["x"].float(), w13, w2, case["topk_weights"], case["topk_ids"]).to(torch.bfloat16)
+        torch.save({"out": out}, os.path.join(HERE, f"w8a16_{name}.pt"))
+        print("w8a16", name, tuple(out.shape))
+
     # appended: dense W8A8 linear, tests/test_i8gemm.py::_reference_dynamic_scaled_mm of the reference
     for name in cases.I8GEMM_CASES:
         case = cases.i8gemm_case(name)

@@ -36,7 +36,7 @@ def test_enable_quick_calibrates_on_the_gpu_and_the_forward_uses_the_table(cuda_
                 assert set(int(t) for t in timings) == set(planner_runtime.CANDIDATE_TILES)
                 assert all(v > 0.0 for v in timings.values()), (kind, bucket, timings)
                 chosen = profile["tiles"][kind][bucket][0]
-                assert timings[str(chosen)] <= 1.03 * min(timings.values()) + 1e-9
+                assert timings[str(chosen)] <= 1.05 * min(timings.values()) + 1e-9
         assert profile["gpu_name"] == torch.cuda.get_device_name() and profile["sm_count"] > 0
         assert len(messages) == 2 * len(buckets) and all(f"H={shape.hidden} I={shape.inter}" in m for m in messages)
         with pytest.raises(FileExistsError, match="already exists"):

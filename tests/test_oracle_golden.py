@@ -71,6 +71,16 @@ def test_bf16_oracle_variants_against_fused_moe_naive(name):
     assert float((out - golden).norm() / golden.norm()) <= 5e-3
 
 
+@pytest.mark.parametrize("name", cases.W8A16_CASES)
+def test_w8a16_oracle_against_fused_moe_naive_on_dequantised_weights(name):
+    """W8A16 = int8 weights x per-channel scale with unquantised bf16 activations: the oracle against the reference's
+    fused_moe_naive run on q * scale (fp32): relative L2 <= 5e-3."""
+    case = cases.w8a8_case(name)
+    golden = torch.load(os.path.join(GOLDEN, f"w8a16_{name}.pt"))["out"].float()
+    out = oracle.w8a16_forward(case["x"], case["w13"], case["s13"], case["w2"], case["s2"], case["topk_weights"], case["topk_ids"]).float()
+    assert float((out - golden).norm() / golden.norm()) <= 5e-3
+
+
 def test_expneg_tracks_exp():
     for gate in (-20.0, -3.3, -1.0, -1e-3, 0.0, 1e-3, 0.5, 2.0, 9.99, 10.0, 40.0):
         assert oracle.expneg(gate) == pytest.approx(math.exp(-gate), rel=3e-7)
