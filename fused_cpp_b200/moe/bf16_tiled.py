@@ -457,6 +457,8 @@ def fused_moe_tiled(input, weights, topk_weights, topk_ids, *, w13_bias=None, w2
             raise ValueError("cache_dequant is supported only by W8A16 fused MoE weights")
         return fused_moe_bf16_tiled(input, weights, topk_weights, topk_ids, w13_bias=w13_bias, w2_bias=w2_bias, **common)
     if isinstance(weights, PreparedW8A16TiledFusedMoEWeights):
+        if w13_bias is not None or w2_bias is not None:
+            raise ValueError("W8A16 fused MoE does not support w13_bias or w2_bias")
         return fused_moe_w8a16_tiled(input, weights, topk_weights, topk_ids, cache_dequant=cache_dequant, **common)
     if isinstance(weights, PreparedW8A8TiledFusedMoEWeights):
         if w13_bias is not None or w2_bias is not None:
