@@ -39,12 +39,17 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ s
   if (token >= tokens) return;
   const float* row = logits + token * experts;
   float score[kPerLane];   // what the weights are made of
-  float choice[kPerLane];  // what the selection compares (score + bias when a bias is given)
+  // What the selection compares.  Without a selection bias that is the logit itself: softmax and sigmoid are
+  // monotone, so the top-k of the scores is the top-k of the logits, and comparing logits keeps the choice free of
+  // the rounding of exp and of the division (two logits that differ always order the same way).  With a bias the
+  // selection compares score + bias.
+  float choice[kPerLane];
   float row_max = -INFINITY;
 #pragma unroll
   for (int i = 0; i < kPerLane; ++i) {
     const int e = lane + 32 * i;
     score[i] = e < experts ? row[e] : -INFINITY;
+    choice[i] = score[i];
     row_max = fmaxf(row_max, score[i]);
   }
   row_max = warp_max(row_max);
@@ -59,7 +64,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ s
         score[i] = expf(__fsub_rn(score[i], row_max));
         denominator = __fadd_rn(denominator, score[i]);
       }
-      choice[i] = selection_bias != nullptr ? __fadd_rn(score[i], selection_bias[e]) : score[i];
+      if (selection_bias != nullptr) choice[i] = __fadd_rn(score[i], selection_bias[e]);
     } else {
       score[i] = 0.0f;
       choice[i] = -INFINITY;
@@ -71,7 +76,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ s
     for (int i = 0; i < kPerLane; ++i) {
       score[i] = __fdiv_rn(score[i], denominator);  // the softmax probability
       const int e = lane + 32 * i;
-      if (e < experts) choice[i] = selection_bias != nullptr ? __fadd_rn(score[i], selection_bias[e]) : score[i];
+      if (e < experts && selection_bias != nullptr) choice[i] = __fadd_rn(score[i], selection_bias[e]);
     }
   }
   // k rounds of arg-max.  Lane r keeps the r-th winner.

@@ -288,13 +288,14 @@ FMOE_API int fmoe_i8gemm_dynamic_scaled_mm_pair(const void* x_bf16, int64_t rows
 /* The step in front of the path: expert scores -> top_k ids and routing weights, in the types the forward entry
  * points take, so that the ids go from the router to the route build without leaving the GPU.
  *   scoring softmax: p = softmax(logits[t, :]);  sigmoid: p = 1 / (1 + exp(-logits[t, :]))
- *   selection:       the top_k experts by p (+ selection_bias[e] when given; the bias only steers the choice),
- *                    ties to the lower expert id
+ *   selection:       without a bias the top_k experts by logit (the same experts as by p, since both scorings are
+ *                    monotone, and free of the rounding of exp); with selection_bias[e] the top_k by p + bias (the
+ *                    bias only steers the choice); ties to the lower expert id
  *   weights:         p of the chosen experts, divided by their sum when renormalize != 0, times
  *                    routed_scaling_factor
  * The reference takes topk_weights / topk_ids as inputs (src/fused_cpp/moe/naive.py:4-7) and its callers compute
  * them in PyTorch; there is no reference kernel to match, parity is against torch.softmax / torch.topk on the
- * same logits (ids equal, weights to fp32 rounding).  experts <= 2048, top_k <= min(32, experts). */
+ * same logits (ids equal to torch.topk of the logits, weights to fp32 rounding).  experts <= 2048, top_k <= min(32, experts). */
 FMOE_API int fmoe_router_topk(const float* logits, const float* selection_bias, int64_t tokens, int32_t experts, int32_t top_k,
                               int32_t scoring, int32_t renormalize, float routed_scaling_factor, float* topk_weights,
                               int64_t* topk_ids, void* stream);

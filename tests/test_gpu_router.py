@@ -1,6 +1,8 @@
 """Router front-end (fmoe_router_topk) against torch on the CPU: softmax / sigmoid scoring, top-k, renormalised
-weights.  Ids must match torch.topk wherever the reference scores are not within rounding of each other;
-weights match to fp32 rounding (rtol 1e-5: the exp implementations differ in the last place)."""
+weights.  Without a selection bias the kernel selects on the logits (softmax and sigmoid are monotone), so the ids
+are EXACTLY torch.topk of the logits; with a bias they must match torch.topk of score + bias wherever two of those
+sums are not within rounding of each other.  Weights match to fp32 rounding (rtol 1e-5: the exp implementations
+differ in the last place)."""
 from __future__ import annotations
 
 import pytest
@@ -30,6 +32,9 @@ def _check(logits, top_k, scoring="softmax", bias=None, renormalize=True, scalin
     weights, ids = weights.cpu(), ids.cpu()
     ref_weights, ref_ids, choice = _reference(logits, top_k, scoring, bias, renormalize, scaling)
     assert ids.dtype == torch.int64 and weights.dtype == torch.float32
+    if bias is None:
+        # Selection on the logits: exactly torch.topk of the logits (distinct values: no tie rule involved).
+        assert torch.equal(ids, torch.topk(logits, top_k, dim=-1).indices)
     # Same experts in the same order, except where two reference scores are equal to rounding (then either is right).
     mine = choice.gather(1, ids)
     theirs = choice.gather(1, ref_ids)
