@@ -53,7 +53,8 @@ class Config(ctypes.Structure):
         ("numerics", ctypes.c_int32), ("gemm_impl", ctypes.c_int32), ("gate_up_tile", ctypes.c_int32),
         ("down_tile", ctypes.c_int32), ("swiglu_limit", ctypes.c_float), ("activation", ctypes.c_int32),
         ("stage_timer", ctypes.c_void_p), ("dump_acc1", ctypes.c_void_p), ("dump_acc2", ctypes.c_void_p),
-        ("w13_bias", ctypes.c_void_p), ("w2_bias", ctypes.c_void_p),
+        ("w13_bias", ctypes.c_void_p), ("w2_bias", ctypes.c_void_p), ("route_rows_bf16", ctypes.c_int32),
+        ("reserved1", ctypes.c_int32),
     ]
 
 
@@ -277,7 +278,8 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
                 gemm_impl: int = GEMM_AUTO, gate_up_tile: int = 0, down_tile: int = 0, swiglu_limit: float | None = None,
                 out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None,
                 stage_timer: "StageTimer | None" = None, diagnostic: bool = False, activation: int = ACTIVATION_SILU,
-                w13_bias: torch.Tensor | None = None, w2_bias: torch.Tensor | None = None, w8a16: bool = False) -> ForwardResult:
+                w13_bias: torch.Tensor | None = None, w2_bias: torch.Tensor | None = None, w8a16: bool = False,
+                route_rows_bf16: bool = False) -> ForwardResult:
     """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8, or, with
     w8a16=True, the W8A16 path (bf16 activations are not quantised).
     diagnostic=True (or gemm_impl=GEMM_SIMT) runs the call in the diagnostic library instead of the product one."""
@@ -312,6 +314,7 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
     config.down_tile = down_tile
     config.swiglu_limit = (10.0 if int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
     config.activation = int(activation)
+    config.route_rows_bf16 = 1 if route_rows_bf16 else 0
     if w13_bias is not None:
         w13_bias = _require_cuda("w13_bias", w13_bias, torch.float32)
         if tuple(w13_bias.shape) != (experts, two_i):

@@ -196,6 +196,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (!f.int8 && cfg.swiglu_limit != 0.0f && cfg.swiglu_limit != 10.0f) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "BF16 supports swiglu_limit 0 (plain SiLU) or 10.0");
   }
+  if (cfg.route_rows_bf16 != 0 && cfg.route_rows_bf16 != 1) return fail(FMOE_ERR_INVALID_ARGUMENT, "route_rows_bf16 must be 0 or 1");
   if (cfg.activation != FMOE_ACTIVATION_SILU && cfg.activation != FMOE_ACTIVATION_GELU && cfg.activation != FMOE_ACTIVATION_SWIGLUOAI) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown activation %d", cfg.activation);
   }
@@ -374,7 +375,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   dn.y = nullptr;
   dn.route_out = route_out;
   dn.row_out_ptrs = row_out_ptrs;
-  dn.route_out_bf16 = peer && f.peer_rows_bf16 ? 1 : 0;
+  // bf16 route rows: the peer-memory return in its compact form, or the single-GPU compact mode of fmoe_config.
+  const bool compact_rows = peer ? f.peer_rows_bf16 : (cfg.route_rows_bf16 != 0 && !f.rows_mode);
+  dn.route_out_bf16 = compact_rows ? 1 : 0;
   dn.dump_acc = cfg.dump_acc2;
   dn.row_tile = tile_dn;
 #ifdef FMOE_DIAG
@@ -392,7 +395,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (error != cudaSuccess) return cuda_fail(error, "down grouped GEMM");
   mark(FMOE_STAGE_DOWN + 1);
 
-  if (!f.rows_mode) {
+  if (!f.rows_mode && compact_rows) {
+    error = fmoe::launch_merge_bf16_rows(reinterpret_cast<const uint16_t*>(route_out), f.topk_weights, f.tokens, f.top_k, f.hidden,
+                                         f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream, reinterpret_cast<const int*>(base + layout.route_pos));
+    if (error != cudaSuccess) return cuda_fail(error, "top-k merge");
+  } else if (!f.rows_mode) {
     error = fmoe::launch_merge(route_out, f.topk_weights, f.tokens, f.top_k, f.hidden, f.int8 ? 0 : 1, static_cast<uint16_t*>(out), stream,
                                reinterpret_cast<const int*>(base + layout.route_pos));
     if (error != cudaSuccess) return cuda_fail(error, "top-k merge");

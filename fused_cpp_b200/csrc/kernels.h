@@ -114,7 +114,7 @@ cudaError_t launch_merge(const float* route_out, const float* topk_weights, int6
                          int tree, uint16_t* out, cudaStream_t stream, const int* route_pos = nullptr);
 // Same with the route rows stored as bf16 (opt-in compact return of the expert-parallel path).
 cudaError_t launch_merge_bf16_rows(const uint16_t* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
-                                   int tree, uint16_t* out, cudaStream_t stream);
+                                   int tree, uint16_t* out, cudaStream_t stream, const int* route_pos = nullptr);
 
 // ---- grouped GEMM, shared argument block
 struct GroupedGemmArgs {
@@ -152,7 +152,7 @@ struct GroupedGemmArgs {
   int activation;
   int w8a16;                 // weights are int8 with w_scale, activations bf16 (one-SM kernel widens the tile to bf16)
   int gate_up_one_box;       // two-SM gate_up: the weight rows of a stage arrive as one 16 KB TMA box (set by the launcher)
-  int route_out_bf16;        // with row_out_ptrs: the result rows are stored as bf16 (2 bytes per channel) instead of fp32
+  int route_out_bf16;        // the result rows are stored as bf16 (2 bytes per channel, rows 2 * n_out bytes apart) instead of fp32
   // Diagnostic build only (compiled with -DFMOE_DIAG, the separate libfused_moe_b200_diag.so; the product library
   // ignores the field): bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.
   int diag;

@@ -47,6 +47,65 @@ __device__ __forceinline__ float4 load_row4(const void* route_out, int64_t eleme
   }
 }
 
+// The same merge over bf16 rows with eight channels per thread: one 16-byte load per slot, one 16-byte store.
+__global__ void __launch_bounds__(kMergeThreads)
+merge_bf16_rows8_kernel(const uint16_t* __restrict__ route_out, const float* __restrict__ topk_weights, const int* __restrict__ route_pos,
+                        int top_k, int hidden, int tree, uint16_t* __restrict__ out) {
+  __shared__ float weights[kMaxTopK];
+  __shared__ bool present[kMaxTopK];
+  const int64_t token = blockIdx.x;
+  if (threadIdx.x < top_k) {
+    weights[threadIdx.x] = topk_weights[token * top_k + threadIdx.x];
+    present[threadIdx.x] = route_pos == nullptr || route_pos[token * top_k + threadIdx.x] >= 0;
+  }
+  __syncthreads();
+  const int h = (blockIdx.y * kMergeThreads + threadIdx.x) * 8;
+  if (h >= hidden) return;
+  const int64_t base = token * top_k * static_cast<int64_t>(hidden) + h;
+  const bool fixed = tree && (top_k == 2 || top_k == 4 || top_k == 6 || top_k == 8);
+  float result[8];
+  if (fixed) {
+    uint4 rows[8];
+    for (int slot = 0; slot < top_k; ++slot) {
+      rows[slot] = present[slot] ? *reinterpret_cast<const uint4*>(route_out + base + static_cast<int64_t>(slot) * hidden) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int lane = 0; lane < 8; ++lane) {
+      float values[8];
+#pragma unroll
+      for (int slot = 0; slot < 8; ++slot) {
+        const uint32_t word = reinterpret_cast<const uint32_t*>(&rows[slot])[lane >> 1];
+        values[slot] = __uint_as_float((lane & 1) ? (word & 0xffff0000u) : (word << 16));
+      }
+      switch (top_k) {
+        case 2: result[lane] = merge_fixed<2>(values, weights); break;
+        case 4: result[lane] = merge_fixed<4>(values, weights); break;
+        case 6: result[lane] = merge_fixed<6>(values, weights); break;
+        default: result[lane] = merge_fixed<8>(values, weights); break;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int lane = 0; lane < 8; ++lane) result[lane] = 0.0f;
+    for (int slot = 0; slot < top_k; ++slot) {
+      const uint4 row = present[slot] ? *reinterpret_cast<const uint4*>(route_out + base + static_cast<int64_t>(slot) * hidden) : make_uint4(0, 0, 0, 0);
+      const float w = weights[slot];
+      const uint32_t words[4] = {row.x, row.y, row.z, row.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        result[2 * i] = __fmaf_rn(__uint_as_float(words[i] << 16), w, result[2 * i]);
+        result[2 * i + 1] = __fmaf_rn(__uint_as_float(words[i] & 0xffff0000u), w, result[2 * i + 1]);
+      }
+    }
+  }
+  uint4 packed;
+  packed.x = static_cast<uint32_t>(f32_to_bf16_bits(result[0])) | (static_cast<uint32_t>(f32_to_bf16_bits(result[1])) << 16);
+  packed.y = static_cast<uint32_t>(f32_to_bf16_bits(result[2])) | (static_cast<uint32_t>(f32_to_bf16_bits(result[3])) << 16);
+  packed.z = static_cast<uint32_t>(f32_to_bf16_bits(result[4])) | (static_cast<uint32_t>(f32_to_bf16_bits(result[5])) << 16);
+  packed.w = static_cast<uint32_t>(f32_to_bf16_bits(result[6])) | (static_cast<uint32_t>(f32_to_bf16_bits(result[7])) << 16);
+  *reinterpret_cast<uint4*>(out + token * hidden + h) = packed;
+}
+
 template <bool kBf16Rows>
 __global__ void __launch_bounds__(kMergeThreads)
 merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_weights, const int* __restrict__ route_pos, int top_k,
@@ -114,11 +173,16 @@ cudaError_t launch_merge(const float* route_out, const float* topk_weights, int6
 }
 
 cudaError_t launch_merge_bf16_rows(const uint16_t* route_out, const float* topk_weights, int64_t tokens, int top_k, int hidden,
-                                   int tree, uint16_t* out, cudaStream_t stream) {
+                                   int tree, uint16_t* out, cudaStream_t stream, const int* route_pos) {
   if (tokens <= 0) return cudaSuccess;
   if (top_k > kMaxTopK) return cudaErrorInvalidValue;
+  if (hidden % 8 == 0) {
+    const dim3 grid8(static_cast<unsigned>(tokens), (hidden / 8 + kMergeThreads - 1) / kMergeThreads);
+    merge_bf16_rows8_kernel<<<grid8, kMergeThreads, 0, stream>>>(route_out, topk_weights, route_pos, top_k, hidden, tree, out);
+    return cudaGetLastError();
+  }
   const dim3 grid(static_cast<unsigned>(tokens), (hidden / 4 + kMergeThreads - 1) / kMergeThreads);
-  merge_kernel<true><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, nullptr, top_k, hidden, tree, out);
+  merge_kernel<true><<<grid, kMergeThreads, 0, stream>>>(route_out, topk_weights, route_pos, top_k, hidden, tree, out);
   return cudaGetLastError();
 }
 

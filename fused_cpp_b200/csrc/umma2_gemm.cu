@@ -411,7 +411,8 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         } else if constexpr (!kGateUp) {
           t.column_rowptr = args.row_out_ptrs != nullptr
                                 ? args.row_out_ptrs[row]
-                                : reinterpret_cast<uint64_t>(args.route_out + static_cast<int64_t>(args.sorted_routes[row]) * n_out);
+                                : reinterpret_cast<uint64_t>(args.route_out) +
+                                      static_cast<uint64_t>(args.sorted_routes[row]) * n_out * (args.route_out_bf16 ? 2 : 4);
         }
       }
       const int n = info.block * kChannelsPerUnit + channel_in_unit;

@@ -415,7 +415,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         } else if constexpr (!kGateUp) {
           meta->rowptr[c] = args.row_out_ptrs != nullptr
                                 ? args.row_out_ptrs[row0 + c]
-                                : reinterpret_cast<uint64_t>(args.route_out + static_cast<int64_t>(args.sorted_routes[row0 + c]) * n_out);
+                                : reinterpret_cast<uint64_t>(args.route_out) +
+                                      static_cast<uint64_t>(args.sorted_routes[row0 + c]) * n_out * (args.route_out_bf16 ? 2 : 4);
         }
       }
       float scale_gate = 1.0f, scale_up = 1.0f;

@@ -48,6 +48,13 @@ def _gemm_impl() -> int:
     return table[value]
 
 
+def _route_rows_bf16() -> bool:
+    """The reference's opt-in for bf16 route storage, FUSED_CPP_MOE_W2_BF16_ROUTE=1 (default off,
+    csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1016-1019): here it selects the compact route rows of every path
+    (fmoe_config.route_rows_bf16): half the bytes of the largest intermediate, output to tolerance instead of bit for bit."""
+    return os.environ.get("FUSED_CPP_MOE_W2_BF16_ROUTE", "0") not in ("", "0")
+
+
 def _sync_check() -> bool:
     return os.environ.get("FUSED_CPP_MOE_SYNC_CHECK", "1") != "0"
 
@@ -201,7 +208,8 @@ def fused_moe_w8a8_tiled_async_plan_v2(
     w2 = w2_packed.reshape(experts, w2_n, w2_k)
     result = _lib.moe_forward(input, w13, w2, topk_weights, topk_ids, s13=w13_scales, s2=w2_scales, numerics=_numerics(),
                               gemm_impl=_gemm_impl(), gate_up_tile=_tile_from(task_w13_window_tiles),
-                              down_tile=_tile_from(task_w2_window_tiles), swiglu_limit=float(swiglu_limit), out=out)
+                              down_tile=_tile_from(task_w2_window_tiles), swiglu_limit=float(swiglu_limit), out=out,
+                              route_rows_bf16=_route_rows_bf16())
     if _sync_check():
         result.raise_for_status()
     if out is not None:
@@ -286,7 +294,7 @@ def _bf16_forward(input, w13_packed, w13_k, w13_n, w2_packed, w2_k, w2_n, topk_w
         weights = torch.ones_like(weights)
     result = _lib.moe_forward(input, w13, w2, weights, topk_ids.to(torch.int64), gemm_impl=_gemm_impl(), gate_up_tile=gate_up_tile,
                               down_tile=down_tile, swiglu_limit=limit, out=out, activation=activation_id, w13_bias=w13_bias,
-                              w2_bias=w2_bias)
+                              w2_bias=w2_bias, route_rows_bf16=_route_rows_bf16())
     if _sync_check():
         result.raise_for_status()
     return result.out
@@ -587,7 +595,7 @@ def fused_moe_w8a16_tiled_async_plan_v2(
         weights = torch.ones_like(weights)
     result = _lib.moe_forward(input, w13, w2, weights, topk_ids.to(torch.int64), s13=s13.contiguous(), s2=s2.contiguous(), w8a16=True,
                               gate_up_tile=_tile_from(task_w13_window_tiles), down_tile=_tile_from(task_w2_window_tiles),
-                              swiglu_limit=limit, out=out, activation=activation_id)
+                              swiglu_limit=limit, out=out, activation=activation_id, route_rows_bf16=_route_rows_bf16())
     if _sync_check():
         result.raise_for_status()
     return result.out

@@ -73,6 +73,14 @@ typedef struct fmoe_config {
    * to the gate_up accumulators before the activation, w2_bias[E, H] to every route row before the top-k merge. */
   const float* w13_bias;
   const float* w2_bias;
+  /* 1 = compact route rows (opt-in): the down GEMM stores every route's result row as bf16 instead of fp32 and the
+   * merge widens them again: half the bytes of the largest intermediate (4*T*K*H written and read at fp32).  The
+   * int8 / int32 stages are untouched and stay bit-exact; the bf16 output is then computed from rows rounded to
+   * bf16, so it matches the fp32-row result to tolerance (relative L2 <= 5e-3), not bit for bit.  0 (default)
+   * keeps the reference's fp32 rows (csrc/moe/arm/i8mm_w8a8/kernels.cpp:248-257; its BF16 path has the same
+   * opt-in, FUSED_CPP_MOE_W2_BF16_ROUTE, csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1016-1019). */
+  int32_t route_rows_bf16;
+  int32_t reserved1;
 } fmoe_config;
 
 /* Gated activations of the BF16 op (activation_to_bf16, csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1911-1936):

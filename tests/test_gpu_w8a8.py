@@ -140,6 +140,30 @@ def test_w8a8_more_than_65535_tokens(cuda_device):
     _check_all_stages(case, result, 0)
 
 
+@pytest.mark.parametrize("name", ["cfg1", "wide", "ragged"])
+def test_w8a8_compact_route_rows_keep_the_integer_stages_exact(cuda_device, name):
+    """route_rows_bf16 (opt-in): the down GEMM stores bf16 rows.  Everything up to and including the int32 down
+    accumulators stays bit-exact; the stored rows are the bf16 rounding of the exact fp32 rows; the output is the
+    reference's fma chain over those rounded rows (exactly), hence within tolerance of the fp32-row result."""
+    case = cases.w8a8_case(name)
+    result = _run(case, cuda_device, dump=True, route_rows_bf16=True)
+    assert result.status()[0] == 0
+    tokens, hidden = case["x"].shape
+    top_k = case["topk_ids"].shape[1]
+    routes = tokens * top_k
+    out_ref, d = oracle.w8a8_forward(case["x"], case["w13"], case["s13"], case["w2"], case["s2"], case["topk_weights"], case["topk_ids"], 0,
+                                     dumps=True)
+    order = result.region("sorted_routes", torch.int32, (routes,)).cpu().long()
+    assert torch.equal(result.acc1.cpu(), d["acc1"][order]) and torch.equal(result.acc2.cpu(), d["acc2"][order])
+    assert torch.equal(result.region("yq", torch.int8, (routes, case["w13"].shape[1] // 2)).cpu(), d["yq"][order])
+    rows = result.region("route_out", torch.bfloat16, (routes, hidden)).cpu()
+    assert torch.equal(rows.view(torch.int16), d["route_out"].to(torch.bfloat16).view(torch.int16)), "rows are not the rounded exact rows"
+    merged = oracle.merge_w8a8_path(rows.float().view(tokens, top_k, hidden), case["topk_weights"])
+    assert torch.equal(result.out.cpu().view(torch.int16), merged.view(torch.int16))
+    error = (result.out.cpu().float() - out_ref.float()).norm() / out_ref.float().norm()
+    assert float(error) <= 5e-3
+
+
 def test_w8a8_repeated_call_is_bit_identical(cuda_device):
     case = cases.w8a8_case("ragged")
     first = _run(case, cuda_device).out.clone()
