@@ -233,8 +233,13 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   // 128-row tile above 64 tokens.
   const bool split = umma && !f.w8a16 && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
   const bool w8a16_wide = f.w8a16 && f.tokens > kSplitRows;
-  const int tile_gu = split ? kSplitRows : (w8a16_wide && cfg.gate_up_tile == 0) ? 128 : pick_row_tile(cfg.gate_up_tile, f.tokens, umma);
-  const int tile_dn = split ? kSplitRows : (w8a16_wide && cfg.down_tile == 0) ? 128 : pick_row_tile(cfg.down_tile, f.tokens, umma);
+  int tile_gu = split ? kSplitRows : (w8a16_wide && cfg.gate_up_tile == 0) ? 128 : pick_row_tile(cfg.gate_up_tile, f.tokens, umma);
+  int tile_dn = split ? kSplitRows : (w8a16_wide && cfg.down_tile == 0) ? 128 : pick_row_tile(cfg.down_tile, f.tokens, umma);
+  if (f.w8a16) {
+    // The token-major W8A16 kernel holds a work item in the 128 lanes of one accumulator: taller tiles are cut to 128.
+    tile_gu = tile_gu > 128 ? 128 : tile_gu;
+    tile_dn = tile_dn > 128 ? 128 : tile_dn;
+  }
   if (umma && (!fmoe::umma_row_tile_supported(tile_gu) || !fmoe::umma_row_tile_supported(tile_dn))) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128, 256 or 512 = two-SM pairs (got %d, %d)", tile_gu, tile_dn);
   }

@@ -26,7 +26,12 @@
 // fused_moe_bf16_tiled.cpp:4916-5000, 8740-8760): the weight tile arrives as int8 (half the HBM bytes of bf16) in a
 // landing area of the stage, eight more warps (6..13) widen it to bf16 -- exact, |q| <= 128 -- into the 128-byte
 // swizzled operand tile the kind::f16 MMA reads, and the epilogue multiplies by the per-output-channel scale in
-// fp32.  Everything else is the BF16 instance of this kernel.
+// fp32.  This instance runs TOKEN-MAJOR: the token tile is the A operand (M = 128 lanes = token rows, of which the
+// item's rows are real) and the widened weight tile the B operand (N = 256 = 128 gate + 128 up channels, or 128 for
+// down), because a tcgen05.mma of M = 128 takes about the same time whatever its N: with the weights on the N side
+// one instruction covers 256 x 16 weights instead of 128 x 16, and the tensor pipe keeps up with int8 weights
+// arriving at HBM speed (weight-major it could not: eight MMAs per 16 KB of weights against a budget of five).
+// An epilogue thread then owns a token row and stores eight channels at a time.
 // Accumulators are double-buffered in TMEM when two buffers fit in 512 columns, so the epilogue of
 // one unit overlaps the main loop of the next.  No load uses cluster multicast; weight-tile reuse
 // between row tiles of one expert comes from L2 (adjacent work items run concurrently).
@@ -76,14 +81,19 @@ struct TileConfig {
   // holds the widened bf16 weight tile; a few stages suffice (widen one while the MMAs read another).
   static constexpr int kStageBytes = kW8A16 ? kWeightBytes : kWeightBytes + kTokenBytes;
   static constexpr int kInt8TileBytes = kWeightTiles * kBlockM * kLandingRowBytes;
-  static constexpr int kLandingBytes = kW8A16 ? kTokenBytes + kInt8TileBytes : 0;
-  static constexpr int kStagesRaw = kW8A16 ? w8a16_stages(FMOE_W8A16_STAGES, kStageBytes, kTokenBytes + kInt8TileBytes, kSmemBudget)
+  // W8A16 runs token-major (see the kernel): the token tile is the MMA's A operand and the MMA always reads 128 rows
+  // of it, so its region is 128 rows tall whatever the row tile (the TMA load fills the first kRowTile rows).
+  static constexpr int kTokenRegionBytes = kW8A16 ? kBlockM * kBlockKBytes : kTokenBytes;
+  static constexpr int kLandingBytes = kW8A16 ? kTokenRegionBytes + kInt8TileBytes : 0;
+  static constexpr int kStagesRaw = kW8A16 ? w8a16_stages(FMOE_W8A16_STAGES, kStageBytes, kTokenRegionBytes + kInt8TileBytes, kSmemBudget)
                                             : kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kLandingSlotsRaw = kW8A16 ? (kSmemBudget - kStages * kStageBytes) / kLandingBytes : 0;
   static constexpr int kLandingSlots = kLandingSlotsRaw > 8 ? 8 : kLandingSlotsRaw;
   static constexpr int kLandingOffset = kStages * kStageBytes;  // the landing ring follows the operand stages
-  static constexpr int kAccColumns = kWeightTiles * kRowTile;
+  // Accumulator columns: tokens (weight-major: one block of kRowTile columns per weight tile) or, token-major,
+  // the channels of the unit (128 per weight tile).
+  static constexpr int kAccColumns = kW8A16 ? kWeightTiles * kBlockM : kWeightTiles * kRowTile;
   static constexpr int kAccBuffers = (2 * kAccColumns <= 512) ? 2 : 1;
   static constexpr int kTmemColumnsRaw = kAccBuffers * kAccColumns;
   static constexpr int kTmemColumns = kTmemColumnsRaw <= 32 ? 32 : kTmemColumnsRaw <= 64 ? 64 : kTmemColumnsRaw <= 128 ? 128
@@ -92,6 +102,7 @@ struct TileConfig {
   static constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kOperandBytes) + 7168 /*control block*/;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
   static_assert(!kW8A16 || kLandingSlots >= 2, "W8A16 needs at least two landing slots");
+  static_assert(!kW8A16 || kRowTile <= kBlockM, "token-major W8A16 holds an item's rows in the 128 lanes of one accumulator");
   static_assert(kAccColumns <= 512, "accumulator does not fit tensor memory");
 };
 
@@ -120,6 +131,8 @@ static_assert(sizeof(SmemControl) <= 7168, "control block exceeds its shared-mem
 // Four int8 values (one 32-bit word) -> four bf16 values, exactly.  byte ^ 0x80 is the value + 128 as an unsigned
 // byte; placed in the low mantissa bits of 2^23 it makes the float 2^23 + 128 + value, and subtracting 2^23 + 128
 // leaves the value itself, whose upper 16 bits are its bf16 form (|value| <= 128 has at most 8 significant bits).
+// (Both MMA operands stay bf16: an instruction descriptor that mixed an fp16 B operand with the bf16 A operand,
+// which would halve this arithmetic, ended in a launch error on this driver and is not used.)
 __device__ __forceinline__ void widen_int8x4(uint32_t word, uint32_t* low_pair, uint32_t* high_pair) {
   const uint32_t biased = word ^ 0x80808080u;
   const float magic = 8388736.0f;  // 2^23 + 128
@@ -205,11 +218,12 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
             ptx::mbar_wait(&ctl->landing_free[slot], slot_phase ^ 1u, abort_flag, status, 6);
             uint8_t* landing = smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes;
             const int x = kb * kBlockKElems;
-            ptx::mbar_arrive_expect_tx(&ctl->landed[slot], Cfg::kLandingBytes);
+            ptx::mbar_arrive_expect_tx(&ctl->landed[slot], Cfg::kTokenBytes + Cfg::kInt8TileBytes);
             ptx::tma_load_2d(landing, &token_map, &ctl->landed[slot], x, row0);
-            ptx::tma_load_2d(landing + Cfg::kTokenBytes, &weight_map, &ctl->landed[slot], x, weight_row);
+            ptx::tma_load_2d(landing + Cfg::kTokenRegionBytes, &weight_map, &ctl->landed[slot], x, weight_row);
             if (kGateUp) {
-              ptx::tma_load_2d(landing + Cfg::kTokenBytes + kBlockM * kLandingRowBytes, &weight_map, &ctl->landed[slot], x, weight_row + args.n_out);
+              ptx::tma_load_2d(landing + Cfg::kTokenRegionBytes + kBlockM * kLandingRowBytes, &weight_map, &ctl->landed[slot], x,
+                               weight_row + args.n_out);
             }
             ++landed_issued;
             if (++slot == Cfg::kLandingSlots) {
@@ -290,7 +304,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
         uint8_t* stage_base = smem + static_cast<size_t>(stage) * Cfg::kStageBytes;
         ptx::mbar_wait(&ctl->landed[slot], slot_phase, abort_flag, status, 5);
-        const uint8_t* landing = smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes + Cfg::kTokenBytes;
+        const uint8_t* landing = smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes + Cfg::kTokenRegionBytes;
         if (!FMOE_DIAG_BIT(args, 8)) {
           // Consecutive threads take consecutive 16-byte units (16 weights) of the landing slot: conflict-free
           // loads; the two 16-byte bf16 chunks of a unit go to swizzled positions that are conflict-free as well.
@@ -350,7 +364,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         decode_unit(args.items, unit, n_blocks, &item, &block);
         const int item_rows = args.items[4 * item + 2];
         const int mma_n = min(kRowTile, (item_rows + 15) & ~15);
-        const uint32_t idesc = ptx::make_instr_desc(kInt8, kBlockM, mma_n);
+        // Weight-major: M = 128 channels, N = the item's rows.  Token-major (W8A16): M = 128 token lanes, N = the
+        // unit's channels (gate and up tiles are one 256-row B operand).
+        const uint32_t idesc = kW8A16 ? ptx::make_instr_desc(false, kBlockM, Cfg::kWeightTiles * kBlockM) : ptx::make_instr_desc(kInt8, kBlockM, mma_n);
         ptx::mbar_wait(&ctl->acc_empty[buffer], (use & 1u) ^ 1u, abort_flag, status, 2);
         ptx::tcgen05_fence_after();
         const uint32_t acc = tmem_base + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
@@ -367,6 +383,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
             const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
             const uint64_t desc_tok = ptx::make_smem_desc_sw128(token_addr + ks * kUmmaKBytes);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+            if constexpr (kW8A16) {
+              ptx::umma_ss<false>(acc, desc_tok, desc_gate, idesc, accumulate);  // A = tokens, B = gate (+ up) channels
+              continue;
+            }
             ptx::umma_ss<kInt8>(acc, desc_gate, desc_tok, idesc, accumulate);
             if (kGateUp) {
               const uint64_t desc_up = ptx::make_smem_desc_sw128(stage_addr + kBlockM * kBlockKBytes + ks * kUmmaKBytes);
@@ -408,6 +428,80 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       const int rows = args.items[4 * item + 2];
       const bool channel_ok = n < n_out;
       ColumnMeta* meta = &ctl->meta[local & 1];
+      if constexpr (kW8A16) {
+        // Token-major: this thread owns token row `channel_in_block` of the item (TMEM lane = token), the columns are
+        // the unit's channels.  The per-channel scales of the unit go to shared memory first: scale[c] for the gate
+        // (or only) tile's channel n0 + c, scale[128 + c] for the up tile's.
+        const int n0 = block * kBlockM;
+        {
+          const float* s = args.w_scale + static_cast<int64_t>(expert) * n_total;
+          meta->scale[epilogue_thread] = n0 + epilogue_thread < n_out ? s[n0 + epilogue_thread] : 0.0f;
+          if (kGateUp) meta->scale[kBlockM + epilogue_thread] = n0 + epilogue_thread < n_out ? s[n_out + n0 + epilogue_thread] : 0.0f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 4);
+        ptx::tcgen05_fence_after();
+        const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
+        const int token = channel_in_block;  // 0..127
+        const bool row_ok = token < rows;
+        const bool warp_has_rows = quarter * 32 < rows;  // warp-uniform: the tcgen05.ld below needs the whole warp
+        const int channels = min(kBlockM, n_out - n0);   // a multiple of 16
+        uint8_t* out_row = nullptr;
+        if (row_ok) {
+          if constexpr (kGateUp) {
+            out_row = reinterpret_cast<uint8_t*>(args.y + static_cast<int64_t>(row0 + token) * n_out + n0);
+          } else {
+            const uint64_t base = args.row_out_ptrs != nullptr
+                                      ? args.row_out_ptrs[row0 + token]
+                                      : reinterpret_cast<uint64_t>(args.route_out) +
+                                            static_cast<uint64_t>(args.sorted_routes[row0 + token]) * n_out * (args.route_out_bf16 ? 2 : 4);
+            out_row = reinterpret_cast<uint8_t*>(base) + static_cast<size_t>(n0) * (args.route_out_bf16 ? 2 : 4);
+          }
+        }
+        for (int c0 = 0; warp_has_rows && c0 < channels; c0 += 8) {
+          uint32_t gate_bits[8];
+          uint32_t up_bits[8];
+          ptx::tmem_ld_x8(acc + c0, gate_bits);
+          if (kGateUp) ptx::tmem_ld_x8(acc + kBlockM + c0, up_bits);
+          ptx::tmem_ld_wait();
+          if (!row_ok) continue;
+          if constexpr (kGateUp) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              uint16_t pair[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const float gate = __fmul_rn(__uint_as_float(gate_bits[j + h]), meta->scale[c0 + j + h]);
+                const float up = __fmul_rn(__uint_as_float(up_bits[j + h]), meta->scale[kBlockM + c0 + j + h]);
+                pair[h] = activation == FMOE_ACT_SILU ? swiglu_to_bf16_with(gate, up, limit, ctl->exp_table)
+                                                      : other_activation_to_bf16(activation, gate, up);
+              }
+              packed[j >> 1] = static_cast<uint32_t>(pair[0]) | (static_cast<uint32_t>(pair[1]) << 16);
+            }
+            *reinterpret_cast<uint4*>(out_row + c0 * 2) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          } else {
+            float values[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) values[j] = __fmul_rn(__uint_as_float(gate_bits[j]), meta->scale[c0 + j]);
+            if (args.route_out_bf16) {
+              uint32_t packed[4];
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                packed[j >> 1] = static_cast<uint32_t>(f32_to_bf16_bits(values[j])) | (static_cast<uint32_t>(f32_to_bf16_bits(values[j + 1])) << 16);
+              }
+              *reinterpret_cast<uint4*>(out_row + c0 * 2) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            } else {
+              *reinterpret_cast<float4*>(out_row + c0 * 4) = make_float4(values[0], values[1], values[2], values[3]);
+              *reinterpret_cast<float4*>(out_row + c0 * 4 + 16) = make_float4(values[4], values[5], values[6], values[7]);
+            }
+          }
+        }
+        ptx::tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctl->acc_empty[buffer]);
+        continue;
+      }
       for (int c = epilogue_thread; c < rows; c += 128) {
         if (kInt8) meta->scale[c] = args.a_scale[row0 + c];
         if constexpr (kDense) {
@@ -591,7 +685,13 @@ cudaError_t launch_tile(const GroupedGemmArgs& args, cudaStream_t stream) {
     case 32: return launch_config<kInt8, kGateUp, 32, kDense, kW8A16>(args, stream);
     case 64: return launch_config<kInt8, kGateUp, 64, kDense, kW8A16>(args, stream);
     case 128: return launch_config<kInt8, kGateUp, 128, kDense, kW8A16>(args, stream);
-    case 256: return launch_config<kInt8, kGateUp, 256, kDense, kW8A16>(args, stream);
+    case 256:
+      // Token-major W8A16 holds an item in the 128 lanes of one accumulator: no 256-row tile.
+      if constexpr (kW8A16) {
+        return cudaErrorInvalidValue;
+      } else {
+        return launch_config<kInt8, kGateUp, 256, kDense, kW8A16>(args, stream);
+      }
     default: return cudaErrorInvalidValue;
   }
 }
@@ -614,7 +714,7 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& caller_args, bool in
   if (args.w8a16) {
     // int8 weights with bf16 activations: the one-SM kernel with its widening warps, for every row tile.
     if (int8 || args.dense_out != nullptr || args.w_scale == nullptr) return cudaErrorInvalidValue;
-    if (args.row_tile == kPairRowTile) args.row_tile = 256;
+    if (args.row_tile > 128) return cudaErrorInvalidValue;  // the caller caps W8A16 work items at 128 rows
     return gate_up ? launch_tile<false, true, false, true>(args, stream) : launch_tile<false, false, false, true>(args, stream);
   }
   if (args.row_tile == kPairRowTile) {
