@@ -53,8 +53,11 @@ WORKLOADS = {
     "w8a8_prefill_zipf_v3_T2048": {"kind": "int8", "tokens": 2048, "skew": True},
     # Routed experts plus one always-active shared expert (expert id E, route K, weight 1).
     "w8a8_ep_shared_v3_T16384": {"kind": "int8", "tokens": 16384, "shared": True},
-    # int8 weights, unquantised bf16 activations: the W8A8 layer's weights through the W8A16 entry point.
+    # int8 weights, 16-bit activations: the W8A8 layer's weights through the W8A16 entry point, in its default form
+    # (activations as 16-bit fixed point per row on the int8 tensor cores) and in the form that keeps the activations
+    # bf16 bit for bit and widens the weight tiles on the SM.
     "w8a16_decode_v3_T64": {"kind": "w8a16", "tokens": 64},
+    "w8a16_decode_v3_T64_bf16act": {"kind": "w8a16", "tokens": 64, "w8a16_form": "bf16"},
     "bf16_decode_v3_T64": {"kind": "bf16", "tokens": 64},
     "bf16_decode_v3_T32": {"kind": "bf16", "tokens": 32},
     "bf16_decode_v3_T8": {"kind": "bf16", "tokens": 8},
@@ -67,7 +70,7 @@ WORKLOADS = {
     "w8a8_small_zipf_T8192": {"kind": "int8", "tokens": 8192, "skew": True, "dims": SMALL},
 }
 DEFAULT_WORKLOAD = "w8a8_decode_v3_T64"
-EXTRA_POINTS = ["w8a8_prefill_v3_T8192", "w8a8_prefill_v3_T8192_bf16rows", "w8a8_prefill_zipf_v3_T8192", "w8a8_ep_shared_v3_T16384", "w8a16_decode_v3_T64", "bf16_decode_v3_T64",
+EXTRA_POINTS = ["w8a8_prefill_v3_T8192", "w8a8_prefill_v3_T8192_bf16rows", "w8a8_prefill_zipf_v3_T8192", "w8a8_ep_shared_v3_T16384", "w8a16_decode_v3_T64", "w8a16_decode_v3_T64_bf16act", "bf16_decode_v3_T64",
                 "bf16_decode_v3_T32", "bf16_decode_v3_T8", "bf16_decode_v3_T1", "w8a8_small_T16", "w8a8_small_zipf_T8192"]
 EP_POINTS = ["w8a8_ep_shared_v3_T16384", "w8a8_ep_shared_v3_T16384:bf16_return", "bf16_decode_v3_T64"]
 SWEEP_TOKENS = (1, 8, 64, 512, 4096, 16384)
@@ -81,7 +84,7 @@ def dims_of(spec: dict) -> dict:
     return dict(spec.get("dims", V3))
 
 
-DTYPE_LABEL = {"int8": "int8(w8a8)", "bf16": "bf16", "w8a16": "bf16 x int8 weights (w8a16)"}
+DTYPE_LABEL = {"int8": "int8(w8a8)", "bf16": "bf16", "w8a16": "16-bit activations x int8 weights (w8a16)"}
 
 
 def weight_kind(kind: str) -> str:
@@ -471,7 +474,8 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
 
     def step(stage_timer=None):
         return _lib.moe_forward(x, weights["w13"], weights["w2"], tw_run, ids_run, s13=weights["s13"], s2=weights["s2"], stage_timer=stage_timer,
-                                w8a16=kind == "w8a16", route_rows_bf16=bool(spec.get("route_rows_bf16", False)))
+                                w8a16=kind == "w8a16", route_rows_bf16=bool(spec.get("route_rows_bf16", False)),
+                                w8a16_form=_lib.W8A16_BF16_ACTIVATIONS if spec.get("w8a16_form") == "bf16" else _lib.W8A16_FIXED_POINT)
 
     for _ in range(warmup):
         step()
@@ -504,6 +508,8 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
         "launch_mode": "cuda_graph_replay" if graph is not None else "eager", "eager_ms_per_step": eager_ms_per_step,
         "l2": "flushed between steps (a buffer of twice the L2 is written)" if flush is not None else "inputs larger than L2",
         "route_rows": "bf16 (opt-in compact rows: output to tolerance, not bit-exact)" if spec.get("route_rows_bf16") else "fp32 (the reference's)",
+        **({"w8a16_form": "bf16 activations, weights widened on the SM" if spec.get("w8a16_form") == "bf16"
+            else "activations as 16-bit fixed point per row (two int8 planes), int8 tensor cores"} if kind == "w8a16" else {}),
         "value": tokens / (ms_per_step * 1e-3), "active_experts": work["active_experts"],
         "stage_ms": {k: round(v, 5) for k, v in stage_ms.items()},
         "roofline": gate_up_roofline(kind, gu_bytes, gu_ops, stage_ms["gate_up"], peaks, ncu_traffic_bytes(name), int8_peak),
@@ -534,6 +540,8 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
         previous = moe.set_default_moe_planner_runtime(own_runtime)
         previous_rows = os.environ.get("FUSED_CPP_MOE_W2_BF16_ROUTE")
         os.environ["FUSED_CPP_MOE_W2_BF16_ROUTE"] = "1" if spec.get("route_rows_bf16") else "0"
+        previous_form = os.environ.get("FUSED_CPP_MOE_W8A16_FORM")
+        os.environ["FUSED_CPP_MOE_W8A16_FORM"] = spec.get("w8a16_form", "fixed")
         try:
             x_pin, w_pin, ids_pin = x_host.pin_memory(), w_host.pin_memory(), ids_host.pin_memory()
             out_pin = torch.empty((tokens, hidden), dtype=torch.bfloat16).pin_memory()
@@ -563,6 +571,10 @@ def run_point(name: str, spec: dict, layer: dict, device: torch.device, steps: i
                 os.environ.pop("FUSED_CPP_MOE_W2_BF16_ROUTE", None)
             else:
                 os.environ["FUSED_CPP_MOE_W2_BF16_ROUTE"] = previous_rows
+            if previous_form is None:
+                os.environ.pop("FUSED_CPP_MOE_W8A16_FORM", None)
+            else:
+                os.environ["FUSED_CPP_MOE_W8A16_FORM"] = previous_form
         point["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": tokens * hidden * 2 + tokens * top_k * 4 + tokens * top_k * 8,
                         "d2h_bytes_per_step": tokens * hidden * 2,

@@ -48,13 +48,28 @@ EXPORTS = (
 STAGES = ("route", "quant_in", "gate_up", "quant_mid", "down", "merge")
 
 
+W8A16_FIXED_POINT = 0
+W8A16_BF16_ACTIVATIONS = 1
+
+
+def w8a16_form_from_env() -> int:
+    """FUSED_CPP_MOE_W8A16_FORM: "fixed" (default; activations as 16-bit fixed point on the int8 tensor cores) or "bf16"
+    (activations stay bf16, weights widened on the SM)."""
+    value = os.environ.get("FUSED_CPP_MOE_W8A16_FORM", "fixed").strip().lower()
+    if value in ("fixed", "fixed_point", "0", ""):
+        return W8A16_FIXED_POINT
+    if value in ("bf16", "bf16_activations", "1"):
+        return W8A16_BF16_ACTIVATIONS
+    raise ValueError(f"FUSED_CPP_MOE_W8A16_FORM must be 'fixed' or 'bf16', got {value!r}")
+
+
 class Config(ctypes.Structure):
     _fields_ = [
         ("numerics", ctypes.c_int32), ("gemm_impl", ctypes.c_int32), ("gate_up_tile", ctypes.c_int32),
         ("down_tile", ctypes.c_int32), ("swiglu_limit", ctypes.c_float), ("activation", ctypes.c_int32),
         ("stage_timer", ctypes.c_void_p), ("dump_acc1", ctypes.c_void_p), ("dump_acc2", ctypes.c_void_p),
         ("w13_bias", ctypes.c_void_p), ("w2_bias", ctypes.c_void_p), ("route_rows_bf16", ctypes.c_int32),
-        ("reserved1", ctypes.c_int32),
+        ("w8a16_form", ctypes.c_int32),
     ]
 
 
@@ -279,9 +294,10 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
                 out: torch.Tensor | None = None, dump: bool = False, workspace: torch.Tensor | None = None,
                 stage_timer: "StageTimer | None" = None, diagnostic: bool = False, activation: int = ACTIVATION_SILU,
                 w13_bias: torch.Tensor | None = None, w2_bias: torch.Tensor | None = None, w8a16: bool = False,
-                route_rows_bf16: bool = False) -> ForwardResult:
+                route_rows_bf16: bool = False, w8a16_form: int | None = None) -> ForwardResult:
     """One routed-expert MoE forward through the C ABI.  int8 weights (with s13/s2) select W8A8, or, with
-    w8a16=True, the W8A16 path (bf16 activations are not quantised).
+    w8a16=True, the W8A16 path (16-bit activations; w8a16_form picks W8A16_FIXED_POINT, the default, or
+    W8A16_BF16_ACTIVATIONS; None reads FUSED_CPP_MOE_W8A16_FORM = "fixed" | "bf16").
     diagnostic=True (or gemm_impl=GEMM_SIMT) runs the call in the diagnostic library instead of the product one."""
     quantised_weights = w13.dtype == torch.int8
     if w8a16 and not quantised_weights:
@@ -315,6 +331,7 @@ def moe_forward(x, w13, w2, topk_weights, topk_ids, *, s13=None, s2=None, numeri
     config.swiglu_limit = (10.0 if int8 else 0.0) if swiglu_limit is None else float(swiglu_limit)
     config.activation = int(activation)
     config.route_rows_bf16 = 1 if route_rows_bf16 else 0
+    config.w8a16_form = w8a16_form_from_env() if w8a16_form is None else int(w8a16_form)
     if w13_bias is not None:
         w13_bias = _require_cuda("w13_bias", w13_bias, torch.float32)
         if tuple(w13_bias.shape) != (experts, two_i):

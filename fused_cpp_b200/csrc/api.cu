@@ -89,7 +89,9 @@ int make_layout(bool int8, int64_t tokens, int top_k, int experts, int hidden, i
   layout->a_rows = take(with_route_out ? rows * hidden * (int8 ? 1 : 2) : 256);
   layout->a_scale = take(sizeof(float) * rows);
   layout->y = take(rows * inter * 2);
-  layout->yq = take(int8 ? rows * inter : 0);
+  // W8A16 (which uses the 16-bit layout) holds the two int8 planes of the intermediate in a_rows when they fit
+  // there (inter <= hidden: the activation planes are dead by then), else here.
+  layout->yq = take(int8 ? rows * inter : (inter > hidden ? rows * inter * 2 : 0));
   layout->y_scale = take(sizeof(float) * rows);
   layout->route_out = take(with_route_out ? sizeof(float) * rows * hidden : sizeof(uint64_t) * rows);
   layout->route_pos = take(sizeof(int) * rows);
@@ -206,6 +208,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   if (f.w8a16 && (cfg.w13_bias != nullptr || cfg.w2_bias != nullptr)) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "W8A16 takes no w13_bias / w2_bias");
   }
+  if (cfg.w8a16_form != FMOE_W8A16_FIXED_POINT && cfg.w8a16_form != FMOE_W8A16_BF16_ACTIVATIONS) {
+    return fail(FMOE_ERR_INVALID_ARGUMENT, "unknown w8a16_form %d", cfg.w8a16_form);
+  }
   if (cfg.activation != FMOE_ACTIVATION_SILU && cfg.swiglu_limit != 0.0f) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "swiglu_limit is only valid with the SiLU activation");
   }
@@ -231,6 +236,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   // the batch size (pick_row_tile).
   // W8A16 runs every expert through the one-SM kernel (the int8 -> bf16 widening lives there): no split, and a
   // 128-row tile above 64 tokens.
+  // Its fixed-point form runs on the int8 one-SM kernel with two token rows (planes) per route: the kernel's row tile
+  // is twice the routes of a work item, which caps an item at 128 routes as well.
+  const bool planes = f.w8a16 && umma && cfg.w8a16_form == FMOE_W8A16_FIXED_POINT;
   const bool split = umma && !f.w8a16 && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
   const bool w8a16_wide = f.w8a16 && f.tokens > kSplitRows;
   int tile_gu = split ? kSplitRows : (w8a16_wide && cfg.gate_up_tile == 0) ? 128 : pick_row_tile(cfg.gate_up_tile, f.tokens, umma);
@@ -307,6 +315,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     error = fmoe::launch_gather_rows(static_cast<const uint16_t*>(f.x), routes, f.hidden / 2, sorted_routes, 1, valid_rows,
                                      reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
     if (error == cudaSuccess) error = fmoe::launch_gather_scalars(f.rows_scale, routes, sorted_routes, valid_rows, a_scale, stream);
+  } else if (planes) {
+    error = fmoe::launch_split_rows_planes(static_cast<const uint16_t*>(f.x), routes, f.hidden, sorted_routes, f.top_k, valid_rows,
+                                           reinterpret_cast<int8_t*>(base + layout.a_rows), a_scale, stream);
   } else if (f.int8) {
     error = fmoe::launch_quantize_tokens_scatter(static_cast<const uint16_t*>(f.x), f.tokens, f.hidden, f.top_k,
                                                  reinterpret_cast<const int*>(base + layout.route_pos), cfg.numerics,
@@ -334,7 +345,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.k = f.hidden;
   gu.n_out = f.inter;
   gu.numerics = cfg.numerics;
-  gu.w8a16 = f.w8a16 ? 1 : 0;
+  gu.w8a16 = planes ? 2 : (f.w8a16 ? 1 : 0);
   gu.swiglu_limit = cfg.swiglu_limit;
   gu.activation = cfg.activation;
   gu.expert_bias = cfg.w13_bias;
@@ -342,11 +353,12 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.route_out = nullptr;
   gu.dump_acc = cfg.dump_acc1;
   gu.total_rows = routes;
-  gu.row_tile = tile_gu;
+  gu.row_tile = planes ? 2 * tile_gu : tile_gu;
+  const bool int8_gemm = f.int8 || planes;
 #ifdef FMOE_DIAG
-  error = umma ? fmoe::launch_umma_grouped_gemm(gu, f.int8, true, stream) : fmoe::launch_simt_grouped_gemm(gu, f.int8, true, stream);
+  error = umma ? fmoe::launch_umma_grouped_gemm(gu, int8_gemm, true, stream) : fmoe::launch_simt_grouped_gemm(gu, f.int8, true, stream);
 #else
-  error = fmoe::launch_umma_grouped_gemm(gu, f.int8, true, stream);
+  error = fmoe::launch_umma_grouped_gemm(gu, int8_gemm, true, stream);
 #endif
   if (error == cudaSuccess && split) {
     fmoe::GroupedGemmArgs big = gu;
@@ -364,6 +376,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     error = fmoe::launch_quantize_rows(y, routes, f.inter, nullptr, 1, valid_rows, cfg.numerics, 0, yq, y_scale, stream);
     if (error != cudaSuccess) return cuda_fail(error, "intermediate quantise");
     down_rows = yq;
+  } else if (planes) {
+    int8_t* y_planes = reinterpret_cast<int8_t*>(base + (f.inter > f.hidden ? layout.yq : layout.a_rows));
+    error = fmoe::launch_split_rows_planes(y, routes, f.inter, nullptr, 1, valid_rows, y_planes, y_scale, stream);
+    if (error != cudaSuccess) return cuda_fail(error, "intermediate planes");
+    down_rows = y_planes;
   }
   mark(FMOE_STAGE_QUANT_MID + 1);
 
@@ -384,11 +401,11 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   const bool compact_rows = peer ? f.peer_rows_bf16 : (cfg.route_rows_bf16 != 0 && !f.rows_mode);
   dn.route_out_bf16 = compact_rows ? 1 : 0;
   dn.dump_acc = cfg.dump_acc2;
-  dn.row_tile = tile_dn;
+  dn.row_tile = planes ? 2 * tile_dn : tile_dn;
 #ifdef FMOE_DIAG
-  error = umma ? fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
+  error = umma ? fmoe::launch_umma_grouped_gemm(dn, int8_gemm, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
 #else
-  error = fmoe::launch_umma_grouped_gemm(dn, f.int8, false, stream);
+  error = fmoe::launch_umma_grouped_gemm(dn, int8_gemm, false, stream);
 #endif
   if (error == cudaSuccess && split) {
     fmoe::GroupedGemmArgs big = dn;

@@ -130,6 +130,24 @@ __device__ __forceinline__ float dequantize(int32_t accumulator, float activatio
   return __fmul_rn(__fmul_rn(value, activation_scale), channel_scale);
 }
 
+// Two-plane (16-bit fixed point) activations.  A row's values are X = rint(x / scale), scale = amax / kPlaneFullScale
+// (1 for an all-zero row), |X| <= 32512 = 127 * 256, carried as X = 256 * high + low with low in [-128, 127] and high
+// in [-127, 127].  The exact integer dot product with an int8 weight row is 256 * acc(high) + acc(low) (below 2^37 in
+// magnitude); it is rounded to fp32 once, then scaled by the row scale and the channel scale in that order.
+constexpr float kPlaneFullScale = 32512.0f;
+
+__device__ __forceinline__ float plane_row_scale(float amax) { return amax > 0.0f ? __fdiv_rn(amax, kPlaneFullScale) : 1.0f; }
+
+__device__ __forceinline__ int plane_fixed_point(float value, float scale) {
+  const float rounded = rintf(__fdiv_rn(value, scale));  // ties to even
+  return static_cast<int>(fmaxf(fminf(rounded, kPlaneFullScale), -kPlaneFullScale));
+}
+
+__device__ __forceinline__ float dequantize_planes(int32_t high, int32_t low, float activation_scale, float channel_scale) {
+  const long long exact = static_cast<long long>(high) * 256 + static_cast<long long>(low);
+  return __fmul_rn(__fmul_rn(__ll2float_rn(exact), activation_scale), channel_scale);
+}
+
 __device__ __forceinline__ float row_scale_from_amax(float amax, int numerics) {
   if (numerics == FMOE_NUMERICS_NATIVE) return amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
   const float scale = __fdiv_rn(amax, 127.0f);

@@ -51,6 +51,10 @@ cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, 
 // (route_pos[t*top_k+slot], -1 = dropped): same bits as quantising per route, one read of x per token.
 cudaError_t launch_quantize_tokens_scatter(const uint16_t* x, int64_t tokens, int cols, int top_k, const int* route_pos,
                                            int numerics, int8_t* q, float* scale, cudaStream_t stream);
+// W8A16 in its fixed-point form: bf16 row p (gathered by token when sorted_routes is given) -> 16-bit fixed point per
+// row, stored as two int8 rows (high plane at 2p, low plane at 2p + 1 of `planes`), row scale in scale[p].
+cudaError_t launch_split_rows_planes(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
+                                     const int* valid_rows, int8_t* planes, float* scale, cudaStream_t stream);
 // Same for fp32 sources (dense linear).  clamp_low is -128 or -127.
 cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
                                        int8_t* q, float* scale, cudaStream_t stream);
@@ -150,7 +154,9 @@ struct GroupedGemmArgs {
   // activation of the gate_up epilogue: FMOE_ACT_SILU (with swiglu_limit), FMOE_ACT_GELU, FMOE_ACT_SWIGLUOAI.
   const float* expert_bias;
   int activation;
-  int w8a16;                 // weights are int8 with w_scale, activations bf16 (one-SM kernel widens the tile to bf16)
+  int w8a16;                 // int8 weights with w_scale and 16-bit activations: 1 = bf16 rows, the one-SM kernel widens the weight
+                             // tile to bf16; 2 = two int8 planes per route (a_rows holds 2 * total_rows rows, a_scale one
+                             // scale per route, row_tile counts plane rows), the int8 one-SM kernel pairs accumulator columns
   int gate_up_one_box;       // two-SM gate_up: the weight rows of a stage arrive as one 16 KB TMA box (set by the launcher)
   int route_out_bf16;        // the result rows are stored as bf16 (2 bytes per channel, rows 2 * n_out bytes apart) instead of fp32
   // Diagnostic build only (compiled with -DFMOE_DIAG, the separate libfused_moe_b200_diag.so; the product library

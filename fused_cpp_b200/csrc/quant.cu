@@ -192,6 +192,47 @@ quantize_tokens_scatter_kernel(const uint16_t* __restrict__ x, int cols, int top
   }
 }
 
+// W8A16 in its fixed-point form.  cols % 16 == 0.  One CTA per route row p (gathered by token when sorted_routes is
+// given): the bf16 row becomes 16-bit fixed point (plane_fixed_point) and is stored as two int8 rows, the high plane at
+// row 2p and the low plane at row 2p + 1 of `planes`; scale_out[p] is the row scale.
+__global__ void __launch_bounds__(kQuantThreads)
+split_rows_planes_kernel(const uint16_t* __restrict__ x, int cols, const int* __restrict__ sorted_routes, int top_k,
+                         const int* __restrict__ valid_rows, int8_t* __restrict__ planes, float* __restrict__ scale_out) {
+  __shared__ float smem[32];
+  const int64_t row = blockIdx.x;
+  if (valid_rows && row >= *valid_rows) return;
+  const int64_t src_row = sorted_routes ? static_cast<int64_t>(sorted_routes[row] / top_k) : row;
+  const uint4* src = reinterpret_cast<const uint4*>(x + src_row * cols);
+  const int vec16 = cols >> 4;
+  float local = 0.0f;
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    local = fmaxf(local, amax8(src[2 * v]));
+    local = fmaxf(local, amax8(src[2 * v + 1]));
+  }
+  const float amax = block_max(local, smem);
+  const float scale = plane_row_scale(amax);
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  uint4* high_row = reinterpret_cast<uint4*>(planes + (2 * row) * cols);
+  uint4* low_row = reinterpret_cast<uint4*>(planes + (2 * row + 1) * cols);
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    float values[16];
+    unpack8(src[2 * v], values);
+    unpack8(src[2 * v + 1], values + 8);
+    uint32_t high[4] = {0, 0, 0, 0};
+    uint32_t low[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int fixed = plane_fixed_point(values[i], scale);
+      const int low_part = ((fixed + 128) & 255) - 128;
+      const int high_part = (fixed - low_part) >> 8;  // fixed - low_part is a multiple of 256
+      high[i >> 2] |= (static_cast<uint32_t>(high_part) & 0xffu) << (8 * (i & 3));
+      low[i >> 2] |= (static_cast<uint32_t>(low_part) & 0xffu) << (8 * (i & 3));
+    }
+    high_row[v] = make_uint4(high[0], high[1], high[2], high[3]);
+    low_row[v] = make_uint4(low[0], low[1], low[2], low[3]);
+  }
+}
+
 // Dense linear: arbitrary cols, fp32 or bf16 source, zero-padded to cols_padded, clamp to [-128,127]
 // (single GEMM) or [-127,127] (paired GEMMs) with division and ties-to-even (csrc/i8gemm.cpp:384-399, :492-506).
 __global__ void __launch_bounds__(kQuantThreads)
@@ -266,6 +307,14 @@ cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, 
     quantize_rows_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows,
                                                                                        numerics, weight_mode, q, scale);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_split_rows_planes(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
+                                     const int* valid_rows, int8_t* planes, float* scale, cudaStream_t stream) {
+  if (out_rows <= 0) return cudaSuccess;
+  split_rows_planes_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows, planes,
+                                                                                         scale);
   return cudaGetLastError();
 }
 

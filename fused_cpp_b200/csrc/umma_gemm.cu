@@ -144,11 +144,18 @@ __device__ __forceinline__ void widen_int8x4(uint32_t word, uint32_t* low_pair, 
   *high_pair = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
 }
 
-template <bool kInt8, bool kGateUp, int kRowTile, bool kDense, bool kW8A16 = false>
+// kPlanes (an instance of the int8 kernel; W8A16 in its fixed-point form): every activation row arrives as two int8
+// rows, row 2p = the high plane and row 2p + 1 = the low plane of the row's 16-bit fixed-point values
+// X = 256 * high + low, so a work item of r routes has 2r token rows and its accumulator columns come in pairs:
+// the exact integer dot product of route p with a channel is 256 * column(2p) + column(2p + 1).  Work items are
+// given in routes; loads, the MMA's N and the epilogue count plane rows.
+template <bool kInt8, bool kGateUp, int kRowTile, bool kDense, bool kW8A16 = false, bool kPlanes = false>
 __global__ void __launch_bounds__(kW8A16 ? kThreadsW8A16 : kThreads, 1)
 umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap token_map,
                          GroupedGemmArgs args) {
   static_assert(!kW8A16 || (!kInt8 && !kDense), "W8A16 is an instance of the bf16 grouped kernel");
+  static_assert(!kPlanes || (kInt8 && !kDense && !kW8A16), "the two-plane form is an instance of the int8 grouped kernel");
+  constexpr int kRowsPerRoute = kPlanes ? 2 : 1;
   using Cfg = TileConfig<kGateUp, kRowTile, kW8A16>;
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
@@ -252,7 +259,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         decode_unit(args.items, unit, n_blocks, &item, &block);
         const int n0 = block * kBlockM;
         const int expert = args.items[4 * item + 0];
-        const int row0 = args.items[4 * item + 1];
+        const int row0 = args.items[4 * item + 1] * kRowsPerRoute;
         const int weight_row = expert * n_total + n0;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
@@ -362,7 +369,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         // few columns of tensor-core time, not a full tile.  Unused accumulator columns are never read.
         int item, block;
         decode_unit(args.items, unit, n_blocks, &item, &block);
-        const int item_rows = args.items[4 * item + 2];
+        const int item_rows = args.items[4 * item + 2] * kRowsPerRoute;
         const int mma_n = min(kRowTile, (item_rows + 15) & ~15);
         // Weight-major: M = 128 channels, N = the item's rows.  Token-major (W8A16): M = 128 token lanes, N = the
         // unit's channels (gate and up tiles are one 256-row B operand).
@@ -415,7 +422,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
     const int numerics = args.numerics;
     const float limit = args.swiglu_limit;
     const int activation = args.activation;
-    uint32_t* const dump = static_cast<uint32_t*>(args.dump_acc);
+    uint32_t* const dump = kPlanes ? nullptr : static_cast<uint32_t*>(args.dump_acc);  // the dump holds one row per route
     int local = 0;
     for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
       const int buffer = local % Cfg::kAccBuffers;
@@ -424,8 +431,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       decode_unit(args.items, unit, n_blocks, &item, &block);
       const int n = block * kBlockM + channel_in_block;
       const int expert = args.items[4 * item + 0];
-      const int row0 = args.items[4 * item + 1];
-      const int rows = args.items[4 * item + 2];
+      const int row0 = args.items[4 * item + 1] * kRowsPerRoute;  // token rows (two per route in the two-plane form)
+      const int rows = args.items[4 * item + 2] * kRowsPerRoute;
       const bool channel_ok = n < n_out;
       ColumnMeta* meta = &ctl->meta[local & 1];
       if constexpr (kW8A16) {
@@ -503,14 +510,15 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         continue;
       }
       for (int c = epilogue_thread; c < rows; c += 128) {
-        if (kInt8) meta->scale[c] = args.a_scale[row0 + c];
+        const int route_row = (row0 + c) / kRowsPerRoute;  // sorted position of the column's route
+        if (kInt8) meta->scale[c] = args.a_scale[route_row];
         if constexpr (kDense) {
           meta->rowptr[c] = reinterpret_cast<uint64_t>(args.dense_out) + static_cast<uint64_t>(row0 + c) * n_out * (args.dense_out_bf16 ? 2 : 4);
         } else if constexpr (!kGateUp) {
           meta->rowptr[c] = args.row_out_ptrs != nullptr
-                                ? args.row_out_ptrs[row0 + c]
+                                ? args.row_out_ptrs[route_row]
                                 : reinterpret_cast<uint64_t>(args.route_out) +
-                                      static_cast<uint64_t>(args.sorted_routes[row0 + c]) * n_out * (args.route_out_bf16 ? 2 : 4);
+                                      static_cast<uint64_t>(args.sorted_routes[route_row]) * n_out * (args.route_out_bf16 ? 2 : 4);
         }
       }
       float scale_gate = 1.0f, scale_up = 1.0f;
@@ -540,6 +548,28 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         if (channel_ok) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
+            if constexpr (kPlanes) {
+              // Columns (j, j + 1) = (high, low) plane of one route; rows is even, so the pair is complete.
+              if ((j & 1) == 0 && c0 + j < rows) {
+                const float a = meta->scale[c0 + j];
+                if constexpr (kGateUp) {
+                  const float gate = dequantize_planes(static_cast<int>(gate_bits[j]), static_cast<int>(gate_bits[j + 1]), a, scale_gate);
+                  const float up = dequantize_planes(static_cast<int>(up_bits[j]), static_cast<int>(up_bits[j + 1]), a, scale_up);
+                  args.y[static_cast<int64_t>((row0 + c0 + j) >> 1) * n_out + n] =
+                      activation == FMOE_ACT_SILU ? swiglu_to_bf16_with(gate, up, limit, ctl->exp_table)
+                                                  : other_activation_to_bf16(activation, gate, up);
+                } else {
+                  const float value = dequantize_planes(static_cast<int>(gate_bits[j]), static_cast<int>(gate_bits[j + 1]), a, scale_gate);
+                  const uint64_t rowptr = meta->rowptr[c0 + j];
+                  if (args.route_out_bf16) {
+                    reinterpret_cast<uint16_t*>(rowptr)[n] = f32_to_bf16_bits(value);
+                  } else {
+                    reinterpret_cast<float*>(rowptr)[n] = value;
+                  }
+                }
+              }
+              continue;
+            }
             if (c0 + j < rows) {
               if (dump != nullptr) {
                 uint32_t* out = dump + static_cast<int64_t>(row0 + c0 + j) * n_total;
@@ -651,10 +681,10 @@ bool make_landing_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool kInt8, bool kGateUp, int kRowTile, bool kDense, bool kW8A16 = false>
+template <bool kInt8, bool kGateUp, int kRowTile, bool kDense, bool kW8A16 = false, bool kPlanes = false>
 cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   using Cfg = TileConfig<kGateUp, kRowTile, kW8A16>;
-  auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile, kDense, kW8A16>;
+  auto kernel = umma_grouped_gemm_kernel<kInt8, kGateUp, kRowTile, kDense, kW8A16, kPlanes>;
   static PerDeviceOnce configured;
   const int device = current_device_ordinal();
   if (configured.needed(device)) {
@@ -666,7 +696,8 @@ cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   CUtensorMap weight_map, token_map;
   const bool weights_ok = kW8A16 ? make_landing_map(&weight_map, args.weights, static_cast<uint64_t>(args.experts) * n_total, args.k)
                                  : make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total, args.k, kBlockM);
-  if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowTile)) {
+  const uint64_t token_rows = static_cast<uint64_t>(args.total_rows) * (kPlanes ? 2 : 1);
+  if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, token_rows, args.k, kRowTile)) {
     return cudaErrorInvalidValue;
   }
   const int n_blocks = (args.n_out + kBlockM - 1) / kBlockM;
@@ -678,19 +709,19 @@ cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-template <bool kInt8, bool kGateUp, bool kDense, bool kW8A16 = false>
+template <bool kInt8, bool kGateUp, bool kDense, bool kW8A16 = false, bool kPlanes = false>
 cudaError_t launch_tile(const GroupedGemmArgs& args, cudaStream_t stream) {
   switch (args.row_tile) {
-    case 16: return launch_config<kInt8, kGateUp, 16, kDense, kW8A16>(args, stream);
-    case 32: return launch_config<kInt8, kGateUp, 32, kDense, kW8A16>(args, stream);
-    case 64: return launch_config<kInt8, kGateUp, 64, kDense, kW8A16>(args, stream);
-    case 128: return launch_config<kInt8, kGateUp, 128, kDense, kW8A16>(args, stream);
+    case 16: return launch_config<kInt8, kGateUp, 16, kDense, kW8A16, kPlanes>(args, stream);
+    case 32: return launch_config<kInt8, kGateUp, 32, kDense, kW8A16, kPlanes>(args, stream);
+    case 64: return launch_config<kInt8, kGateUp, 64, kDense, kW8A16, kPlanes>(args, stream);
+    case 128: return launch_config<kInt8, kGateUp, 128, kDense, kW8A16, kPlanes>(args, stream);
     case 256:
       // Token-major W8A16 holds an item in the 128 lanes of one accumulator: no 256-row tile.
       if constexpr (kW8A16) {
         return cudaErrorInvalidValue;
       } else {
-        return launch_config<kInt8, kGateUp, 256, kDense, kW8A16>(args, stream);
+        return launch_config<kInt8, kGateUp, 256, kDense, kW8A16, kPlanes>(args, stream);
       }
     default: return cudaErrorInvalidValue;
   }
@@ -711,6 +742,13 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& caller_args, bool in
   args.diag = 0;
 #endif
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
+  if (args.w8a16 == 2) {
+    // int8 weights, activations as two int8 planes per route: the int8 one-SM kernel with paired accumulator columns;
+    // row_tile counts plane rows (two per route).
+    if (!int8 || args.dense_out != nullptr || args.w_scale == nullptr || args.a_scale == nullptr) return cudaErrorInvalidValue;
+    if (args.row_tile == kPairRowTile) return cudaErrorInvalidValue;
+    return gate_up ? launch_tile<true, true, false, false, true>(args, stream) : launch_tile<true, false, false, false, true>(args, stream);
+  }
   if (args.w8a16) {
     // int8 weights with bf16 activations: the one-SM kernel with its widening warps, for every row tile.
     if (int8 || args.dense_out != nullptr || args.w_scale == nullptr) return cudaErrorInvalidValue;

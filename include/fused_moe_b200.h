@@ -80,8 +80,23 @@ typedef struct fmoe_config {
    * keeps the reference's fp32 rows (csrc/moe/arm/i8mm_w8a8/kernels.cpp:248-257; its BF16 path has the same
    * opt-in, FUSED_CPP_MOE_W2_BF16_ROUTE, csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1016-1019). */
   int32_t route_rows_bf16;
-  int32_t reserved1;
+  int32_t w8a16_form;    /* fmoe_w8a16_forward only: FMOE_W8A16_* below */
 } fmoe_config;
+
+/* How fmoe_w8a16_forward carries the 16-bit activations to the int8 weights.
+ * FIXED_POINT (default): every activation row (and every row of the intermediate) becomes 16-bit fixed point,
+ *   X = rint(x / a), a = rowmax / 32512, held as two int8 planes X = 256 * high + low; both planes meet the int8
+ *   weights as they lie in HBM on the int8 tensor-core path, the exact integer dot product 256 * acc(high) + acc(low)
+ *   is rounded to fp32 once, then multiplied by a and by the channel scale.  |x - a X| <= rowmax * 2^-16: 128 times
+ *   finer than one bf16 step at the row maximum; elements below rowmax / 128 lose relative precision, which the
+ *   dot product does not see (against the bf16-activation form: relative L2 of 2e-4 on the fp32 route rows of N(0,1)
+ *   inputs, most of it bf16 roundings of intermediate elements that fall the other way).
+ *   Nothing is widened on the SM, so decode streams the weights at the HBM rate like the W8A8 path.
+ * BF16_ACTIVATIONS: the activations stay bf16 bit for bit; the int8 weight tiles are widened to bf16 on the SM after
+ *   they crossed HBM as bytes and the product runs on the bf16 tensor-core path with fp32 accumulation.  About half
+ *   the decode speed (the widening, not HBM, is the limit). */
+#define FMOE_W8A16_FIXED_POINT 0
+#define FMOE_W8A16_BF16_ACTIVATIONS 1
 
 /* Gated activations of the BF16 op (activation_to_bf16, csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:1911-1936):
  * SILU = gate * up / (1 + exp(-gate)) with the optional clamp of swiglu_limit; GELU = gelu_erf(gate) * up;
@@ -208,10 +223,10 @@ FMOE_API int fmoe_bf16_forward(const void* x, const void* w13, const void* w2, c
 
 /* ---- W8A16 routed-expert MoE ----------------------------------------------------------------- */
 
-/* int8 weights with per-output-channel fp32 scales (layouts of the W8A8 entry point), bf16 activations that are NOT
- * quantised: acc = sum_k x[k] * q[n, k] in fp32 on the bf16 tensor-core path (the int8 weights are widened to bf16
- * exactly, inside the kernel, after they crossed HBM as bytes), value = acc * scale[n], then the BF16 path's
- * activation, fp32 route rows and tree / chain merge.  Replaces fused_moe_w8a16_tiled_async_plan_v2
+/* int8 weights with per-output-channel fp32 scales (layouts of the W8A8 entry point) and 16-bit activations:
+ * value = (sum_k x[k] * q[n, k]) * scale[n] with the sum taken in one of the two forms of fmoe_config.w8a16_form
+ * (16-bit fixed point per row on the int8 tensor cores, or bf16 activations against weights widened to bf16 with fp32
+ * accumulation), then the BF16 path's activation, fp32 route rows and tree / chain merge.  Replaces fused_moe_w8a16_tiled_async_plan_v2
  * (csrc/moe/common/api.h:113-124; csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:8740-8760) in its "scale the
  * accumulator" form; the reference's cache_dequant variant, which rounds q * scale to bf16 before multiplying, is
  * not reproduced (results agree to the BF16 tolerance).  Workspace: fmoe_bf16_workspace_layout.  No biases. */

@@ -486,6 +486,71 @@ int fmoe_oracle_w8a16_forward(const uint16_t* x, const int8_t* w13, const float*
 }
 
 /*
+ * W8A16 with the activations carried as 16-bit fixed point per row (the form the CUDA library runs by default; not a
+ * statement of the reference, whose W8A16 kernels keep bf16 activations - it is pinned to the reference only through
+ * the tolerance against fmoe_oracle_w8a16_forward and the fused_moe_naive golden outputs).  Per row:
+ * a = amax / 32512 (1 for an all-zero row), X[k] = clamp(rint(x[k] / a), +-32512); the integer dot product
+ * sum_k X[k] * q[n,k] is exact (int64), rounded to fp32 once, value = (fp32(dot) * a) * scale[n]; then the BF16 path
+ * (activation to bf16, the same fixed-point step on the intermediate row, fp32 route rows, tree / chain merge).
+ */
+static float fixed_point_row(const uint16_t* row, int n, int32_t* fixed) {
+  float maximum = 0.0f;
+  for (int i = 0; i < n; ++i) maximum = fmaxf(maximum, fabsf(bf16_to_f32(row[i])));
+  const float scale = maximum > 0.0f ? maximum / 32512.0f : 1.0f;
+  for (int i = 0; i < n; ++i) {
+    float value = rintf(bf16_to_f32(row[i]) / scale);
+    value = fmaxf(fminf(value, 32512.0f), -32512.0f);
+    fixed[i] = (int32_t)value;
+  }
+  return scale;
+}
+
+static inline float dot_fixed_i8(const int32_t* a, const int8_t* b, int n) {
+  int64_t sum = 0;
+  for (int i = 0; i < n; ++i) sum += (int64_t)a[i] * (int64_t)b[i];
+  return (float)sum; /* one rounding, to nearest even */
+}
+
+int fmoe_oracle_w8a16_fixed_forward(const uint16_t* x, const int8_t* w13, const float* s13, const int8_t* w2, const float* s2,
+                                    const float* topk_w, const int64_t* topk_ids, int64_t tokens, int top_k, int experts,
+                                    int hidden, int inter, float swiglu_limit, int activation, uint16_t* out, uint16_t* dump_y,
+                                    float* dump_route_out) {
+  const int64_t routes = tokens * top_k;
+  for (int64_t route = 0; route < routes; ++route) {
+    if (topk_ids[route] < 0 || topk_ids[route] >= experts) return -1;
+  }
+  float* route_out = dump_route_out ? dump_route_out : (float*)malloc(sizeof(float) * (size_t)(routes > 0 ? routes : 1) * hidden);
+#pragma omp parallel
+  {
+    uint16_t* y = (uint16_t*)malloc(sizeof(uint16_t) * (size_t)inter);
+    int32_t* fixed = (int32_t*)malloc(sizeof(int32_t) * (size_t)(hidden > inter ? hidden : inter));
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t route = 0; route < routes; ++route) {
+      const int64_t token = route / top_k;
+      const int64_t expert = topk_ids[route];
+      const float a = fixed_point_row(x + token * hidden, hidden, fixed);
+      const int8_t* w13_e = w13 + expert * 2 * (int64_t)inter * hidden;
+      const float* s13_e = s13 + expert * 2 * (int64_t)inter;
+      for (int j = 0; j < inter; ++j) {
+        const float gate = (dot_fixed_i8(fixed, w13_e + (int64_t)j * hidden, hidden) * a) * s13_e[j];
+        const float up = (dot_fixed_i8(fixed, w13_e + (int64_t)(inter + j) * hidden, hidden) * a) * s13_e[inter + j];
+        y[j] = activation == 0 ? swiglu_to_bf16(gate, up, swiglu_limit) : other_activation_to_bf16(activation, gate, up);
+      }
+      const float a2 = fixed_point_row(y, inter, fixed);
+      const int8_t* w2_e = w2 + expert * (int64_t)hidden * inter;
+      const float* s2_e = s2 + expert * (int64_t)hidden;
+      for (int h = 0; h < hidden; ++h) route_out[route * hidden + h] = (dot_fixed_i8(fixed, w2_e + (int64_t)h * inter, inter) * a2) * s2_e[h];
+      if (dump_y) memcpy(dump_y + route * inter, y, sizeof(uint16_t) * (size_t)inter);
+    }
+    free(y);
+    free(fixed);
+  }
+  fmoe_oracle_merge_bf16_path(route_out, topk_w, tokens, top_k, hidden, out);
+  if (!dump_route_out) free(route_out);
+  return 0;
+}
+
+/*
  * Dense dynamic-quant W8A8 linear, scalar fallback of csrc/i8gemm.cpp:366-399: per-row
  * scale = amax/127 (1 when the row is zero), q = clamp(nearbyint(x/scale), -128, 127),
  * out = (acc * x_scale) * w_scale[n] (+ bias).  x is fp32 here (bf16 callers widen first).

@@ -152,9 +152,11 @@ def bf16_forward(x, w13, w2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps:
     return (out, d) if dumps else out
 
 
-def w8a16_forward(x, w13, s13, w2, s2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps: bool = False, activation: int = 0):
+def w8a16_forward(x, w13, s13, w2, s2, topk_w, topk_ids, swiglu_limit: float = 0.0, dumps: bool = False, activation: int = 0,
+                  fixed_point: bool = False):
     """fmoe_oracle_w8a16_forward: int8 weights + per-channel scales, bf16 activations.  Returns out bf16 [T,H]
-    (and {y, route_out} with dumps=True)."""
+    (and {y, route_out} with dumps=True).  fixed_point=True: fmoe_oracle_w8a16_fixed_forward, the activations as
+    16-bit fixed point per row with exact integer dot products (the CUDA library's default W8A16 form)."""
     tokens, hidden = x.shape
     experts, two_i, _ = w13.shape
     inter = two_i // 2
@@ -169,7 +171,8 @@ def w8a16_forward(x, w13, s13, w2, s2, topk_w, topk_ids, swiglu_limit: float = 0
     s13 = s13.to(torch.float32).reshape(experts, two_i).contiguous()
     s2 = s2.to(torch.float32).reshape(experts, hidden).contiguous()
     topk_w, topk_ids = topk_w.to(torch.float32).contiguous(), topk_ids.to(torch.int64).contiguous()
-    status = lib().fmoe_oracle_w8a16_forward(
+    entry = lib().fmoe_oracle_w8a16_fixed_forward if fixed_point else lib().fmoe_oracle_w8a16_forward
+    status = entry(
         _ptr(x), _ptr(w13), _ptr(s13), _ptr(w2), _ptr(s2), _ptr(topk_w), _ptr(topk_ids),
         ctypes.c_int64(tokens), ctypes.c_int(top_k), ctypes.c_int(experts), ctypes.c_int(hidden), ctypes.c_int(inter),
         ctypes.c_float(swiglu_limit), ctypes.c_int(activation), _ptr(out), _ptr(d.get("y")), _ptr(d.get("route_out")))

@@ -1,7 +1,10 @@
-"""W8A16 routed-expert MoE on the GPU (int8 weights widened to bf16 inside the kernel, per-channel scale on the fp32
-accumulator) against the CPU oracle and the golden output of the reference's fused_moe_naive on the dequantised
-weights.  Tolerances are the BF16 path's: relative L2 <= 5e-3, max-abs <= 1e-2 x RMS on the fp32 route rows; the
-merge is checked exactly on the GPU's own route rows.
+"""W8A16 routed-expert MoE on the GPU against the CPU oracle and the golden output of the reference's fused_moe_naive
+on the dequantised weights, in both forms of the library: "fixed" (default: activations as 16-bit fixed point per row,
+two int8 planes on the int8 tensor cores, exact integer dot products) and "bf16" (activations stay bf16, the int8
+weight tiles are widened to bf16 inside the kernel).  Tolerances against the bf16-activation oracle and the golden are
+the BF16 path's: relative L2 <= 5e-3, max-abs <= 1e-2 x RMS on the fp32 route rows; the merge is checked exactly on
+the GPU's own route rows.  The fixed form is also compared BIT FOR BIT with its own restatement in the oracle
+(intermediate rows and fp32 route rows).
 """
 from __future__ import annotations
 
@@ -20,12 +23,35 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
-def _run(case, device, **kw):
+FORMS = {"fixed": _lib.W8A16_FIXED_POINT, "bf16": _lib.W8A16_BF16_ACTIVATIONS}
+
+
+def _run(case, device, form="fixed", **kw):
     c = {k: v.to(device) for k, v in case.items()}
-    return _lib.moe_forward(c["x"], c["w13"], c["w2"], c["topk_weights"], c["topk_ids"], s13=c["s13"], s2=c["s2"], w8a16=True, **kw)
+    return _lib.moe_forward(c["x"], c["w13"], c["w2"], c["topk_weights"], c["topk_ids"], s13=c["s13"], s2=c["s2"], w8a16=True,
+                            w8a16_form=FORMS[form], **kw)
 
 
-def _check(case, result, limit=0.0):
+def _check_fixed_bit_exact(case, result, limit=0.0):
+    """The fixed-point form against fmoe_oracle_w8a16_fixed_forward: integer dot products are exact, so the bf16
+    intermediate, the fp32 route rows and the output must agree bit for bit."""
+    tokens, hidden = case["x"].shape
+    experts, two_i, _ = case["w13"].shape
+    top_k = case["topk_ids"].shape[1]
+    routes = tokens * top_k
+    out_ref, d = oracle.w8a16_forward(case["x"], case["w13"], case["s13"], case["w2"], case["s2"], case["topk_weights"], case["topk_ids"],
+                                      limit, dumps=True, fixed_point=True)
+    _, _, order = oracle.route_build(case["topk_ids"], experts)
+    y = result.region("y", torch.bfloat16, (routes, two_i // 2)).cpu()
+    assert torch.equal(y.view(torch.int16), d["y"][order.long()].view(torch.int16)), "intermediate rows differ from the fixed-point oracle"
+    route_out = result.region("route_out", torch.float32, (routes, hidden)).cpu()
+    assert torch.equal(route_out.view(torch.int32), d["route_out"].view(torch.int32)), "route rows differ from the fixed-point oracle"
+    assert torch.equal(result.out.cpu().view(torch.int16), out_ref.view(torch.int16))
+
+
+def _check(case, result, limit=0.0, form="bf16"):
+    if form == "fixed":
+        _check_fixed_bit_exact(case, result, limit)
     assert result.status()[0] == 0
     tokens, hidden = case["x"].shape
     experts, two_i, _ = case["w13"].shape
@@ -47,41 +73,87 @@ def _check(case, result, limit=0.0):
     _assert_close_bf16(result.out.cpu(), out_ref, "output vs oracle")
 
 
+@pytest.mark.parametrize("form", sorted(FORMS))
 @pytest.mark.parametrize("tile", [0, 16, 32, 64, 128, 256])
 @pytest.mark.parametrize("name", cases.W8A16_CASES)
-def test_w8a16_matches_oracle_for_every_row_tile(cuda_device, name, tile):
+def test_w8a16_matches_oracle_for_every_row_tile(cuda_device, name, tile, form):
     case = cases.w8a8_case(name)
-    _check(case, _run(case, cuda_device, gate_up_tile=tile, down_tile=tile))
+    _check(case, _run(case, cuda_device, form, gate_up_tile=tile, down_tile=tile), form=form)
 
 
+@pytest.mark.parametrize("form", sorted(FORMS))
 @pytest.mark.parametrize("name", cases.W8A16_CASES)
-def test_w8a16_matches_reference_golden(cuda_device, name):
+def test_w8a16_matches_reference_golden(cuda_device, name, form):
     case = cases.w8a8_case(name)
     golden = torch.load(os.path.join(GOLDEN, f"w8a16_{name}.pt"))["out"].float()
-    out = _run(case, cuda_device).out.cpu().float()
+    out = _run(case, cuda_device, form).out.cpu().float()
     assert float((out - golden).norm() / golden.norm()) <= 5e-3
 
 
-def test_w8a16_clamped_swiglu(cuda_device):
+@pytest.mark.parametrize("form", sorted(FORMS))
+def test_w8a16_clamped_swiglu(cuda_device, form):
     case = cases.w8a8_case("ragged")
     case["x"] = (case["x"].float() * 300).to(torch.bfloat16)  # push gate / up beyond the clamp
-    _check(case, _run(case, cuda_device, swiglu_limit=10.0), 10.0)
+    _check(case, _run(case, cuda_device, form, swiglu_limit=10.0), 10.0, form=form)
 
 
+@pytest.mark.parametrize("form", sorted(FORMS))
 @pytest.mark.parametrize("shape", ["decode", "prefill"])
-def test_w8a16_at_v3_dims(cuda_device, shape):
-    """H = 7168, I = 2048 with 8 experts: 112 / 32 K blocks of 64 weights through the widening warps."""
+def test_w8a16_at_v3_dims(cuda_device, shape, form):
+    """H = 7168, I = 2048 with 8 experts: 112 / 32 K blocks of 64 weights through the widening warps (bf16 form), 56 / 16
+    K blocks of 128 against two planes per route (fixed form)."""
     from tests.test_gpu_v3_dims import _w8a8_case
 
     case = _w8a8_case(shape)
-    _check(case, _run(case, cuda_device))
+    _check(case, _run(case, cuda_device, form), form=form)
 
 
-def test_w8a16_repeated_call_is_bit_identical(cuda_device):
+def test_w8a16_fixed_point_survives_outliers_and_zero_rows(cuda_device):
+    """Rows whose maximum is 2^10 times their typical value (elements far below max / 128 round to the fixed-point
+    quantum), an all-zero token and a token of one non-zero element: the fixed form stays bit-exact against its
+    restatement and within the tolerance of the bf16-activation oracle."""
+    case = cases.w8a8_case("ragged")
+    x = case["x"].float()
+    x[0].zero_()
+    x[1].zero_()
+    x[1, 5] = -3.0
+    x[2, 7] = 1024.0 * float(x[2].abs().mean())
+    x[3, 0] = -1024.0 * float(x[3].abs().mean())
+    case["x"] = x.to(torch.bfloat16)
+    result = _run(case, cuda_device, "fixed")
+    _check_fixed_bit_exact(case, result)
+    # Against the bf16-activation statement only the relative L2 is asked here: the outlier rows make intermediate
+    # elements of order 1e4, where one bf16 step that falls the other way already moves an output element by more than
+    # 1e-2 x RMS, whichever form computed it.
+    tokens, hidden = case["x"].shape
+    routes = tokens * case["topk_ids"].shape[1]
+    _, d = oracle.w8a16_forward(case["x"], case["w13"], case["s13"], case["w2"], case["s2"], case["topk_weights"], case["topk_ids"], dumps=True)
+    route_out = result.region("route_out", torch.float32, (routes, hidden)).cpu()
+    assert float((route_out - d["route_out"]).norm() / d["route_out"].norm()) <= 5e-3
+
+
+@pytest.mark.parametrize("form", sorted(FORMS))
+def test_w8a16_repeated_call_is_bit_identical(cuda_device, form):
     case = cases.w8a8_case("wide")
-    first = _run(case, cuda_device).out.clone()
-    second = _run(case, cuda_device).out.clone()
+    first = _run(case, cuda_device, form).out.clone()
+    second = _run(case, cuda_device, form).out.clone()
     assert torch.equal(first.view(torch.int16), second.view(torch.int16))
+
+
+def test_w8a16_intermediate_wider_than_hidden(cuda_device):
+    """inter > hidden: the planes of the intermediate do not fit the activation-plane region and use their own."""
+    generator = torch.Generator().manual_seed(77)
+    tokens, hidden, inter, experts, top_k = 24, 64, 160, 4, 2
+    case = {
+        "x": torch.randn((tokens, hidden), generator=generator).to(torch.bfloat16),
+        "w13": torch.randint(-127, 128, (experts, 2 * inter, hidden), generator=generator, dtype=torch.int8),
+        "s13": torch.rand((experts, 2 * inter), generator=generator) * 0.002 + 0.0005,
+        "w2": torch.randint(-127, 128, (experts, hidden, inter), generator=generator, dtype=torch.int8),
+        "s2": torch.rand((experts, hidden), generator=generator) * 0.002 + 0.0005,
+        "topk_weights": torch.rand((tokens, top_k), generator=generator),
+        "topk_ids": torch.stack([torch.randperm(experts, generator=generator)[:top_k] for _ in range(tokens)]),
+    }
+    _check(case, _run(case, cuda_device, "fixed"), form="fixed")
 
 
 def test_w8a16_public_ops(cuda_device):
