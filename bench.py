@@ -761,6 +761,9 @@ def run_single_gpu(args) -> None:
             point = run_point(name, other, layers.get(other), device, max(3, args.steps // 4) if heavy else args.steps, args.warmup, True,
                               None, int8_peak, runtimes.get(other))
             points.append({k: point[k] for k in POINT_KEYS if k in point})
+        for rows, k, n in DENSE_POINTS:
+            points.append(run_dense_point(rows, k, n, device, max(3, args.steps // 4) if rows > 1024 else args.steps, args.warmup,
+                                          measured_peaks(), int8_peak))
     cpu = None
     if not args.skip_cpu:
         cpu = time_cpu_port(args.workload, spec, layers.get(spec), 1, 3, budget_s=40.0)
@@ -780,6 +783,45 @@ def run_single_gpu(args) -> None:
         "eager_ms_per_step": head["eager_ms_per_step"], "points": points,
     }
     print(json.dumps(line), flush=True)
+
+
+# ---- dense W8A8 linear (the i8gemm op next to the MoE path) -------------------------------------------------
+
+# (rows, K, N): a decode and a prefill batch through an output projection of the DeepSeek-V3 attention block
+# (16384 -> 7168) and through its query up-projection (1536 -> 24576).
+DENSE_POINTS = [(64, 16384, 7168), (8192, 16384, 7168), (64, 1536, 24576), (8192, 1536, 24576)]
+
+
+def run_dense_point(rows: int, k: int, n: int, device: torch.device, steps: int, warmup: int, peaks: dict, int8_peak: dict | None) -> dict:
+    """fused_cpp.i8gemm.dynamic_scaled_mm (row quantiser + tcgen05 GEMM with the dense epilogue) on seeded inputs."""
+    from fused_cpp_b200 import i8gemm
+
+    generator = torch.Generator().manual_seed(SEED + rows + k + n)
+    weight = torch.randint(-127, 128, (n, k), generator=generator, dtype=torch.int8).to(device)
+    scale = (torch.rand((n,), generator=generator) * 1.5 + 0.5).div_(127.0 * k ** 0.5).to(device)
+    x = torch.randn((rows, k), generator=generator).to(torch.bfloat16).to(device)
+    prepared = i8gemm.prepare(weight, scale)
+    nbytes = n * k + rows * k * 2 + rows * k + rows * n * 2  # weights, rows in, int8 rows written and re-read once, out
+    flush = L2Flush(device) if nbytes < 4 * L2_BYTES else None
+
+    def step():
+        return i8gemm.dynamic_scaled_mm(x, prepared, out_dtype=torch.bfloat16)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    ms = time_steps(step, steps, flush)
+    ops = 2.0 * rows * n * k
+    tensor_peak = int8_peak["burst_tops"] if int8_peak else 2.0 * peaks["bf16_tflops"]
+    t_hbm, t_tensor = nbytes / (peaks["hbm_gbs"] * 1e9), ops / (tensor_peak * 1e12)
+    bound = "hbm" if t_hbm >= t_tensor else "tensor"
+    return {"workload": f"i8gemm_dense_M{rows}_K{k}_N{n}", "tokens": rows, "dtype": "int8(w8a8)", "ms_per_step": ms,
+            "value": rows / (ms * 1e-3), "launch_mode": "eager (row quantiser + GEMM, two launches)",
+            "l2": "flushed between steps (a buffer of twice the L2 is written)" if flush is not None else "inputs larger than L2",
+            "roofline": {"bound": bound, "achieved": nbytes / (ms * 1e-3) / 1e9 if bound == "hbm" else ops / (ms * 1e-3) / 1e12,
+                         "peak": peaks["hbm_gbs"] if bound == "hbm" else tensor_peak, "unit": "GB/s" if bound == "hbm" else "TOP/s",
+                         "frac": (t_hbm if bound == "hbm" else t_tensor) / (ms * 1e-3), "whole_op": True,
+                         "algorithmic_bytes": nbytes, "ops": ops}}
 
 
 # ---- expert parallel over the GPUs of one box (launched by torch.distributed.run) ----------------------------
