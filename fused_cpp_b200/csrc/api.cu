@@ -826,7 +826,8 @@ int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mod
   float best_ms = 0.0f;
   for (int round = 0; round < 4 && error == cudaSuccess; ++round) {
     cudaEventRecord(begin, nullptr);
-    error = fmoe::launch_mma_rate_probe(int8 != 0, n, iterations, mode, sms, status_block, nullptr);
+    error = (mode & 8) ? fmoe::launch_mma_rate_pair_probe(int8 != 0, n, iterations, mode & ~8, sms, status_block, nullptr)
+                       : fmoe::launch_mma_rate_probe(int8 != 0, n, iterations, mode, sms, status_block, nullptr);
     cudaEventRecord(end, nullptr);
     if (error == cudaSuccess) error = cudaEventSynchronize(end);
     float ms = 0.0f;
@@ -838,7 +839,8 @@ int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mod
   if (status_block) cudaFree(status_block);
   if (error != cudaSuccess) return cuda_fail(error, "MMA rate probe");
   const double elements_k = int8 ? 32.0 : 16.0;
-  const double ops = 2.0 * 128.0 * n * elements_k * static_cast<double>(iterations) * sms;
+  // One-SM MMAs: 128 x n per SM; two-SM MMAs (mode bit 3): 256 x n per pair of SMs.
+  const double ops = 2.0 * 128.0 * n * elements_k * static_cast<double>(iterations) * ((mode & 8) ? (sms & ~1) : sms);
   *tera_ops_per_s = static_cast<float>(ops / (best_ms * 1e-3) / 1e12);
   return FMOE_OK;
 }

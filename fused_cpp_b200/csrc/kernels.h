@@ -213,5 +213,7 @@ cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8
 
 // ---- probe.cu (diagnostic library only): tcgen05.mma issue-rate probe (128 x n x 32-byte MMAs back to back on every CTA)
 cudaError_t launch_mma_rate_probe(bool int8, int n, int iterations, int mode, int blocks, int* status, cudaStream_t stream);
+// The same for two-SM MMAs (256 x n x 32 bytes issued by the leader of every two-CTA cluster).
+cudaError_t launch_mma_rate_pair_probe(bool int8, int n, int iterations, int mode, int blocks, int* status, cudaStream_t stream);
 
 }  // namespace fmoe

@@ -4,7 +4,10 @@
 // roofline" in the prefill regime.  No global memory is touched; results are discarded.
 // mode bit 0 fills the operands with a non-zero pattern instead of zeros (zero operands toggle few wires and
 // draw less power than real data, so they give the rate at full clock rather than a sustainable one);
-// mode >> 8 = c > 0 commits to an mbarrier after every c MMAs, the cadence of a pipelined GEMM main loop.
+// mode >> 8 = c > 0 commits to an mbarrier after every c MMAs, the cadence of a pipelined GEMM main loop;
+// mode bit 1 lets a second thread (warp 1) issue the same chain into a second accumulator at the same time, and
+// mode bit 2 makes the one issuing thread alternate between the two accumulators (two independent chains): they
+// tell a limit of the issuing thread from one of the tensor pipe.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -31,27 +34,32 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int n, int iterations,
     reinterpret_cast<uint4*>(smem)[i] = make_uint4(h, h ^ 0x15150a0au, h ^ 0x2a0a2a15u, h ^ 0x0f0f3030u);
   }
   if (threadIdx.x == 0) {
-    ptx::mbar_init(&done, 1);
+    ptx::mbar_init(&done, (mode & 2) ? 2 : 1);
     ptx::mbar_init(&cadence, 1);
     abort_flag = 0;
     ptx::fence_barrier_init();
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 0) {
-    ptx::tmem_alloc(&tmem_base, 256);
+    ptx::tmem_alloc(&tmem_base, 512);
     ptx::tmem_relinquish();
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
   ptx::tcgen05_fence_after();
-  if (threadIdx.x == 0) {
+  const bool second_issuer = (mode & 2) != 0;
+  const bool alternate = (mode & 4) != 0;
+  if (threadIdx.x == 0 || (second_issuer && threadIdx.x == 32)) {
     const uint32_t a = ptx::smem_u32(smem);
     const uint32_t b = a + 16384;
     const uint32_t idesc = ptx::make_instr_desc(kInt8, 128, n);
     const int commit_every = mode >> 8;
-    for (int i = 0; i < iterations; ++i) {
+    const uint32_t accumulator = tmem_base + (threadIdx.x == 32 ? 256u : 0u);
+    const int mine = second_issuer ? iterations / 2 : iterations;  // the same number of MMAs per launch in every mode
+    for (int i = 0; i < mine; ++i) {
       const uint32_t k = static_cast<uint32_t>(i & 3) * 32;
-      ptx::umma_ss<kInt8>(tmem_base, ptx::make_smem_desc_sw128(a + k), ptx::make_smem_desc_sw128(b + k), idesc, i > 0 ? 1u : 0u);
+      const uint32_t target = accumulator + ((alternate && (i & 1)) ? 256u : 0u);
+      ptx::umma_ss<kInt8>(target, ptx::make_smem_desc_sw128(a + k), ptx::make_smem_desc_sw128(b + k), idesc, i > 1 ? 1u : 0u);
       if (commit_every > 0 && (i + 1) % commit_every == 0) ptx::tcgen05_commit(&cadence);
     }
     ptx::tcgen05_commit(&done);
@@ -61,7 +69,83 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int n, int iterations,
   __syncthreads();
   if (warp == 0) {
     ptx::tcgen05_fence_after();
-    ptx::tmem_dealloc(tmem_base, 256);
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// The same chain issued by the leader of a two-CTA cluster as tcgen05.mma.cta_group::2 of 256 x n x 32 bytes (every
+// CTA holds 128 A rows and n / 2 B rows in its shared memory).  mode >> 8 = c > 0: after every c MMAs the leader commits
+// to one mbarrier in each of the two CTAs, the cadence of the two-SM grouped GEMM's main loop.
+template <bool kInt8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1) mma_rate_pair_kernel(int n, int iterations, int mode, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  __shared__ uint64_t done;
+  __shared__ uint64_t cadence;
+  __shared__ uint32_t tmem_base;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5;
+  uint32_t cta;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta));
+  for (int i = threadIdx.x; i < (16384 + 16384) / 16; i += blockDim.x) {
+    const uint32_t h = (mode & 1) ? ((static_cast<uint32_t>(i) * 2654435761u) >> 7) & 0x3f3f3f3fu : 0u;
+    reinterpret_cast<uint4*>(smem)[i] = make_uint4(h, h ^ 0x15150a0au, h ^ 0x2a0a2a15u, h ^ 0x0f0f3030u);
+  }
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&done, 1);
+    ptx::mbar_init(&cadence, 1);
+    abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(&tmem_base)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  ptx::tcgen05_fence_after();
+  if (cta == 0 && threadIdx.x == 0) {
+    const uint32_t a = ptx::smem_u32(smem);
+    const uint32_t b = a + 16384;
+    const uint32_t idesc = ptx::make_instr_desc(kInt8, 256, n);
+    const int commit_every = mode >> 8;
+    uint32_t cadence0, cadence1, done0;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(cadence0) : "r"(ptx::smem_u32(&cadence)), "r"(0u));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(cadence1) : "r"(ptx::smem_u32(&cadence)), "r"(1u));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(done0) : "r"(ptx::smem_u32(&done)), "r"(0u));
+    for (int i = 0; i < iterations; ++i) {
+      const uint32_t k = static_cast<uint32_t>(i & 3) * 32;
+      const uint64_t desc_a = ptx::make_smem_desc_sw128(a + k);
+      const uint64_t desc_b = ptx::make_smem_desc_sw128(b + k);
+      const uint32_t accumulate = i > 0 ? 1u : 0u;
+      if constexpr (kInt8) {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+                     "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                     : "memory");
+      } else {
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_base),
+                     "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                     : "memory");
+      }
+      if (commit_every > 0 && (i + 1) % commit_every == 0) {
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cadence0) : "memory");
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cadence1) : "memory");
+      }
+    }
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(done0) : "memory");
+    ptx::mbar_wait(&done, 0, &abort_flag, status, 32);
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  // Neither CTA leaves (or frees tensor memory) while the other may still read its operands.
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (warp == 0) {
+    ptx::tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
@@ -73,6 +157,15 @@ cudaError_t launch_mma_rate_probe(bool int8, int n, int iterations, int mode, in
   cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (error != cudaSuccess) return error;
   kernel<<<blocks, 128, smem, stream>>>(n, iterations, mode, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_mma_rate_pair_probe(bool int8, int n, int iterations, int mode, int blocks, int* status, cudaStream_t stream) {
+  const size_t smem = 1024 + 16384 + 16384;
+  auto kernel = int8 ? mma_rate_pair_kernel<true> : mma_rate_pair_kernel<false>;
+  cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (error != cudaSuccess) return error;
+  kernel<<<blocks & ~1, 128, smem, stream>>>(n, iterations, mode, status);
   return cudaGetLastError();
 }
 
