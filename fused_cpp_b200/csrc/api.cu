@@ -707,11 +707,14 @@ DenseLayout dense_layout(int64_t rows, int k) {
   return d;
 }
 
+// Row tile of the dense GEMM: the smallest one-SM tile that holds a decode batch, the two-SM kernel (256-row work
+// items) for anything taller than one 128-row tile.
 int dense_row_tile(int64_t rows) {
   if (rows <= 16) return 16;
   if (rows <= 32) return 32;
   if (rows <= 64) return 64;
-  return 128;
+  if (rows <= 128) return 128;
+  return fmoe::kPairRowTile;
 }
 
 // One int8 GEMM with the dense epilogue over already-quantised rows.
@@ -759,7 +762,8 @@ int dense_prologue(const void* x, int x_is_bf16, int64_t rows, int k, int clamp_
                                              reinterpret_cast<float*>(base + layout->scale), stream);
   }
   if (error == cudaSuccess) {
-    error = fmoe::launch_dense_items(rows, *row_tile, layout->max_items, reinterpret_cast<int*>(base + layout->items),
+    error = fmoe::launch_dense_items(rows, *row_tile == fmoe::kPairRowTile ? 256 : *row_tile, layout->max_items,
+                                     reinterpret_cast<int*>(base + layout->items),
                                      reinterpret_cast<int*>(base + layout->status), stream);
   }
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm activation quantisation");

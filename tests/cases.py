@@ -102,12 +102,19 @@ I8GEMM_CASES = {
     "f32": (24, 64, 96, torch.float32, torch.float32, False),
     "wide": (150, 300, 200, torch.bfloat16, torch.bfloat16, False),
     "deep": (40, 2048, 272, torch.bfloat16, torch.float32, True),
+    # taller than one 128-row tile: the two-SM kernel's dense epilogue (three 256-row items, two channel blocks, fp32 + bias)
+    "tall": (600, 512, 384, torch.bfloat16, torch.float32, True),
+    "tall_bf16": (300, 144, 520, torch.bfloat16, torch.bfloat16, False),
 }
+
+
+# Seed offsets are fixed per name (the committed golden outputs depend on them), not derived from the table's order.
+I8GEMM_SEEDS = {"deep": 0, "f32": 1, "m1": 2, "m4": 3, "m9": 4, "wide": 5, "tall": 6, "tall_bf16": 7}
 
 
 def i8gemm_case(name: str) -> dict:
     m, k, n, x_dtype, out_dtype, with_bias = I8GEMM_CASES[name]
-    generator = torch.Generator().manual_seed(7000 + sorted(I8GEMM_CASES).index(name))
+    generator = torch.Generator().manual_seed(7000 + I8GEMM_SEEDS[name])
     weight = torch.randint(-16, 17, (n, k), dtype=torch.int8, generator=generator)
     weight_scale = torch.rand(n, generator=generator) * 0.05 + 0.01
     bias = torch.randn(n, generator=generator).to(torch.bfloat16) if with_bias else None
