@@ -316,8 +316,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
                                      reinterpret_cast<uint16_t*>(base + layout.a_rows), stream);
     if (error == cudaSuccess) error = fmoe::launch_gather_scalars(f.rows_scale, routes, sorted_routes, valid_rows, a_scale, stream);
   } else if (planes) {
-    error = fmoe::launch_split_rows_planes(static_cast<const uint16_t*>(f.x), routes, f.hidden, sorted_routes, f.top_k, valid_rows,
-                                           reinterpret_cast<int8_t*>(base + layout.a_rows), a_scale, stream);
+    error = fmoe::launch_split_tokens_scatter_planes(static_cast<const uint16_t*>(f.x), f.tokens, f.hidden, f.top_k,
+                                                     reinterpret_cast<const int*>(base + layout.route_pos),
+                                                     reinterpret_cast<int8_t*>(base + layout.a_rows), a_scale, stream);
   } else if (f.int8) {
     error = fmoe::launch_quantize_tokens_scatter(static_cast<const uint16_t*>(f.x), f.tokens, f.hidden, f.top_k,
                                                  reinterpret_cast<const int*>(base + layout.route_pos), cfg.numerics,

@@ -55,6 +55,10 @@ cudaError_t launch_quantize_tokens_scatter(const uint16_t* x, int64_t tokens, in
 // row, stored as two int8 rows (high plane at 2p, low plane at 2p + 1 of `planes`), row scale in scale[p].
 cudaError_t launch_split_rows_planes(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
                                      const int* valid_rows, int8_t* planes, float* scale, cudaStream_t stream);
+// The same split once per token, written to the sorted positions of its top_k routes (route_pos[t * top_k + slot],
+// -1 = dropped).
+cudaError_t launch_split_tokens_scatter_planes(const uint16_t* x, int64_t tokens, int cols, int top_k, const int* route_pos, int8_t* planes,
+                                               float* scale, cudaStream_t stream);
 // Same for fp32 sources (dense linear).  clamp_low is -128 or -127.
 cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
                                        int8_t* q, float* scale, cudaStream_t stream);

@@ -47,6 +47,46 @@ __device__ __forceinline__ float4 load_row4(const void* route_out, int64_t eleme
   }
 }
 
+// Tree merge of four channels with the slot count known at compile time: every row load and every product sits in a
+// register (a loop over a run-time slot count indexes its row array dynamically, which sends it to local memory).
+template <int TopK, bool kBf16Rows>
+__device__ __forceinline__ void tree_merge4(const void* route_out, int64_t base, int hidden, const bool* present, const float* weights,
+                                            float* result) {
+  float4 rows[TopK];
+#pragma unroll
+  for (int slot = 0; slot < TopK; ++slot) {
+    rows[slot] = present[slot] ? load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  }
+#pragma unroll
+  for (int lane = 0; lane < 4; ++lane) {
+    float values[TopK];
+#pragma unroll
+    for (int slot = 0; slot < TopK; ++slot) values[slot] = reinterpret_cast<const float*>(&rows[slot])[lane];
+    result[lane] = merge_fixed<TopK>(values, weights);
+  }
+}
+
+// The same for eight channels of bf16 rows (one 16-byte load per slot).
+template <int TopK>
+__device__ __forceinline__ void tree_merge8_bf16(const uint16_t* route_out, int64_t base, int hidden, const bool* present, const float* weights,
+                                                 float* result) {
+  uint4 rows[TopK];
+#pragma unroll
+  for (int slot = 0; slot < TopK; ++slot) {
+    rows[slot] = present[slot] ? *reinterpret_cast<const uint4*>(route_out + base + static_cast<int64_t>(slot) * hidden) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int lane = 0; lane < 8; ++lane) {
+    float values[TopK];
+#pragma unroll
+    for (int slot = 0; slot < TopK; ++slot) {
+      const uint32_t word = reinterpret_cast<const uint32_t*>(&rows[slot])[lane >> 1];
+      values[slot] = __uint_as_float((lane & 1) ? (word & 0xffff0000u) : (word << 16));
+    }
+    result[lane] = merge_fixed<TopK>(values, weights);
+  }
+}
+
 // The same merge over bf16 rows with eight channels per thread: one 16-byte load per slot, one 16-byte store.
 __global__ void __launch_bounds__(kMergeThreads)
 merge_bf16_rows8_kernel(const uint16_t* __restrict__ route_out, const float* __restrict__ topk_weights, const int* __restrict__ route_pos,
@@ -65,24 +105,11 @@ merge_bf16_rows8_kernel(const uint16_t* __restrict__ route_out, const float* __r
   const bool fixed = tree && (top_k == 2 || top_k == 4 || top_k == 6 || top_k == 8);
   float result[8];
   if (fixed) {
-    uint4 rows[8];
-    for (int slot = 0; slot < top_k; ++slot) {
-      rows[slot] = present[slot] ? *reinterpret_cast<const uint4*>(route_out + base + static_cast<int64_t>(slot) * hidden) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int lane = 0; lane < 8; ++lane) {
-      float values[8];
-#pragma unroll
-      for (int slot = 0; slot < 8; ++slot) {
-        const uint32_t word = reinterpret_cast<const uint32_t*>(&rows[slot])[lane >> 1];
-        values[slot] = __uint_as_float((lane & 1) ? (word & 0xffff0000u) : (word << 16));
-      }
-      switch (top_k) {
-        case 2: result[lane] = merge_fixed<2>(values, weights); break;
-        case 4: result[lane] = merge_fixed<4>(values, weights); break;
-        case 6: result[lane] = merge_fixed<6>(values, weights); break;
-        default: result[lane] = merge_fixed<8>(values, weights); break;
-      }
+    switch (top_k) {
+      case 2: tree_merge8_bf16<2>(route_out, base, hidden, present, weights, result); break;
+      case 4: tree_merge8_bf16<4>(route_out, base, hidden, present, weights, result); break;
+      case 6: tree_merge8_bf16<6>(route_out, base, hidden, present, weights, result); break;
+      default: tree_merge8_bf16<8>(route_out, base, hidden, present, weights, result); break;
     }
   } else {
 #pragma unroll
@@ -127,21 +154,11 @@ merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_
   float result[4];
   const bool fixed = tree && (top_k == 2 || top_k == 4 || top_k == 6 || top_k == 8);
   if (fixed) {
-    float4 rows[8];
-    for (int slot = 0; slot < top_k; ++slot) {
-      rows[slot] = present[slot] ? load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-#pragma unroll
-    for (int lane = 0; lane < 4; ++lane) {
-      float values[8];
-#pragma unroll
-      for (int slot = 0; slot < 8; ++slot) values[slot] = reinterpret_cast<const float*>(&rows[slot])[lane];
-      switch (top_k) {
-        case 2: result[lane] = merge_fixed<2>(values, weights); break;
-        case 4: result[lane] = merge_fixed<4>(values, weights); break;
-        case 6: result[lane] = merge_fixed<6>(values, weights); break;
-        default: result[lane] = merge_fixed<8>(values, weights); break;
-      }
+    switch (top_k) {
+      case 2: tree_merge4<2, kBf16Rows>(route_out, base, hidden, present, weights, result); break;
+      case 4: tree_merge4<4, kBf16Rows>(route_out, base, hidden, present, weights, result); break;
+      case 6: tree_merge4<6, kBf16Rows>(route_out, base, hidden, present, weights, result); break;
+      default: tree_merge4<8, kBf16Rows>(route_out, base, hidden, present, weights, result); break;
     }
   } else {
     result[0] = result[1] = result[2] = result[3] = 0.0f;

@@ -233,6 +233,51 @@ split_rows_planes_kernel(const uint16_t* __restrict__ x, int cols, const int* __
   }
 }
 
+// The same split once per TOKEN, stored to the sorted positions of its top_k routes (route_pos, -1 = dropped): the bits
+// every route would get from split_rows_planes_kernel, one read of x and one fixed-point conversion per token.
+__global__ void __launch_bounds__(kQuantThreads)
+split_tokens_scatter_planes_kernel(const uint16_t* __restrict__ x, int cols, int top_k, const int* __restrict__ route_pos,
+                                   int8_t* __restrict__ planes, float* __restrict__ scale_out) {
+  __shared__ float smem[32];
+  __shared__ int positions[32];
+  const int64_t token = blockIdx.x;
+  if (threadIdx.x < top_k) positions[threadIdx.x] = route_pos[token * top_k + threadIdx.x];
+  const uint4* src = reinterpret_cast<const uint4*>(x + token * cols);
+  const int vec16 = cols >> 4;
+  float local = 0.0f;
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    local = fmaxf(local, amax8(src[2 * v]));
+    local = fmaxf(local, amax8(src[2 * v + 1]));
+  }
+  const float amax = block_max(local, smem);  // its barriers also publish positions[]
+  const float scale = plane_row_scale(amax);
+  if (threadIdx.x < top_k && positions[threadIdx.x] >= 0) scale_out[positions[threadIdx.x]] = scale;
+  for (int v = threadIdx.x; v < vec16; v += kQuantThreads) {
+    float values[16];
+    unpack8(src[2 * v], values);
+    unpack8(src[2 * v + 1], values + 8);
+    uint32_t high[4] = {0, 0, 0, 0};
+    uint32_t low[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int fixed = plane_fixed_point(values[i], scale);
+      const int low_part = ((fixed + 128) & 255) - 128;
+      const int high_part = (fixed - low_part) >> 8;
+      high[i >> 2] |= (static_cast<uint32_t>(high_part) & 0xffu) << (8 * (i & 3));
+      low[i >> 2] |= (static_cast<uint32_t>(low_part) & 0xffu) << (8 * (i & 3));
+    }
+    const uint4 high_vector = make_uint4(high[0], high[1], high[2], high[3]);
+    const uint4 low_vector = make_uint4(low[0], low[1], low[2], low[3]);
+    for (int slot = 0; slot < top_k; ++slot) {
+      const int64_t position = positions[slot];
+      if (position >= 0) {
+        reinterpret_cast<uint4*>(planes + (2 * position) * cols)[v] = high_vector;
+        reinterpret_cast<uint4*>(planes + (2 * position + 1) * cols)[v] = low_vector;
+      }
+    }
+  }
+}
+
 // Dense linear: arbitrary cols, fp32 or bf16 source, zero-padded to cols_padded, clamp to [-128,127]
 // (single GEMM) or [-127,127] (paired GEMMs) with division and ties-to-even (csrc/i8gemm.cpp:384-399, :492-506).
 __global__ void __launch_bounds__(kQuantThreads)
@@ -315,6 +360,13 @@ cudaError_t launch_split_rows_planes(const uint16_t* x, int64_t out_rows, int co
   if (out_rows <= 0) return cudaSuccess;
   split_rows_planes_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows, planes,
                                                                                          scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_split_tokens_scatter_planes(const uint16_t* x, int64_t tokens, int cols, int top_k, const int* route_pos, int8_t* planes,
+                                               float* scale, cudaStream_t stream) {
+  if (tokens <= 0) return cudaSuccess;
+  split_tokens_scatter_planes_kernel<<<static_cast<unsigned>(tokens), kQuantThreads, 0, stream>>>(x, cols, top_k, route_pos, planes, scale);
   return cudaGetLastError();
 }
 

@@ -57,7 +57,11 @@ def _worker(rank, world, port, scenario, queue):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     try:
         import datetime
-        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+        try:
+            dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+        except Exception as error:  # noqa: BLE001 - the rendezvous itself failed: the runner tries again on a fresh port
+            queue.put((rank, "rendezvous", f"{type(error).__name__}: {error}"))
+            return
         queue.put((rank, "ok", scenario(rank, world)))
     except Exception as error:  # noqa: BLE001
         queue.put((rank, "error", f"{type(error).__name__}: {error}\n{traceback.format_exc()[-600:]}"))
@@ -83,12 +87,14 @@ def _run_once(scenario, world):
 
 
 def _run(scenario, world=2):
-    # The port is picked before the ranks start, so another process can take it in between; a rendezvous that
-    # fails for that reason (and only for that reason) is tried once more on a fresh port.
-    results = _run_once(scenario, world)
-    trouble = [payload for status, payload in results.values() if status == "error" and any(t in str(payload) for t in _RENDEZVOUS_TROUBLE)]
-    if trouble:
+    # The port is picked before the ranks start, so another process can take it in between; a run whose rendezvous
+    # failed (and only that: the scenario never started on that rank) is tried again on a fresh port, twice at most.
+    for _ in range(3):
         results = _run_once(scenario, world)
+        trouble = [payload for status, payload in results.values()
+                   if status == "rendezvous" or (status == "error" and any(t in str(payload) for t in _RENDEZVOUS_TROUBLE))]
+        if not trouble:
+            break
     return results
 
 
