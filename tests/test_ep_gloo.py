@@ -47,6 +47,24 @@ class OracleBackend:
         return merge(route_out.view(tokens, top_k, -1), topk_weights)
 
 
+def _by_value(payload):
+    """Tensors leave a rank as numpy arrays: a torch tensor put on a multiprocessing queue travels as a handle that
+    the receiver has to fetch from the sender, and a rank that has already exited cannot serve it."""
+    if isinstance(payload, torch.Tensor):
+        return ("tensor", payload.detach().cpu().contiguous().numpy())
+    if isinstance(payload, (tuple, list)):
+        return type(payload)(_by_value(item) for item in payload)
+    return payload
+
+
+def _from_value(payload):
+    if isinstance(payload, tuple) and len(payload) == 2 and isinstance(payload[0], str) and payload[0] == "tensor":
+        return torch.from_numpy(payload[1])
+    if isinstance(payload, (tuple, list)):
+        return type(payload)(_from_value(item) for item in payload)
+    return payload
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -62,7 +80,7 @@ def _worker(rank, world, port, scenario, queue):
         except Exception as error:  # noqa: BLE001 - the rendezvous itself failed: the runner tries again on a fresh port
             queue.put((rank, "rendezvous", f"{type(error).__name__}: {error}"))
             return
-        queue.put((rank, "ok", scenario(rank, world)))
+        queue.put((rank, "ok", _by_value(scenario(rank, world))))
     except Exception as error:  # noqa: BLE001
         queue.put((rank, "error", f"{type(error).__name__}: {error}\n{traceback.format_exc()[-600:]}"))
     finally:
@@ -83,7 +101,7 @@ def _run_once(scenario, world):
     results = [queue.get(timeout=180) for _ in procs]
     for p in procs:
         p.join(timeout=60)
-    return {rank: (status, payload) for rank, status, payload in results}
+    return {rank: (status, _from_value(payload) if status == "ok" else payload) for rank, status, payload in results}
 
 
 def _run(scenario, world=2):
