@@ -234,17 +234,22 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   // go through the one-SM kernel (64-row tile, every weight byte streamed once), the others through the
   // two-SM kernel (256-row work items).  Up to 64 tokens no expert can exceed 64 rows and the tile follows
   // the batch size (pick_row_tile).
-  // W8A16 runs every expert through the one-SM kernel (the int8 -> bf16 widening lives there): no split, and a
-  // 128-row tile above 64 tokens.
-  // Its fixed-point form runs on the int8 one-SM kernel with two token rows (planes) per route: the kernel's row tile
-  // is twice the routes of a work item, which caps an item at 128 routes as well.
+  // W8A16.  Its fixed-point form runs on the int8 kernels with two token rows (planes) per route: the kernel's row
+  // tile is twice the routes of a work item, so an item holds at most 128 routes; above 64 tokens the experts are
+  // split like W8A8's (thin ones to the one-SM kernel, the others to the two-SM kernel in 128-route items).  Its
+  // bf16-activation form runs every expert through the one-SM kernel (the int8 -> bf16 widening lives there): no
+  // split, and a 128-row tile above 64 tokens.
   const bool planes = f.w8a16 && umma && cfg.w8a16_form == FMOE_W8A16_FIXED_POINT;
-  const bool split = umma && !f.w8a16 && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
-  const bool w8a16_wide = f.w8a16 && f.tokens > kSplitRows;
+  const bool split = umma && (!f.w8a16 || planes) && cfg.gate_up_tile == 0 && cfg.down_tile == 0 && f.tokens > kSplitRows;
+  const bool w8a16_wide = f.w8a16 && !planes && f.tokens > kSplitRows;
   int tile_gu = split ? kSplitRows : (w8a16_wide && cfg.gate_up_tile == 0) ? 128 : pick_row_tile(cfg.gate_up_tile, f.tokens, umma);
   int tile_dn = split ? kSplitRows : (w8a16_wide && cfg.down_tile == 0) ? 128 : pick_row_tile(cfg.down_tile, f.tokens, umma);
-  if (f.w8a16) {
-    // The token-major W8A16 kernel holds a work item in the 128 lanes of one accumulator: taller tiles are cut to 128.
+  if (planes) {
+    // Tiles given by the caller: 16..128 routes per item on the one-SM kernel, 512 = the two-SM kernel; 256 is cut to 128.
+    if (tile_gu == 256) tile_gu = 128;
+    if (tile_dn == 256) tile_dn = 128;
+  } else if (f.w8a16) {
+    // The token-major widening kernel holds a work item in the 128 lanes of one accumulator: taller tiles are cut to 128.
     tile_gu = tile_gu > 128 ? 128 : tile_gu;
     tile_dn = tile_dn > 128 ? 128 : tile_dn;
   }
@@ -252,8 +257,9 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     return fail(FMOE_ERR_INVALID_ARGUMENT, "row tiles must be 16, 32, 64, 128, 256 or 512 = two-SM pairs (got %d, %d)", tile_gu, tile_dn);
   }
   // Tile 512 selects the two-SM kernel, whose work items hold up to 256 rows.
-  const int item_rows_gu = tile_gu == fmoe::kPairRowTile ? 256 : tile_gu;
-  const int item_rows_dn = tile_dn == fmoe::kPairRowTile ? 256 : tile_dn;
+  const int pair_item_rows = planes ? 128 : 256;  // routes of a two-SM work item (256 token rows either way)
+  const int item_rows_gu = tile_gu == fmoe::kPairRowTile ? pair_item_rows : tile_gu;
+  const int item_rows_dn = tile_dn == fmoe::kPairRowTile ? pair_item_rows : tile_dn;
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   char* base = static_cast<char*>(workspace);
@@ -267,7 +273,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   int* items_dn = items_gu + 4 * static_cast<size_t>(max_items);
   int* items_gu_big = items_dn + 4 * static_cast<size_t>(max_items);
   int* items_dn_big = items_gu_big + 4 * static_cast<size_t>(max_items);
-  const fmoe::ItemLists lists{item_rows_gu, item_rows_dn, items_gu, items_dn, max_items, split ? kSplitRows : 0, split ? 256 : 0,
+  const fmoe::ItemLists lists{item_rows_gu, item_rows_dn, items_gu, items_dn, max_items, split ? kSplitRows : 0, split ? pair_item_rows : 0,
                               items_gu_big, items_dn_big};
   int* scratch = reinterpret_cast<int*>(base + layout.scratch);
   float* a_scale = reinterpret_cast<float*>(base + layout.a_scale);
@@ -354,7 +360,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   gu.route_out = nullptr;
   gu.dump_acc = cfg.dump_acc1;
   gu.total_rows = routes;
-  gu.row_tile = planes ? 2 * tile_gu : tile_gu;
+  gu.row_tile = (planes && tile_gu != fmoe::kPairRowTile) ? 2 * tile_gu : tile_gu;
   const bool int8_gemm = f.int8 || planes;
 #ifdef FMOE_DIAG
   error = umma ? fmoe::launch_umma_grouped_gemm(gu, int8_gemm, true, stream) : fmoe::launch_simt_grouped_gemm(gu, f.int8, true, stream);
@@ -366,7 +372,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     big.items = items_gu_big;
     big.item_count_word = fmoe::kStatusItemsC;
     big.row_tile = fmoe::kPairRowTile;
-    error = fmoe::launch_umma_grouped_gemm(big, f.int8, true, stream);
+    error = fmoe::launch_umma_grouped_gemm(big, int8_gemm, true, stream);
   }
   if (error != cudaSuccess) return cuda_fail(error, "gate_up grouped GEMM");
   mark(FMOE_STAGE_GATE_UP + 1);
@@ -402,7 +408,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
   const bool compact_rows = peer ? f.peer_rows_bf16 : (cfg.route_rows_bf16 != 0 && !f.rows_mode);
   dn.route_out_bf16 = compact_rows ? 1 : 0;
   dn.dump_acc = cfg.dump_acc2;
-  dn.row_tile = planes ? 2 * tile_dn : tile_dn;
+  dn.row_tile = (planes && tile_dn != fmoe::kPairRowTile) ? 2 * tile_dn : tile_dn;
 #ifdef FMOE_DIAG
   error = umma ? fmoe::launch_umma_grouped_gemm(dn, int8_gemm, false, stream) : fmoe::launch_simt_grouped_gemm(dn, f.int8, false, stream);
 #else
@@ -413,7 +419,7 @@ int run_forward(const Forward& f, const fmoe_config* config, void* out, void* wo
     big.items = items_dn_big;
     big.item_count_word = fmoe::kStatusItemsD;
     big.row_tile = fmoe::kPairRowTile;
-    error = fmoe::launch_umma_grouped_gemm(big, f.int8, false, stream);
+    error = fmoe::launch_umma_grouped_gemm(big, int8_gemm, false, stream);
   }
   if (error != cudaSuccess) return cuda_fail(error, "down grouped GEMM");
   mark(FMOE_STAGE_DOWN + 1);

@@ -66,6 +66,28 @@ __device__ __forceinline__ void tree_merge4(const void* route_out, int64_t base,
   }
 }
 
+// Chain merge (fused multiply-adds in slot order from zero) of four channels with the slot count known at compile
+// time: the row loads are issued together instead of one per loop iteration.  Same operations in the same order as
+// the run-time loop.
+template <int TopK, bool kBf16Rows>
+__device__ __forceinline__ void chain_merge4(const void* route_out, int64_t base, int hidden, const bool* present, const float* weights,
+                                             float* result) {
+  float4 rows[TopK];
+#pragma unroll
+  for (int slot = 0; slot < TopK; ++slot) {
+    rows[slot] = present[slot] ? load_row4<kBf16Rows>(route_out, base + static_cast<int64_t>(slot) * hidden) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  }
+  result[0] = result[1] = result[2] = result[3] = 0.0f;
+#pragma unroll
+  for (int slot = 0; slot < TopK; ++slot) {
+    const float w = weights[slot];
+    result[0] = __fmaf_rn(rows[slot].x, w, result[0]);
+    result[1] = __fmaf_rn(rows[slot].y, w, result[1]);
+    result[2] = __fmaf_rn(rows[slot].z, w, result[2]);
+    result[3] = __fmaf_rn(rows[slot].w, w, result[3]);
+  }
+}
+
 // The same for eight channels of bf16 rows (one 16-byte load per slot).
 template <int TopK>
 __device__ __forceinline__ void tree_merge8_bf16(const uint16_t* route_out, int64_t base, int hidden, const bool* present, const float* weights,
@@ -160,6 +182,12 @@ merge_kernel(const void* __restrict__ route_out, const float* __restrict__ topk_
       case 6: tree_merge4<6, kBf16Rows>(route_out, base, hidden, present, weights, result); break;
       default: tree_merge4<8, kBf16Rows>(route_out, base, hidden, present, weights, result); break;
     }
+  } else if (top_k == 8) {
+    chain_merge4<8, kBf16Rows>(route_out, base, hidden, present, weights, result);
+  } else if (top_k == 9) {
+    chain_merge4<9, kBf16Rows>(route_out, base, hidden, present, weights, result);
+  } else if (top_k == 4) {
+    chain_merge4<4, kBf16Rows>(route_out, base, hidden, present, weights, result);
   } else {
     result[0] = result[1] = result[2] = result[3] = 0.0f;
     for (int slot = 0; slot < top_k; ++slot) {

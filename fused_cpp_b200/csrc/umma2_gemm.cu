@@ -189,26 +189,34 @@ struct UnitInfo {
   int expert, row0, rows, block;
 };
 
-__device__ __forceinline__ UnitInfo load_unit(const int* __restrict__ items, int64_t unit, int64_t units, int n_blocks) {
+// rows_per_route: 2 in the two-plane form (first row and row count come back in token rows), else 1.
+__device__ __forceinline__ UnitInfo load_unit(const int* __restrict__ items, int64_t unit, int64_t units, int n_blocks, int rows_per_route = 1) {
   UnitInfo info = {0, 0, 0, 0};
   if (unit < units) {
     const int item = static_cast<int>(unit / n_blocks);
     const int4 packed = __ldg(reinterpret_cast<const int4*>(items) + item);
     info.expert = packed.x;
-    info.row0 = packed.y;
-    info.rows = packed.z;
+    info.row0 = packed.y * rows_per_route;
+    info.rows = packed.z * rows_per_route;
     info.block = static_cast<int>(unit - static_cast<int64_t>(item) * n_blocks);
   }
   return info;
 }
 
-template <bool kInt8, bool kGateUp, bool kDense>
+// kPlanes (an instance of the int8 kernel; W8A16 in its fixed-point form): every route arrives as two int8 token rows,
+// the high plane at row 2p and the low plane at row 2p + 1 of its 16-bit fixed-point activations, so a work item of r
+// routes has 2r token rows (at most 128 routes) and accumulator columns (2j, 2j + 1) belong to route j: the exact
+// integer dot product is 256 * column(2j) + column(2j + 1) (common.cuh: dequantize_planes).  Work items are given in
+// routes; loads, the MMA's N and the epilogue count plane rows.
+template <bool kInt8, bool kGateUp, bool kDense, bool kPlanes = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap token_map,
                               GroupedGemmArgs args) {
+  static_assert(!kPlanes || (kInt8 && !kDense), "the two-plane form is an instance of the int8 grouped kernel");
   constexpr int kElemBytes = kInt8 ? 1 : 2;
   constexpr int kBlockKElems = kBlockKBytes / kElemBytes;
   constexpr int kChannelsPerUnit = kGateUp ? 128 : 256;  // output channels one pair finishes per work unit
+  constexpr int kRowsPerRoute = kPlanes ? 2 : 1;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -262,9 +270,9 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
-      UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks);
+      UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks, kRowsPerRoute);
       for (int64_t unit = first_unit; unit < units; unit += unit_stride) {
-        const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks);  // in flight during this unit
+        const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks, kRowsPerRoute);  // in flight during this unit
         // The MMA takes the first N/2 token rows from the leader's tile and the other N/2 from the follower's.
         const int mma_n = min(kPairTokens, (cur.rows + 31) & ~31);
         const int token_row = cur.row0 + (mma_n / 2) * static_cast<int>(cta);
@@ -337,9 +345,9 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       uint32_t phase = 0;
       uint32_t a_lo = a_lo_stage0;
       int local = 0;
-      UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks);
+      UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks, kRowsPerRoute);
       for (int64_t unit = first_unit; unit < units; unit += unit_stride, ++local) {
-        const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks);
+        const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks, kRowsPerRoute);
         const uint32_t buffer = static_cast<uint32_t>(local) & 1u;
         const uint32_t use = static_cast<uint32_t>(local) >> 1;
         // N follows the rows this unit really has (a multiple of 32 for two-SM MMAs).
@@ -384,7 +392,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
     const bool native = args.numerics == FMOE_NUMERICS_NATIVE;
     const float limit = args.swiglu_limit;
     const int activation = args.activation;
-    uint32_t* const dump = static_cast<uint32_t*>(args.dump_acc);
+    uint32_t* const dump = kPlanes ? nullptr : static_cast<uint32_t*>(args.dump_acc);  // the dump holds one row per route
     const bool low = lane < 16;  // gate_up: lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same channels
     // Output channel of this thread inside the unit's channel block.
     const int channel_in_unit = kGateUp ? 64 * static_cast<int>(cta) + 16 * quarter + (lane & 15)
@@ -404,7 +412,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       ThreadUnit t = {0.0f, 0ull, kInt8 ? 1.0f : 0.0f, kInt8 ? 1.0f : 0.0f, 0.0f};
       if (!valid) return t;
       if (tid < info.rows) {
-        const int row = info.row0 + tid;
+        const int row = (info.row0 + tid) / kRowsPerRoute;  // sorted position of the column's route
         if (kInt8) t.column_scale = args.a_scale[row];
         if constexpr (kDense) {
           t.column_rowptr = reinterpret_cast<uint64_t>(args.dense_out) + static_cast<uint64_t>(row) * n_out * (args.dense_out_bf16 ? 2 : 4);
@@ -463,8 +471,8 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       }
     };
 
-    UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks);
-    UnitInfo next = load_unit(args.items, first_unit + unit_stride, units, n_blocks);
+    UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks, kRowsPerRoute);
+    UnitInfo next = load_unit(args.items, first_unit + unit_stride, units, n_blocks, kRowsPerRoute);
     ThreadUnit mine = fetch(cur, first_unit < units);
     if (tid < 256) {
       ctl->meta[0].scale[tid] = mine.column_scale;
@@ -478,7 +486,7 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
       const uint32_t use = static_cast<uint32_t>(local) >> 1;
       // Loads for the next unit (and the work item of the one after) are issued now and consumed after this unit.
       const ThreadUnit upcoming = fetch(next, unit + unit_stride < units);
-      const UnitInfo after = load_unit(args.items, unit + 2 * unit_stride, units, n_blocks);
+      const UnitInfo after = load_unit(args.items, unit + 2 * unit_stride, units, n_blocks, kRowsPerRoute);
 
       const int rows = cur.rows;
       const int row0 = cur.row0;
@@ -497,7 +505,44 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         ptx::tmem_ld_wait();
         const int col0 = chunk * 32;
         const bool fast = block_full && col0 + 32 <= rows && dump == nullptr;  // warp-uniform
-        if constexpr (kGateUp) {
+        if constexpr (kGateUp && kPlanes) {
+          // Columns 4q .. 4q + 3 are the (high, low) planes of two routes.  Lanes l (gate) and l + 16 (up) hold the same
+          // channel: the gate lane finishes the first route of the four columns, the up lane the second, each receiving
+          // the other's two plane values of that route.
+          const float* scale = meta->scale + col0;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t first = __shfl_xor_sync(0xffffffffu, low ? v[4 * q + 2] : v[4 * q], 16);
+            const uint32_t second = __shfl_xor_sync(0xffffffffu, low ? v[4 * q + 3] : v[4 * q + 1], 16);
+            const int column = col0 + 4 * q + (low ? 0 : 2);  // plane row of this lane's route inside the item
+            if (column >= rows || !channel_ok) continue;
+            const int gate_high = static_cast<int>(low ? v[4 * q] : first);
+            const int gate_low = static_cast<int>(low ? v[4 * q + 1] : second);
+            const int up_high = static_cast<int>(low ? first : v[4 * q + 2]);
+            const int up_low = static_cast<int>(low ? second : v[4 * q + 3]);
+            const float a = scale[4 * q + (low ? 0 : 2)];
+            const float gate = dequantize_planes(gate_high, gate_low, a, mine.scale_gate);
+            const float up = dequantize_planes(up_high, up_low, a, mine.scale_up);
+            args.y[static_cast<int64_t>((row0 + column) >> 1) * n_out + n] =
+                activation == FMOE_ACT_SILU ? swiglu_to_bf16_with(gate, up, limit, exp_table) : other_activation_to_bf16(activation, gate, up);
+          }
+        } else if constexpr (kPlanes) {
+          // down: adjacent columns are the two planes of one route; the route's output row address is staged per column.
+          const bool bf16_out = args.route_out_bf16 != 0;
+          const uint64_t n_bytes = static_cast<uint64_t>(n) * (bf16_out ? 2 : 4);
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const int column = col0 + j;
+            if (column >= rows || !channel_ok) continue;
+            const float value = dequantize_planes(static_cast<int>(v[j]), static_cast<int>(v[j + 1]), meta->scale[column], mine.scale_gate);
+            const uint64_t rowptr = meta->rowptr[column];
+            if (bf16_out) {
+              *reinterpret_cast<uint16_t*>(rowptr + n_bytes) = f32_to_bf16_bits(value);
+            } else {
+              *reinterpret_cast<float*>(rowptr + n_bytes) = value;
+            }
+          }
+        } else if constexpr (kGateUp) {
           // Lanes l (gate) and l + 16 (up) hold the same channel: the gate lane finishes the even columns, the
           // up lane the odd ones, each receiving the other's value of that column.  Output rows are the sorted
           // rows themselves: row0 + column.
@@ -661,9 +706,9 @@ bool make_gate_up_map(CUtensorMap* map, const void* base, bool int8, uint64_t ex
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool kInt8, bool kGateUp, bool kDense>
+template <bool kInt8, bool kGateUp, bool kDense, bool kPlanes = false>
 cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
-  auto kernel = umma_pair_grouped_gemm_kernel<kInt8, kGateUp, kDense>;
+  auto kernel = umma_pair_grouped_gemm_kernel<kInt8, kGateUp, kDense, kPlanes>;
   static PerDeviceOnce configured;
   const int device = current_device_ordinal();
   if (configured.needed(device)) {
@@ -686,7 +731,8 @@ cudaError_t launch_pair(const GroupedGemmArgs& args, cudaStream_t stream) {
   } else {
     weights_ok = make_tensor_map(&weight_map, args.weights, kInt8, static_cast<uint64_t>(args.experts) * n_total, args.k, kRowsPerCta);
   }
-  if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, static_cast<uint64_t>(args.total_rows), args.k, kRowsPerCta)) {
+  const uint64_t token_rows = static_cast<uint64_t>(args.total_rows) * (kPlanes ? 2 : 1);
+  if (!weights_ok || !make_tensor_map(&token_map, args.a_rows, kInt8, token_rows, args.k, kRowsPerCta)) {
     return cudaErrorInvalidValue;
   }
   const int sms = sm_count_of_current_device();
@@ -710,6 +756,11 @@ bool umma_pair_supported(bool gate_up, int n_out, int64_t output_rows) {
 cudaError_t launch_umma_pair_grouped_gemm(const GroupedGemmArgs& args, bool int8, bool gate_up, cudaStream_t stream) {
   if (args.max_items <= 0 || args.total_rows <= 0) return cudaSuccess;
   if (!umma_pair_supported(gate_up, args.n_out, args.total_rows)) return cudaErrorInvalidValue;
+  if (args.w8a16 == 2) {
+    // W8A16 in its fixed-point form: int8 kernel, two token rows per route, work items of at most 128 routes.
+    if (!int8 || args.dense_out != nullptr || args.a_scale == nullptr) return cudaErrorInvalidValue;
+    return gate_up ? launch_pair<true, true, false, true>(args, stream) : launch_pair<true, false, false, true>(args, stream);
+  }
   if (args.dense_out != nullptr) {
     if (!int8 || gate_up) return cudaErrorInvalidValue;
     return launch_pair<true, false, true>(args, stream);

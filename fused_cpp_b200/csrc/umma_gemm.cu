@@ -746,7 +746,7 @@ cudaError_t launch_umma_grouped_gemm(const GroupedGemmArgs& caller_args, bool in
     // int8 weights, activations as two int8 planes per route: the int8 one-SM kernel with paired accumulator columns;
     // row_tile counts plane rows (two per route).
     if (!int8 || args.dense_out != nullptr || args.w_scale == nullptr || args.a_scale == nullptr) return cudaErrorInvalidValue;
-    if (args.row_tile == kPairRowTile) return cudaErrorInvalidValue;
+    if (args.row_tile == kPairRowTile) return launch_umma_pair_grouped_gemm(args, true, gate_up, stream);  // items of at most 128 routes
     return gate_up ? launch_tile<true, true, false, false, true>(args, stream) : launch_tile<true, false, false, false, true>(args, stream);
   }
   if (args.w8a16) {

@@ -74,7 +74,7 @@ def _check(case, result, limit=0.0, form="bf16"):
 
 
 @pytest.mark.parametrize("form", sorted(FORMS))
-@pytest.mark.parametrize("tile", [0, 16, 32, 64, 128, 256])
+@pytest.mark.parametrize("tile", [0, 16, 32, 64, 128, 256, 512])
 @pytest.mark.parametrize("name", cases.W8A16_CASES)
 def test_w8a16_matches_oracle_for_every_row_tile(cuda_device, name, tile, form):
     case = cases.w8a8_case(name)
