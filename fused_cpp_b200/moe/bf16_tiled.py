@@ -248,6 +248,16 @@ def prepare_routed_shared_moe_w8a16_tiled_quantized_weights(routed_w13_weight, r
 # ---- forward -------------------------------------------------------------------------------------
 
 def _plan_args(plan: AsyncMoEPlanV2):
+    """The plan as the native op's positional arguments.  Plans are frozen, so the tuple is built once per plan object
+    and kept on it."""
+    cached = plan.__dict__.get("_native_args")
+    if cached is None:
+        cached = _build_plan_args(plan)
+        object.__setattr__(plan, "_native_args", cached)
+    return cached
+
+
+def _build_plan_args(plan: AsyncMoEPlanV2):
     def i64(t):
         return t.to(torch.int64).contiguous()
     return (i64(plan.task_expert_ids), i64(plan.task_core_begins), i64(plan.task_threads), i64(plan.task_dep_offsets),

@@ -8,6 +8,8 @@ geometry selectors and carry the row-tile of the gate_up / down grouped GEMM (0 
 """
 from __future__ import annotations
 
+import functools
+
 from dataclasses import dataclass, fields
 from typing import Mapping, Sequence
 
@@ -285,7 +287,14 @@ def upgrade_legacy_async_plan(plan: Mapping[str, object]) -> dict[str, object]:
 
 
 def gpu_placeholder_plan(gate_up_tile: int = 0, down_tile: int = 0) -> AsyncMoEPlanV2:
-    """The one-task strict plan a GPU runtime hands to the op: no CPU placement, tile ids in the window fields."""
+    """The one-task strict plan a GPU runtime hands to the op: no CPU placement, tile ids in the window fields.
+    One (immutable) object per tile pair: building and validating twenty small tensors per forward is measurable
+    next to a decode layer of 1.4 ms."""
+    return _cached_placeholder_plan(int(gate_up_tile), int(down_tile))
+
+
+@functools.lru_cache(maxsize=256)
+def _cached_placeholder_plan(gate_up_tile: int, down_tile: int) -> AsyncMoEPlanV2:
     return AsyncMoEPlanV2(
         num_threads=1, execution_mode=ASYNC_MOE_EXECUTION_STRICT,
         thread_cpu_ids=torch.zeros(1, dtype=torch.int64), task_expert_ids=torch.zeros(1, dtype=torch.int64),
