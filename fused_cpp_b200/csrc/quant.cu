@@ -342,6 +342,14 @@ cudaError_t launch_quantize_rows(const uint16_t* x, int64_t out_rows, int cols, 
   if (out_rows <= 0) return cudaSuccess;
   const int vec16 = cols >> 4;
   const unsigned warp_blocks = static_cast<unsigned>((out_rows + kQuantThreads / 32 - 1) / (kQuantThreads / 32));
+  // A few rows (decode): one CTA per row spreads a row over 256 threads, where one warp per row would walk its 64
+  // values per lane alone on an SM (10.7 us against the other kernel's ~5 us for 8 rows of 2048 columns).
+  const bool few_rows = out_rows <= 592;  // four CTAs per SM at most
+  if (few_rows) {
+    quantize_rows_kernel<<<static_cast<unsigned>(out_rows), kQuantThreads, 0, stream>>>(x, cols, sorted_routes, top_k, valid_rows,
+                                                                                       numerics, weight_mode, q, scale);
+    return cudaGetLastError();
+  }
   if (vec16 <= 64) {
     quantize_rows_warp_kernel<2><<<warp_blocks, kQuantThreads, 0, stream>>>(x, out_rows, cols, sorted_routes, top_k, valid_rows, numerics,
                                                                              weight_mode, q, scale);
