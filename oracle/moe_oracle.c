@@ -16,6 +16,10 @@
  *   BF16 expert FFN      src/fused_cpp/moe/naive.py:223-269 ; csrc/moe/arm/sve_bf16/packing.cpp:51-73
  *   BF16 top-k merge     csrc/moe/arm/sve_bf16/route_merge.cpp:48-86
  *   dense W8A8 linear    csrc/i8gemm.cpp:366-399 (scalar fallback)
+ *   W8A16 expert FFN     csrc/moe/arm/common/fused_moe_bf16_tiled.cpp:4916-4948, 8740-8760 (int8 weights, bf16
+ *                        activations, channel scale on the fp32 accumulator); the variant with the activations as
+ *                        16-bit fixed point per row is the CUDA library's own default form, restated here so that it
+ *                        can be checked bit for bit, and pinned to the reference to tolerance only
  *
  * Parity pins: tests/golden holds outputs of the reference's own Python functions
  * (tests/test_moe_w8a8.py::_quantize_row/_reference and fused_cpp.moe.naive.fused_moe_naive)
