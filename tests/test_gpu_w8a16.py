@@ -108,6 +108,26 @@ def test_w8a16_at_v3_dims(cuda_device, shape, form):
     _check(case, _run(case, cuda_device, form), form=form)
 
 
+@pytest.mark.parametrize("form", sorted(FORMS))
+@pytest.mark.parametrize("activation", [_lib.ACTIVATION_GELU, _lib.ACTIVATION_SWIGLUOAI], ids=["gelu", "swigluoai"])
+@pytest.mark.parametrize("name", ["ragged", "wide"])
+def test_w8a16_other_activations(cuda_device, name, activation, form):
+    """gelu and swigluoai (gate channels then up channels, as the library takes them) through both forms and both
+    kernels ("wide" has experts above 64 rows: the two-SM kernel in the fixed form)."""
+    case = cases.w8a8_case(name)
+    result = _run(case, cuda_device, form, activation=activation)
+    assert result.status()[0] == 0
+    args = (case["x"], case["w13"], case["s13"], case["w2"], case["s2"], case["topk_weights"], case["topk_ids"])
+    expected = oracle.w8a16_forward(*args, 0.0, activation=int(activation)).float()
+    out = result.out.cpu().float()
+    assert float((out - expected).norm() / expected.norm()) <= 5e-3
+    if form == "fixed":
+        exact = oracle.w8a16_forward(*args, 0.0, activation=int(activation), fixed_point=True)
+        # erf / exp of the two sides come from different libraries: the bf16 rounding of the intermediate may differ
+        # in the last place on a few elements, so this is a tolerance far below the form's own, not bit-equality.
+        assert float((out - exact.float()).norm() / exact.float().norm()) <= 2e-3
+
+
 def test_w8a16_fixed_point_survives_outliers_and_zero_rows(cuda_device):
     """Rows whose maximum is 2^10 times their typical value (elements far below max / 128 round to the fixed-point
     quantum), an all-zero token and a token of one non-zero element: the fixed form stays bit-exact against its
