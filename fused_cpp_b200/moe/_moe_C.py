@@ -559,8 +559,10 @@ def fused_moe_w8a16_tiled_async_plan_v2(
         global_num_experts=-1, skip_weighted=False, silu_poly_degree=5, backend_n_tile=8, out=None, early_merge=-1,
         cache_dequant=False):
     """The W8A16 forward op (csrc/moe/module.cpp:180-194).  cache_dequant is accepted and has no effect: it selects
-    the reference's cached bf16 copy of a weight window, a CPU cache-blocking device; here the int8 tile is widened
-    in shared memory on every pass and the per-channel scale multiplies the fp32 accumulator."""
+    the reference's cached bf16 copy of a weight window, a CPU cache-blocking device; here the int8 weights meet the
+    activations as they lie in memory (activations as 16-bit fixed point per row on the int8 tensor cores, or, with
+    FUSED_CPP_MOE_W8A16_FORM=bf16, bf16 activations against weight tiles widened in shared memory) and the per-channel
+    scale multiplies the accumulator."""
     if plan_version != 2:
         raise RuntimeError("W8A16 async plan requires plan_version 2")
     if input.dim() != 2 or input.dtype != torch.bfloat16 or input.device.type != "cuda":
