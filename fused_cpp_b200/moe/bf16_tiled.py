@@ -34,7 +34,8 @@ class PreparedBF16TiledFusedMoEWeights:
 
 @dataclass(frozen=True)
 class PreparedW8A16TiledFusedMoEWeights:
-    """Per-output-channel int8 expert weights + fp32 scales, multiplied with unquantised bf16 activations."""
+    """Per-output-channel int8 expert weights + fp32 scales for the W8A16 path (16-bit activations: 16-bit fixed point per
+    row by default, or bf16 as they are with FUSED_CPP_MOE_W8A16_FORM=bf16)."""
     w13: tuple[torch.Tensor, int, int, torch.Tensor]
     w2: tuple[torch.Tensor, int, int, torch.Tensor]
     fused_silu: bool = True

@@ -20,7 +20,7 @@ W8A8_SHAPES = {
     "cfg1": synthetic.CONFIG_SMALL_W8A8,
 }
 W8A8_CASES = ["ref23", "tiny", "ragged", "wide", "cfg1"]
-# W8A16 reuses the int8 weights and scales of these W8A8 cases with the bf16 activations left unquantised.
+# W8A16 reuses the int8 weights and scales of these W8A8 cases with 16-bit activations (bf16, or their 16-bit fixed-point form).
 W8A16_CASES = ["tiny", "ragged", "wide", "cfg1"]
 
 BF16_SHAPES = {
