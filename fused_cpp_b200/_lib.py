@@ -571,14 +571,16 @@ class PeerContext:
 
 
 def probe_mma_rate(int8: bool, n: int = 256, iterations: int = 20000, *, nonzero: bool = False, commit_every: int = 0,
-                   second_issuer: bool = False, alternate: bool = False, two_sm: bool = False) -> float:
+                   second_issuer: bool = False, alternate: bool = False, two_sm: bool = False, round_trips: bool = False) -> float:
     """Measured dense tensor-core peak (tera-ops/s) for a 128 x n MMA tile on the current GPU.
 
     nonzero: operands hold a non-zero pattern instead of zeros; commit_every: a tcgen05.commit after every c MMAs;
     second_issuer: two threads of different warps issue half of the MMAs each, into separate accumulators;
     alternate: the one issuing thread alternates between two accumulators; two_sm: cta_group::2 MMAs of 256 x n issued
-    by the leader of every two-CTA cluster."""
+    by the leader of every two-CTA cluster; round_trips (needs commit_every = c): rounds of c MMAs, a commit and a wait
+    for it, so that c x the time per MMA is the latency of one pipeline stage."""
     value = ctypes.c_float(0.0)
-    mode = (1 if nonzero else 0) | (2 if second_issuer else 0) | (4 if alternate else 0) | (8 if two_sm else 0) | (commit_every << 8)
+    mode = ((1 if nonzero else 0) | (2 if second_issuer else 0) | (4 if alternate else 0) | (8 if two_sm else 0) | (16 if round_trips else 0)
+            | (commit_every << 8))
     check(load_diag().fmoe_probe_mma_rate(1 if int8 else 0, n, iterations, mode, ctypes.byref(value)), load_diag())
     return float(value.value)

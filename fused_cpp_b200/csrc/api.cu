@@ -822,6 +822,8 @@ int fmoe_probe_mma_rate(int32_t int8, int32_t n, int32_t iterations, int32_t mod
   int status = check_device();
   if (status != FMOE_OK) return status;
   // The iteration cap keeps one launch (about 0.1 us per MMA at n = 256) far below the kernels' one-second wait limit.
+  if ((mode & 16) && (mode >> 8) <= 0) return fail(FMOE_ERR_INVALID_ARGUMENT, "probe: the round-trip mode needs c = mode >> 8 > 0");
+  if ((mode & 16) && iterations > 100000) iterations = 100000;  // a round trip is microseconds, not tens of nanoseconds
   if (tera_ops_per_s == nullptr || iterations <= 0 || iterations > 1000000 || n < 16 || n > 256 || n % 16 != 0) {
     return fail(FMOE_ERR_INVALID_ARGUMENT, "probe: n must be a multiple of 16 in [16, 256] and iterations in 1..1000000");
   }

@@ -55,6 +55,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// One lane of the (converged) warp: true in exactly one lane.  Code that feeds tcgen05.mma / TMA should keep the whole
+// warp in the loop and predicate only the issuing instructions with this flag: addresses, descriptors and counters then
+// stay warp-uniform, and the compiler can hold them in the uniform registers those instructions read.  Inside a
+// `lane == 0` branch every operand has to be moved over from ordinary registers each time.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(elected));
+  return elected != 0;
+}
+
+// Non-blocking test of a phase (mbarrier.try_wait may park the thread for a while before it answers).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait.  Returns true when the phase completed, false when the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int site) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -62,6 +93,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   while (true) {
     for (int spin = 0; spin < 64; ++spin) {
       if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag) return false;
+    if (global_timer_ns() - start > kWaitLimitNs) {
+      *abort_flag = 1;
+      if (atomicCAS(status + kStatusError, 0, FMOE_ERR_DEVICE_WAIT) == 0) {
+        status[kStatusDetail] = static_cast<int>(blockIdx.x);
+        status[kStatusWaitSite] = site;
+      }
+      return false;
+    }
+  }
+}
+
+// The same bounded wait, polling with test_wait: for the one or two threads of a CTA whose wake-up latency is on the
+// critical path of the pipeline.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int site) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer_ns();
+  while (true) {
+    for (int spin = 0; spin < 256; ++spin) {
+      if (mbar_test_wait(bar, parity)) return true;
     }
     if (*abort_flag) return false;
     if (global_timer_ns() - start > kWaitLimitNs) {

@@ -203,6 +203,15 @@ __device__ __forceinline__ UnitInfo load_unit(const int* __restrict__ items, int
   return info;
 }
 
+// The same unit with every field taken from lane 0 (all lanes hold the same values already).
+__device__ __forceinline__ UnitInfo warp_uniform(UnitInfo info) {
+  info.expert = __shfl_sync(0xffffffffu, info.expert, 0);
+  info.row0 = __shfl_sync(0xffffffffu, info.row0, 0);
+  info.rows = __shfl_sync(0xffffffffu, info.rows, 0);
+  info.block = __shfl_sync(0xffffffffu, info.block, 0);
+  return info;
+}
+
 // kPlanes (an instance of the int8 kernel; W8A16 in its fixed-point form): every route arrives as two int8 token rows,
 // the high plane at row 2p and the low plane at row 2p + 1 of its 16-bit fixed-point activations, so a work item of r
 // routes has 2r token rows (at most 128 routes) and accumulator columns (2j, 2j + 1) belong to route j: the exact
@@ -222,13 +231,15 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   PairControl* ctl = reinterpret_cast<PairControl*>(smem + static_cast<size_t>(kStages) * kStageBytes);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);  // the same value, known to be warp-uniform
   const int lane = threadIdx.x & 31;
   const uint32_t cta = cluster_cta_rank();
   const bool leader = cta == 0;
   int* status = args.status_rw;
 
-  const int items = min(args.status[args.item_count_word], args.max_items);
+  // (Values that come from global loads pass through a shuffle where the warps that feed TMA and the tensor pipe use
+  // them: it changes nothing but lets the compiler treat them as warp-uniform.)
+  const int items = __shfl_sync(0xffffffffu, min(args.status[args.item_count_word], args.max_items), 0);
   const int n_blocks = (args.n_out + kChannelsPerUnit - 1) / kChannelsPerUnit;
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   const int64_t units = static_cast<int64_t>(items) * n_blocks;
@@ -257,22 +268,26 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
   __syncthreads();
   cluster_sync();  // the peer's barriers are initialised before anything signals them
   ptx::tcgen05_fence_after();
-  const uint32_t tmem_base = ctl->tmem_base;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);
   volatile int* abort_flag = &ctl->abort_flag;
   const uint32_t smem_base = ptx::smem_u32(smem);
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
-    if (lane == 0) {
-      ptx::prefetch_tensormap(&weight_map);
-      ptx::prefetch_tensormap(&token_map);
+    // The whole warp walks the loop; one elected lane issues the loads (ptx::elect_one).
+    {
+      const bool issuer = ptx::elect_one();
+      if (issuer) {
+        ptx::prefetch_tensormap(&weight_map);
+        ptx::prefetch_tensormap(&token_map);
+      }
       const uint32_t full_leader0 = map_to_cta(ptx::smem_u32(&ctl->full[0]), 0);
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
-      UnitInfo cur = load_unit(args.items, first_unit, units, n_blocks, kRowsPerRoute);
+      UnitInfo cur = warp_uniform(load_unit(args.items, first_unit, units, n_blocks, kRowsPerRoute));
       for (int64_t unit = first_unit; unit < units; unit += unit_stride) {
-        const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks, kRowsPerRoute);  // in flight during this unit
+        const UnitInfo next = warp_uniform(load_unit(args.items, unit + unit_stride, units, n_blocks, kRowsPerRoute));  // in flight during this unit
         // The MMA takes the first N/2 token rows from the leader's tile and the other N/2 from the follower's.
         const int mma_n = min(kPairTokens, (cur.rows + 31) & ~31);
         const int token_row = cur.row0 + (mma_n / 2) * static_cast<int>(cta);
@@ -281,7 +296,9 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         const int group = channel0 >> 4;                         // gate_up: 16-channel group
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 11);
-          if (FMOE_DIAG_BIT(args, 2)) {
+          if (!issuer) {
+            // the other lanes only keep step
+          } else if (FMOE_DIAG_BIT(args, 2)) {
             if (leader) ptx::mbar_arrive(&ctl->full[stage]);
           } else {
             const uint32_t dst = smem_base + static_cast<uint32_t>(stage) * kStageBytes;
@@ -330,7 +347,9 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
-    if (leader && lane == 0) {
+    // The whole warp walks the loop (waits included); one elected lane issues the MMAs and commits (ptx::elect_one).
+    if (leader) {
+      const bool issuer = ptx::elect_one();
       // Descriptor words (see ptx::make_smem_desc_sw128): the low word holds the start address >> 4 and the
       // ignored leading offset, the high word the 1024-byte group stride, version 1 and SWIZZLE_128B.
       const uint32_t desc_hi = static_cast<uint32_t>(1024 >> 4) | (1u << 14) | (2u << 29);
@@ -350,8 +369,10 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         const UnitInfo next = load_unit(args.items, unit + unit_stride, units, n_blocks, kRowsPerRoute);
         const uint32_t buffer = static_cast<uint32_t>(local) & 1u;
         const uint32_t use = static_cast<uint32_t>(local) >> 1;
-        // N follows the rows this unit really has (a multiple of 32 for two-SM MMAs).
-        const int mma_n = min(kPairTokens, (cur.rows + 31) & ~31);
+        // N follows the rows this unit really has (a multiple of 32 for two-SM MMAs).  The row count comes from a global
+        // load; the shuffle tells the compiler that every lane holds the same value.
+        const int unit_rows = __shfl_sync(0xffffffffu, cur.rows, 0);
+        const int mma_n = min(kPairTokens, (unit_rows + 31) & ~31);
         const uint32_t idesc = ptx::make_instr_desc(kInt8, 2 * kRowsPerCta, mma_n);
         ptx::mbar_wait(&ctl->acc_empty[buffer], (use & 1u) ^ 1u, abort_flag, status, 12);
         ptx::tcgen05_fence_after();
@@ -360,15 +381,17 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->full[stage], phase, abort_flag, status, 13);
           ptx::tcgen05_fence_after();
-          if (!FMOE_DIAG_BIT(args, 4)) {
+          if (issuer) {
+            if (!FMOE_DIAG_BIT(args, 4)) {
 #pragma unroll
-            for (uint32_t ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
-              umma_pair<kInt8>(acc, a_lo + 2u * ks, a_lo + kTokenStep + 2u * ks, desc_hi, idesc, accumulate);
-              accumulate = 1;
+              for (uint32_t ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
+                umma_pair<kInt8>(acc, a_lo + 2u * ks, a_lo + kTokenStep + 2u * ks, desc_hi, idesc, ks == 0 ? accumulate : 1u);
+              }
             }
+            tcgen05_commit_pair(empty_c0 + 8u * static_cast<uint32_t>(stage));
+            tcgen05_commit_pair(empty_c1 + 8u * static_cast<uint32_t>(stage));
           }
-          tcgen05_commit_pair(empty_c0 + 8u * static_cast<uint32_t>(stage));
-          tcgen05_commit_pair(empty_c1 + 8u * static_cast<uint32_t>(stage));
+          accumulate = 1;
           a_lo += kStageStep;
           if (++stage == kStages) {
             stage = 0;
@@ -376,8 +399,10 @@ umma_pair_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, co
             a_lo = a_lo_stage0;
           }
         }
-        tcgen05_commit_pair(accfull_c0 + 8u * buffer);
-        tcgen05_commit_pair(accfull_c1 + 8u * buffer);
+        if (issuer) {
+          tcgen05_commit_pair(accfull_c0 + 8u * buffer);
+          tcgen05_commit_pair(accfull_c1 + 8u * buffer);
+        }
         cur = next;
       }
     }

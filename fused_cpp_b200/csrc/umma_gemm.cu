@@ -164,11 +164,13 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   SmemControl* ctl = reinterpret_cast<SmemControl*>(smem + static_cast<size_t>(Cfg::kOperandBytes));
 
-  const int warp = threadIdx.x >> 5;
+  // Warp index, item count and (below) the tensor-memory base pass through a shuffle: the same values, but known to the
+  // compiler as warp-uniform, which the warps that feed TMA and the tensor pipe need (ptx::elect_one).
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   int* status = args.status_rw;
 
-  const int items = min(args.status[args.item_count_word], args.max_items);
+  const int items = __shfl_sync(0xffffffffu, min(args.status[args.item_count_word], args.max_items), 0);
   const int n_blocks = (args.n_out + kBlockM - 1) / kBlockM;
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   const int64_t units = static_cast<int64_t>(items) * n_blocks;
@@ -199,14 +201,18 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
   ptx::tcgen05_fence_before();
   __syncthreads();
   ptx::tcgen05_fence_after();
-  const uint32_t tmem_base = ctl->tmem_base;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, ctl->tmem_base, 0);
   volatile int* abort_flag = &ctl->abort_flag;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      ptx::prefetch_tensormap(&weight_map);
-      ptx::prefetch_tensormap(&token_map);
+    // The whole warp walks the loops; one elected lane issues the loads.
+    {
+      const bool issuer = ptx::elect_one();
+      if (issuer) {
+        ptx::prefetch_tensormap(&weight_map);
+        ptx::prefetch_tensormap(&token_map);
+      }
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
@@ -219,18 +225,22 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
           int item, block;
           decode_unit(args.items, unit, n_blocks, &item, &block);
-          const int weight_row = args.items[4 * item + 0] * n_total + block * kBlockM;
-          const int row0 = args.items[4 * item + 1];
+        item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
+        block = __shfl_sync(0xffffffffu, block, 0);
+          const int weight_row = __shfl_sync(0xffffffffu, args.items[4 * item + 0], 0) * n_total + block * kBlockM;
+          const int row0 = __shfl_sync(0xffffffffu, args.items[4 * item + 1], 0);
           for (int kb = 0; kb < k_blocks; ++kb) {
             ptx::mbar_wait(&ctl->landing_free[slot], slot_phase ^ 1u, abort_flag, status, 6);
-            uint8_t* landing = smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes;
-            const int x = kb * kBlockKElems;
-            ptx::mbar_arrive_expect_tx(&ctl->landed[slot], Cfg::kTokenBytes + Cfg::kInt8TileBytes);
-            ptx::tma_load_2d(landing, &token_map, &ctl->landed[slot], x, row0);
-            ptx::tma_load_2d(landing + Cfg::kTokenRegionBytes, &weight_map, &ctl->landed[slot], x, weight_row);
-            if (kGateUp) {
-              ptx::tma_load_2d(landing + Cfg::kTokenRegionBytes + kBlockM * kLandingRowBytes, &weight_map, &ctl->landed[slot], x,
-                               weight_row + args.n_out);
+            if (issuer) {
+              uint8_t* landing = smem + Cfg::kLandingOffset + static_cast<size_t>(slot) * Cfg::kLandingBytes;
+              const int x = kb * kBlockKElems;
+              ptx::mbar_arrive_expect_tx(&ctl->landed[slot], Cfg::kTokenBytes + Cfg::kInt8TileBytes);
+              ptx::tma_load_2d(landing, &token_map, &ctl->landed[slot], x, row0);
+              ptx::tma_load_2d(landing + Cfg::kTokenRegionBytes, &weight_map, &ctl->landed[slot], x, weight_row);
+              if (kGateUp) {
+                ptx::tma_load_2d(landing + Cfg::kTokenRegionBytes + kBlockM * kLandingRowBytes, &weight_map, &ctl->landed[slot], x,
+                                 weight_row + args.n_out);
+              }
             }
             ++landed_issued;
             if (++slot == Cfg::kLandingSlots) {
@@ -257,14 +267,18 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       for (int64_t unit = blockIdx.x; !kW8A16 && unit < units; unit += gridDim.x) {
         int item, block;
         decode_unit(args.items, unit, n_blocks, &item, &block);
+        item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
+        block = __shfl_sync(0xffffffffu, block, 0);
         const int n0 = block * kBlockM;
-        const int expert = args.items[4 * item + 0];
-        const int row0 = args.items[4 * item + 1] * kRowsPerRoute;
+        const int expert = __shfl_sync(0xffffffffu, args.items[4 * item + 0], 0);
+        const int row0 = __shfl_sync(0xffffffffu, args.items[4 * item + 1], 0) * kRowsPerRoute;
         const int weight_row = expert * n_total + n0;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
           uint8_t* stage_base = smem + static_cast<size_t>(stage) * Cfg::kStageBytes;
-          if (FMOE_DIAG_BIT(args, 2)) {
+          if (!issuer) {
+            // the other lanes only keep step
+          } else if (FMOE_DIAG_BIT(args, 2)) {
             ptx::mbar_arrive(&ctl->full[stage]);
           } else {
             ptx::mbar_arrive_expect_tx(&ctl->full[stage], Cfg::kStageBytes);
@@ -357,7 +371,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop (waits included); one elected lane issues the MMAs and commits.
+    {
+      const bool issuer = ptx::elect_one();
       int stage = 0;
       uint32_t phase = 0;
       int slot = 0;  // W8A16: landing slot of the K block (its token tile is the MMA's B operand)
@@ -369,7 +385,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         // few columns of tensor-core time, not a full tile.  Unused accumulator columns are never read.
         int item, block;
         decode_unit(args.items, unit, n_blocks, &item, &block);
-        const int item_rows = args.items[4 * item + 2] * kRowsPerRoute;
+        item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
+        block = __shfl_sync(0xffffffffu, block, 0);
+        const int item_rows = __shfl_sync(0xffffffffu, args.items[4 * item + 2], 0) * kRowsPerRoute;
         const int mma_n = min(kRowTile, (item_rows + 15) & ~15);
         // Weight-major: M = 128 channels, N = the item's rows.  Token-major (W8A16): M = 128 token lanes, N = the
         // unit's channels (gate and up tiles are one 256-row B operand).
@@ -386,7 +404,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
                                              : stage_addr + Cfg::kWeightBytes;
 #pragma unroll
           for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
-            if (FMOE_DIAG_BIT(args, 4)) break;
+            if (FMOE_DIAG_BIT(args, 4) || !issuer) break;
             const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
             const uint64_t desc_tok = ptx::make_smem_desc_sw128(token_addr + ks * kUmmaKBytes);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
@@ -400,9 +418,9 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
               ptx::umma_ss<kInt8>(acc + kRowTile, desc_up, desc_tok, idesc, accumulate);
             }
           }
-          ptx::tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs have read it
+          if (issuer) ptx::tcgen05_commit(&ctl->empty[stage]);  // frees the stage once these MMAs have read it
           if constexpr (kW8A16) {
-            ptx::tcgen05_commit(&ctl->landing_free[slot]);  // ... and, with the converter warps' arrivals, the landing slot
+            if (issuer) ptx::tcgen05_commit(&ctl->landing_free[slot]);  // ... and, with the converter warps' arrivals, the landing slot
             if (++slot == Cfg::kLandingSlots) slot = 0;
           }
           if (++stage == Cfg::kStages) {
@@ -410,7 +428,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
             phase ^= 1u;
           }
         }
-        ptx::tcgen05_commit(&ctl->acc_full[buffer]);  // accumulator complete
+        if (issuer) ptx::tcgen05_commit(&ctl->acc_full[buffer]);  // accumulator complete
       }
     }
   } else {
@@ -429,6 +447,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
       int item, block;
       decode_unit(args.items, unit, n_blocks, &item, &block);
+        item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
+        block = __shfl_sync(0xffffffffu, block, 0);
       const int n = block * kBlockM + channel_in_block;
       const int expert = args.items[4 * item + 0];
       const int row0 = args.items[4 * item + 1] * kRowsPerRoute;  // token rows (two per route in the two-plane form)
