@@ -179,6 +179,37 @@ __device__ __forceinline__ int quantize_value_torchref_fast(float value, float s
   return static_cast<int>(fmaxf(fminf(nearest, 127.0f), -127.0f));
 }
 
+// Four values at once, the same rule with the conversions taken out of the common path.  The product is clamped
+// first (rint and a clamp at the integers +-127 commute; the order of fminf / fmaxf is quantize_value's, so NaN ends
+// at +127 there too); adding 1.5 * 2^23 rounds it to the nearest integer, ties to even, in the low mantissa bits, so
+// the byte is read out of the sum's bit pattern and subtracting the constant again gives rint(product) for the
+// boundary test: no FRND and no F2I, which issue at a quarter of the FADD rate.  A clamped product is an integer
+// (distance 0) and the exact quotient then rounds to +-127 as well.  One test per four values; the exact division
+// decides all four when any of them is near a boundary.
+__device__ __forceinline__ uint32_t quantize4_torchref_fast(const float* values, float scale, float inverse) {
+  constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+  uint32_t bits[4];
+  float worst = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float product = fmaxf(fminf(__fmul_rn(values[i], inverse), 127.0f), -127.0f);
+    const float shifted = __fadd_rn(product, kMagic);
+    const float nearest = __fsub_rn(shifted, kMagic);
+    worst = fmaxf(worst, fabsf(__fsub_rn(product, nearest)));
+    bits[i] = __float_as_uint(shifted);
+  }
+  if (worst > 0.4999f) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      packed |= (static_cast<uint32_t>(quantize_value(values[i], scale, FMOE_NUMERICS_TORCHREF)) & 0xffu) << (8 * i);
+    }
+    return packed;
+  }
+  // Low byte of each sum = the integer in two's complement.
+  return __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+}
+
 __device__ __forceinline__ float quantize_operand(float scale, int numerics) {
   return numerics == FMOE_NUMERICS_NATIVE ? __fdiv_rn(1.0f, scale) : scale;
 }

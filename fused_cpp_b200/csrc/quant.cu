@@ -47,6 +47,7 @@ __device__ __forceinline__ float amax8(const uint4& v) {
 
 // operand: 1/scale (NATIVE) or scale (TORCHREF); inverse: 1/scale, used by the TORCHREF fast path.
 __device__ __forceinline__ uint32_t pack4(const float* values, float operand, float inverse, int numerics) {
+  if (numerics == FMOE_NUMERICS_TORCHREF) return quantize4_torchref_fast(values, operand, inverse);
   uint32_t packed = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
