@@ -387,11 +387,48 @@ cudaError_t launch_quantize_tokens_scatter(const uint16_t* x, int64_t tokens, in
   return cudaGetLastError();
 }
 
+// The same quantiser for bf16 rows whose length is a multiple of 8: 16-byte loads, 8-byte stores, and the division
+// replaced as in quantize4_torchref_fast (the statement is the same clamp(rint(x / scale)); with scale = amax / 127 of
+// the same row no quotient rounds below -127, so the lower clamp of -128 some callers ask for never binds).
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_rows_dense_bf16x8_kernel(const uint16_t* __restrict__ x, int cols, int cols_padded, int8_t* __restrict__ q,
+                                  float* __restrict__ scale_out) {
+  __shared__ float smem[32];
+  const int64_t row = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(x + row * cols);
+  const int vec8 = cols >> 3;
+  float local = 0.0f;
+  for (int v = threadIdx.x; v < vec8; v += kQuantThreads) local = fmaxf(local, amax8(src[v]));
+  const float amax = block_max(local, smem);
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  const float inverse = __fdiv_rn(1.0f, scale);
+  uint2* dst = reinterpret_cast<uint2*>(q + row * cols_padded);
+  const int vec8_padded = cols_padded >> 3;
+  for (int v = threadIdx.x; v < vec8_padded; v += kQuantThreads) {
+    uint2 out = make_uint2(0u, 0u);
+    if (v < vec8) {
+      float values[8];
+      unpack8(src[v], values);
+      out.x = quantize4_torchref_fast(values, scale, inverse);
+      out.y = quantize4_torchref_fast(values + 4, scale, inverse);
+    }
+    dst[v] = out;
+  }
+}
+
 cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
                                        int8_t* q, float* scale, cudaStream_t stream) {
   if (rows <= 0) return cudaSuccess;
-  quantize_rows_dense_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(
-      x, x_is_bf16, cols, cols_padded, static_cast<float>(clamp_low), q, scale);
+  const bool vector_form = x_is_bf16 && cols % 8 == 0 && cols_padded % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+                           (reinterpret_cast<uintptr_t>(q) & 7u) == 0;
+  if (vector_form) {
+    quantize_rows_dense_bf16x8_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(static_cast<const uint16_t*>(x), cols,
+                                                                                                cols_padded, q, scale);
+  } else {
+    quantize_rows_dense_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(
+        x, x_is_bf16, cols, cols_padded, static_cast<float>(clamp_low), q, scale);
+  }
   return cudaGetLastError();
 }
 
