@@ -166,20 +166,11 @@ __device__ __forceinline__ int quantize_value(float value, float scale_or_invers
   return static_cast<int>(rounded);
 }
 
-// TORCHREF quantisation of one value with the division replaced by a multiplication wherever that cannot change
+// TORCHREF quantisation of four values with the division replaced by a multiplication wherever that cannot change
 // the result.  value * (1/scale) differs from the correctly rounded value / scale by at most a few units in the
 // last place (below 4e-5 in absolute terms for |quotient| <= 128), so the two round to the same integer unless
-// the product lies within 1e-4 of a half-integer; only then, or when the product is not an ordinary number in
-// the clamped range's neighbourhood, the exact division decides.  Bit-identical to quantize_value(TORCHREF).
-__device__ __forceinline__ int quantize_value_torchref_fast(float value, float scale, float inverse) {
-  const float product = __fmul_rn(value, inverse);
-  const float nearest = rintf(product);
-  const float distance = fabsf(__fsub_rn(product, nearest));
-  if (!(fabsf(product) < 200.0f) || distance > 0.4999f) return quantize_value(value, scale, FMOE_NUMERICS_TORCHREF);
-  return static_cast<int>(fmaxf(fminf(nearest, 127.0f), -127.0f));
-}
-
-// Four values at once, the same rule with the conversions taken out of the common path.  The product is clamped
+// the product lies within 1e-4 of a half-integer; only then the exact division decides.  Bit-identical to
+// quantize_value(TORCHREF).  The conversions are taken out of the common path as well.  The product is clamped
 // first (rint and a clamp at the integers +-127 commute; the order of fminf / fmaxf is quantize_value's, so NaN ends
 // at +127 there too); adding 1.5 * 2^23 rounds it to the nearest integer, ties to even, in the low mantissa bits, so
 // the byte is read out of the sum's bit pattern and subtracting the constant again gives rint(product) for the

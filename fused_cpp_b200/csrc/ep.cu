@@ -273,12 +273,14 @@ peer_dispatch_kernel(const uint16_t* __restrict__ x, const int64_t* __restrict__
       uint32_t words[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
+        if (numerics == FMOE_NUMERICS_TORCHREF) {
+          words[w] = quantize4_torchref_fast(values + 4 * w, operand, inverse);
+          continue;
+        }
         uint32_t word = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int q = numerics == FMOE_NUMERICS_TORCHREF ? quantize_value_torchref_fast(values[4 * w + i], operand, inverse)
-                                                           : quantize_value(values[4 * w + i], operand, numerics);
-          word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+          word |= (static_cast<uint32_t>(quantize_value(values[4 * w + i], operand, numerics)) & 0xffu) << (8 * i);
         }
         words[w] = word;
       }

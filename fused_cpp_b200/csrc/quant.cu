@@ -51,9 +51,7 @@ __device__ __forceinline__ uint32_t pack4(const float* values, float operand, fl
   uint32_t packed = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int q = numerics == FMOE_NUMERICS_TORCHREF ? quantize_value_torchref_fast(values[i], operand, inverse)
-                                                     : quantize_value(values[i], operand, numerics);
-    packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+    packed |= (static_cast<uint32_t>(quantize_value(values[i], operand, numerics)) & 0xffu) << (8 * i);
   }
   return packed;
 }
