@@ -763,16 +763,11 @@ int dense_prologue(const void* x, int x_is_bf16, int64_t rows, int k, int clamp_
   }
   char* base = static_cast<char*>(workspace);
   *row_tile = dense_row_tile(rows);
-  cudaError_t error = cudaMemsetAsync(base + layout->status, 0, sizeof(int) * fmoe::kStatusWords, stream);
-  if (error == cudaSuccess) {
-    error = fmoe::launch_quantize_rows_dense(x, x_is_bf16, rows, k, layout->k_padded, clamp_low, reinterpret_cast<int8_t*>(base + layout->xq),
-                                             reinterpret_cast<float*>(base + layout->scale), stream);
-  }
-  if (error == cudaSuccess) {
-    error = fmoe::launch_dense_items(rows, *row_tile == fmoe::kPairRowTile ? 256 : *row_tile, layout->max_items,
-                                     reinterpret_cast<int*>(base + layout->items),
-                                     reinterpret_cast<int*>(base + layout->status), stream);
-  }
+  // One launch: the quantiser's first block also resets the status block and writes the GEMM's work items.
+  const cudaError_t error = fmoe::launch_quantize_rows_dense(
+      x, x_is_bf16, rows, k, layout->k_padded, clamp_low, reinterpret_cast<int8_t*>(base + layout->xq),
+      reinterpret_cast<float*>(base + layout->scale), *row_tile == fmoe::kPairRowTile ? 256 : *row_tile, layout->max_items,
+      reinterpret_cast<int*>(base + layout->items), reinterpret_cast<int*>(base + layout->status), stream);
   return error == cudaSuccess ? FMOE_OK : cuda_fail(error, "i8gemm activation quantisation");
 }
 }  // namespace

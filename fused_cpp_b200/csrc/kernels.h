@@ -36,8 +36,6 @@ cudaError_t launch_route_build(const int64_t* topk_ids, int64_t routes, int expe
 // Work items from per-expert counts / offsets of rows that are already in expert order (scratch: 2 * experts + 1 ints).
 cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, const ItemLists& lists, int* scratch, int* status,
                                      cudaStream_t stream);
-// Work items of a dense [rows, K] x [N, K]^T product: one "expert", consecutive row tiles.
-cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream);
 
 // ---- quant.cu
 // Quantise rows of a bf16 matrix to int8 with one fp32 scale per row.  When `sorted_routes` is
@@ -61,7 +59,8 @@ cudaError_t launch_split_tokens_scatter_planes(const uint16_t* x, int64_t tokens
                                                float* scale, cudaStream_t stream);
 // Same for fp32 sources (dense linear).  clamp_low is -128 or -127.
 cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
-                                       int8_t* q, float* scale, cudaStream_t stream);
+                                       int8_t* q, float* scale, int row_tile, int max_items, int* items, int* status,
+                                       cudaStream_t stream);
 // Copy bf16 rows into expert-sorted order: out[p] = x[sorted_routes[p] / top_k].
 cudaError_t launch_gather_rows(const uint16_t* x, int64_t out_rows, int cols, const int* sorted_routes, int top_k,
                                const int* valid_rows, uint16_t* out, cudaStream_t stream);

@@ -279,9 +279,36 @@ split_tokens_scatter_planes_kernel(const uint16_t* __restrict__ x, int cols, int
 
 // Dense linear: arbitrary cols, fp32 or bf16 source, zero-padded to cols_padded, clamp to [-128,127]
 // (single GEMM) or [-127,127] (paired GEMMs) with division and ties-to-even (csrc/i8gemm.cpp:384-399, :492-506).
+// Status block and work items of the dense GEMM that follows (one "expert", row tiles of row_tile rows; the group key
+// of decode_unit in the fourth word), written by block 0 of the quantiser so that the op needs no launches of its own
+// for them.  Every status word is written: the block starts out in an unknown state.
+struct DenseItems {
+  int64_t rows;
+  int row_tile;
+  int max_items;
+  int* items;
+  int* status;
+};
+
+__device__ __forceinline__ void write_dense_items(const DenseItems& d) {
+  const int tiles = static_cast<int>((d.rows + d.row_tile - 1) / d.row_tile);
+  const int count = tiles < d.max_items ? tiles : d.max_items;
+  for (int t = threadIdx.x; t < count; t += blockDim.x) {
+    d.items[4 * t + 0] = 0;
+    d.items[4 * t + 1] = t * d.row_tile;
+    d.items[4 * t + 2] = static_cast<int>(min(static_cast<int64_t>(d.row_tile), d.rows - static_cast<int64_t>(t) * d.row_tile));
+    d.items[4 * t + 3] = count < 2048 ? (0 | (count << 20)) : (t | (1 << 20));
+  }
+  if (threadIdx.x < kStatusWords) {
+    const int word = threadIdx.x;
+    d.status[word] = (word == kStatusItems || word == kStatusItemsB) ? count : word == kStatusActive ? (d.rows > 0 ? 1 : 0) : 0;
+  }
+}
+
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_rows_dense_kernel(const void* __restrict__ x, int x_is_bf16, int cols, int cols_padded, float clamp_low,
-                           int8_t* __restrict__ q, float* __restrict__ scale_out) {
+                           int8_t* __restrict__ q, float* __restrict__ scale_out, DenseItems dense_items) {
+  if (blockIdx.x == 0) write_dense_items(dense_items);
   __shared__ float smem[32];
   const int64_t row = blockIdx.x;
   const float* xf = static_cast<const float*>(x) + row * cols;
@@ -390,8 +417,9 @@ cudaError_t launch_quantize_tokens_scatter(const uint16_t* x, int64_t tokens, in
 // the same row no quotient rounds below -127, so the lower clamp of -128 some callers ask for never binds).
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_rows_dense_bf16x8_kernel(const uint16_t* __restrict__ x, int cols, int cols_padded, int8_t* __restrict__ q,
-                                  float* __restrict__ scale_out) {
+                                  float* __restrict__ scale_out, DenseItems dense_items) {
   __shared__ float smem[32];
+  if (blockIdx.x == 0) write_dense_items(dense_items);
   const int64_t row = blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(x + row * cols);
   const int vec8 = cols >> 3;
@@ -416,16 +444,18 @@ quantize_rows_dense_bf16x8_kernel(const uint16_t* __restrict__ x, int cols, int 
 }
 
 cudaError_t launch_quantize_rows_dense(const void* x, int x_is_bf16, int64_t rows, int cols, int cols_padded, int clamp_low,
-                                       int8_t* q, float* scale, cudaStream_t stream) {
+                                       int8_t* q, float* scale, int row_tile, int max_items, int* items, int* status,
+                                       cudaStream_t stream) {
   if (rows <= 0) return cudaSuccess;
+  const DenseItems dense_items = {rows, row_tile, max_items, items, status};
   const bool vector_form = x_is_bf16 && cols % 8 == 0 && cols_padded % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
                            (reinterpret_cast<uintptr_t>(q) & 7u) == 0;
   if (vector_form) {
     quantize_rows_dense_bf16x8_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(static_cast<const uint16_t*>(x), cols,
-                                                                                                cols_padded, q, scale);
+                                                                                                cols_padded, q, scale, dense_items);
   } else {
     quantize_rows_dense_kernel<<<static_cast<unsigned>(rows), kQuantThreads, 0, stream>>>(
-        x, x_is_bf16, cols, cols_padded, static_cast<float>(clamp_low), q, scale);
+        x, x_is_bf16, cols, cols_padded, static_cast<float>(clamp_low), q, scale, dense_items);
   }
   return cudaGetLastError();
 }

@@ -291,21 +291,6 @@ items_from_counts_kernel(int experts, const int* __restrict__ counts, const int*
   build_items(experts, counts, offsets, lists, scan_tmp, status);
 }
 
-__global__ void dense_items_kernel(int64_t rows, int row_tile, int max_items, int* items, int* status) {
-  const int tiles = static_cast<int>((rows + row_tile - 1) / row_tile);
-  const int count = tiles < max_items ? tiles : max_items;
-  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < count; t += gridDim.x * blockDim.x) {
-    items[4 * t + 0] = 0;
-    items[4 * t + 1] = t * row_tile;
-    items[4 * t + 2] = static_cast<int>(min(static_cast<int64_t>(row_tile), rows - static_cast<int64_t>(t) * row_tile));
-    items[4 * t + 3] = count < 2048 ? (0 | (count << 20)) : (t | (1 << 20));
-  }
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    status[kStatusItems] = count;
-    status[kStatusItemsB] = count;
-    status[kStatusActive] = rows > 0 ? 1 : 0;
-  }
-}
 }  // namespace
 
 cudaError_t launch_items_from_counts(int experts, const int* counts, const int* offsets, const ItemLists& lists, int* scratch, int* status,
@@ -314,10 +299,6 @@ cudaError_t launch_items_from_counts(int experts, const int* counts, const int* 
   return cudaGetLastError();
 }
 
-cudaError_t launch_dense_items(int64_t rows, int row_tile, int max_items, int* items, int* status, cudaStream_t stream) {
-  dense_items_kernel<<<8, 256, 0, stream>>>(rows, row_tile, max_items, items, status);
-  return cudaGetLastError();
-}
 
 // ---- allocation-free route build ---------------------------------------------------------------
 //
