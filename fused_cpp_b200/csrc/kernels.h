@@ -161,6 +161,13 @@ struct GroupedGemmArgs {
                              // tile to bf16; 2 = two int8 planes per route (a_rows holds 2 * total_rows rows, a_scale one
                              // scale per route, row_tile counts plane rows), the int8 one-SM kernel pairs accumulator columns
   int gate_up_one_box;       // two-SM gate_up: the weight rows of a stage arrive as one 16 KB TMA box (set by the launcher)
+  // Dense GEMM over few rows (one-SM kernel): the K range of every (row tile, channel block) is cut into dense_splits
+  // parts that run as work units of their own, so that a product with few channel blocks still fills the SMs.  The
+  // parts add their int32 accumulators into dense_partial[rows, n_out] (zero on entry) and count themselves in
+  // dense_counters[unit] (zero on entry); the part that arrives last dequantises and stores.  0 or 1 = no split.
+  int dense_splits;
+  int* dense_partial;
+  int* dense_counters;
   int route_out_bf16;        // the result rows are stored as bf16 (2 bytes per channel, rows 2 * n_out bytes apart) instead of fp32
   // Diagnostic build only (compiled with -DFMOE_DIAG, the separate libfused_moe_b200_diag.so; the product library
   // ignores the field): bit 0 = epilogue does no work, bit 1 = producer loads nothing, bit 2 = no MMA is issued.

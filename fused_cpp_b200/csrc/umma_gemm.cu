@@ -122,6 +122,7 @@ struct SmemControl {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
+  int last_part;           // dense split-K: this CTA holds the last part of its unit and finishes it
   uint32_t exp_table[64];  // copy of kExp2Table: divergent lookups are served by 32 banks
   ColumnMeta meta[2];
 };
@@ -175,6 +176,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
   const int n_total = kGateUp ? 2 * args.n_out : args.n_out;
   const int64_t units = static_cast<int64_t>(items) * n_blocks;
   const int k_blocks = (args.k + kBlockKElems - 1) / kBlockKElems;
+  // Dense split-K: `parts` work units per (row tile, channel block), part p over K blocks [p k_blocks / parts,
+  // (p + 1) k_blocks / parts).  Everything else runs with parts == 1.
+  const int parts = kDense ? (args.dense_splits > 1 ? args.dense_splits : 1) : 1;
+  const int64_t part_units = units * parts;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -264,7 +269,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
           }
         }
       }
-      for (int64_t unit = blockIdx.x; !kW8A16 && unit < units; unit += gridDim.x) {
+      for (int64_t part_unit = blockIdx.x; !kW8A16 && part_unit < part_units; part_unit += gridDim.x) {
+        const int64_t unit = part_unit / parts;
+        const int part = static_cast<int>(part_unit - unit * parts);
+        const int kb_begin = part * k_blocks / parts, kb_end = (part + 1) * k_blocks / parts;
         int item, block;
         decode_unit(args.items, unit, n_blocks, &item, &block);
         item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
@@ -273,7 +281,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         const int expert = __shfl_sync(0xffffffffu, args.items[4 * item + 0], 0);
         const int row0 = __shfl_sync(0xffffffffu, args.items[4 * item + 1], 0) * kRowsPerRoute;
         const int weight_row = expert * n_total + n0;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, status, 1);
           uint8_t* stage_base = smem + static_cast<size_t>(stage) * Cfg::kStageBytes;
           if (!issuer) {
@@ -378,7 +386,10 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       uint32_t phase = 0;
       int slot = 0;  // W8A16: landing slot of the K block (its token tile is the MMA's B operand)
       int local = 0;
-      for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
+      for (int64_t part_unit = blockIdx.x; part_unit < part_units; part_unit += gridDim.x, ++local) {
+        const int64_t unit = part_unit / parts;
+        const int part = static_cast<int>(part_unit - unit * parts);
+        const int kb_begin = part * k_blocks / parts, kb_end = (part + 1) * k_blocks / parts;
         const int buffer = local % Cfg::kAccBuffers;
         const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
         // The MMA's N follows the rows this unit really has (multiple of 16): a tail item of a few rows costs a
@@ -395,7 +406,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         ptx::mbar_wait(&ctl->acc_empty[buffer], (use & 1u) ^ 1u, abort_flag, status, 2);
         ptx::tcgen05_fence_after();
         const uint32_t acc = tmem_base + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ptx::mbar_wait(&ctl->full[stage], phase, abort_flag, status, 3);
           ptx::tcgen05_fence_after();
           const uint32_t stage_addr = ptx::smem_u32(smem + static_cast<size_t>(stage) * Cfg::kStageBytes);
@@ -407,7 +418,7 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
             if (FMOE_DIAG_BIT(args, 4) || !issuer) break;
             const uint64_t desc_gate = ptx::make_smem_desc_sw128(stage_addr + ks * kUmmaKBytes);
             const uint64_t desc_tok = ptx::make_smem_desc_sw128(token_addr + ks * kUmmaKBytes);
-            const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+            const uint32_t accumulate = (kb > kb_begin || ks > 0) ? 1u : 0u;
             if constexpr (kW8A16) {
               ptx::umma_ss<false>(acc, desc_tok, desc_gate, idesc, accumulate);  // A = tokens, B = gate (+ up) channels
               continue;
@@ -442,7 +453,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
     const int activation = args.activation;
     uint32_t* const dump = kPlanes ? nullptr : static_cast<uint32_t*>(args.dump_acc);  // the dump holds one row per route
     int local = 0;
-    for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x, ++local) {
+    for (int64_t part_unit = blockIdx.x; part_unit < part_units; part_unit += gridDim.x, ++local) {
+      const int64_t unit = part_unit / parts;
       const int buffer = local % Cfg::kAccBuffers;
       const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
       int item, block;
@@ -559,6 +571,55 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       ptx::mbar_wait(&ctl->acc_full[buffer], use & 1u, abort_flag, status, 4);
       ptx::tcgen05_fence_after();
       const uint32_t acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buffer * Cfg::kAccColumns);
+      if constexpr (kDense) {
+        if (parts > 1) {
+          // This part's int32 sums go into the shared table; the part that finds the other parts' counts complete reads
+          // the totals back and finishes the unit (integer addition: the order of the parts changes nothing).
+          for (int c0 = 0; c0 < rows; c0 += 8) {
+            uint32_t bits[8];
+            ptx::tmem_ld_x8(acc + c0, bits);
+            ptx::tmem_ld_wait();
+            if (channel_ok) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (c0 + j < rows) atomicAdd(args.dense_partial + static_cast<int64_t>(row0 + c0 + j) * n_out + n, static_cast<int>(bits[j]));
+              }
+            }
+          }
+          ptx::tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&ctl->acc_empty[buffer]);
+          __threadfence();  // this thread's additions are visible before the count below
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (epilogue_thread == 0) ctl->last_part = atomicAdd(args.dense_counters + unit, 1) == parts - 1 ? 1 : 0;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (ctl->last_part) {
+            __threadfence();  // the other parts' additions, published before their counts, are visible after ours
+            if (channel_ok) {
+              // Sixteen rows at a time: the loads of a batch are in flight together.
+              for (int c0 = 0; c0 < rows; c0 += 16) {
+                int totals[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  totals[j] = c0 + j < rows ? __ldcg(args.dense_partial + static_cast<int64_t>(row0 + c0 + j) * n_out + n) : 0;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  if (c0 + j >= rows) break;
+                  const float value = __fadd_rn(dequantize(totals[j], meta->scale[c0 + j], scale_gate, numerics), bias);
+                  const uint64_t rowptr = meta->rowptr[c0 + j];
+                  if (args.dense_out_bf16) {
+                    reinterpret_cast<uint16_t*>(rowptr)[n] = f32_to_bf16_bits(value);
+                  } else {
+                    reinterpret_cast<float*>(rowptr)[n] = value;
+                  }
+                }
+              }
+            }
+          }
+          continue;
+        }
+      }
       for (int c0 = 0; c0 < (FMOE_DIAG_BIT(args, 1) ? 0 : rows); c0 += 8) {
         uint32_t gate_bits[8];
         uint32_t up_bits[8];
@@ -721,7 +782,7 @@ cudaError_t launch_config(const GroupedGemmArgs& args, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
   const int n_blocks = (args.n_out + kBlockM - 1) / kBlockM;
-  int64_t grid = static_cast<int64_t>(args.max_items) * n_blocks;
+  int64_t grid = static_cast<int64_t>(args.max_items) * n_blocks * (kDense && args.dense_splits > 1 ? args.dense_splits : 1);
   const int sms = sm_count_of_current_device();
   if (grid > sms) grid = sms;
   if (grid <= 0) return cudaSuccess;

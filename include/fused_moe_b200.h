@@ -282,7 +282,9 @@ FMOE_API int fmoe_ep_combine_finish(const float* returned_rows, const int32_t* s
 
 /* ---- dense W8A8 linear ----------------------------------------------------------------------- */
 
-/* Workspace bytes for the dense calls below (quantised rows, scales, work items, status block). */
+/* Workspace bytes for the dense calls below (quantised rows, scales, work items, status block, and for at most 16
+ * rows the int32 table in which the K-split parts of a product meet; n = the widest N that will use the workspace.
+ * A call given less than this for its N runs without the split). */
 FMOE_API size_t fmoe_i8gemm_workspace_bytes(int64_t rows, int32_t k, int32_t n);
 
 /* out[M,N] = dequant( quant_rows(x[M,K]) @ w^T ) (+ bias): per-row dynamic int8 quantisation

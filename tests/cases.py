@@ -105,11 +105,14 @@ I8GEMM_CASES = {
     # taller than one 128-row tile: the two-SM kernel's dense epilogue (three 256-row items, two channel blocks, fp32 + bias)
     "tall": (600, 512, 384, torch.bfloat16, torch.float32, True),
     "tall_bf16": (300, 144, 520, torch.bfloat16, torch.bfloat16, False),
+    # at most 16 rows, long K, few and ragged channel blocks: the one-SM kernel cuts K into parts that meet in an int32 table
+    "skinny": (16, 1536, 200, torch.bfloat16, torch.bfloat16, False),
+    "skinny_f32in": (13, 4096, 136, torch.float32, torch.float32, True),
 }
 
 
 # Seed offsets are fixed per name (the committed golden outputs depend on them), not derived from the table's order.
-I8GEMM_SEEDS = {"deep": 0, "f32": 1, "m1": 2, "m4": 3, "m9": 4, "wide": 5, "tall": 6, "tall_bf16": 7}
+I8GEMM_SEEDS = {"deep": 0, "f32": 1, "m1": 2, "m4": 3, "m9": 4, "wide": 5, "tall": 6, "tall_bf16": 7, "skinny": 8, "skinny_f32in": 9}
 
 
 def i8gemm_case(name: str) -> dict:
