@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import datetime
 import os
-import socket
+import tempfile
 import traceback
 
 import pytest
@@ -17,11 +17,6 @@ from tests import cases
 
 pytestmark = pytest.mark.gpu
 
-
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
 
 
 def _single_gpu(case, device, shared=None, scaling=1.0):
@@ -40,12 +35,14 @@ def _single_gpu(case, device, shared=None, scaling=1.0):
     return _lib.moe_forward(c["x"], w13, w2, w.contiguous(), ids.contiguous(), s13=s13, s2=s2).out
 
 
-def _ep_worker(rank, world, port, kind, with_shared, impl, queue):
+def _ep_worker(rank, world, store_path, kind, with_shared, impl, queue):
     try:
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        os.environ.update(NCCL_NVLS_ENABLE="0")
         device = torch.device("cuda", rank)
         torch.cuda.set_device(device)
-        dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120), device_id=device)
+        # Rendezvous through a file: a TCP port picked by the parent can be taken again before rank 0 listens on it.
+        dist.init_process_group("nccl", init_method=f"file://{store_path}", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=120), device_id=device)
         case = cases.w8a8_case("wide") if kind == "int8" else cases.bf16_case("top8")
         experts = case["w13"].shape[0]
         if kind == "int8" and experts % world:
@@ -104,13 +101,14 @@ def _ep_worker(rank, world, port, kind, with_shared, impl, queue):
 def _run_ep(world, kind, with_shared, impl="nccl"):
     context = mp.get_context("spawn")
     queue = context.Queue()
-    port = _free_port()
-    procs = [context.Process(target=_ep_worker, args=(r, world, port, kind, with_shared, impl, queue)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [queue.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
+    with tempfile.TemporaryDirectory() as folder:
+        store_path = os.path.join(folder, "rendezvous")
+        procs = [context.Process(target=_ep_worker, args=(r, world, store_path, kind, with_shared, impl, queue)) for r in range(world)]
+        for p in procs:
+            p.start()
+        results = [queue.get(timeout=300) for _ in procs]
+        for p in procs:
+            p.join(timeout=60)
     for rank, status, detail in results:
         assert status == "ok", (rank, status, detail)
 
