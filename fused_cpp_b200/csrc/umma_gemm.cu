@@ -230,8 +230,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
         for (int64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
           int item, block;
           decode_unit(args.items, unit, n_blocks, &item, &block);
-        item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
-        block = __shfl_sync(0xffffffffu, block, 0);
+          item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
+          block = __shfl_sync(0xffffffffu, block, 0);
           const int weight_row = __shfl_sync(0xffffffffu, args.items[4 * item + 0], 0) * n_total + block * kBlockM;
           const int row0 = __shfl_sync(0xffffffffu, args.items[4 * item + 1], 0);
           for (int kb = 0; kb < k_blocks; ++kb) {
@@ -459,8 +459,8 @@ umma_grouped_gemm_kernel(const __grid_constant__ CUtensorMap weight_map, const _
       const uint32_t use = static_cast<uint32_t>(local / Cfg::kAccBuffers);
       int item, block;
       decode_unit(args.items, unit, n_blocks, &item, &block);
-        item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
-        block = __shfl_sync(0xffffffffu, block, 0);
+      item = __shfl_sync(0xffffffffu, item, 0);  // read from the item list: the same in every lane
+      block = __shfl_sync(0xffffffffu, block, 0);
       const int n = block * kBlockM + channel_in_block;
       const int expert = args.items[4 * item + 0];
       const int row0 = args.items[4 * item + 1] * kRowsPerRoute;  // token rows (two per route in the two-plane form)
